@@ -1,0 +1,109 @@
+"""CPU restatement of CNTK's striped quantized gradient exchange (TEST INFRASTRUCTURE ONLY).
+
+Follows AllReduceDistGradAggregator<float>::AggregateGradientsImpl
+(Source/1BitSGD/AllReduceDistGradAggregator.h:237-566) and the V2 twin
+QuantizedMPICommunicatorImpl::QuantizedAggregate<float>
+(Source/1BitSGD/QuantizedDistributedCommunicator.h:285-539) step by step, with the K MPI
+ranks simulated in one process and the MPI messages replaced by array copies.  The
+arithmetic of every quantize / unquantize call is done by a backend from
+``oracle.backend`` (the reference's own headers when ``RefBackend`` is used).
+
+Parity status: the reference has no test that pins the exchange numerically (only
+training-loss tolerances), and its owner adds received stripes in MPI arrival order
+(:389-421), which is not deterministic for K >= 3.  This restatement fixes the order to
+"own stripe first, then sources by ascending rank"; that choice is the pin.
+
+Arrays: an fp32 M x N column-major matrix is a C-contiguous numpy array of shape (N, M),
+so a column stripe [start, start+n) is the row slice ``a[start:start+n]``.
+"""
+import numpy as np
+
+
+def stripe(num_cols, rank, K):
+    """GetStripeForNode (AllReduceDistGradAggregator.h:56-65): (start column, number of columns)."""
+    per, rem = divmod(num_cols, K)
+    return per * rank + min(rem, rank), per + (1 if rank < rem else 0)
+
+
+class ExchangeState:
+    """Per-rank persistent state: the pre-aggregation residual (M x N) and the stripe residual
+    (M x n_rank) of every tensor, zero-initialised (1BitSGD/MatrixQuantizer.h:27-30;
+    AllReduceDistGradAggregator.h:87, :97)."""
+
+    def __init__(self, shapes, K):
+        self.shapes = [tuple(s) for s in shapes]  # (M, N) per tensor
+        self.K = K
+        self.res = [[np.zeros((N, M), np.float32) for (M, N) in self.shapes] for _ in range(K)]
+        self.sres = [[np.zeros((stripe(N, r, K)[1], M), np.float32) for (M, N) in self.shapes] for r in range(K)]
+
+    def reset(self):
+        """ResetResidue on every quantizer (AllReduceDistGradAggregator.h:121-136)."""
+        for per_rank in self.res + self.sres:
+            for a in per_rank:
+                a[...] = 0
+
+
+def aggregate_step(backend, state, grads, bits, zero_thr=True, self_quant=True, v2_identity_at_k1=False):
+    """One AggregateGradients call on all K simulated ranks.
+
+    ``grads[r][i]`` is rank r's (N_i, M_i) float32 gradient; it is overwritten with the aggregate,
+    as the reference does (gradients are aggregated in place, :281, :521).
+    Returns ``packed[r][i]``: the fully gathered packed matrix each rank unquantized from
+    (identical on all ranks), for wire-format comparison.
+    """
+    K, shapes = state.K, state.shapes
+    T = len(shapes)
+    if K == 1 and v2_identity_at_k1:
+        # QuantizedDistributedCommunicator.h:75-81: a single worker returns its inputs untouched.
+        return None
+    col_bytes = [backend.packed_col_bytes(M, bits) for (M, N) in shapes]
+
+    # step 1 (:290-300): every rank quantizes every gradient against its own residual, in place.
+    packed = [[np.zeros(shapes[i][1] * col_bytes[i], np.uint8) for i in range(T)] for _ in range(K)]
+    for r in range(K):
+        for i in range(T):
+            backend.quantize(grads[r][i], state.res[r][i], state.res[r][i], packed[r][i], bits, zero_thr)
+
+    if K == 1:
+        # V1 with one rank: the own stripe is unquantized into the gradient (:366-375); no stripe is ever
+        # received, so the requantization at :429-435 never fires; the final unquantize (:516-522) rewrites
+        # the gradient from the same packed data.
+        for i in range(T):
+            backend.unquantize(packed[0][i], grads[0][i], bits, add=False)
+        return packed
+
+    # steps 2-5: the owner of each stripe builds the aggregate inside its own gradient slice and requantizes.
+    agg_packed = [[None] * T for _ in range(K)]
+    for r in range(K):
+        for i in range(T):
+            M, N = shapes[i]
+            s, n = stripe(N, r, K)
+            if n == 0:
+                continue
+            C = col_bytes[i]
+            agg = grads[r][i][s:s + n]  # ColumnSlice view of the gradient (:281)
+            if self_quant:
+                backend.unquantize(packed[r][i][s * C:(s + n) * C], agg, bits, add=False)  # :366-375
+            for src in range(K):  # fixed order: ascending source rank (reference: arrival order, :389-421)
+                if src == r:
+                    continue
+                backend.unquantize(packed[src][i][s * C:(s + n) * C], agg, bits, add=True)  # :421
+            out = np.zeros(n * C, np.uint8)
+            backend.quantize(agg, state.sres[r][i], state.sres[r][i], out, bits, zero_thr)  # :429-435
+            agg_packed[r][i] = out
+
+    # steps 7-9 (:459-522): all-gather of the requantized stripes, then every rank unquantizes everything.
+    gathered = []
+    for i in range(T):
+        M, N = shapes[i]
+        C = col_bytes[i]
+        full = np.zeros(N * C, np.uint8)
+        for r in range(K):
+            s, n = stripe(N, r, K)
+            if n:
+                full[s * C:(s + n) * C] = agg_packed[r][i]
+        gathered.append(full)
+    for r in range(K):
+        for i in range(T):
+            backend.unquantize(gathered[i], grads[r][i], bits, add=False)
+    return [gathered for _ in range(K)]

@@ -1,0 +1,195 @@
+"""CPU checks that pin the oracle: the plain-C restatement (oracle/qagg_oracle.c) must reproduce the
+fixtures that tests/golden/make_golden.py wrote from the reference's own headers, the known answers
+obtained from those headers, and -- when the reference-built library is present -- its output directly."""
+import json
+import os
+import struct
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import make_golden as mg  # noqa: E402
+
+from oracle import exchange as ox  # noqa: E402
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(scope="module")
+def digests():
+    with open(os.path.join(GOLD, "golden_digests.json")) as f:
+        return json.load(f)
+
+
+@pytest.fixture(scope="module")
+def small():
+    return np.load(os.path.join(GOLD, "golden_small.npz"))
+
+
+def test_input_generator_has_not_drifted(digests):
+    for (rows, cols, low, high, seed) in mg.UNIT_CASES:
+        got = [mg.sha(mg.uniform_input(rows, cols, low, high, seed + it)) for it in range(mg.ITERS)]
+        assert got == digests["inputs"][f"{rows}x{cols}_seed{seed}"], "numpy input stream changed; regenerate fixtures"
+
+
+@pytest.mark.parametrize("case", mg.UNIT_CASES, ids=lambda c: f"{c[0]}x{c[1]}")
+def test_port_reproduces_reference_unit_grid(oracle_port, digests, case):
+    rows, cols, low, high, seed = case
+    for bits in mg.BITS:
+        for zero_thr in ((False, True) if bits == 1 else (False,)):
+            key = f"{rows}x{cols}_seed{seed}_b{bits}_z{int(zero_thr)}"
+            d, _ = mg.run_unit_case(oracle_port, rows, cols, low, high, seed, bits, zero_thr)
+            assert d == digests["unit"][key], key
+
+
+def test_port_matches_full_small_arrays(oracle_port, small):
+    rows, cols, low, high, seed = mg.UNIT_CASES[0]
+    for bits in (1, 2, 4):
+        for zero_thr in ((False, True) if bits == 1 else (False,)):
+            key = f"{rows}x{cols}_seed{seed}_b{bits}_z{int(zero_thr)}"
+            keep = []
+            mg.run_unit_case(oracle_port, rows, cols, low, high, seed, bits, zero_thr, keep)
+            for it, (g, p, r, o) in enumerate(keep):
+                np.testing.assert_array_equal(g, small[f"{key}_it{it}_in"])
+                np.testing.assert_array_equal(p, small[f"{key}_it{it}_packed"])
+                np.testing.assert_array_equal(r, small[f"{key}_it{it}_res"])
+                np.testing.assert_array_equal(o, small[f"{key}_it{it}_out"])
+
+
+def test_port_reproduces_config1_round_trip(oracle_port, digests):
+    """2048 x 2048, N(0, 0.01^2), seed 0 + step, 1 bit, ten error-feedback steps (first three checked here to
+    keep the CPU suite short; the GPU suite checks all ten)."""
+    be = oracle_port
+    for zero_thr in (True, False):
+        res = np.zeros((2048, 2048), np.float32)
+        out = np.zeros((2048, 2048), np.float32)
+        packed = np.zeros(2048 * be.packed_col_bytes(2048, 1), np.uint8)
+        for step in range(3):
+            g = mg.normal_input(2048, 2048, 0.01, step)
+            exp = digests["config1"][f"z{int(zero_thr)}"][step]
+            assert mg.sha(g) == exp["in"]
+            be.quantize(g, res, res, packed, 1, zero_thr)
+            be.unquantize(packed, out, 1, add=False)
+            assert mg.sha(packed) == exp["packed"]
+            assert mg.sha(res) == exp["residual"]
+            assert mg.sha(out) == exp["out"]
+
+
+def test_conservation_invariant(oracle_port):
+    """in + prevResidual + prevOut == newResidual + newOut within (hi - lo) * 1e-4
+    (Tests/UnitTests/MathTests/MatrixQuantizerTests.cpp:327-338)."""
+    be = oracle_port
+    for (rows, cols, low, high, seed) in mg.UNIT_CASES:
+        for bits in (1, 2, 4, 8):
+            res = np.zeros((cols, rows), np.float32)
+            out = np.zeros((cols, rows), np.float32)
+            packed = np.zeros(cols * be.packed_col_bytes(rows, bits), np.uint8)
+            for it in range(mg.ITERS):
+                g = mg.uniform_input(rows, cols, low, high, seed + it)
+                lhs = g + res + (out if it > 0 else 0)
+                be.quantize(g, res, res, packed, bits, True)
+                be.unquantize(packed, out, bits, add=(it > 0))
+                assert np.max(np.abs(lhs - (res + out))) <= (high - low) * 1e-4
+
+
+def _words(packed_col):
+    return [struct.unpack("<I", packed_col[8 + 4 * w: 12 + 4 * w].tobytes())[0] for w in range((len(packed_col) - 8) // 4)]
+
+
+def test_known_answers_from_reference_headers(oracle_port):
+    be = oracle_port
+    assert be.packed_col_bytes(70, 1) == 20 and be.packed_col_bytes(2048, 1) == 264
+    # all-zero column, M = 70, 1 bit, zero threshold: range collapses, every real row's bit is 1, padding bits 0
+    g = np.zeros((1, 70), np.float32)
+    r = np.zeros((1, 70), np.float32)
+    p = np.zeros(20, np.uint8)
+    be.quantize(g, r, r, p, 1, True)
+    assert struct.unpack("<ff", p[:8].tobytes()) == (0.0, 0.0)
+    assert _words(p) == [0x00FFFFFF, 0x007FFFFF, 0x007FFFFF]
+    assert not r.any()
+    o = np.ones((1, 70), np.float32)
+    be.unquantize(p, o, 1, add=False)
+    assert not o.any()
+    # M = 64, 4 bits, ramp: lower/upper = -/+ 4 * sqrt(sum v^2 / M); nibble k of word w is the level of row w + 8k
+    g = ((np.arange(64, dtype=np.float32) - np.float32(31.5)) * np.float32(0.01)).reshape(1, 64)
+    r = np.zeros((1, 64), np.float32)
+    p = np.zeros(be.packed_col_bytes(64, 4), np.uint8)
+    be.quantize(g, r, r, p, 4, True)
+    lo, hi = struct.unpack("<ff", p[:8].tobytes())
+    assert abs(hi - 0.738918) < 1e-6 and lo == -hi
+    assert _words(p) == [0x99876554, 0xA9876654, 0xA9876654, 0xA9877654, 0xA9877654, 0xA9887654, 0xA9887654, 0xA9987655]
+    # M = 64, 1 bit, mean threshold, ramp around 0.5
+    g = (np.float32(0.5) + (np.arange(64, dtype=np.float32) - np.float32(31.5)) * np.float32(0.01)).reshape(1, 64)
+    r = np.zeros((1, 64), np.float32)
+    p = np.zeros(be.packed_col_bytes(64, 1), np.uint8)
+    be.quantize(g, r, r, p, 1, False)
+    lo, hi = struct.unpack("<ff", p[:8].tobytes())
+    assert abs(lo - 0.18) < 1e-6 and abs(hi - 0.82) < 1e-6
+    assert _words(p) == [0xFFFF0000, 0xFFFF0000]
+
+
+def test_stripe_partition(oracle_port):
+    for N in (0, 1, 3, 7, 8, 9, 429, 2048, 50000):
+        for K in (1, 2, 3, 4, 8):
+            covered = 0
+            for r in range(K):
+                s, n = ox.stripe(N, r, K)
+                assert (s, n) == oracle_port.stripe(N, r, K)
+                assert s == covered
+                covered += n
+            assert covered == N
+
+
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 8])
+def test_exchange_restatement_matches_fixtures(oracle_port, digests, K):
+    for bits in (1, 2, 4):
+        for zero_thr in ((True, False) if bits == 1 else (True,)):
+            for self_quant in (True, False):
+                key = f"K{K}_b{bits}_z{int(zero_thr)}_s{int(self_quant)}"
+                assert mg.run_exchange(oracle_port, K, bits, zero_thr, self_quant) == digests["exchange"][key], key
+
+
+def test_exchange_all_ranks_agree_and_v2_identity(oracle_port):
+    K = 3
+    st = ox.ExchangeState(mg.EXCHANGE_SHAPES, K)
+    grads = mg.exchange_inputs(K, 0)
+    ox.aggregate_step(oracle_port, st, grads, 1)
+    for i in range(len(mg.EXCHANGE_SHAPES)):
+        for r in range(1, K):
+            np.testing.assert_array_equal(grads[0][i], grads[r][i])
+    st1 = ox.ExchangeState(mg.EXCHANGE_SHAPES, 1)
+    g1 = mg.exchange_inputs(1, 0)
+    keep = [a.copy() for a in g1[0]]
+    assert ox.aggregate_step(oracle_port, st1, g1, 1, v2_identity_at_k1=True) is None
+    for a, b in zip(g1[0], keep):
+        np.testing.assert_array_equal(a, b)
+
+
+def test_port_equals_reference_build_directly(oracle_port, oracle_ref):
+    """Random shapes incl. odd row counts, all-zero columns, NaN-free extremes: byte-identical outputs."""
+    rng = np.random.default_rng(7)
+    for trial in range(40):
+        M = int(rng.integers(1, 300))
+        N = int(rng.integers(1, 20))
+        bits = int(rng.choice([1, 2, 4, 8, 16, 32]))
+        zero_thr = bool(rng.integers(0, 2))
+        scale = float(10.0 ** rng.integers(-6, 2))
+        res_a = np.zeros((N, M), np.float32)
+        res_b = np.zeros((N, M), np.float32)
+        for it in range(3):
+            g = (rng.standard_normal((N, M)) * scale).astype(np.float32)
+            if trial % 5 == 0:
+                g[rng.integers(0, N)] = 0.0
+            pa = np.zeros(N * oracle_port.packed_col_bytes(M, bits), np.uint8)
+            pb = np.zeros_like(pa)
+            oracle_port.quantize(g, res_a, res_a, pa, bits, zero_thr)
+            oracle_ref.quantize(g, res_b, res_b, pb, bits, zero_thr)
+            np.testing.assert_array_equal(pa, pb)
+            np.testing.assert_array_equal(res_a.view(np.uint32), res_b.view(np.uint32))
+            oa = np.full((N, M), 0.25, np.float32)
+            ob_ = np.full((N, M), 0.25, np.float32)
+            oracle_port.unquantize(pa, oa, bits, add=bool(it % 2))
+            oracle_ref.unquantize(pb, ob_, bits, add=bool(it % 2))
+            np.testing.assert_array_equal(oa.view(np.uint32), ob_.view(np.uint32))
