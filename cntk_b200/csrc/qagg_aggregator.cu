@@ -1,0 +1,758 @@
+// qagg_aggregator.cu -- communicator and striped aggregator behind include/qagg.h.
+//
+// One aggregation step on rank r of K (AllReduceDistGradAggregator.h:237-566 restated for device buffers):
+//   K1  one launch quantizes every gradient against its residual and writes each packed column straight into
+//       the region of the send buffer that belongs to the column's owner (own columns go to the receive slot);
+//   X1  grouped ncclSend/ncclRecv: region p -> rank p, one message per peer covering all tensors;
+//   K2  one launch per step: for every owned stripe, unpack the K stripes, add them in rank order (own first),
+//       add the stripe residual, requantize into this rank's slot of the gather buffer;
+//   X2  ncclAllGather of the (equal-sized, padded) slots;
+//   K3  one launch unpacks every tensor from the gather buffer into the gradient.
+// All buffers live for the lifetime of the aggregator; nothing is allocated per step.
+#include "../../include/qagg.h"
+#include "qagg_internal.h"
+
+#include <nccl.h>
+
+#include <algorithm>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+using namespace qagg;
+
+struct qagg_comm
+{
+    int rank = 0;
+    int K = 1;
+    int device = 0;
+    ncclComm_t nccl = nullptr;
+    bool local = false; // member of an in-process group (device-to-device copies instead of NCCL)
+};
+
+namespace {
+
+inline int64_t align_up(int64_t v, int64_t a)
+{
+    return (v + a - 1) / a * a;
+}
+
+int check_nccl(ncclResult_t r, const char* what)
+{
+    if (r == ncclSuccess)
+        return QAGG_OK;
+    return fail(QAGG_ENCCL, std::string(what) + ": " + ncclGetErrorString(r));
+}
+
+struct DevBuf
+{
+    void* p = nullptr;
+    ~DevBuf()
+    {
+        if (p)
+            cudaFree(p);
+    }
+    int alloc(size_t bytes, bool zero)
+    {
+        if (bytes == 0)
+            bytes = 16;
+        int rc = check_cuda(cudaMalloc(&p, bytes), "cudaMalloc");
+        if (rc)
+            return rc;
+        if (zero)
+            return check_cuda(cudaMemset(p, 0, bytes), "cudaMemset");
+        return QAGG_OK;
+    }
+};
+
+} // namespace
+
+struct qagg_aggregator
+{
+    qagg_comm* comm = nullptr;
+    int T = 0;
+    int bits = 1;
+    int flags = 0;
+    int mode = 0;
+    std::vector<int64_t> M, N, colBytes;
+    // stripe geometry: [p][i]
+    std::vector<std::vector<int64_t>> sStart, sN, tOff;
+    std::vector<int64_t> regionBytes; // packed bytes of rank p's stripes over all tensors (16-byte aligned blocks)
+    std::vector<int64_t> sendOff;     // offset of region p in the send buffer
+    int64_t slotBytes = 0;            // regionBytes[rank], padded: size of one receive slot
+    int64_t gatherSlot = 0;           // max region, padded: size of one gather slot
+    DevBuf sendbuf, recvbuf, gatherbuf, resAll, sresAll, tables, hostStage;
+    std::vector<float*> res, sres;
+    // device tables and their host mirrors
+    std::vector<QTensor> hK1, hK2, hK3;
+    std::vector<QItem> iK1, iK2, iK3;
+    QTensor *dK1 = nullptr, *dK2 = nullptr, *dK3 = nullptr;
+    QItem *dI1 = nullptr, *dI2 = nullptr, *dI3 = nullptr;
+    std::vector<int> k2Tensor; // tensor index of each K2 table entry
+    std::vector<float*> boundGrads;
+    LaunchCfg cfg;
+    int64_t totalValues = 0;
+    bool identity = false;
+    // optional per-phase timing
+    static const int kProfSlots = 64;
+    bool profiling = false;
+    cudaEvent_t ev[kProfSlots][6] = {};
+    long long profSteps = 0; // profiled steps recorded since profiling was switched on or last read
+    // host-path staging
+    DevBuf devGrads;
+    std::vector<float*> devGradPtr;
+
+    ~qagg_aggregator()
+    {
+        for (auto& slot : ev)
+            for (auto& e : slot)
+                if (e)
+                    cudaEventDestroy(e);
+    }
+    int mark(int i, cudaStream_t st)
+    {
+        if (!profiling)
+            return QAGG_OK;
+        return check_cuda(cudaEventRecord(ev[profSteps % kProfSlots][i], st), "cudaEventRecord");
+    }
+    unsigned char* send_region(int p) const { return static_cast<unsigned char*>(sendbuf.p) + sendOff[p]; }
+    unsigned char* recv_slot(int src) const { return static_cast<unsigned char*>(recvbuf.p) + (int64_t) src * slotBytes; }
+    unsigned char* gather_slot(int p) const { return static_cast<unsigned char*>(gatherbuf.p) + (int64_t) p * gatherSlot; }
+};
+
+namespace {
+
+void make_items(std::vector<QItem>& items, int tensor, int64_t M, int64_t N, int c)
+{
+    for (int64_t col0 = 0; col0 < N; col0 += c)
+        items.push_back(QItem{tensor, (int) col0, (int) std::min<int64_t>(c, N - col0)});
+}
+
+int build_tables(qagg_aggregator* a)
+{
+    const int K = a->comm->K, r = a->comm->rank, T = a->T;
+    a->hK1.assign(T, QTensor{});
+    a->hK3.assign(T, QTensor{});
+    a->hK2.clear();
+    a->k2Tensor.clear();
+    a->iK1.clear();
+    a->iK2.clear();
+    a->iK3.clear();
+    std::vector<std::pair<int64_t, QItem>> cost1, cost2;
+    for (int i = 0; i < T; ++i)
+    {
+        const int64_t M = a->M[i], N = a->N[i];
+        if (M == 0 || N == 0)
+            continue;
+        QTensor& q1 = a->hK1[i];
+        fill_layout(&q1, M, N, a->bits);
+        q1.res_in = a->res[i];
+        q1.res_out = a->res[i];
+        q1.K = K;
+        q1.per = N / K;
+        q1.rem = N % K;
+        QTensor& q3 = a->hK3[i];
+        q3 = q1;
+        q3.res_in = nullptr;
+        q3.res_out = nullptr;
+        for (int p = 0; p < K; ++p)
+        {
+            if (K == 1)
+                q1.pk[p] = a->gather_slot(0) + a->tOff[0][i];
+            else
+                q1.pk[p] = (p == r ? a->recv_slot(r) : a->send_region(p)) + a->tOff[p][i];
+            q3.pk[p] = a->gather_slot(p) + a->tOff[p][i];
+        }
+        {
+            std::vector<QItem> tmp;
+            const int c = cols_per_item(M, N, a->cfg.smemFloats, nullptr);
+            make_items(tmp, i, M, N, c);
+            for (auto& it : tmp)
+                cost1.push_back({M * it.ncols, it});
+            make_items(a->iK3, i, M, N, unq_cols_per_item(M));
+        }
+        if (K > 1 && a->sN[r][i] > 0)
+        {
+            QTensor q2 = {};
+            fill_layout(&q2, M, a->sN[r][i], a->bits);
+            q2.res_in = a->sres[i];
+            q2.res_out = a->sres[i];
+            q2.selfRaw = (a->flags & QAGG_SELF_QUANTIZED) ? 0 : 1;
+            q2.nsrc = K;
+            q2.src[0] = a->recv_slot(r) + a->tOff[r][i];
+            int s = 1;
+            for (int src = 0; src < K; ++src)
+                if (src != r)
+                    q2.src[s++] = a->recv_slot(src) + a->tOff[r][i];
+            q2.pk[0] = a->gather_slot(r) + a->tOff[r][i];
+            const int e = (int) a->hK2.size();
+            a->hK2.push_back(q2);
+            a->k2Tensor.push_back(i);
+            std::vector<QItem> tmp;
+            const int c = cols_per_item(M, q2.N, a->cfg.smemFloats, nullptr);
+            make_items(tmp, e, M, q2.N, c);
+            for (auto& it : tmp)
+                cost2.push_back({M * it.ncols, it});
+        }
+    }
+    // tallest work first: the ordered walk of a column takes time proportional to its height
+    auto byCost = [](const std::pair<int64_t, QItem>& x, const std::pair<int64_t, QItem>& y) { return x.first > y.first; };
+    std::stable_sort(cost1.begin(), cost1.end(), byCost);
+    std::stable_sort(cost2.begin(), cost2.end(), byCost);
+    for (auto& c : cost1)
+        a->iK1.push_back(c.second);
+    for (auto& c : cost2)
+        a->iK2.push_back(c.second);
+    return QAGG_OK;
+}
+
+size_t table_bytes(const qagg_aggregator* a)
+{
+    return (a->hK1.size() + a->hK2.size() + a->hK3.size()) * sizeof(QTensor) +
+           (a->iK1.size() + a->iK2.size() + a->iK3.size()) * sizeof(QItem) + 256;
+}
+
+// copies the host tables to the device (synchronously: only when the bound gradient pointers change)
+int upload_tables(qagg_aggregator* a)
+{
+    unsigned char* base = static_cast<unsigned char*>(a->tables.p);
+    size_t off = 0;
+    auto put = [&](const void* src, size_t bytes, void** devp) -> int {
+        *devp = base + off;
+        if (bytes)
+        {
+            int rc = check_cuda(cudaMemcpy(base + off, src, bytes, cudaMemcpyHostToDevice), "table upload");
+            if (rc)
+                return rc;
+        }
+        off += align_up((int64_t) bytes, 16);
+        return QAGG_OK;
+    };
+    int rc;
+    if ((rc = put(a->hK1.data(), a->hK1.size() * sizeof(QTensor), (void**) &a->dK1)))
+        return rc;
+    if ((rc = put(a->hK2.data(), a->hK2.size() * sizeof(QTensor), (void**) &a->dK2)))
+        return rc;
+    if ((rc = put(a->hK3.data(), a->hK3.size() * sizeof(QTensor), (void**) &a->dK3)))
+        return rc;
+    if ((rc = put(a->iK1.data(), a->iK1.size() * sizeof(QItem), (void**) &a->dI1)))
+        return rc;
+    if ((rc = put(a->iK2.data(), a->iK2.size() * sizeof(QItem), (void**) &a->dI2)))
+        return rc;
+    if ((rc = put(a->iK3.data(), a->iK3.size() * sizeof(QItem), (void**) &a->dI3)))
+        return rc;
+    return QAGG_OK;
+}
+
+int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
+{
+    bool same = (a->boundGrads.size() == (size_t) a->T);
+    for (int i = 0; same && i < a->T; ++i)
+        same = (a->boundGrads[i] == grads[i]);
+    if (same)
+        return QAGG_OK;
+    for (int i = 0; i < a->T; ++i)
+    {
+        if (!grads[i] && a->M[i] * a->N[i] > 0)
+            return fail(QAGG_EINVAL, "qagg_agg_step: null gradient pointer");
+        a->hK1[i].grad = grads[i];
+        a->hK3[i].out = grads[i];
+    }
+    const int r = a->comm->rank;
+    for (size_t e = 0; e < a->hK2.size(); ++e)
+    {
+        const int i = a->k2Tensor[e];
+        a->hK2[e].grad = grads[i] + a->sStart[r][i] * a->M[i];
+    }
+    // an earlier step may still be reading the old tables
+    int rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+    if (rc)
+        return rc;
+    rc = upload_tables(a);
+    if (rc)
+        return rc;
+    a->boundGrads.assign(grads, grads + a->T);
+    return QAGG_OK;
+}
+
+int launch_k1(qagg_aggregator* a, cudaStream_t st)
+{
+    return check_cuda(launch_colquant(st, false, a->mode, nullptr, a->dK1, a->dI1, (int) a->iK1.size(), 0, a->cfg), "quantize launch");
+}
+int launch_k2(qagg_aggregator* a, cudaStream_t st)
+{
+    return check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg), "reduce-requantize launch");
+}
+int launch_k3(qagg_aggregator* a, cudaStream_t st)
+{
+    return check_cuda(launch_unquantize(st, false, nullptr, a->dK3, a->dI3, (int) a->iK3.size(), 0, a->cfg), "unquantize launch");
+}
+
+} // namespace
+
+extern "C" {
+
+int qagg_unique_id(void* out)
+{
+    if (!out)
+        return fail(QAGG_EINVAL, "qagg_unique_id: null pointer");
+    static_assert(sizeof(ncclUniqueId) <= QAGG_UNIQUE_ID_BYTES, "unique id does not fit");
+    ncclUniqueId id;
+    int rc = check_nccl(ncclGetUniqueId(&id), "ncclGetUniqueId");
+    if (rc)
+        return rc;
+    std::memset(out, 0, QAGG_UNIQUE_ID_BYTES);
+    std::memcpy(out, &id, sizeof(id));
+    return QAGG_OK;
+}
+
+int qagg_comm_create(const void* unique_id, int rank, int num_ranks, int device, qagg_comm** out)
+{
+    if (!out || num_ranks < 1 || num_ranks > QAGG_MAXK || rank < 0 || rank >= num_ranks)
+        return fail(QAGG_EINVAL, "qagg_comm_create: bad arguments");
+    int rc = check_cuda(cudaSetDevice(device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    std::unique_ptr<qagg_comm> c(new qagg_comm);
+    c->rank = rank;
+    c->K = num_ranks;
+    c->device = device;
+    if (num_ranks > 1)
+    {
+        if (!unique_id)
+            return fail(QAGG_EINVAL, "qagg_comm_create: unique id required for more than one rank");
+        ncclUniqueId id;
+        std::memcpy(&id, unique_id, sizeof(id));
+        rc = check_nccl(ncclCommInitRank(&c->nccl, num_ranks, id, rank), "ncclCommInitRank");
+        if (rc)
+            return rc;
+    }
+    *out = c.release();
+    return QAGG_OK;
+}
+
+int qagg_comm_create_local_group(int num_ranks, int device, qagg_comm** out)
+{
+    if (!out || num_ranks < 1 || num_ranks > QAGG_MAXK)
+        return fail(QAGG_EINVAL, "qagg_comm_create_local_group: bad arguments");
+    int rc = check_cuda(cudaSetDevice(device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    for (int r = 0; r < num_ranks; ++r)
+    {
+        qagg_comm* c = new qagg_comm;
+        c->rank = r;
+        c->K = num_ranks;
+        c->device = device;
+        c->local = true;
+        out[r] = c;
+    }
+    return QAGG_OK;
+}
+
+int qagg_comm_rank(const qagg_comm* c)
+{
+    return c ? c->rank : fail(QAGG_EINVAL, "null communicator");
+}
+
+int qagg_comm_size(const qagg_comm* c)
+{
+    return c ? c->K : fail(QAGG_EINVAL, "null communicator");
+}
+
+int qagg_comm_destroy(qagg_comm* c)
+{
+    if (!c)
+        return QAGG_OK;
+    int rc = QAGG_OK;
+    if (c->nccl)
+        rc = check_nccl(ncclCommDestroy(c->nccl), "ncclCommDestroy");
+    delete c;
+    return rc;
+}
+
+int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, int bits, int flags, qagg_aggregator** out)
+{
+    if (!comm || !out || num_tensors < 0 || (num_tensors > 0 && (!M || !N)))
+        return fail(QAGG_EINVAL, "qagg_agg_create: bad arguments");
+    if (!bits_ok(bits))
+        return fail(QAGG_EINVAL, "bits must be a power of two in 1..32");
+    int rc = check_cuda(cudaSetDevice(comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    std::unique_ptr<qagg_aggregator> a(new qagg_aggregator);
+    a->comm = comm;
+    a->T = num_tensors;
+    a->bits = bits;
+    a->flags = flags;
+    a->mode = mode_of(bits, flags & QAGG_ZERO_THRESHOLD);
+    const int K = comm->K, r = comm->rank;
+    a->identity = (K == 1) && (flags & QAGG_V2_IDENTITY_K1);
+    rc = check_cuda(get_launch_cfg(comm->device, &a->cfg), "cudaGetDeviceProperties");
+    if (rc)
+        return rc;
+    a->M.assign(M, M + num_tensors);
+    a->N.assign(N, N + num_tensors);
+    a->colBytes.resize(num_tensors);
+    int64_t resFloats = 0, sresFloats = 0;
+    for (int i = 0; i < num_tensors; ++i)
+    {
+        if (M[i] < 0 || N[i] < 0 || M[i] > 0x3fffffffLL || N[i] > 0x7fffffffLL)
+            return fail(QAGG_EINVAL, "qagg_agg_create: bad tensor shape");
+        a->colBytes[i] = 8 + 4 * ((M[i] * bits + 31) / 32);
+        a->totalValues += M[i] * N[i];
+        resFloats += align_up(M[i] * N[i], 4);
+    }
+    a->sStart.assign(K, std::vector<int64_t>(num_tensors));
+    a->sN.assign(K, std::vector<int64_t>(num_tensors));
+    a->tOff.assign(K, std::vector<int64_t>(num_tensors));
+    a->regionBytes.assign(K, 0);
+    a->sendOff.assign(K, 0);
+    int64_t sendTotal = 0;
+    for (int p = 0; p < K; ++p)
+    {
+        int64_t off = 0;
+        for (int i = 0; i < num_tensors; ++i)
+        {
+            qagg_stripe(N[i], p, K, &a->sStart[p][i], &a->sN[p][i]);
+            a->tOff[p][i] = off;
+            off += align_up(a->sN[p][i] * a->colBytes[i], 16);
+        }
+        a->regionBytes[p] = off;
+        a->sendOff[p] = sendTotal;
+        sendTotal += align_up(off, 256);
+        a->gatherSlot = std::max(a->gatherSlot, align_up(off, 256));
+    }
+    a->slotBytes = align_up(a->regionBytes[r], 256);
+    for (int i = 0; i < num_tensors; ++i)
+        sresFloats += align_up(M[i] * a->sN[r][i], 4);
+
+    if ((rc = a->sendbuf.alloc((size_t) sendTotal, true)))
+        return rc;
+    if ((rc = a->recvbuf.alloc((size_t) (a->slotBytes * K), true)))
+        return rc;
+    if ((rc = a->gatherbuf.alloc((size_t) (a->gatherSlot * K), true)))
+        return rc;
+    if ((rc = a->resAll.alloc((size_t) resFloats * 4, true)))
+        return rc;
+    if ((rc = a->sresAll.alloc((size_t) sresFloats * 4, true)))
+        return rc;
+    a->res.resize(num_tensors);
+    a->sres.resize(num_tensors);
+    int64_t ro = 0, so = 0;
+    for (int i = 0; i < num_tensors; ++i)
+    {
+        a->res[i] = static_cast<float*>(a->resAll.p) + ro;
+        ro += align_up(M[i] * N[i], 4);
+        a->sres[i] = (a->sN[r][i] > 0 && K > 1) ? static_cast<float*>(a->sresAll.p) + so : nullptr;
+        so += align_up(M[i] * a->sN[r][i], 4);
+    }
+    if ((rc = build_tables(a.get())))
+        return rc;
+    if ((rc = a->tables.alloc(table_bytes(a.get()), true)))
+        return rc;
+    *out = a.release();
+    return QAGG_OK;
+}
+
+static int exchange_scatter(qagg_aggregator* a, cudaStream_t st)
+{
+    const int K = a->comm->K, r = a->comm->rank;
+    int rc = check_nccl(ncclGroupStart(), "ncclGroupStart");
+    if (rc)
+        return rc;
+    for (int p = 0; p < K; ++p)
+    {
+        if (p == r)
+            continue;
+        if (a->regionBytes[p] > 0)
+            if ((rc = check_nccl(ncclSend(a->send_region(p), (size_t) a->regionBytes[p], ncclChar, p, a->comm->nccl, st), "ncclSend")))
+                return rc;
+        if (a->regionBytes[r] > 0)
+            if ((rc = check_nccl(ncclRecv(a->recv_slot(p), (size_t) a->regionBytes[r], ncclChar, p, a->comm->nccl, st), "ncclRecv")))
+                return rc;
+    }
+    return check_nccl(ncclGroupEnd(), "ncclGroupEnd");
+}
+
+static int exchange_gather(qagg_aggregator* a, cudaStream_t st)
+{
+    const int r = a->comm->rank;
+    return check_nccl(ncclAllGather(a->gather_slot(r), a->gatherbuf.p, (size_t) a->gatherSlot, ncclChar, a->comm->nccl, st), "ncclAllGather");
+}
+
+int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream)
+{
+    if (!a || (a->T > 0 && !grads))
+        return fail(QAGG_EINVAL, "qagg_agg_step: bad arguments");
+    if (a->comm->local && a->comm->K > 1)
+        return fail(QAGG_ESTATE, "aggregators of a local group must be stepped with qagg_agg_step_group");
+    if (a->identity || a->totalValues == 0)
+        return QAGG_OK;
+    cudaStream_t st = (cudaStream_t) stream;
+    int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    if ((rc = bind_grads(a, grads, st)))
+        return rc;
+    if ((rc = a->mark(0, st)))
+        return rc;
+    if ((rc = launch_k1(a, st)))
+        return rc;
+    if ((rc = a->mark(1, st)))
+        return rc;
+    if (a->comm->K > 1)
+    {
+        if ((rc = exchange_scatter(a, st)))
+            return rc;
+        if ((rc = a->mark(2, st)))
+            return rc;
+        if ((rc = launch_k2(a, st)))
+            return rc;
+        if ((rc = a->mark(3, st)))
+            return rc;
+        if ((rc = exchange_gather(a, st)))
+            return rc;
+    }
+    else
+    {
+        if ((rc = a->mark(2, st)) || (rc = a->mark(3, st)))
+            return rc;
+    }
+    if ((rc = a->mark(4, st)))
+        return rc;
+    if ((rc = launch_k3(a, st)))
+        return rc;
+    if ((rc = a->mark(5, st)))
+        return rc;
+    if (a->profiling)
+        a->profSteps++;
+    return QAGG_OK;
+}
+
+int qagg_agg_set_profiling(qagg_aggregator* a, int enabled)
+{
+    if (!a)
+        return fail(QAGG_EINVAL, "null aggregator");
+    if (enabled)
+    {
+        int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+        if (rc)
+            return rc;
+        for (auto& slot : a->ev)
+            for (auto& e : slot)
+                if (!e && (rc = check_cuda(cudaEventCreate(&e), "cudaEventCreate")))
+                    return rc;
+    }
+    a->profiling = enabled != 0;
+    a->profSteps = 0;
+    return QAGG_OK;
+}
+
+int qagg_agg_phase_ms(qagg_aggregator* a, float* out5)
+{
+    if (!a || !out5)
+        return fail(QAGG_EINVAL, "qagg_agg_phase_ms: bad arguments");
+    if (a->profSteps == 0)
+        return fail(QAGG_ESTATE, "qagg_agg_phase_ms: no profiled step has been recorded");
+    const long long n = std::min<long long>(a->profSteps, qagg_aggregator::kProfSlots);
+    double sum[5] = {0, 0, 0, 0, 0};
+    for (long long k = 0; k < n; ++k)
+    {
+        const int slot = (int) ((a->profSteps - 1 - k) % qagg_aggregator::kProfSlots);
+        int rc = check_cuda(cudaEventSynchronize(a->ev[slot][5]), "cudaEventSynchronize");
+        if (rc)
+            return rc;
+        for (int i = 0; i < 5; ++i)
+        {
+            float ms = 0.f;
+            if ((rc = check_cuda(cudaEventElapsedTime(&ms, a->ev[slot][i], a->ev[slot][i + 1]), "cudaEventElapsedTime")))
+                return rc;
+            sum[i] += ms;
+        }
+    }
+    for (int i = 0; i < 5; ++i)
+        out5[i] = (float) (sum[i] / (double) n);
+    a->profSteps = 0;
+    return QAGG_OK;
+}
+
+int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* const* const* grads, void* stream)
+{
+    if (!aggs || !grads || num_ranks < 1)
+        return fail(QAGG_EINVAL, "qagg_agg_step_group: bad arguments");
+    cudaStream_t st = (cudaStream_t) stream;
+    const int K = num_ranks;
+    for (int r = 0; r < K; ++r)
+    {
+        if (!aggs[r] || aggs[r]->comm->K != K || aggs[r]->comm->rank != r || !aggs[r]->comm->local)
+            return fail(QAGG_ESTATE, "qagg_agg_step_group: aggregators are not ranks 0..K-1 of one local group");
+        if (aggs[r]->T != aggs[0]->T || aggs[r]->bits != aggs[0]->bits || aggs[r]->M != aggs[0]->M || aggs[r]->N != aggs[0]->N)
+            return fail(QAGG_ESTATE, "qagg_agg_step_group: aggregators disagree on tensor shapes or bits");
+    }
+    if (aggs[0]->identity || aggs[0]->totalValues == 0)
+        return QAGG_OK;
+    int rc = check_cuda(cudaSetDevice(aggs[0]->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    for (int r = 0; r < K; ++r)
+    {
+        if ((rc = bind_grads(aggs[r], grads[r], st)))
+            return rc;
+        if ((rc = launch_k1(aggs[r], st)))
+            return rc;
+    }
+    if (K > 1)
+    {
+        // scatter: region p of rank r's send buffer -> receive slot r of rank p
+        for (int r = 0; r < K; ++r)
+            for (int p = 0; p < K; ++p)
+                if (p != r && aggs[r]->regionBytes[p] > 0)
+                    if ((rc = check_cuda(cudaMemcpyAsync(aggs[p]->recv_slot(r), aggs[r]->send_region(p), (size_t) aggs[r]->regionBytes[p],
+                                                         cudaMemcpyDeviceToDevice, st), "stripe copy")))
+                        return rc;
+        for (int r = 0; r < K; ++r)
+            if ((rc = launch_k2(aggs[r], st)))
+                return rc;
+        // all-gather: gather slot r of rank r -> gather slot r of every other rank
+        for (int r = 0; r < K; ++r)
+            for (int p = 0; p < K; ++p)
+                if (p != r && aggs[r]->regionBytes[r] > 0)
+                    if ((rc = check_cuda(cudaMemcpyAsync(aggs[p]->gather_slot(r), aggs[r]->gather_slot(r), (size_t) aggs[r]->regionBytes[r],
+                                                         cudaMemcpyDeviceToDevice, st), "aggregated stripe copy")))
+                        return rc;
+    }
+    for (int r = 0; r < K; ++r)
+        if ((rc = launch_k3(aggs[r], st)))
+            return rc;
+    return QAGG_OK;
+}
+
+int qagg_agg_step_host(qagg_aggregator* a, float* const* host_grads, void* stream)
+{
+    if (!a || (a->T > 0 && !host_grads))
+        return fail(QAGG_EINVAL, "qagg_agg_step_host: bad arguments");
+    cudaStream_t st = (cudaStream_t) stream;
+    int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    if (!a->devGrads.p)
+    {
+        int64_t floats = 0;
+        for (int i = 0; i < a->T; ++i)
+            floats += align_up(a->M[i] * a->N[i], 4);
+        if ((rc = a->devGrads.alloc((size_t) floats * 4, false)))
+            return rc;
+        a->devGradPtr.resize(a->T);
+        int64_t o = 0;
+        for (int i = 0; i < a->T; ++i)
+        {
+            a->devGradPtr[i] = static_cast<float*>(a->devGrads.p) + o;
+            o += align_up(a->M[i] * a->N[i], 4);
+        }
+    }
+    for (int i = 0; i < a->T; ++i)
+    {
+        const size_t bytes = (size_t) (a->M[i] * a->N[i]) * 4;
+        if (bytes && (rc = check_cuda(cudaMemcpyAsync(a->devGradPtr[i], host_grads[i], bytes, cudaMemcpyHostToDevice, st), "gradient upload")))
+            return rc;
+    }
+    if ((rc = qagg_agg_step(a, a->devGradPtr.data(), stream)))
+        return rc;
+    for (int i = 0; i < a->T; ++i)
+    {
+        const size_t bytes = (size_t) (a->M[i] * a->N[i]) * 4;
+        if (bytes && (rc = check_cuda(cudaMemcpyAsync(host_grads[i], a->devGradPtr[i], bytes, cudaMemcpyDeviceToHost, st), "gradient download")))
+            return rc;
+    }
+    return check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+}
+
+int qagg_agg_reset_residuals(qagg_aggregator* a, void* stream)
+{
+    if (!a)
+        return fail(QAGG_EINVAL, "null aggregator");
+    cudaStream_t st = (cudaStream_t) stream;
+    int64_t resFloats = 0, sresFloats = 0;
+    const int r = a->comm->rank;
+    for (int i = 0; i < a->T; ++i)
+    {
+        resFloats += align_up(a->M[i] * a->N[i], 4);
+        sresFloats += align_up(a->M[i] * a->sN[r][i], 4);
+    }
+    int rc = check_cuda(cudaMemsetAsync(a->resAll.p, 0, (size_t) std::max<int64_t>(resFloats, 1) * 4, st), "cudaMemsetAsync");
+    if (rc)
+        return rc;
+    return check_cuda(cudaMemsetAsync(a->sresAll.p, 0, (size_t) std::max<int64_t>(sresFloats, 1) * 4, st), "cudaMemsetAsync");
+}
+
+int qagg_agg_residuals(qagg_aggregator* a, int tensor, float** residual, float** stripe_residual)
+{
+    if (!a || tensor < 0 || tensor >= a->T)
+        return fail(QAGG_EINVAL, "qagg_agg_residuals: bad arguments");
+    if (residual)
+        *residual = a->res[tensor];
+    if (stripe_residual)
+        *stripe_residual = a->sres[tensor];
+    return QAGG_OK;
+}
+
+int qagg_agg_copy_residual(qagg_aggregator* a, int tensor, int which, float* dst_dev, void* stream)
+{
+    if (!a || tensor < 0 || tensor >= a->T || !dst_dev || which < 0 || which > 1)
+        return fail(QAGG_EINVAL, "qagg_agg_copy_residual: bad arguments");
+    const int r = a->comm->rank;
+    const float* src = which ? a->sres[tensor] : a->res[tensor];
+    const int64_t n = a->M[tensor] * (which ? a->sN[r][tensor] : a->N[tensor]);
+    if (n == 0 || !src)
+        return QAGG_OK;
+    return check_cuda(cudaMemcpyAsync(dst_dev, src, (size_t) n * 4, cudaMemcpyDeviceToDevice, (cudaStream_t) stream), "residual copy");
+}
+
+int qagg_agg_copy_packed(qagg_aggregator* a, int tensor, void* dst_dev, void* stream)
+{
+    if (!a || tensor < 0 || tensor >= a->T || !dst_dev)
+        return fail(QAGG_EINVAL, "qagg_agg_copy_packed: bad arguments");
+    const int K = a->comm->K;
+    for (int p = 0; p < K; ++p)
+    {
+        const int64_t bytes = a->sN[p][tensor] * a->colBytes[tensor];
+        if (bytes == 0)
+            continue;
+        int rc = check_cuda(cudaMemcpyAsync(static_cast<unsigned char*>(dst_dev) + a->sStart[p][tensor] * a->colBytes[tensor],
+                                            a->gather_slot(p) + a->tOff[p][tensor], (size_t) bytes, cudaMemcpyDeviceToDevice, (cudaStream_t) stream),
+                            "packed copy");
+        if (rc)
+            return rc;
+    }
+    return QAGG_OK;
+}
+
+int64_t qagg_agg_wire_bytes(const qagg_aggregator* a)
+{
+    if (!a)
+        return fail(QAGG_EINVAL, "null aggregator");
+    const int K = a->comm->K, r = a->comm->rank;
+    int64_t b = 0;
+    for (int p = 0; p < K; ++p)
+        if (p != r)
+            b += a->regionBytes[p] + a->regionBytes[r];
+    return b;
+}
+
+int qagg_agg_launches_per_step(const qagg_aggregator* a)
+{
+    if (!a)
+        return fail(QAGG_EINVAL, "null aggregator");
+    if (a->identity || a->totalValues == 0)
+        return 0;
+    return (a->comm->K > 1 && !a->iK2.empty()) ? 3 : 2;
+}
+
+int qagg_agg_destroy(qagg_aggregator* a)
+{
+    delete a;
+    return QAGG_OK;
+}
+
+} // extern "C"

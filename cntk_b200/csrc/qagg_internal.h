@@ -1,0 +1,85 @@
+// qagg_internal.h -- structures shared by the kernels, the single-matrix C entry points and the aggregator.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#define QAGG_MAXK 16 // most ranks in one group (one 8-GPU box needs 8)
+
+namespace qagg {
+
+// Everything the column kernels need to know about one matrix.  Used for
+//   - the pre-aggregation quantize   (source = grad + residual, all N columns, packed column j routed to its owner),
+//   - the owner's reduce-requantize  (source = sum of `nsrc` packed stripes (+ raw own stripe) + stripe residual),
+//   - the final unquantize           (packed column j fetched from its owner's gather slot).
+struct QTensor
+{
+    const float* grad;   // quantize: gradient, M x N.  reduce: raw own stripe (M x N) or nullptr.  unquantize: unused
+    const float* res_in; // residual read
+    float* res_out;      // residual written (may equal res_in)
+    float* out;          // unquantize: destination, M x N
+    long long M, N;      // rows, columns handled by this descriptor
+    int Q;               // 32-bit words per packed column = ceil(M * bits / 32)
+    int colBytes;        // 8 + 4 * Q
+    int bits;
+    int K;               // owners the packed columns are routed over (1 = one contiguous packed matrix)
+    long long per, rem;  // N / K and N % K: owner p holds columns [p*per + min(p, rem), ...) (GetStripeForNode)
+    unsigned char* pk[QAGG_MAXK]; // packed base for owner p; its first column is that owner's stripe start
+    int nsrc;                           // reduce: number of packed sources
+    int selfRaw;                        // reduce: 1 = start from `grad` instead of src[0]
+    const unsigned char* src[QAGG_MAXK]; // reduce: packed sources, M x N each, summed in index order
+};
+
+struct QItem
+{
+    int tensor;
+    int col0;
+    int ncols;
+};
+
+enum QuantMode
+{
+    MODE_ONEBIT_ZERO = 0, // 1 bit, threshold 0, separate level means
+    MODE_ONEBIT_MEAN = 1, // 1 bit, threshold = column mean
+    MODE_MULTIBIT = 2     // 2..32 bits, range = +-4 sigma
+};
+
+// shared-memory row stride (in floats) of one staged column: >= M, multiple of 4, == 4 mod 32 so that
+// 128-bit reads of the same rows of neighbouring columns fall into distinct banks
+__host__ __device__ inline int smem_stride(long long M)
+{
+    long long s = (M + 3) & ~3LL;
+    s += (36 - (s & 31)) & 31;
+    return (int) s;
+}
+
+struct LaunchCfg
+{
+    int numSMs = 0;
+    int smemFloats = 0;  // dynamic shared memory per CTA, in floats
+    int ctasPerSM = 0;
+};
+
+// cols per work item for a matrix of M rows under a given shared-memory budget; *resident tells whether whole
+// columns fit (else the kernel streams the column through shared memory in chunks and reads its inputs twice)
+int cols_per_item(long long M, long long N, int smemFloats, bool* resident);
+
+// launchers (qagg_kernels.cu).  `single` != nullptr: one matrix described by value, items derived from the block index.
+// otherwise `tensors`/`items` are device tables.
+cudaError_t launch_colquant(cudaStream_t st, bool stripes, int mode, const QTensor* single, const QTensor* tensors,
+                            const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg);
+cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, const QTensor* tensors,
+                              const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg);
+cudaError_t get_launch_cfg(int device, LaunchCfg* cfg);
+int unq_cols_per_item(long long M);
+
+// error plumbing (qagg_capi.cu)
+int fail(int code, const std::string& msg);
+int check_cuda(cudaError_t e, const char* what);
+bool bits_ok(int bits);
+int mode_of(int bits, int zeroThr);
+void fill_layout(QTensor* t, long long M, long long N, int bits);
+
+} // namespace qagg

@@ -1,0 +1,229 @@
+"""ctypes bindings of libqagg.so (see include/qagg.h for the contract of every call).
+
+Device buffers are passed as integers (``tensor.data_ptr()``); torch is used by callers only to own device
+memory and streams.  Every wrapper raises ``QaggError`` with the library's message on a non-zero status.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libqagg.so")
+
+ZERO_THRESHOLD = 1
+SELF_QUANTIZED = 2
+V2_IDENTITY_K1 = 4
+UNIQUE_ID_BYTES = 128
+
+EXPORTS = [
+    "qagg_last_error", "qagg_abi_version", "qagg_packed_col_bytes", "qagg_packed_bytes", "qagg_stripe",
+    "qagg_quantize", "qagg_unquantize", "qagg_reduce_requantize", "qagg_quantize_to_host", "qagg_unquantize_from_host",
+    "qagg_unique_id", "qagg_comm_create", "qagg_comm_create_local_group", "qagg_comm_rank", "qagg_comm_size",
+    "qagg_comm_destroy", "qagg_agg_create", "qagg_agg_step", "qagg_agg_step_group", "qagg_agg_step_host",
+    "qagg_agg_reset_residuals", "qagg_agg_residuals", "qagg_agg_copy_residual", "qagg_agg_copy_packed", "qagg_agg_wire_bytes",
+    "qagg_agg_launches_per_step", "qagg_agg_set_profiling", "qagg_agg_phase_ms", "qagg_agg_destroy",
+]
+
+
+class QaggError(RuntimeError):
+    pass
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(f"{LIB_PATH} is missing: build it with `python -m cntk_b200.build` (there is no CPU fallback)")
+
+_lib = ctypes.CDLL(LIB_PATH)
+c_i64, c_int, c_vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+
+_lib.qagg_last_error.restype = ctypes.c_char_p
+_lib.qagg_packed_col_bytes.restype = c_i64
+_lib.qagg_packed_col_bytes.argtypes = [c_i64, c_int]
+_lib.qagg_packed_bytes.restype = c_i64
+_lib.qagg_packed_bytes.argtypes = [c_i64, c_i64, c_int]
+_lib.qagg_stripe.argtypes = [c_i64, c_int, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64)]
+_lib.qagg_quantize.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
+_lib.qagg_unquantize.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
+_lib.qagg_reduce_requantize.argtypes = [c_vp, ctypes.POINTER(c_vp), c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
+_lib.qagg_quantize_to_host.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
+_lib.qagg_unquantize_from_host.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
+_lib.qagg_unique_id.argtypes = [c_vp]
+_lib.qagg_comm_create.argtypes = [c_vp, c_int, c_int, c_int, ctypes.POINTER(c_vp)]
+_lib.qagg_comm_create_local_group.argtypes = [c_int, c_int, ctypes.POINTER(c_vp)]
+_lib.qagg_comm_rank.argtypes = [c_vp]
+_lib.qagg_comm_size.argtypes = [c_vp]
+_lib.qagg_comm_destroy.argtypes = [c_vp]
+_lib.qagg_agg_create.argtypes = [c_vp, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, c_int, ctypes.POINTER(c_vp)]
+_lib.qagg_agg_step.argtypes = [c_vp, ctypes.POINTER(c_vp), c_vp]
+_lib.qagg_agg_step_group.argtypes = [ctypes.POINTER(c_vp), c_int, ctypes.POINTER(ctypes.POINTER(c_vp)), c_vp]
+_lib.qagg_agg_step_host.argtypes = [c_vp, ctypes.POINTER(c_vp), c_vp]
+_lib.qagg_agg_reset_residuals.argtypes = [c_vp, c_vp]
+_lib.qagg_agg_residuals.argtypes = [c_vp, c_int, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
+_lib.qagg_agg_copy_residual.argtypes = [c_vp, c_int, c_int, c_vp, c_vp]
+_lib.qagg_agg_copy_packed.argtypes = [c_vp, c_int, c_vp, c_vp]
+_lib.qagg_agg_wire_bytes.restype = c_i64
+_lib.qagg_agg_wire_bytes.argtypes = [c_vp]
+_lib.qagg_agg_launches_per_step.argtypes = [c_vp]
+_lib.qagg_agg_set_profiling.argtypes = [c_vp, c_int]
+_lib.qagg_agg_phase_ms.argtypes = [c_vp, ctypes.POINTER(ctypes.c_float)]
+_lib.qagg_agg_destroy.argtypes = [c_vp]
+
+
+def raw():
+    """The ctypes handle itself (for symbol checks)."""
+    return _lib
+
+
+def last_error():
+    return _lib.qagg_last_error().decode()
+
+
+def _ok(rc):
+    if rc != 0:
+        raise QaggError(f"qagg error {rc}: {last_error()}")
+
+
+def packed_col_bytes(M, bits):
+    v = _lib.qagg_packed_col_bytes(M, bits)
+    if v < 0:
+        _ok(int(v))
+    return int(v)
+
+
+def packed_bytes(M, N, bits):
+    v = _lib.qagg_packed_bytes(M, N, bits)
+    if v < 0:
+        _ok(int(v))
+    return int(v)
+
+
+def stripe(num_cols, rank, K):
+    s, n = c_i64(), c_i64()
+    _ok(_lib.qagg_stripe(num_cols, rank, K, ctypes.byref(s), ctypes.byref(n)))
+    return int(s.value), int(n.value)
+
+
+def quantize(grad_ptr, res_in_ptr, res_out_ptr, packed_ptr, M, N, bits, zero_thr=True, stream=0):
+    _ok(_lib.qagg_quantize(stream, grad_ptr, res_in_ptr, res_out_ptr, packed_ptr, M, N, bits, int(bool(zero_thr))))
+
+
+def unquantize(packed_ptr, out_ptr, M, N, bits, add=False, stream=0):
+    _ok(_lib.qagg_unquantize(stream, packed_ptr, out_ptr, M, N, bits, int(bool(add))))
+
+
+def reduce_requantize(stripe_ptrs, self_raw_ptr, sres_in_ptr, sres_out_ptr, packed_out_ptr, M, n, bits, zero_thr=True, stream=0):
+    K = len(stripe_ptrs)
+    arr = (c_vp * K)(*[c_vp(p) if p else c_vp(None) for p in stripe_ptrs])
+    _ok(_lib.qagg_reduce_requantize(stream, arr, K, self_raw_ptr, sres_in_ptr, sres_out_ptr, packed_out_ptr, M, n, bits,
+                                    int(bool(zero_thr))))
+
+
+def quantize_to_host(grad_ptr, res_in_ptr, res_out_ptr, dev_scratch_ptr, host_packed_ptr, M, N, bits, zero_thr=True, stream=0):
+    _ok(_lib.qagg_quantize_to_host(stream, grad_ptr, res_in_ptr, res_out_ptr, dev_scratch_ptr, host_packed_ptr, M, N, bits,
+                                   int(bool(zero_thr))))
+
+
+def unquantize_from_host(host_packed_ptr, dev_scratch_ptr, out_ptr, M, N, bits, add=False, stream=0):
+    _ok(_lib.qagg_unquantize_from_host(stream, host_packed_ptr, dev_scratch_ptr, out_ptr, M, N, bits, int(bool(add))))
+
+
+def unique_id():
+    buf = ctypes.create_string_buffer(UNIQUE_ID_BYTES)
+    _ok(_lib.qagg_unique_id(buf))
+    return buf.raw
+
+
+class Comm:
+    def __init__(self, handle):
+        self.h = handle
+
+    @staticmethod
+    def create(unique_id_bytes, rank, K, device):
+        h = c_vp()
+        buf = ctypes.create_string_buffer(unique_id_bytes, UNIQUE_ID_BYTES) if unique_id_bytes else None
+        _ok(_lib.qagg_comm_create(buf, rank, K, device, ctypes.byref(h)))
+        return Comm(h)
+
+    @staticmethod
+    def local_group(K, device):
+        arr = (c_vp * K)()
+        _ok(_lib.qagg_comm_create_local_group(K, device, arr))
+        return [Comm(c_vp(arr[i])) for i in range(K)]
+
+    @property
+    def rank(self):
+        return _lib.qagg_comm_rank(self.h)
+
+    @property
+    def size(self):
+        return _lib.qagg_comm_size(self.h)
+
+    def destroy(self):
+        if self.h:
+            _ok(_lib.qagg_comm_destroy(self.h))
+            self.h = None
+
+
+class Aggregator:
+    """qagg_aggregator handle.  ``shapes`` is a list of (M, N)."""
+
+    def __init__(self, comm, shapes, bits, flags=ZERO_THRESHOLD | SELF_QUANTIZED):
+        self.comm, self.shapes, self.bits, self.flags = comm, [tuple(s) for s in shapes], bits, flags
+        T = len(shapes)
+        Ms = (c_i64 * T)(*[s[0] for s in shapes])
+        Ns = (c_i64 * T)(*[s[1] for s in shapes])
+        h = c_vp()
+        _ok(_lib.qagg_agg_create(comm.h, T, Ms, Ns, bits, flags, ctypes.byref(h)))
+        self.h = h
+
+    def _ptrs(self, ptrs):
+        return (c_vp * len(ptrs))(*[c_vp(p) for p in ptrs])
+
+    def step(self, grad_ptrs, stream=0):
+        _ok(_lib.qagg_agg_step(self.h, self._ptrs(grad_ptrs), stream))
+
+    def step_host(self, host_grad_ptrs, stream=0):
+        _ok(_lib.qagg_agg_step_host(self.h, self._ptrs(host_grad_ptrs), stream))
+
+    def reset_residuals(self, stream=0):
+        _ok(_lib.qagg_agg_reset_residuals(self.h, stream))
+
+    def residual_ptrs(self, tensor):
+        r, s = c_vp(), c_vp()
+        _ok(_lib.qagg_agg_residuals(self.h, tensor, ctypes.byref(r), ctypes.byref(s)))
+        return r.value, s.value
+
+    def copy_residual(self, tensor, which, dst_ptr, stream=0):
+        _ok(_lib.qagg_agg_copy_residual(self.h, tensor, which, dst_ptr, stream))
+
+    def copy_packed(self, tensor, dst_ptr, stream=0):
+        _ok(_lib.qagg_agg_copy_packed(self.h, tensor, dst_ptr, stream))
+
+    def set_profiling(self, enabled):
+        _ok(_lib.qagg_agg_set_profiling(self.h, int(bool(enabled))))
+
+    def phase_ms(self):
+        """[quantize, scatter, reduce-requantize, all-gather, unquantize] device milliseconds of the last profiled step."""
+        out = (ctypes.c_float * 5)()
+        _ok(_lib.qagg_agg_phase_ms(self.h, out))
+        return [float(x) for x in out]
+
+    @property
+    def wire_bytes(self):
+        return int(_lib.qagg_agg_wire_bytes(self.h))
+
+    @property
+    def launches_per_step(self):
+        return int(_lib.qagg_agg_launches_per_step(self.h))
+
+    def destroy(self):
+        if self.h:
+            _ok(_lib.qagg_agg_destroy(self.h))
+            self.h = None
+
+
+def step_group(aggs, grad_ptrs, stream=0):
+    """grad_ptrs[r][i]: device pointers of rank r's gradients."""
+    K = len(aggs)
+    ha = (c_vp * K)(*[a.h for a in aggs])
+    rows = [(c_vp * len(g))(*[c_vp(p) for p in g]) for g in grad_ptrs]
+    pp = (ctypes.POINTER(c_vp) * K)(*[ctypes.cast(r, ctypes.POINTER(c_vp)) for r in rows])
+    _ok(_lib.qagg_agg_step_group(ha, K, pp, stream))

@@ -1,0 +1,158 @@
+/*
+ * qagg.h -- C ABI of libqagg: B200 (sm_100a) implementation of CNTK's quantized data-parallel
+ * gradient aggregation (1-bit SGD): the 1/2/4/8/16/32-bit column quantizer with error-feedback
+ * residual, the packed QuantizedMatrix wire layout, and the striped exchange.
+ *
+ * Conventions
+ *   - Every entry point returns 0 on success and a negative QAGG_E* code on failure; nothing
+ *     throws, aborts or exits.  qagg_last_error() returns the calling thread's last message.
+ *   - fp32 matrices are column-major, M rows x N columns, element (i, j) at j*M + i, as CNTK's
+ *     Matrix<float> (Source/Math/ColumnQuantizer.h:10).
+ *   - A packed matrix is N columns of qagg_packed_col_bytes(M, bits) bytes each:
+ *         float lower; float upper; uint32 words[Q];   Q = ceil(M*bits/32)
+ *     word w holds rows w, w+Q, w+2Q, ...; the k-th of them at bit k*bits
+ *     (Source/Math/QuantizedMatrix.h:27-48, Source/Math/ColumnQuantizer.h:50-65).  A column range
+ *     [start, start+n) of a packed matrix is the byte range [start*C, (start+n)*C): that is a stripe,
+ *     and the wire message.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  Device entry
+ *     points only enqueue work; they do not synchronise unless stated.
+ *   - Results are bit-identical to the reference CPU quantizer (MatrixQuantizerCPU): per-column sums
+ *     are accumulated in row order in fp32 without fused multiply-add.
+ *   - There is no CPU fallback: without a CUDA device every compute entry point fails with
+ *     QAGG_ECUDA.
+ */
+#ifndef QAGG_H_
+#define QAGG_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QAGG_OK 0
+#define QAGG_EINVAL (-1)   /* bad argument (bits not a power of two in 1..32, negative size, null pointer ...) */
+#define QAGG_ECUDA (-2)    /* a CUDA runtime call or kernel launch failed */
+#define QAGG_ENCCL (-3)    /* an NCCL call failed */
+#define QAGG_ESTATE (-4)   /* object used in the wrong state (e.g. mismatched group) */
+#define QAGG_ETIMEOUT (-5) /* a bounded device-side wait ran out */
+
+/* flags of qagg_agg_create (defaults of the reference: both set, Source/SGDLib/SGD.cpp:2323-2327,
+ * bindings/python/cntk/train/distributed.py:135-140) */
+#define QAGG_ZERO_THRESHOLD 1  /* 1-bit: threshold at 0 instead of the column mean (zeroThresholdFor1Bit) */
+#define QAGG_SELF_QUANTIZED 2  /* owner starts its aggregate from its own QUANTIZED stripe (useQuantizationForSelfStripe) */
+#define QAGG_V2_IDENTITY_K1 4  /* one worker: leave inputs untouched (QuantizedDistributedCommunicator.h:75-81)
+                                  instead of V1's quantize -> unquantize round trip */
+
+typedef struct qagg_comm qagg_comm;
+typedef struct qagg_aggregator qagg_aggregator;
+
+/* Last error message of the calling thread ("" if none). */
+const char* qagg_last_error(void);
+/* ABI version of this header (bumped on incompatible change). */
+int qagg_abi_version(void);
+
+/* ---- layout helpers ------------------------------------------------------------------------ */
+
+/* QuantizedColumn<float>::QuantizedColumnSize (Source/Math/QuantizedMatrix.h:42-47). <0 on bad args. */
+int64_t qagg_packed_col_bytes(int64_t M, int bits);
+/* QuantizedMatrix<float>::GetSize (Source/Math/QuantizedMatrix.cpp): N * column size. */
+int64_t qagg_packed_bytes(int64_t M, int64_t N, int bits);
+/* GetStripeForNode (Source/1BitSGD/AllReduceDistGradAggregator.h:56-65). */
+int qagg_stripe(int64_t num_cols, int rank, int num_ranks, int64_t* start_col, int64_t* num_cols_in_stripe);
+
+/* ---- single-matrix quantizer (device buffers) ------------------------------------------------- */
+
+/* MatrixQuantizerImpl<float>::QuantizeAsync (Source/Math/MatrixQuantizerImpl.h:31;
+ * GPU body Source/Math/MatrixQuantizerGPU.cu:226-269, kernels Source/Math/MatrixQuantizer_kernel.cu:132-179):
+ * per column, range statistics of grad+res_in, quantize, pack, res_out = (grad+res_in) - unquantized.
+ * res_in may equal res_out.  All pointers are device pointers; `packed` receives qagg_packed_bytes(). */
+int qagg_quantize(void* stream, const float* grad, const float* res_in, float* res_out, void* packed,
+                  int64_t M, int64_t N, int bits, int zero_threshold);
+
+/* MatrixQuantizerImpl<float>::UnquantizeAsync (Source/Math/MatrixQuantizerImpl.h:34;
+ * Source/Math/MatrixQuantizerGPU.cu:286-334, kernel Source/Math/MatrixQuantizer_kernel.cu:181-202):
+ * out = (add ? out : 0) + unquantized(packed). */
+int qagg_unquantize(void* stream, const void* packed, float* out, int64_t M, int64_t N, int bits, int add);
+
+/* The stripe owner's work in one pass (Source/1BitSGD/AllReduceDistGradAggregator.h:366-375, 405-435):
+ *   agg = self_raw ? self_raw : unquantized(stripes[0]);  agg += unquantized(stripes[s]) for s = 1..K-1 in order;
+ *   then quantize agg against the stripe residual into packed_out (same rules as qagg_quantize).
+ * `stripes` is a HOST array of K device pointers to packed M x n matrices (stripes[0] may be NULL when
+ * self_raw is given).  The fp32 aggregate is never written to memory. */
+int qagg_reduce_requantize(void* stream, const void* const* stripes, int K, const float* self_raw,
+                           const float* sres_in, float* sres_out, void* packed_out,
+                           int64_t M, int64_t n, int bits, int zero_threshold);
+
+/* ---- single-matrix quantizer, packed buffer on the HOST ---------------------------------------- */
+
+/* As the reference's GPU quantizer is driven (packed QuantizedMatrix on the CPU, Source/Math/MatrixQuantizerGPU.cu:243,
+ * 260-268, 300-325): device gradient/residual, packed words delivered to / taken from host memory.  `dev_scratch`
+ * is a device buffer of qagg_packed_bytes() the caller owns.  Both calls return after the copy has completed. */
+int qagg_quantize_to_host(void* stream, const float* grad, const float* res_in, float* res_out, void* dev_scratch,
+                          void* host_packed, int64_t M, int64_t N, int bits, int zero_threshold);
+int qagg_unquantize_from_host(void* stream, const void* host_packed, void* dev_scratch, float* out,
+                              int64_t M, int64_t N, int bits, int add);
+
+/* ---- communicator ---------------------------------------------------------------------------------
+ * Replaces the MPI point-to-point traffic of the reference (Source/1BitSGD/AllReduceDistGradAggregator.h:303-365,
+ * 459-502; Source/Common/Include/MPIWrapper.h:74-177) by NCCL send/recv and all-gather of packed stripes between
+ * device buffers; bootstrap as Source/Math/NcclComm.cpp:96-111 (a unique id made on rank 0, distributed by the caller). */
+
+#define QAGG_UNIQUE_ID_BYTES 128
+/* Fill `out` (QAGG_UNIQUE_ID_BYTES) with a fresh NCCL unique id; call on one rank, distribute by any means. */
+int qagg_unique_id(void* out);
+/* One rank of a K-rank group on CUDA device `device`.  K == 1 needs no id (may be NULL) and never touches NCCL. */
+int qagg_comm_create(const void* unique_id, int rank, int num_ranks, int device, qagg_comm** out);
+/* K ranks living in THIS process on ONE device, exchanging by device-to-device copies: how the reference's own
+ * multi-rank GPU tests run (all ranks on GPU 0; Tests/EndToEndTests/Speech/DNN/Parallel1BitQuantization/baseline.gpu.txt).
+ * Fills out[0..K-1].  Aggregators built on these must be stepped with qagg_agg_step_group. */
+int qagg_comm_create_local_group(int num_ranks, int device, qagg_comm** out);
+int qagg_comm_rank(const qagg_comm* c);
+int qagg_comm_size(const qagg_comm* c);
+int qagg_comm_destroy(qagg_comm* c);
+
+/* ---- aggregator -------------------------------------------------------------------------------------
+ * AllReduceDistGradAggregator<float> (Source/1BitSGD/AllReduceDistGradAggregator.h:40-147, 237-566) and
+ * QuantizedMPICommunicatorImpl::QuantizedAggregateInPlace (Source/1BitSGD/QuantizedDistributedCommunicator.h:51-61,
+ * 285-539).  Owns the residuals (zeroed at creation), the packed send/receive/gather buffers and the stripe
+ * residuals for its lifetime; tensor shapes are fixed at creation. */
+int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, int bits, int flags,
+                    qagg_aggregator** out);
+/* One AggregateGradients call: grads[i] (device, M[i] x N[i]) is replaced in place by the aggregate over all ranks.
+ * Enqueues on `stream`; returns without waiting.  `grads` is a host array. */
+int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream);
+/* The same for all K aggregators of a local group, in lock step: grads[r][i]. */
+int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* const* const* grads, void* stream);
+/* The same through HOST gradient buffers (pinned memory recommended): copies host_grads[i] to the device, aggregates,
+ * copies the result back into host_grads[i], and waits for completion. */
+int qagg_agg_step_host(qagg_aggregator* a, float* const* host_grads, void* stream);
+/* ResetResidue on both quantizer sets (AllReduceDistGradAggregator.h:121-136; also what V2's CreateCheckpoint does,
+ * Source/1BitSGD/QuantizedDataParallelDistributedLearner.h:73-91). */
+int qagg_agg_reset_residuals(qagg_aggregator* a, void* stream);
+/* Device pointers to internal state, for inspection: the M x N residual and the M x n stripe residual of tensor i
+ * (stripe pointer NULL when this rank owns no column of it). */
+int qagg_agg_residuals(qagg_aggregator* a, int tensor, float** residual, float** stripe_residual);
+/* Copy the residual (which = 0, M x N floats) or the stripe residual (which = 1, M x n floats) of tensor i into a
+ * device buffer, on `stream`. */
+int qagg_agg_copy_residual(qagg_aggregator* a, int tensor, int which, float* dst_dev, void* stream);
+/* Copy the gathered packed matrix of tensor i (what every rank unquantized from in the last step) into a device
+ * buffer of qagg_packed_bytes(M[i], N[i], bits), in the reference's contiguous layout. */
+int qagg_agg_copy_packed(qagg_aggregator* a, int tensor, void* dst_dev, void* stream);
+/* Per-phase device timing of the steps that follow (no reference counterpart; the reference only has the wall-clock
+ * "Actual gradient aggregation time" trace, AllReduceDistGradAggregator.h:241-246, 560-565).  When enabled, each step records
+ * CUDA events on its stream around its five phases.  qagg_agg_phase_ms waits for the recorded steps and returns the mean
+ * milliseconds per step, over the (at most 64) most recent steps since the last read, for
+ * {quantize, scatter, reduce-requantize, all-gather, unquantize} (about 0 for phases a 1-rank step skips). */
+int qagg_agg_set_profiling(qagg_aggregator* a, int enabled);
+int qagg_agg_phase_ms(qagg_aggregator* a, float* out5);
+/* Bytes one step sends over the wire from this rank (scatter + gather), and kernels it launches. */
+int64_t qagg_agg_wire_bytes(const qagg_aggregator* a);
+int qagg_agg_launches_per_step(const qagg_aggregator* a);
+int qagg_agg_destroy(qagg_aggregator* a);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QAGG_H_ */

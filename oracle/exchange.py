@@ -43,7 +43,18 @@ class ExchangeState:
                 a[...] = 0
 
 
-def aggregate_step(backend, state, grads, bits, zero_thr=True, self_quant=True, v2_identity_at_k1=False):
+def _each_rank(executor, fn, K):
+    """Run fn(r) for every simulated rank: serially, or on `executor` threads (one per rank, as the reference runs one
+    single-threaded quantizer per MPI rank; the C checkers release the GIL while they compute)."""
+    if executor is None:
+        for r in range(K):
+            fn(r)
+    else:
+        for f in [executor.submit(fn, r) for r in range(K)]:
+            f.result()
+
+
+def aggregate_step(backend, state, grads, bits, zero_thr=True, self_quant=True, v2_identity_at_k1=False, executor=None):
     """One AggregateGradients call on all K simulated ranks.
 
     ``grads[r][i]`` is rank r's (N_i, M_i) float32 gradient; it is overwritten with the aggregate,
@@ -60,9 +71,12 @@ def aggregate_step(backend, state, grads, bits, zero_thr=True, self_quant=True, 
 
     # step 1 (:290-300): every rank quantizes every gradient against its own residual, in place.
     packed = [[np.zeros(shapes[i][1] * col_bytes[i], np.uint8) for i in range(T)] for _ in range(K)]
-    for r in range(K):
+
+    def quantize_all(r):
         for i in range(T):
             backend.quantize(grads[r][i], state.res[r][i], state.res[r][i], packed[r][i], bits, zero_thr)
+
+    _each_rank(executor, quantize_all, K)
 
     if K == 1:
         # V1 with one rank: the own stripe is unquantized into the gradient (:366-375); no stripe is ever
@@ -74,7 +88,8 @@ def aggregate_step(backend, state, grads, bits, zero_thr=True, self_quant=True, 
 
     # steps 2-5: the owner of each stripe builds the aggregate inside its own gradient slice and requantizes.
     agg_packed = [[None] * T for _ in range(K)]
-    for r in range(K):
+
+    def own_stripes(r):
         for i in range(T):
             M, N = shapes[i]
             s, n = stripe(N, r, K)
@@ -92,6 +107,8 @@ def aggregate_step(backend, state, grads, bits, zero_thr=True, self_quant=True, 
             backend.quantize(agg, state.sres[r][i], state.sres[r][i], out, bits, zero_thr)  # :429-435
             agg_packed[r][i] = out
 
+    _each_rank(executor, own_stripes, K)
+
     # steps 7-9 (:459-522): all-gather of the requantized stripes, then every rank unquantizes everything.
     gathered = []
     for i in range(T):
@@ -103,7 +120,9 @@ def aggregate_step(backend, state, grads, bits, zero_thr=True, self_quant=True, 
             if n:
                 full[s * C:(s + n) * C] = agg_packed[r][i]
         gathered.append(full)
-    for r in range(K):
+    def unquantize_all(r):
         for i in range(T):
             backend.unquantize(gathered[i], grads[r][i], bits, add=False)
+
+    _each_rank(executor, unquantize_all, K)
     return [gathered for _ in range(K)]

@@ -1,0 +1,164 @@
+"""GPU parity of the striped aggregator against the CPU restatement of the exchange (oracle/exchange.py).
+
+K ranks live in one process on one device and exchange by device-to-device copies (qagg_comm_create_local_group),
+which is how the reference's own multi-rank GPU tests ran (all ranks on GPU 0).  Every rank's aggregated gradients,
+residuals, stripe residuals and the gathered packed words must be byte-identical to the oracle's, step after step."""
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import make_golden as mg  # noqa: E402
+
+from oracle import exchange as ox  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def G():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import gpu_util
+    return gpu_util
+
+
+def run_group(G, oracle, shapes, K, bits, zero_thr, self_quant, steps, make_inputs, check_every=1, v2_identity=False):
+    from cntk_b200 import lib
+    flags = (lib.ZERO_THRESHOLD if zero_thr else 0) | (lib.SELF_QUANTIZED if self_quant else 0) | (lib.V2_IDENTITY_K1 if v2_identity else 0)
+    comms = lib.Comm.local_group(K, 0)
+    aggs = [lib.Aggregator(c, shapes, bits, flags) for c in comms]
+    st = ox.ExchangeState(shapes, K)
+    dgrads = [[torch.zeros((N, M), dtype=torch.float32, device=G.DEV) for (M, N) in shapes] for _ in range(K)]
+    try:
+        for step in range(steps):
+            grads = make_inputs(K, step)
+            for r in range(K):
+                for i in range(len(shapes)):
+                    dgrads[r][i].copy_(torch.from_numpy(grads[r][i]))
+            packed = ox.aggregate_step(oracle, st, grads, bits, zero_thr, self_quant, v2_identity_at_k1=v2_identity)
+            lib.step_group(aggs, [[t.data_ptr() for t in dgrads[r]] for r in range(K)])
+            if (step + 1) % check_every and step != steps - 1:
+                continue
+            for r in range(K):
+                for i, (M, N) in enumerate(shapes):
+                    G.assert_same_bits(G.host(dgrads[r][i]), grads[r][i], f"step {step} rank {r} tensor {i} aggregate")
+                    if v2_identity and K == 1:
+                        continue
+                    res = torch.empty((N, M), dtype=torch.float32, device=G.DEV)
+                    aggs[r].copy_residual(i, 0, res.data_ptr())
+                    G.assert_same_bits(G.host(res), st.res[r][i], f"step {step} rank {r} tensor {i} residual")
+                    n = ox.stripe(N, r, K)[1]
+                    if n and K > 1:
+                        sres = torch.empty((n, M), dtype=torch.float32, device=G.DEV)
+                        aggs[r].copy_residual(i, 1, sres.data_ptr())
+                        G.assert_same_bits(G.host(sres), st.sres[r][i], f"step {step} rank {r} tensor {i} stripe residual")
+                    if packed is not None:
+                        pk = torch.zeros(lib.packed_bytes(M, N, bits), dtype=torch.uint8, device=G.DEV)
+                        aggs[r].copy_packed(i, pk.data_ptr())
+                        G.assert_same_bits(G.host(pk), packed[r][i], f"step {step} rank {r} tensor {i} gathered packed words")
+    finally:
+        for a in aggs:
+            a.destroy()
+        for c in comms:
+            c.destroy()
+
+
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("bits,zero_thr", [(1, True), (1, False), (2, True), (4, True)])
+@pytest.mark.parametrize("self_quant", [True, False])
+def test_small_exchange_bit_exact(G, oracle_port, K, bits, zero_thr, self_quant):
+    """The fixture gradient set (includes N < K and single-column tensors), three steps."""
+    run_group(G, oracle_port, mg.EXCHANGE_SHAPES, K, bits, zero_thr, self_quant, mg.EXCHANGE_STEPS, mg.exchange_inputs)
+
+
+def test_small_exchange_matches_committed_fixture(G, oracle_port):
+    """Final aggregate of the K=2 and K=3 fixtures written by tests/golden/make_golden.py from the reference build."""
+    small = np.load(os.path.join(os.path.dirname(__file__), "golden", "golden_small.npz"))
+    from cntk_b200 import lib
+    for K in (2, 3):
+        comms = lib.Comm.local_group(K, 0)
+        aggs = [lib.Aggregator(c, mg.EXCHANGE_SHAPES, 1) for c in comms]
+        dgrads = None
+        for step in range(mg.EXCHANGE_STEPS):
+            grads = mg.exchange_inputs(K, step)
+            dgrads = [[G.dev(g) for g in grads[r]] for r in range(K)]
+            lib.step_group(aggs, [[t.data_ptr() for t in dgrads[r]] for r in range(K)])
+        key = f"K{K}_b1_z1_s1"
+        for i, (M, N) in enumerate(mg.EXCHANGE_SHAPES):
+            G.assert_same_bits(G.host(dgrads[0][i]), small[f"exchange_{key}_final_agg_t{i}"], f"{key} tensor {i}")
+            pk = torch.zeros(lib.packed_bytes(M, N, 1), dtype=torch.uint8, device=G.DEV)
+            aggs[0].copy_packed(i, pk.data_ptr())
+            G.assert_same_bits(G.host(pk), small[f"exchange_{key}_final_packed_t{i}"], f"{key} packed {i}")
+        for a in aggs:
+            a.destroy()
+        for c in comms:
+            c.destroy()
+
+
+def test_v2_single_worker_is_identity(G, oracle_port):
+    run_group(G, oracle_port, mg.EXCHANGE_SHAPES, 1, 1, True, True, 2, mg.exchange_inputs, v2_identity=True)
+
+
+# speech-DNN-shaped gradient set scaled down 8x per dimension (same structure: weights + bias vectors)
+SPEECH_SMALL = [(256, 54)] + [(256, 256)] * 6 + [(1163, 256)] + [(256, 1)] * 7 + [(1163, 1)]
+
+
+def speech_inputs(K, step):
+    return [[mg.normal_input(M, N, 1e-3, 1000 * r + step + 7919 * i) for i, (M, N) in enumerate(SPEECH_SMALL)] for r in range(K)]
+
+
+@pytest.mark.parametrize("K", [1, 2, 4, 8])
+def test_speech_shaped_set_100_steps_bit_exact(G, oracle_port, K):
+    """1-bit SGD aggregation of a speech-DNN-shaped set, residual carried over 100 steps, seed = 1000*rank + step.
+    Checked every 25 steps and at the end: aggregated gradients, both residual sets and packed words, all bit-exact."""
+    run_group(G, oracle_port, SPEECH_SMALL, K, 1, True, True, 100, speech_inputs, check_every=25)
+
+
+RESNET_SMALL = [(64, 147), (64, 64), (64, 576), (256, 64), (128, 1152), (512, 128), (64, 1), (256, 1), (512, 1), (100, 512), (100, 1)]
+
+
+def resnet_inputs(K, step):
+    out = []
+    for r in range(K):
+        row = []
+        for i, (M, N) in enumerate(RESNET_SMALL):
+            rng = np.random.default_rng(500000 + 1000 * r + step + 104729 * i)
+            row.append(rng.laplace(0.0, 1e-4, size=(N, M)).astype(np.float32))
+        out.append(row)
+    return out
+
+
+@pytest.mark.parametrize("K", [2, 8])
+def test_resnet_shaped_set_4bit(G, oracle_port, K):
+    """4-bit aggregation of conv-shaped tensors ([out_ch, in_ch*kh*kw]: few rows, many columns) plus BN vectors,
+    Laplace(0, 1e-4) values, 20 steps."""
+    run_group(G, oracle_port, RESNET_SMALL, K, 4, True, True, 20, resnet_inputs, check_every=10)
+
+
+LSTM_SMALL = [(5000, 64), (512, 256), (512, 1), (512, 256), (512, 1), (64, 5000)]
+
+
+def lstm_inputs(K, step):
+    out = []
+    for r in range(K):
+        row = []
+        for i, (M, N) in enumerate(LSTM_SMALL):
+            rng = np.random.default_rng(900000 + 1000 * r + step + 15485863 * i)
+            a = (rng.standard_normal((N, M)) * 5e-4).astype(np.float32)
+            if i == 0:
+                zero_cols = rng.random(N) < 0.9  # 90% of the embedding's columns exactly zero
+                a[zero_cols] = 0.0
+            row.append(a)
+        out.append(row)
+    return out
+
+
+@pytest.mark.parametrize("K", [2, 4])
+def test_lstm_shaped_set_ragged(G, oracle_port, K):
+    """Tall embedding with 90% all-zero columns, wide softmax, bias vectors; 1 bit, 10 steps."""
+    run_group(G, oracle_port, LSTM_SMALL, K, 1, True, True, 10, lstm_inputs, check_every=5)
