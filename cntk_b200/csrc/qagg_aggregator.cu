@@ -88,6 +88,7 @@ struct qagg_aggregator
     std::vector<QItem> iK1, iK2, iK3;
     QTensor *dK1 = nullptr, *dK2 = nullptr, *dK3 = nullptr;
     QItem *dI1 = nullptr, *dI2 = nullptr, *dI3 = nullptr;
+    DevBuf queue; // three pairs of work-queue counters (one pair per kernel), zero when no kernel is running
     std::vector<int> k2Tensor; // tensor index of each K2 table entry
     std::vector<float*> boundGrads;
     LaunchCfg cfg;
@@ -277,15 +278,18 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
 
 int launch_k1(qagg_aggregator* a, cudaStream_t st)
 {
-    return check_cuda(launch_colquant(st, false, a->mode, nullptr, a->dK1, a->dI1, (int) a->iK1.size(), 0, a->cfg), "quantize launch");
+    return check_cuda(launch_colquant(st, false, a->mode, nullptr, a->dK1, a->dI1, (int) a->iK1.size(), 0, a->cfg,
+                                      static_cast<unsigned*>(a->queue.p)), "quantize launch");
 }
 int launch_k2(qagg_aggregator* a, cudaStream_t st)
 {
-    return check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg), "reduce-requantize launch");
+    return check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg,
+                                      static_cast<unsigned*>(a->queue.p) + QAGG_COUNTER_UINTS), "reduce-requantize launch");
 }
 int launch_k3(qagg_aggregator* a, cudaStream_t st)
 {
-    return check_cuda(launch_unquantize(st, false, nullptr, a->dK3, a->dI3, (int) a->iK3.size(), 0, a->cfg), "unquantize launch");
+    return check_cuda(launch_unquantize(st, false, nullptr, a->dK3, a->dI3, (int) a->iK3.size(), 0, a->cfg,
+                                        static_cast<unsigned*>(a->queue.p) + 2 * QAGG_COUNTER_UINTS), "unquantize launch");
 }
 
 } // namespace
@@ -450,6 +454,8 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
     if ((rc = build_tables(a.get())))
         return rc;
     if ((rc = a->tables.alloc(table_bytes(a.get()), true)))
+        return rc;
+    if ((rc = a->queue.alloc(3 * QAGG_COUNTER_UINTS * sizeof(unsigned), true)))
         return rc;
     *out = a.release();
     return QAGG_OK;

@@ -7,6 +7,7 @@
 #include <string>
 
 #define QAGG_MAXK 16 // most ranks in one group (one 8-GPU box needs 8)
+#define QAGG_COUNTER_UINTS 272
 
 namespace qagg {
 
@@ -68,10 +69,13 @@ int cols_per_item(long long M, long long N, int smemFloats, bool* resident);
 
 // launchers (qagg_kernels.cu).  `single` != nullptr: one matrix described by value, items derived from the block index.
 // otherwise `tensors`/`items` are device tables.
+// `counters` (optional, QAGG_COUNTER_UINTS zero-initialised uints in device memory, private to one kernel in flight)
+// switches the kernel from static striding over the items to a shared work queue: [0] next item, [1] CTAs finished
+// (both re-zeroed by the kernel before it ends), [8 + smid] per-SM tickets that spread the walking warps.
 cudaError_t launch_colquant(cudaStream_t st, bool stripes, int mode, const QTensor* single, const QTensor* tensors,
-                            const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg);
+                            const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters = nullptr);
 cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, const QTensor* tensors,
-                              const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg);
+                              const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters = nullptr);
 cudaError_t get_launch_cfg(int device, LaunchCfg* cfg);
 int unq_cols_per_item(long long M);
 

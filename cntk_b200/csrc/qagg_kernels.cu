@@ -5,16 +5,36 @@
 //   * every float operation is an explicit round-to-nearest intrinsic (__fadd_rn, __fmul_rn, __fdiv_rn,
 //     __fsqrt_rn), so nothing is contracted into a fused multiply-add;
 //   * the per-column sums (level sums for 1 bit, sum of squares otherwise, and the mean in mean-threshold
-//     mode) are accumulated in ROW ORDER by one lane per column -- float addition is not associative and the
-//     reference adds sequentially; counts are integers and need no order.
+//     mode) are accumulated in ROW ORDER -- float addition is not associative and the reference adds
+//     sequentially.  Each of the two level sums of a 1-bit column is its own chain (one lane each); counts
+//     are integers, need no order, and are gathered by all threads with redux / shared-memory atomics.
 // A column's fp32 values (gradient + residual, or the sum of the received stripes + stripe residual) are
 // staged once in shared memory; the ordered walk, the quantisation, the bit packing and the residual update
 // all read them from there, so HBM sees each input and each output exactly once.
+//
+// NaN inputs: a NaN in a column makes that column's range NaN, as in the reference, but the payload bits of
+// the resulting NaNs are unspecified.  Zeros of either sign are handled exactly.
 #include "qagg_internal.h"
 
 namespace qagg {
 
-constexpr int NT = 256; // threads per CTA
+constexpr int NT = 256;     // threads per CTA
+constexpr int NWARPS = NT / 32;
+constexpr int CMAX = 128;   // most columns in one work item
+constexpr int UNQ_CMAX = 512;
+
+// optional phase timers for development builds (-DQAGG_PROBE); they expand to nothing in the product
+#ifdef QAGG_PROBE
+__device__ unsigned long long g_probe[8];
+__device__ int g_walkerForce = -1;
+#define PROBE_MARK(var) const long long var = clock64()
+#define PROBE_ADD(i, a, b) \
+    if (threadIdx.x == 0)  \
+    atomicAdd(&g_probe[i], (unsigned long long) ((b) - (a)))
+#else
+#define PROBE_MARK(var)
+#define PROBE_ADD(i, a, b)
+#endif
 
 // ---- value quantizer (ValueQuantizer<float>, Source/Math/ValueQuantizer.h:68-162) ---------------------
 struct ValQ
@@ -63,28 +83,29 @@ __device__ __forceinline__ unsigned quantize_multibit(const ValQ& q, int bits, f
 }
 
 // ---- routing of packed column j to its owner (GetStripeForNode, AllReduceDistGradAggregator.h:56-65) ----
-__device__ __forceinline__ unsigned char* packed_col(const QTensor& T, long long j)
+__device__ __forceinline__ unsigned char* packed_col(const QTensor& T, int j)
 {
     int p = 0;
-    long long start = 0;
+    int start = 0;
     if (T.K > 1)
     {
-        const long long big = (T.per + 1) * T.rem; // columns held by the ranks that got one extra
+        const int per = (int) T.per, rem = (int) T.rem;
+        const int big = (per + 1) * rem; // columns held by the ranks that got one extra
         if (j < big)
         {
-            p = (int) (j / (T.per + 1));
-            start = (long long) p * (T.per + 1);
+            p = j / (per + 1);
+            start = p * (per + 1);
         }
         else
         {
-            p = (int) (T.rem + (j - big) / T.per);
-            start = big + ((long long) p - T.rem) * T.per;
+            p = rem + (j - big) / per;
+            start = big + (p - rem) * per;
         }
     }
-    return T.pk[p] + (j - start) * T.colBytes;
+    return T.pk[p] + (size_t) (j - start) * (size_t) T.colBytes;
 }
 
-// ---- element (row, column j) of the matrix being quantized; slow general form ---------------------------
+// ---- element (row, column j) of the matrix being quantized; slow general form (streamed columns only) ----
 template <bool STRIPES>
 __device__ __forceinline__ float load_v(const QTensor& T, long long j, long long row)
 {
@@ -118,76 +139,26 @@ __device__ __forceinline__ float load_v(const QTensor& T, long long j, long long
     }
 }
 
-// ---- ordered accumulation over rows [0, nrows) of one staged column -------------------------------------
-struct Acc
-{
-    float a0 = 0.0f, a1 = 0.0f; // level sums (1 bit) / sum of squares in a0 (multi-bit)
-    float am = 0.0f;            // plain sum (mean-threshold mode, first pass)
-    unsigned n0 = 0;            // values below the threshold
-};
-
-template <int MODE, bool MEANPASS>
-__device__ __forceinline__ void walk_one(Acc& A, float v, float mean)
-{
-    if (MEANPASS)
-    {
-        A.am = __fadd_rn(A.am, v);
-    }
-    else if (MODE == MODE_MULTIBIT)
-    {
-        const float d = __fsub_rn(v, mean);
-        A.a0 = __fadd_rn(A.a0, __fmul_rn(d, d));
-    }
-    else
-    {
-        if (v < mean)
-        {
-            A.a0 = __fadd_rn(A.a0, v);
-            A.n0++;
-        }
-        else
-        {
-            A.a1 = __fadd_rn(A.a1, v);
-        }
-    }
-}
-
-template <int MODE, bool MEANPASS>
-__device__ __forceinline__ void walk(const float* __restrict__ vcol, int nrows, Acc& A, float mean)
-{
-    int i = 0;
-    for (; i + 4 <= nrows; i += 4)
-    {
-        const float4 v = *reinterpret_cast<const float4*>(vcol + i);
-        walk_one<MODE, MEANPASS>(A, v.x, mean);
-        walk_one<MODE, MEANPASS>(A, v.y, mean);
-        walk_one<MODE, MEANPASS>(A, v.z, mean);
-        walk_one<MODE, MEANPASS>(A, v.w, mean);
-    }
-    for (; i < nrows; ++i)
-        walk_one<MODE, MEANPASS>(A, vcol[i], mean);
-}
-
-// range of one column from its ordered sums (ColumnQuantizer.h:279-316, 320-339)
+// ---- range of one column from its ordered sums (ColumnQuantizer.h:279-316, 320-339) ---------------------
 template <int MODE>
-__device__ __forceinline__ void finalize_range(const Acc& A, float mean, long long M, float& lower, float& upper)
+__device__ __forceinline__ void finalize_range(float a0, float a1, unsigned n0, float mean, long long M, float& lower, float& upper)
 {
     const float rows = (float) (unsigned long long) M;
     if (MODE == MODE_MULTIBIT)
     {
-        const float stddev = __fsqrt_rn(__fdiv_rn(A.a0, rows));
+        const float stddev = __fsqrt_rn(__fdiv_rn(a0, rows));
         const float w = __fmul_rn(4.0f, stddev);
         lower = __fsub_rn(mean, w);
         upper = __fadd_rn(mean, w);
         return;
     }
-    unsigned num0 = A.n0;
-    unsigned num1 = (unsigned) M - A.n0;
+    unsigned num0 = n0;
+    unsigned num1 = (unsigned) M - n0;
     float radius, newmean;
     if (MODE == MODE_ONEBIT_MEAN)
     {
-        const float devacc0 = __fsub_rn(__fmul_rn((float) num0, mean), A.a0);
-        const float devacc1 = __fsub_rn(A.a1, __fmul_rn((float) num1, mean));
+        const float devacc0 = __fsub_rn(__fmul_rn((float) num0, mean), a0);
+        const float devacc1 = __fsub_rn(a1, __fmul_rn((float) num1, mean));
         const float dev = __fdiv_rn(__fadd_rn(devacc0, devacc1), rows);
         radius = __fmul_rn(2.0f, dev);
         newmean = mean;
@@ -198,8 +169,8 @@ __device__ __forceinline__ void finalize_range(const Acc& A, float mean, long lo
             num0 = 1;
         if (num1 == 0)
             num1 = 1;
-        const float mean0 = __fdiv_rn(A.a0, (float) num0);
-        const float mean1 = __fdiv_rn(A.a1, (float) num1);
+        const float mean0 = __fdiv_rn(a0, (float) num0);
+        const float mean1 = __fdiv_rn(a1, (float) num1);
         newmean = __fmul_rn(0.5f, __fadd_rn(mean0, mean1));
         radius = __fmul_rn(2.0f, __fsub_rn(mean1, newmean));
     }
@@ -207,187 +178,575 @@ __device__ __forceinline__ void finalize_range(const Acc& A, float mean, long lo
     upper = __fadd_rn(newmean, radius);
 }
 
-// ---- quantize + pack + residual for word w of column j (QuantizeOneQWord, ColumnQuantizer.h:90-147) --------
-template <int MODE, bool STRIPES, bool RESIDENT>
-__device__ __forceinline__ void quantize_word(const QTensor& T, long long j, int w, const float* __restrict__ vcol,
-                                              float lower, float upper)
+// =================================================================================================================
+// Ordered walks over one staged column.  Rows are consumed sixteen at a time with the next sixteen already loaded,
+// so the only serial dependence is the 4-cycle fp32 add chain of the accumulator.
+// =================================================================================================================
+enum WalkKind
 {
-    const ValQ q = make_valq(T.bits, lower, upper);
-    float* __restrict__ rcol = T.res_out + j * T.M;
-    const long long M = T.M;
-    const int Q = T.Q;
-    unsigned word = 0;
-    if (MODE != MODE_MULTIBIT)
-    {
-        const float val0 = unquantize_val(q, 1, 0u);
-        const float val1 = unquantize_val(q, 1, 1u);
-#pragma unroll 8
-        for (int k = 0; k < 32; ++k)
-        {
-            const long long row = (long long) w + (long long) k * Q;
-            if (row < M)
-            {
-                const float v = RESIDENT ? vcol[row] : load_v<STRIPES>(T, j, row);
-                const bool bit = (MODE == MODE_ONEBIT_ZERO) ? (v >= 0.0f) : (v >= q.qmid);
-                rcol[row] = __fsub_rn(v, bit ? val1 : val0);
-                word |= (bit ? 1u : 0u) << k;
-            }
-        }
-    }
+    WALK_SUM = 0,    // acc += v                               (mean of mean-threshold mode)
+    WALK_SQUARES,    // acc += v * v                           (multi-bit: mean is the constant 0)
+    WALK_MIN0,       // acc += min(v, 0): the rows with v < 0, everything else adds a zero     (zero threshold, lower level)
+    WALK_MAX0,       // acc += max(v, 0): the rows with v > 0, everything else adds a zero     (zero threshold, upper level)
+    WALK_SPLIT_MEAN  // lower lane: rows with v < mean (counted); upper lane: all other rows   (mean threshold)
+};
+// One warp issues at most one instruction every other cycle, so a walk keeps up with its 4-cycle add chain only if it
+// spends no more than two instructions per row.  WALK_MIN0 / WALK_MAX0 do (FMNMX + FADD); they run in two different
+// warps, because inside one warp both levels would have to share one instruction stream.  Adding a zero of either
+// sign leaves these sums unchanged (they start at +0 and a round-to-nearest sum is -0 only if both operands are).
+// min/max drop a NaN (the reference adds it to the upper sum): the staging pass flags such columns and the upper sum
+// is replaced by NaN afterwards.
+// The lane's role (lower / upper level) is DATA, not a template argument: both lanes of a pair must run the same
+// instruction stream, or the warp would execute the two walks one after the other.
+
+// In the split kinds a lane adds a row only if the row belongs to its level; for the other rows it adds +0, which
+// leaves the accumulator unchanged (these sums start at +0 and a round-to-nearest sum with a +0 operand is never -0).
+// The selection is done with integer masks, not predicates or branches: a predicate computed per row would sit on
+// the critical path of every add, and a branch would make the two lanes of a pair diverge on every row.  With masks
+// the selected operands of the next rows are ready long before the add chain needs them, so the walk runs at the
+// latency of one fp32 add per row.
+//   below  = (v - threshold) has its sign bit set   (exactly v < threshold; also true for -0 - +0 = -0, which adds
+//            a harmless -0 to the lower sum where the reference adds it to the upper sum: neither sum changes)
+//   lower lane takes v & below, upper lane takes v & ~below.
+// A NaN row poisons whichever lane its sign bit selects; the reference poisons the upper sum.  Either way the
+// column's range comes out NaN.
+__device__ __forceinline__ float pick_mine(float v, float threshold, int laneMask, bool zeroThreshold, unsigned& cnt, bool count)
+{
+    const int below = __float_as_int(zeroThreshold ? v : __fsub_rn(v, threshold)) >> 31; // all ones when below
+    if (count)
+        cnt += ((v < threshold) && (laneMask == 0)) ? 1u : 0u;                           // lower lane counts its rows (exact compare)
+    return __int_as_float(__float_as_int(v) & (below ^ laneMask));
+}
+
+template <int KIND>
+__device__ __forceinline__ void walk_step(float& acc, unsigned& cnt, float v, float mean, bool upperLane)
+{
+    if (KIND == WALK_SUM)
+        acc = __fadd_rn(acc, v);
+    else if (KIND == WALK_SQUARES)
+        acc = __fadd_rn(acc, __fmul_rn(v, v));
+    else if (KIND == WALK_MIN0)
+        acc = __fadd_rn(acc, fminf(v, 0.0f));
+    else if (KIND == WALK_MAX0)
+        acc = __fadd_rn(acc, fmaxf(v, 0.0f));
     else
+        acc = __fadd_rn(acc, pick_mine(v, mean, upperLane ? -1 : 0, false, cnt, true));
+}
+
+template <int KIND>
+__device__ __forceinline__ void walk_step4(float& acc, unsigned& cnt, const float4& v, float mean, bool upperLane)
+{
+    walk_step<KIND>(acc, cnt, v.x, mean, upperLane);
+    walk_step<KIND>(acc, cnt, v.y, mean, upperLane);
+    walk_step<KIND>(acc, cnt, v.z, mean, upperLane);
+    walk_step<KIND>(acc, cnt, v.w, mean, upperLane);
+}
+
+// Sixteen rows per trip, the next sixteen already in flight: measured at 4.7 cycles per row against 6.9 for eight
+// rows per trip (the per-trip overhead is not hidden behind a 32-cycle chain, but is behind a 64-cycle one).
+template <int KIND>
+__device__ __forceinline__ float walk_rows(const float* __restrict__ vcol, int nrows, float acc, unsigned& cnt, float mean, bool upperLane)
+{
+    int i = 0;
+    if (nrows >= 16)
     {
-        const int bits = T.bits;
-        const int vpw = 32 / bits;
-        for (int k = 0; k < vpw; ++k)
+        const float4* __restrict__ p = reinterpret_cast<const float4*>(vcol);
+        float4 a = p[0], b = p[1], c = p[2], d = p[3];
+        for (; i + 32 <= nrows; i += 16)
         {
-            const long long row = (long long) w + (long long) k * Q;
-            if (row < M)
-            {
-                const float v = RESIDENT ? vcol[row] : load_v<STRIPES>(T, j, row);
-                const unsigned qv = quantize_multibit(q, bits, v);
-                rcol[row] = __fsub_rn(v, unquantize_val(q, bits, qv));
-                word |= qv << (k * bits);
-            }
+            const float4* __restrict__ q = p + (i >> 2) + 4;
+            const float4 na = q[0], nb = q[1], nc = q[2], nd = q[3];
+            walk_step4<KIND>(acc, cnt, a, mean, upperLane);
+            walk_step4<KIND>(acc, cnt, b, mean, upperLane);
+            walk_step4<KIND>(acc, cnt, c, mean, upperLane);
+            walk_step4<KIND>(acc, cnt, d, mean, upperLane);
+            a = na;
+            b = nb;
+            c = nc;
+            d = nd;
         }
+        walk_step4<KIND>(acc, cnt, a, mean, upperLane);
+        walk_step4<KIND>(acc, cnt, b, mean, upperLane);
+        walk_step4<KIND>(acc, cnt, c, mean, upperLane);
+        walk_step4<KIND>(acc, cnt, d, mean, upperLane);
+        i += 16;
     }
-    unsigned char* dst = packed_col(T, j);
-    reinterpret_cast<unsigned*>(dst + 8)[w] = word;
-    if (w == 0)
+    for (; i < nrows; ++i)
+        walk_step<KIND>(acc, cnt, vcol[i], mean, upperLane);
+    return acc;
+}
+
+// per-item scratch that lives behind the staged columns in dynamic shared memory
+struct ColStats
+{
+    float* lower;
+    float* upper;
+    unsigned* n0;   // zero-threshold mode: values < 0, counted while staging
+    unsigned* nan;  // zero-threshold mode: the column holds a NaN
+    float* a0;      // zero-threshold mode: the two level sums, written by the two walking warps
+    float* a1;
+};
+constexpr int COLSTAT_FLOATS = 8; // shared-memory floats reserved per column for the arrays above
+
+// =================================================================================================================
+// Phase A: stage nc whole columns (v = gradient + residual, or sum of stripes + stripe residual).
+// =================================================================================================================
+template <int MODE>
+__device__ __forceinline__ void count4(const float4& v, unsigned& cnt, unsigned& nan)
+{
+    if (MODE == MODE_ONEBIT_ZERO)
     {
-        reinterpret_cast<float*>(dst)[0] = lower;
-        reinterpret_cast<float*>(dst)[1] = upper;
+        cnt += (v.x < 0.0f) + (v.y < 0.0f) + (v.z < 0.0f) + (v.w < 0.0f);
+        nan |= (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
     }
 }
 
-// ---- stage nc whole columns into shared memory -------------------------------------------------------------
-template <bool STRIPES>
-__device__ __forceinline__ void fill_resident(const QTensor& T, int col0, int nc, int stride, float* __restrict__ smem)
+template <int MODE>
+__device__ __forceinline__ void fill_dense(const QTensor& T, int col0, int nc, int stride, float* __restrict__ smem, const ColStats& S)
 {
-    const long long M = T.M;
-    if (!STRIPES)
+    const int M = (int) T.M;
+    const float* __restrict__ g = T.grad + (size_t) col0 * M;
+    const float* __restrict__ r = T.res_in + (size_t) col0 * M;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool vec = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(g) & 15) == 0) && ((reinterpret_cast<uintptr_t>(r) & 15) == 0);
+    if (vec)
     {
-        const float* __restrict__ g = T.grad + (long long) col0 * M;
-        const float* __restrict__ r = T.res_in + (long long) col0 * M;
-        const bool vec = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(g) & 15) == 0) && ((reinterpret_cast<uintptr_t>(r) & 15) == 0);
-        if (vec)
+        // warp task = 32 lanes x UNR float4 of ONE column: all loads of a task are issued before any is used
+        constexpr int UNR = 4;
+        const int M4 = M >> 2;
+        const int nch = (M4 + 32 * UNR - 1) / (32 * UNR);
+        const int ntasks = nc * nch;
+        for (int task = warp; task < ntasks; task += NWARPS)
         {
-            const int M4 = (int) (M >> 2);
-            const int total = nc * M4;
-            for (int idx = threadIdx.x; idx < total; idx += NT)
+            const int col = task / nch;
+            const int ch = task - col * nch;
+            const float4* __restrict__ g4 = reinterpret_cast<const float4*>(g + (size_t) col * M);
+            const float4* __restrict__ r4 = reinterpret_cast<const float4*>(r + (size_t) col * M);
+            float4* __restrict__ v4 = reinterpret_cast<float4*>(smem + (size_t) col * stride);
+            const int base = ch * 32 * UNR + lane;
+            float4 a[UNR], b[UNR];
+#pragma unroll
+            for (int u = 0; u < UNR; ++u)
             {
-                const int col = idx / M4;
-                const int r4 = idx - col * M4;
-                const float4 a = __ldg(reinterpret_cast<const float4*>(g) + idx);
-                const float4 b = __ldg(reinterpret_cast<const float4*>(r) + idx);
-                float4 v;
-                v.x = __fadd_rn(a.x, b.x);
-                v.y = __fadd_rn(a.y, b.y);
-                v.z = __fadd_rn(a.z, b.z);
-                v.w = __fadd_rn(a.w, b.w);
-                *reinterpret_cast<float4*>(smem + (size_t) col * stride + 4 * r4) = v;
+                const int idx = base + 32 * u;
+                if (idx < M4)
+                {
+                    a[u] = __ldcs(g4 + idx);
+                    b[u] = __ldcs(r4 + idx);
+                }
             }
-        }
-        else
-        {
-            const long long total = (long long) nc * M;
-            for (long long idx = threadIdx.x; idx < total; idx += NT)
+            unsigned cnt = 0, nan = 0;
+#pragma unroll
+            for (int u = 0; u < UNR; ++u)
             {
-                const int col = (int) (idx / M);
-                const int row = (int) (idx - (long long) col * M);
-                smem[(size_t) col * stride + row] = __fadd_rn(g[idx], r[idx]);
+                const int idx = base + 32 * u;
+                if (idx < M4)
+                {
+                    float4 v;
+                    v.x = __fadd_rn(a[u].x, b[u].x);
+                    v.y = __fadd_rn(a[u].y, b[u].y);
+                    v.z = __fadd_rn(a[u].z, b[u].z);
+                    v.w = __fadd_rn(a[u].w, b[u].w);
+                    v4[idx] = v;
+                    count4<MODE>(v, cnt, nan);
+                }
+            }
+            if (MODE == MODE_ONEBIT_ZERO)
+            {
+                cnt = __reduce_add_sync(0xffffffffu, cnt);
+                nan = __reduce_or_sync(0xffffffffu, nan);
+                if (lane == 0)
+                {
+                    if (cnt)
+                        atomicAdd(&S.n0[col], cnt);
+                    if (nan)
+                        S.nan[col] = 1u;
+                }
             }
         }
     }
     else
     {
-        // thread <-> (column, word): sources are added in index order; the raw own stripe (if used) comes first
-        const int Q = T.Q;
-        const int bits = T.bits;
-        const int vpw = 32 / bits;
-        const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
-        const int total = nc * Q;
+        const int total = nc * M;
+        int cur = -1;
+        unsigned cnt = 0;
         for (int idx = threadIdx.x; idx < total; idx += NT)
         {
-            const int col = idx / Q;
-            const int w = idx - col * Q;
-            const long long j = (long long) col0 + col;
-            float* __restrict__ vcol = smem + (size_t) col * stride;
-            bool first = true;
-            if (T.selfRaw)
+            const int col = idx / M;
+            const int row = idx - col * M;
+            const float v = __fadd_rn(g[idx], r[idx]);
+            smem[(size_t) col * stride + row] = v;
+            if (MODE == MODE_ONEBIT_ZERO)
             {
-                const float* __restrict__ gcol = T.grad + j * M;
-                for (int k = 0; k < vpw; ++k)
+                if (col != cur)
                 {
-                    const long long row = (long long) w + (long long) k * Q;
-                    if (row < M)
-                        vcol[row] = gcol[row];
+                    if (cnt)
+                        atomicAdd(&S.n0[cur], cnt);
+                    cur = col;
+                    cnt = 0;
                 }
-                first = false;
+                cnt += (v < 0.0f);
+                if (v != v)
+                    S.nan[col] = 1u;
             }
-            for (int s = T.selfRaw ? 1 : 0; s < T.nsrc; ++s)
+        }
+        if (MODE == MODE_ONEBIT_ZERO && cnt)
+            atomicAdd(&S.n0[cur], cnt);
+    }
+}
+
+// thread <-> (column, packed word): the K sources are added in index order, the raw own stripe (if used) first
+template <int MODE>
+__device__ __forceinline__ void fill_stripes(const QTensor& T, int col0, int nc, int stride, float* __restrict__ smem, const ColStats& S)
+{
+    const int M = (int) T.M;
+    const int Q = T.Q;
+    const int bits = T.bits;
+    const int vpw = 32 / bits;
+    const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
+    const int total = nc * Q;
+    for (int idx = threadIdx.x; idx < total; idx += NT)
+    {
+        const int col = idx / Q;
+        const int w = idx - col * Q;
+        const int j = col0 + col;
+        float* __restrict__ vcol = smem + (size_t) col * stride + w;
+        const int nk = min(vpw, (M - w + Q - 1) / Q); // rows w, w+Q, ... below M
+        bool first = true;
+        if (T.selfRaw)
+        {
+            const float* __restrict__ gcol = T.grad + (size_t) j * M + w;
+            for (int k = 0; k < nk; ++k)
+                vcol[k * Q] = gcol[k * Q];
+            first = false;
+        }
+        for (int s = T.selfRaw ? 1 : 0; s < T.nsrc; ++s)
+        {
+            const unsigned char* colp = T.src[s] + (size_t) j * T.colBytes;
+            const ValQ q = make_valq(bits, reinterpret_cast<const float*>(colp)[0], reinterpret_cast<const float*>(colp)[1]);
+            const unsigned word = reinterpret_cast<const unsigned*>(colp + 8)[w];
+            if (bits == 1)
             {
-                const unsigned char* colp = T.src[s] + j * T.colBytes;
-                const ValQ q = make_valq(bits, reinterpret_cast<const float*>(colp)[0], reinterpret_cast<const float*>(colp)[1]);
-                const unsigned word = reinterpret_cast<const unsigned*>(colp + 8)[w];
-                if (bits == 1)
+                const float val0 = unquantize_val(q, 1, 0u);
+                const float val1 = unquantize_val(q, 1, 1u);
+                if (first)
                 {
-                    const float val0 = unquantize_val(q, 1, 0u);
-                    const float val1 = unquantize_val(q, 1, 1u);
 #pragma unroll 8
-                    for (int k = 0; k < 32; ++k)
-                    {
-                        const long long row = (long long) w + (long long) k * Q;
-                        if (row < M)
-                        {
-                            const float val = ((word >> k) & 1u) ? val1 : val0;
-                            vcol[row] = first ? val : __fadd_rn(val, vcol[row]);
-                        }
-                    }
+                    for (int k = 0; k < nk; ++k)
+                        vcol[k * Q] = ((word >> k) & 1u) ? val1 : val0;
                 }
                 else
                 {
-                    for (int k = 0; k < vpw; ++k)
-                    {
-                        const long long row = (long long) w + (long long) k * Q;
-                        if (row < M)
-                        {
-                            const float val = unquantize_val(q, bits, (word >> (k * bits)) & mask);
-                            vcol[row] = first ? val : __fadd_rn(val, vcol[row]);
-                        }
-                    }
+#pragma unroll 8
+                    for (int k = 0; k < nk; ++k)
+                        vcol[k * Q] = __fadd_rn(((word >> k) & 1u) ? val1 : val0, vcol[k * Q]);
                 }
-                first = false;
             }
-            const float* __restrict__ rcol = T.res_in + j * M;
-            for (int k = 0; k < vpw; ++k)
+            else
             {
-                const long long row = (long long) w + (long long) k * Q;
-                if (row < M)
-                    vcol[row] = __fadd_rn(first ? 0.0f : vcol[row], rcol[row]);
+                for (int k = 0; k < nk; ++k)
+                {
+                    const float val = unquantize_val(q, bits, (word >> (k * bits)) & mask);
+                    vcol[k * Q] = first ? val : __fadd_rn(val, vcol[k * Q]);
+                }
             }
+            first = false;
+        }
+        const float* __restrict__ rcol = T.res_in + (size_t) j * M + w;
+        unsigned cnt = 0;
+#pragma unroll 4
+        for (int k = 0; k < nk; ++k)
+        {
+            const float v = __fadd_rn(first ? 0.0f : vcol[k * Q], rcol[k * Q]);
+            vcol[k * Q] = v;
+            if (MODE == MODE_ONEBIT_ZERO)
+            {
+                cnt += (v < 0.0f);
+                if (v != v)
+                    S.nan[col] = 1u;
+            }
+        }
+        if (MODE == MODE_ONEBIT_ZERO && cnt)
+            atomicAdd(&S.n0[col], cnt);
+    }
+}
+
+// =================================================================================================================
+// Phase B: ordered sums and the column range.  1-bit modes use a lane pair per column (one chain per level).
+// =================================================================================================================
+template <int MODE>
+__device__ __forceinline__ void walk_resident(const QTensor& T, int nc, int stride, const float* __restrict__ smem, const ColStats& S,
+                                              int walkerWarp)
+{
+    const int M = (int) T.M;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // round r (16 column pairs, or 32 columns in multi-bit mode) is walked by warp (walkerWarp + r) % NWARPS: the first
+    // round -- the only one for tall columns -- sits on a different warp in each CTA of an SM, so the walkers of the
+    // co-resident CTAs do not share one scheduler
+    if (MODE == MODE_MULTIBIT)
+    {
+        for (int r = 0; r * 32 < nc; ++r)
+        {
+            if (((walkerWarp + r) & (NWARPS - 1)) != warp)
+                continue;
+            const int col = r * 32 + lane;
+            if (col < nc)
+            {
+                unsigned cnt = 0;
+                const float a0 = walk_rows<WALK_SQUARES>(smem + (size_t) col * stride, M, 0.0f, cnt, 0.0f, false);
+                float lo, up;
+                finalize_range<MODE>(a0, 0.0f, 0u, 0.0f, T.M, lo, up);
+                S.lower[col] = lo;
+                S.upper[col] = up;
+            }
+        }
+        return;
+    }
+    if (MODE == MODE_ONEBIT_ZERO)
+    {
+        // round r = 32 columns; its lower sums are walked by warp (walkerWarp + 2r) and its upper sums by the next warp
+        for (int r = 0; r * 32 < nc; ++r)
+        {
+            const int col = r * 32 + lane;
+            const int wl = (walkerWarp + 2 * r) & (NWARPS - 1), wu = (walkerWarp + 2 * r + 1) & (NWARPS - 1);
+            if (col >= nc || (warp != wl && warp != wu))
+                continue;
+            unsigned cnt = 0;
+            const float* vcol = smem + (size_t) col * stride;
+            if (warp == wl)
+            {
+                PROBE_MARK(w0);
+                S.a0[col] = walk_rows<WALK_MIN0>(vcol, M, 0.0f, cnt, 0.0f, false);
+                PROBE_MARK(w1);
+#ifdef QAGG_PROBE
+                if (lane == 0)
+                    atomicAdd(&g_probe[4], (unsigned long long) (w1 - w0));
+#endif
+            }
+            else
+            {
+                S.a1[col] = walk_rows<WALK_MAX0>(vcol, M, 0.0f, cnt, 0.0f, true);
+            }
+        }
+        return;
+    }
+    const bool upperLane = (lane & 1) != 0;
+    for (int r = 0; r * 16 < nc; ++r)
+    {
+        if (((walkerWarp + r) & (NWARPS - 1)) != warp)
+            continue;
+        const int col = r * 16 + (lane >> 1);
+        const bool active = col < nc;
+        const float* vcol = smem + (size_t) (active ? col : 0) * stride;
+        float acc = 0.0f, mean = 0.0f;
+        unsigned cnt = 0;
+        if (MODE == MODE_ONEBIT_MEAN)
+        {
+            float sum = 0.0f;
+            if (active && !upperLane)
+                sum = walk_rows<WALK_SUM>(vcol, M, 0.0f, cnt, 0.0f, false);
+            sum = __shfl_sync(0xffffffffu, sum, lane & ~1);
+            mean = __fdiv_rn(sum, (float) (unsigned) M);
+            if (active)
+                acc = walk_rows<WALK_SPLIT_MEAN>(vcol, M, 0.0f, cnt, mean, upperLane);
+        }
+        const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
+        if (active && !upperLane)
+        {
+            float lo, up;
+            finalize_range<MODE>(acc, other, cnt, mean, T.M, lo, up);
+            S.lower[col] = lo;
+            S.upper[col] = up;
         }
     }
 }
 
 // =================================================================================================================
-// Column quantizer kernel.  One work item = up to 32 adjacent columns of one matrix.
+// Phase C: quantize, pack, residual (QuantizeOneQWord, ColumnQuantizer.h:90-147).
+// =================================================================================================================
+template <int MODE>
+__device__ __forceinline__ unsigned quant_one(const ValQ& q, int bits, float val0, float val1, float v, float& res)
+{
+    if (MODE == MODE_MULTIBIT)
+    {
+        const unsigned qv = quantize_multibit(q, bits, v);
+        res = __fsub_rn(v, unquantize_val(q, bits, qv));
+        return qv;
+    }
+    const bool bit = (MODE == MODE_ONEBIT_ZERO) ? (v >= 0.0f) : (v >= q.qmid);
+    res = __fsub_rn(v, bit ? val1 : val0);
+    return bit ? 1u : 0u;
+}
+
+__device__ __forceinline__ void store_header(unsigned char* dst, float lower, float upper)
+{
+    reinterpret_cast<float*>(dst)[0] = lower;
+    reinterpret_cast<float*>(dst)[1] = upper;
+}
+
+template <int MODE>
+__device__ __forceinline__ void quantize_resident(const QTensor& T, int col0, int nc, int stride, const float* __restrict__ smem, const ColStats& S)
+{
+    const int M = (int) T.M;
+    const int Q = T.Q;
+    const int bits = T.bits;
+    const int vpw = 32 / bits;
+    const bool vec = ((Q & 3) == 0) && ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(T.res_out) & 15) == 0);
+    if (vec)
+    {
+        // thread <-> four adjacent words: rows 4*w4 + k*Q .. +3 are one float4 in shared and in global memory
+        const int Q4 = Q >> 2;
+        const int total = nc * Q4;
+        for (int t = threadIdx.x; t < total; t += NT)
+        {
+            const int col = t / Q4;
+            const int w = (t - col * Q4) * 4;
+            const int j = col0 + col;
+            const float lower = S.lower[col], upper = S.upper[col];
+            const ValQ q = make_valq(bits, lower, upper);
+            const float val0 = unquantize_val(q, 1, 0u), val1 = unquantize_val(q, 1, 1u);
+            const float* __restrict__ vp = smem + (size_t) col * stride + w;
+            float* __restrict__ rp = T.res_out + (size_t) j * M + w;
+            const int nk = min(vpw, (M - w + Q - 1) / Q);
+            unsigned w0 = 0, w1 = 0, w2 = 0, w3 = 0;
+#pragma unroll 4
+            for (int k = 0; k < nk; ++k)
+            {
+                const float4 v = *reinterpret_cast<const float4*>(vp + k * Q);
+                float4 r;
+                const int sh = k * bits;
+                w0 |= quant_one<MODE>(q, bits, val0, val1, v.x, r.x) << sh;
+                w1 |= quant_one<MODE>(q, bits, val0, val1, v.y, r.y) << sh;
+                w2 |= quant_one<MODE>(q, bits, val0, val1, v.z, r.z) << sh;
+                w3 |= quant_one<MODE>(q, bits, val0, val1, v.w, r.w) << sh;
+                __stcs(reinterpret_cast<float4*>(rp + k * Q), r);
+            }
+            unsigned char* dst = packed_col(T, j);
+            unsigned* words = reinterpret_cast<unsigned*>(dst + 8) + w;
+            words[0] = w0;
+            words[1] = w1;
+            words[2] = w2;
+            words[3] = w3;
+            if (w == 0)
+                store_header(dst, lower, upper);
+        }
+    }
+    else
+    {
+        const int total = nc * Q;
+        for (int t = threadIdx.x; t < total; t += NT)
+        {
+            const int col = t / Q;
+            const int w = t - col * Q;
+            const int j = col0 + col;
+            const float lower = S.lower[col], upper = S.upper[col];
+            const ValQ q = make_valq(bits, lower, upper);
+            const float val0 = unquantize_val(q, 1, 0u), val1 = unquantize_val(q, 1, 1u);
+            const float* __restrict__ vp = smem + (size_t) col * stride + w;
+            float* __restrict__ rp = T.res_out + (size_t) j * M + w;
+            const int nk = min(vpw, (M - w + Q - 1) / Q);
+            unsigned word = 0;
+#pragma unroll 8
+            for (int k = 0; k < nk; ++k)
+            {
+                float r;
+                word |= quant_one<MODE>(q, bits, val0, val1, vp[k * Q], r) << (k * bits);
+                rp[k * Q] = r;
+            }
+            unsigned char* dst = packed_col(T, j);
+            reinterpret_cast<unsigned*>(dst + 8)[w] = word;
+            if (w == 0)
+                store_header(dst, lower, upper);
+        }
+    }
+}
+
+// same, for streamed columns: the values are recomputed from the inputs
+template <int MODE, bool STRIPES>
+__device__ __forceinline__ void quantize_streamed(const QTensor& T, int col0, int nc, const ColStats& S)
+{
+    const int M = (int) T.M;
+    const int Q = T.Q;
+    const int bits = T.bits;
+    const int vpw = 32 / bits;
+    const long long total = (long long) nc * Q;
+    for (long long t = threadIdx.x; t < total; t += NT)
+    {
+        const int col = (int) (t / Q);
+        const int w = (int) (t - (long long) col * Q);
+        const int j = col0 + col;
+        const float lower = S.lower[col], upper = S.upper[col];
+        const ValQ q = make_valq(bits, lower, upper);
+        const float val0 = unquantize_val(q, 1, 0u), val1 = unquantize_val(q, 1, 1u);
+        float* __restrict__ rp = T.res_out + (size_t) j * M + w;
+        const int nk = min(vpw, (M - w + Q - 1) / Q);
+        unsigned word = 0;
+        for (int k = 0; k < nk; ++k)
+        {
+            float r;
+            word |= quant_one<MODE>(q, bits, val0, val1, load_v<STRIPES>(T, j, (long long) w + (long long) k * Q), r) << (k * bits);
+            rp[(size_t) k * Q] = r;
+        }
+        unsigned char* dst = packed_col(T, j);
+        reinterpret_cast<unsigned*>(dst + 8)[w] = word;
+        if (w == 0)
+            store_header(dst, lower, upper);
+    }
+}
+
+// =================================================================================================================
+// Column quantizer kernel.  One work item = up to CMAX adjacent columns of one matrix.
 //   A. all threads stage the columns' fp32 values in shared memory (one coalesced pass over the inputs);
-//   B. warp 0 walks them in row order, one lane per column, and derives each column's range;
+//   B. the columns are walked in row order and each column's range is derived;
 //   C. all threads quantize, pack words, write the residual and the packed column to its owner's buffer.
+// Several CTAs are resident per SM, so one CTA's walk overlaps the others' memory phases.  Work items are
+// handed out through a global counter (tallest columns first) when `counters` is given.
 // Columns too tall to stage are streamed through shared memory in chunks for B and re-read for C.
 // =================================================================================================================
 template <bool STRIPES, int MODE, bool TABLE>
-__global__ void __launch_bounds__(NT) k_colquant(const QTensor single, const QTensor* __restrict__ tensors,
-                                                 const QItem* __restrict__ items, int nItems, int colsPerItem, int smemFloats)
+__global__ void __launch_bounds__(NT, 3) k_colquant(const QTensor single, const QTensor* __restrict__ tensors,
+                                                    const QItem* __restrict__ items, int nItems, int colsPerItem, int smemFloats,
+                                                    int numSMs, unsigned* __restrict__ counters)
 {
     extern __shared__ __align__(16) float smem[];
     __shared__ QTensor sT;
-    __shared__ float sLower[32], sUpper[32];
+    __shared__ int sIt;
+    __shared__ int sWalker;
 
-    for (int it = blockIdx.x; it < nItems; it += gridDim.x)
+    // which warp walks: a per-SM ticket when a counter block is given (counters[8 + smid]; it only ever grows and is
+    // used modulo the warp count), else a guess from the block index (CTAs are dealt to the SMs round-robin)
+    if (threadIdx.x == 0)
     {
+        unsigned ticket;
+        if (counters)
+        {
+            unsigned smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            ticket = atomicAdd(&counters[8 + (smid & 255u)], 1u);
+        }
+        else
+        {
+            ticket = blockIdx.x / (unsigned) max(numSMs, 1);
+        }
+        sWalker = (int) (ticket & 3u);
+#ifdef QAGG_PROBE
+        if (g_walkerForce >= 0)
+            sWalker = g_walkerForce;
+#endif
+    }
+    __syncthreads();
+    const int walkerWarp = sWalker;
+
+    for (int iter = 0;; ++iter)
+    {
+        __syncthreads(); // previous item fully done with sT / smem / sIt
+        if (threadIdx.x == 0)
+            sIt = counters ? (int) atomicAdd(&counters[0], 1u) : (int) (blockIdx.x + (unsigned) iter * gridDim.x);
+        __syncthreads();
+        const int it = sIt;
+        if (it >= nItems)
+            break;
         int col0, nc;
-        __syncthreads(); // previous item fully done with sT / smem / sLower
         if (TABLE)
         {
             const QItem item = items[it];
@@ -405,50 +764,66 @@ __global__ void __launch_bounds__(NT) k_colquant(const QTensor single, const QTe
             if (threadIdx.x == 0)
                 sT = single;
         }
+        const int strideGuess = smem_stride(TABLE ? tensors[items[it].tensor].M : single.M);
+        const bool resident = ((long long) nc * (strideGuess + COLSTAT_FLOATS) <= (long long) smemFloats);
+        // per-column scratch sits behind the staged values (resident) or behind the chunk ring (streamed)
+        ColStats S;
+        {
+            float* tail = smem + (resident ? (size_t) nc * strideGuess : (size_t) smemFloats - COLSTAT_FLOATS * (size_t) nc);
+            S.lower = tail;
+            S.upper = tail + nc;
+            S.n0 = reinterpret_cast<unsigned*>(tail + 2 * nc);
+            S.nan = reinterpret_cast<unsigned*>(tail + 3 * nc);
+            S.a0 = tail + 4 * nc;
+            S.a1 = tail + 5 * nc;
+        }
+        for (int i = threadIdx.x; i < nc; i += NT)
+        {
+            S.n0[i] = 0;
+            S.nan[i] = 0;
+        }
         __syncthreads();
         const QTensor& T = sT;
-        const long long M = T.M;
-        const int stride = smem_stride(M);
-        const bool resident = ((long long) nc * stride <= (long long) smemFloats);
-        const int lane = threadIdx.x & 31;
-        const int warp = threadIdx.x >> 5;
+        const int stride = strideGuess;
 
         if (resident)
         {
-            fill_resident<STRIPES>(T, col0, nc, stride, smem);
+            PROBE_MARK(t0);
+            if (STRIPES)
+                fill_stripes<MODE>(T, col0, nc, stride, smem, S);
+            else
+                fill_dense<MODE>(T, col0, nc, stride, smem, S);
             __syncthreads();
-            if (warp == 0 && lane < nc)
+            PROBE_MARK(t1);
+            walk_resident<MODE>(T, nc, stride, smem, S, walkerWarp);
+            __syncthreads();
+            if (MODE == MODE_ONEBIT_ZERO)
             {
-                const float* vcol = smem + (size_t) lane * stride;
-                Acc A;
-                float mean = 0.0f;
-                if (MODE == MODE_ONEBIT_MEAN)
+                for (int col = threadIdx.x; col < nc; col += NT)
                 {
-                    walk<MODE, true>(vcol, (int) M, A, 0.0f);
-                    mean = __fdiv_rn(A.am, (float) (unsigned long long) M);
+                    float lo, up;
+                    finalize_range<MODE>(S.a0[col], S.nan[col] ? __int_as_float(0x7fc00000) : S.a1[col], S.n0[col], 0.0f, T.M, lo, up);
+                    S.lower[col] = lo;
+                    S.upper[col] = up;
                 }
-                walk<MODE, false>(vcol, (int) M, A, mean);
-                float lo, up;
-                finalize_range<MODE>(A, mean, M, lo, up);
-                sLower[lane] = lo;
-                sUpper[lane] = up;
+                __syncthreads();
             }
-            __syncthreads();
-            const int Q = T.Q;
-            const int total = nc * Q;
-            for (int idx = threadIdx.x; idx < total; idx += NT)
-            {
-                const int col = idx / Q;
-                const int w = idx - col * Q;
-                quantize_word<MODE, STRIPES, true>(T, (long long) col0 + col, w, smem + (size_t) col * stride, sLower[col], sUpper[col]);
-            }
+            PROBE_MARK(t2);
+            quantize_resident<MODE>(T, col0, nc, stride, smem, S);
+            PROBE_MARK(t3);
+            PROBE_ADD(0, t0, t1);
+            PROBE_ADD(1, t1, t2);
+            PROBE_ADD(2, t2, t3);
+            PROBE_ADD(3, 0, 1);
         }
         else
         {
-            // chunked: rows [r0, r0+cs) of the nc columns at a time
-            int cs = ((smemFloats / nc - 4) / 32) * 32 + 4;
-            Acc A;
-            float mean = 0.0f;
+            // chunked: rows [r0, r0+cs) of the nc columns at a time, one lane per column, both sums in one lane
+            const long long M = T.M;
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+            const int cs = (((smemFloats - COLSTAT_FLOATS * nc) / nc - 4) / 32) * 32 + 4;
+            float a0 = 0.0f, a1 = 0.0f, am = 0.0f, mean = 0.0f;
+            unsigned n0 = 0, dummy = 0;
             const int passes = (MODE == MODE_ONEBIT_MEAN) ? 2 : 1;
             for (int pass = 0; pass < passes; ++pass)
             {
@@ -466,48 +841,101 @@ __global__ void __launch_bounds__(NT) k_colquant(const QTensor single, const QTe
                     __syncthreads();
                     if (warp == 0 && lane < nc)
                     {
+                        const float* vcol = smem + (size_t) lane * cs;
                         if (meanPass)
-                            walk<MODE, true>(smem + (size_t) lane * cs, nr, A, 0.0f);
+                            am = walk_rows<WALK_SUM>(vcol, nr, am, dummy, 0.0f, false);
+                        else if (MODE == MODE_MULTIBIT)
+                            a0 = walk_rows<WALK_SQUARES>(vcol, nr, a0, dummy, 0.0f, false);
                         else
-                            walk<MODE, false>(smem + (size_t) lane * cs, nr, A, mean);
+                        {
+                            a0 = walk_rows<WALK_SPLIT_MEAN>(vcol, nr, a0, n0, mean, false);
+                            a1 = walk_rows<WALK_SPLIT_MEAN>(vcol, nr, a1, dummy, mean, true);
+                        }
                     }
                     __syncthreads();
                 }
                 if (meanPass)
-                    mean = __fdiv_rn(A.am, (float) (unsigned long long) M);
+                    mean = __fdiv_rn(am, (float) (unsigned long long) M);
             }
             if (warp == 0 && lane < nc)
             {
                 float lo, up;
-                finalize_range<MODE>(A, mean, M, lo, up);
-                sLower[lane] = lo;
-                sUpper[lane] = up;
+                finalize_range<MODE>(a0, a1, n0, mean, M, lo, up);
+                S.lower[lane] = lo;
+                S.upper[lane] = up;
             }
             __syncthreads();
-            const int Q = T.Q;
-            const long long total = (long long) nc * Q;
-            for (long long idx = threadIdx.x; idx < total; idx += NT)
-            {
-                const int col = (int) (idx / Q);
-                const int w = (int) (idx - (long long) col * Q);
-                quantize_word<MODE, STRIPES, false>(T, (long long) col0 + col, w, nullptr, sLower[col], sUpper[col]);
-            }
+            quantize_streamed<MODE, STRIPES>(T, col0, nc, S);
+        }
+    }
+    // the last CTA to leave re-arms the work counter for the next launch
+    if (counters && threadIdx.x == 0)
+    {
+        __threadfence();
+        const unsigned done = atomicAdd(&counters[1], 1u);
+        if (done == gridDim.x - 1)
+        {
+            counters[0] = 0;
+            counters[1] = 0;
+            __threadfence();
         }
     }
 }
 
 // =================================================================================================================
-// Unquantize kernel (UnquantizeOneQWord, ColumnQuantizer.h:150-203): thread <-> packed word, rows w + k*Q.
+// Unquantize kernel (UnquantizeOneQWord, ColumnQuantizer.h:150-203).  Per work item the per-column constants
+// are computed once into shared memory; then, depending on the shape,
+//   words-major  (Q % 4 == 0): thread <-> four adjacent packed words, one float4 store per bit position;
+//   rows-major   (M % 4 == 0): thread <-> four consecutive rows (one float4 store), words fetched through L1;
+//   scalar       otherwise   : thread <-> one packed word, 4-byte stores.
 // =================================================================================================================
+template <bool ADD>
+__device__ __forceinline__ void store_out4(float* p, float4 v)
+{
+    if (ADD)
+    {
+        const float4 o = *reinterpret_cast<const float4*>(p);
+        v.x = __fadd_rn(v.x, o.x);
+        v.y = __fadd_rn(v.y, o.y);
+        v.z = __fadd_rn(v.z, o.z);
+        v.w = __fadd_rn(v.w, o.w);
+        *reinterpret_cast<float4*>(p) = v;
+    }
+    else
+    {
+        __stcs(reinterpret_cast<float4*>(p), v);
+    }
+}
+
+__device__ __forceinline__ float unq_fast(int bits, unsigned field, float ca, float cb)
+{
+    // 1 bit: ca / cb are the two level values.  else: ca = ufactor, cb = quantimin.
+    if (bits == 1)
+        return field ? cb : ca;
+    if (bits == 32)
+        return __uint_as_float(field);
+    return __fadd_rn(__fmul_rn(__fadd_rn((float) field, 0.5f), ca), cb);
+}
+
 template <bool ADD, bool TABLE>
 __global__ void __launch_bounds__(NT) k_unquantize(const QTensor single, const QTensor* __restrict__ tensors,
-                                                   const QItem* __restrict__ items, int nItems, int colsPerItem)
+                                                   const QItem* __restrict__ items, int nItems, int colsPerItem,
+                                                   unsigned* __restrict__ counters)
 {
     __shared__ QTensor sT;
-    for (int it = blockIdx.x; it < nItems; it += gridDim.x)
+    __shared__ int sIt;
+    __shared__ const unsigned* sWords[UNQ_CMAX];
+    __shared__ float sA[UNQ_CMAX], sB[UNQ_CMAX];
+    for (int iter = 0;; ++iter)
     {
-        int col0, nc;
         __syncthreads();
+        if (threadIdx.x == 0)
+            sIt = counters ? (int) atomicAdd(&counters[0], 1u) : (int) (blockIdx.x + (unsigned) iter * gridDim.x);
+        __syncthreads();
+        const int it = sIt;
+        if (it >= nItems)
+            break;
+        int col0, nc;
         if (TABLE)
         {
             const QItem item = items[it];
@@ -527,52 +955,112 @@ __global__ void __launch_bounds__(NT) k_unquantize(const QTensor single, const Q
         }
         __syncthreads();
         const QTensor& T = sT;
-        const long long M = T.M;
+        const int M = (int) T.M;
         const int Q = T.Q;
         const int bits = T.bits;
         const int vpw = 32 / bits;
         const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
-        const long long total = (long long) nc * Q;
-        for (long long idx = threadIdx.x; idx < total; idx += NT)
+        for (int col = threadIdx.x; col < nc; col += NT)
         {
-            const int col = (int) (idx / Q);
-            const int w = (int) (idx - (long long) col * Q);
-            const long long j = (long long) col0 + col;
-            const unsigned char* colp = packed_col(T, j);
+            const unsigned char* colp = packed_col(T, col0 + col);
             const ValQ q = make_valq(bits, reinterpret_cast<const float*>(colp)[0], reinterpret_cast<const float*>(colp)[1]);
-            const unsigned word = reinterpret_cast<const unsigned*>(colp + 8)[w];
-            float* __restrict__ ocol = T.out + j * M;
+            sWords[col] = reinterpret_cast<const unsigned*>(colp + 8);
             if (bits == 1)
             {
-                const float val0 = unquantize_val(q, 1, 0u);
-                const float val1 = unquantize_val(q, 1, 1u);
-#pragma unroll 8
-                for (int k = 0; k < 32; ++k)
-                {
-                    const long long row = (long long) w + (long long) k * Q;
-                    if (row < M)
-                    {
-                        float val = ((word >> k) & 1u) ? val1 : val0;
-                        if (ADD)
-                            val = __fadd_rn(val, ocol[row]);
-                        ocol[row] = val;
-                    }
-                }
+                sA[col] = unquantize_val(q, 1, 0u);
+                sB[col] = unquantize_val(q, 1, 1u);
             }
             else
             {
-                for (int k = 0; k < vpw; ++k)
+                sA[col] = q.ufactor;
+                sB[col] = q.qmin;
+            }
+        }
+        __syncthreads();
+        float* __restrict__ out0 = T.out + (size_t) col0 * M;
+        const bool aligned = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(T.out) & 15) == 0);
+        if (aligned && ((Q & 3) == 0))
+        {
+            const int Q4 = Q >> 2;
+            const int total = nc * Q4;
+            for (int t = threadIdx.x; t < total; t += NT)
+            {
+                const int col = t / Q4;
+                const int w = (t - col * Q4) * 4;
+                const unsigned* __restrict__ words = sWords[col] + w;
+                const unsigned w0 = __ldg(words), w1 = __ldg(words + 1), w2 = __ldg(words + 2), w3 = __ldg(words + 3);
+                const float ca = sA[col], cb = sB[col];
+                float* __restrict__ op = out0 + (size_t) col * M + w;
+                const int nk = min(vpw, (M - w + Q - 1) / Q);
+#pragma unroll 4
+                for (int k = 0; k < nk; ++k)
                 {
-                    const long long row = (long long) w + (long long) k * Q;
-                    if (row < M)
-                    {
-                        float val = unquantize_val(q, bits, (word >> (k * bits)) & mask);
-                        if (ADD)
-                            val = __fadd_rn(val, ocol[row]);
-                        ocol[row] = val;
-                    }
+                    const int sh = k * bits;
+                    float4 v;
+                    v.x = unq_fast(bits, (w0 >> sh) & mask, ca, cb);
+                    v.y = unq_fast(bits, (w1 >> sh) & mask, ca, cb);
+                    v.z = unq_fast(bits, (w2 >> sh) & mask, ca, cb);
+                    v.w = unq_fast(bits, (w3 >> sh) & mask, ca, cb);
+                    store_out4<ADD>(op + k * Q, v);
                 }
             }
+        }
+        else if (aligned && Q >= 4)
+        {
+            const int M4 = M >> 2;
+            const int total = nc * M4;
+            for (int t = threadIdx.x; t < total; t += NT)
+            {
+                const int col = t / M4;
+                const int row = (t - col * M4) * 4;
+                int k = row / Q;
+                int w = row - k * Q;
+                const unsigned* __restrict__ words = sWords[col];
+                const float ca = sA[col], cb = sB[col];
+                float v[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                {
+                    v[i] = unq_fast(bits, (__ldg(words + w) >> (k * bits)) & mask, ca, cb);
+                    if (++w == Q)
+                    {
+                        w = 0;
+                        ++k;
+                    }
+                }
+                store_out4<ADD>(out0 + (size_t) col * M + row, make_float4(v[0], v[1], v[2], v[3]));
+            }
+        }
+        else
+        {
+            const long long total = (long long) nc * Q;
+            for (long long t = threadIdx.x; t < total; t += NT)
+            {
+                const int col = (int) (t / Q);
+                const int w = (int) (t - (long long) col * Q);
+                const unsigned word = __ldg(sWords[col] + w);
+                const float ca = sA[col], cb = sB[col];
+                float* __restrict__ op = out0 + (size_t) col * M + w;
+                const int nk = min(vpw, (M - w + Q - 1) / Q);
+                for (int k = 0; k < nk; ++k)
+                {
+                    float val = unq_fast(bits, (word >> (k * bits)) & mask, ca, cb);
+                    if (ADD)
+                        val = __fadd_rn(val, op[(size_t) k * Q]);
+                    op[(size_t) k * Q] = val;
+                }
+            }
+        }
+    }
+    if (counters && threadIdx.x == 0)
+    {
+        __threadfence();
+        const unsigned done = atomicAdd(&counters[1], 1u);
+        if (done == gridDim.x - 1)
+        {
+            counters[0] = 0;
+            counters[1] = 0;
+            __threadfence();
         }
     }
 }
@@ -582,14 +1070,16 @@ __global__ void __launch_bounds__(NT) k_unquantize(const QTensor single, const Q
 int cols_per_item(long long M, long long N, int smemFloats, bool* resident)
 {
     const int stride = smem_stride(M);
-    long long c = smemFloats / stride;
+    long long c = smemFloats / (stride + COLSTAT_FLOATS);
     bool res = true;
     if (c < 1)
     {
         res = false;
-        c = 8; // streamed in row chunks of smemFloats / 8
+        c = 8; // streamed in row chunks
     }
-    if (c > 32)
+    if (c > CMAX)
+        c = CMAX;
+    if (!res && c > 32)
         c = 32;
     if (c > N)
         c = N;
@@ -602,17 +1092,17 @@ int cols_per_item(long long M, long long N, int smemFloats, bool* resident)
 
 int unq_cols_per_item(long long M)
 {
-    long long c = 65536 / (M > 0 ? M : 1);
+    long long c = 32768 / (M > 0 ? M : 1);
     if (c < 1)
         c = 1;
-    if (c > 4096)
-        c = 4096;
+    if (c > UNQ_CMAX)
+        c = UNQ_CMAX;
     return (int) c;
 }
 
 template <bool STRIPES, int MODE, bool TABLE>
 static cudaError_t launch_cq(cudaStream_t st, const QTensor* single, const QTensor* tensors, const QItem* items,
-                             int nItems, int colsPerItem, const LaunchCfg& cfg)
+                             int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters)
 {
     auto kern = k_colquant<STRIPES, MODE, TABLE>;
     const size_t smemBytes = (size_t) cfg.smemFloats * sizeof(float);
@@ -623,19 +1113,19 @@ static cudaError_t launch_cq(cudaStream_t st, const QTensor* single, const QTens
     if (grid > nItems)
         grid = nItems;
     static const QTensor zero = {};
-    kern<<<grid, NT, smemBytes, st>>>(single ? *single : zero, tensors, items, nItems, colsPerItem, cfg.smemFloats);
+    kern<<<grid, NT, smemBytes, st>>>(single ? *single : zero, tensors, items, nItems, colsPerItem, cfg.smemFloats, cfg.numSMs, counters);
     return cudaGetLastError();
 }
 
 cudaError_t launch_colquant(cudaStream_t st, bool stripes, int mode, const QTensor* single, const QTensor* tensors,
-                            const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg)
+                            const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters)
 {
     if (nItems <= 0)
         return cudaSuccess;
     const bool table = (single == nullptr);
 #define QAGG_CASE(S, MD, TB) \
     if (stripes == S && mode == MD && table == TB) \
-        return launch_cq<S, MD, TB>(st, single, tensors, items, nItems, colsPerItem, cfg);
+        return launch_cq<S, MD, TB>(st, single, tensors, items, nItems, colsPerItem, cfg, counters);
     QAGG_CASE(false, MODE_ONEBIT_ZERO, false)
     QAGG_CASE(false, MODE_ONEBIT_MEAN, false)
     QAGG_CASE(false, MODE_MULTIBIT, false)
@@ -653,7 +1143,7 @@ cudaError_t launch_colquant(cudaStream_t st, bool stripes, int mode, const QTens
 }
 
 cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, const QTensor* tensors,
-                              const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg)
+                              const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters)
 {
     if (nItems <= 0)
         return cudaSuccess;
@@ -665,16 +1155,16 @@ cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, 
     if (single)
     {
         if (add)
-            k_unquantize<true, false><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem);
+            k_unquantize<true, false><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem, counters);
         else
-            k_unquantize<false, false><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem);
+            k_unquantize<false, false><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem, counters);
     }
     else
     {
         if (add)
-            k_unquantize<true, true><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem);
+            k_unquantize<true, true><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem, counters);
         else
-            k_unquantize<false, true><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem);
+            k_unquantize<false, true><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem, counters);
     }
     return cudaGetLastError();
 }
@@ -686,14 +1176,14 @@ cudaError_t get_launch_cfg(int device, LaunchCfg* cfg)
     if (e != cudaSuccess)
         return e;
     cfg->numSMs = prop.multiProcessorCount;
-    // two CTAs per SM: (per-SM shared memory - 1 KB reserved per CTA) / 2, rounded down to 1 KB
-    size_t perSM = prop.sharedMemPerMultiprocessor;
-    size_t perCta = (perSM / 2) - 1024 - 2048; // 2 KB slack for the kernel's static shared memory
-    if (perCta > prop.sharedMemPerBlockOptin - 2048)
-        perCta = prop.sharedMemPerBlockOptin - 2048;
-    perCta &= ~(size_t) 1023;
+    // three CTAs per SM: a third of the SM's shared memory minus the 1 KB the system reserves per CTA and
+    // 1 KB for the kernel's static shared memory
+    cfg->ctasPerSM = 3;
+    size_t perCta = prop.sharedMemPerMultiprocessor / cfg->ctasPerSM - 1024 - 1024;
+    if (perCta > prop.sharedMemPerBlockOptin - 1024)
+        perCta = prop.sharedMemPerBlockOptin - 1024;
+    perCta &= ~(size_t) 15;
     cfg->smemFloats = (int) (perCta / sizeof(float));
-    cfg->ctasPerSM = 2;
     return cudaSuccess;
 }
 
