@@ -67,6 +67,58 @@ struct DevBuf
 
 } // namespace
 
+// Wire layout of one rank's view of the exchange; pure host arithmetic (no device needed).
+//   region p  = the packed stripes owned by rank p, tensor after tensor (each block 16-byte aligned): the message
+//               this rank sends to p in the scatter, and what rank p contributes to the all-gather;
+//   gather slot = the largest region, padded, so that the all-gather moves equal counts.
+struct qagg_plan
+{
+    int rank = 0, K = 1, T = 0, bits = 1;
+    std::vector<int64_t> M, N, colBytes;
+    std::vector<std::vector<int64_t>> sStart, sN, tOff; // [p][i]
+    std::vector<int64_t> regionBytes;
+    int64_t gatherSlot = 0;
+
+    int build(int rank_, int K_, int T_, const int64_t* M_, const int64_t* N_, int bits_)
+    {
+        if (K_ < 1 || K_ > QAGG_MAXK || rank_ < 0 || rank_ >= K_ || T_ < 0 || (T_ > 0 && (!M_ || !N_)))
+            return fail(QAGG_EINVAL, "plan: bad arguments");
+        if (!bits_ok(bits_))
+            return fail(QAGG_EINVAL, "bits must be a power of two in 1..32");
+        rank = rank_;
+        K = K_;
+        T = T_;
+        bits = bits_;
+        M.assign(M_, M_ + T);
+        N.assign(N_, N_ + T);
+        colBytes.resize(T);
+        for (int i = 0; i < T; ++i)
+        {
+            if (M[i] < 0 || N[i] < 0 || M[i] > 0x3fffffffLL || N[i] > 0x7fffffffLL)
+                return fail(QAGG_EINVAL, "plan: bad tensor shape");
+            colBytes[i] = 8 + 4 * ((M[i] * bits + 31) / 32);
+        }
+        sStart.assign(K, std::vector<int64_t>(T));
+        sN.assign(K, std::vector<int64_t>(T));
+        tOff.assign(K, std::vector<int64_t>(T));
+        regionBytes.assign(K, 0);
+        gatherSlot = 0;
+        for (int p = 0; p < K; ++p)
+        {
+            int64_t off = 0;
+            for (int i = 0; i < T; ++i)
+            {
+                qagg_stripe(N[i], p, K, &sStart[p][i], &sN[p][i]);
+                tOff[p][i] = off;
+                off += align_up(sN[p][i] * colBytes[i], 16);
+            }
+            regionBytes[p] = off;
+            gatherSlot = std::max(gatherSlot, align_up(off, 256));
+        }
+        return QAGG_OK;
+    }
+};
+
 struct qagg_aggregator
 {
     qagg_comm* comm = nullptr;
@@ -296,6 +348,45 @@ int launch_k3(qagg_aggregator* a, cudaStream_t st)
 
 extern "C" {
 
+int qagg_plan_create(int rank, int num_ranks, int num_tensors, const int64_t* M, const int64_t* N, int bits, qagg_plan** out)
+{
+    if (!out)
+        return fail(QAGG_EINVAL, "qagg_plan_create: null output");
+    std::unique_ptr<qagg_plan> p(new qagg_plan);
+    int rc = p->build(rank, num_ranks, num_tensors, M, N, bits);
+    if (rc)
+        return rc;
+    *out = p.release();
+    return QAGG_OK;
+}
+
+int64_t qagg_plan_region_bytes(const qagg_plan* p, int peer)
+{
+    if (!p || peer < 0 || peer >= p->K)
+        return fail(QAGG_EINVAL, "qagg_plan_region_bytes: bad arguments");
+    return p->regionBytes[peer];
+}
+
+int64_t qagg_plan_tensor_offset(const qagg_plan* p, int peer, int tensor)
+{
+    if (!p || peer < 0 || peer >= p->K || tensor < 0 || tensor >= p->T)
+        return fail(QAGG_EINVAL, "qagg_plan_tensor_offset: bad arguments");
+    return p->tOff[peer][tensor];
+}
+
+int64_t qagg_plan_gather_slot_bytes(const qagg_plan* p)
+{
+    if (!p)
+        return fail(QAGG_EINVAL, "null plan");
+    return p->gatherSlot;
+}
+
+int qagg_plan_destroy(qagg_plan* p)
+{
+    delete p;
+    return QAGG_OK;
+}
+
 int qagg_unique_id(void* out)
 {
     if (!out)
@@ -381,6 +472,9 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
         return fail(QAGG_EINVAL, "qagg_agg_create: bad arguments");
     if (!bits_ok(bits))
         return fail(QAGG_EINVAL, "bits must be a power of two in 1..32");
+    for (int i = 0; i < num_tensors; ++i)
+        if (M[i] < 0 || N[i] < 0 || M[i] > 0x3fffffffLL || N[i] > 0x7fffffffLL)
+            return fail(QAGG_EINVAL, "qagg_agg_create: bad tensor shape");
     int rc = check_cuda(cudaSetDevice(comm->device), "cudaSetDevice");
     if (rc)
         return rc;
@@ -395,37 +489,29 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
     rc = check_cuda(get_launch_cfg(comm->device, &a->cfg), "cudaGetDeviceProperties");
     if (rc)
         return rc;
-    a->M.assign(M, M + num_tensors);
-    a->N.assign(N, N + num_tensors);
-    a->colBytes.resize(num_tensors);
+    qagg_plan plan;
+    if ((rc = plan.build(r, K, num_tensors, M, N, bits)))
+        return rc;
+    a->M = plan.M;
+    a->N = plan.N;
+    a->colBytes = plan.colBytes;
+    a->sStart = plan.sStart;
+    a->sN = plan.sN;
+    a->tOff = plan.tOff;
+    a->regionBytes = plan.regionBytes;
+    a->gatherSlot = plan.gatherSlot;
     int64_t resFloats = 0, sresFloats = 0;
     for (int i = 0; i < num_tensors; ++i)
     {
-        if (M[i] < 0 || N[i] < 0 || M[i] > 0x3fffffffLL || N[i] > 0x7fffffffLL)
-            return fail(QAGG_EINVAL, "qagg_agg_create: bad tensor shape");
-        a->colBytes[i] = 8 + 4 * ((M[i] * bits + 31) / 32);
         a->totalValues += M[i] * N[i];
         resFloats += align_up(M[i] * N[i], 4);
     }
-    a->sStart.assign(K, std::vector<int64_t>(num_tensors));
-    a->sN.assign(K, std::vector<int64_t>(num_tensors));
-    a->tOff.assign(K, std::vector<int64_t>(num_tensors));
-    a->regionBytes.assign(K, 0);
     a->sendOff.assign(K, 0);
     int64_t sendTotal = 0;
     for (int p = 0; p < K; ++p)
     {
-        int64_t off = 0;
-        for (int i = 0; i < num_tensors; ++i)
-        {
-            qagg_stripe(N[i], p, K, &a->sStart[p][i], &a->sN[p][i]);
-            a->tOff[p][i] = off;
-            off += align_up(a->sN[p][i] * a->colBytes[i], 16);
-        }
-        a->regionBytes[p] = off;
         a->sendOff[p] = sendTotal;
-        sendTotal += align_up(off, 256);
-        a->gatherSlot = std::max(a->gatherSlot, align_up(off, 256));
+        sendTotal += align_up(a->regionBytes[p], 256);
     }
     a->slotBytes = align_up(a->regionBytes[r], 256);
     for (int i = 0; i < num_tensors; ++i)

@@ -242,20 +242,21 @@ __device__ __forceinline__ void walk_step4(float& acc, unsigned& cnt, const floa
     walk_step<KIND>(acc, cnt, v.w, mean, upperLane);
 }
 
-// Sixteen rows per trip, the next sixteen already in flight: measured at 4.7 cycles per row against 6.9 for eight
-// rows per trip (the per-trip overhead is not hidden behind a 32-cycle chain, but is behind a 64-cycle one).
+// Sixteen rows per trip, the next sixteen already in flight.  The loop is counted in trips and the prefetch index of
+// the last trip is clamped (it re-reads its own rows) instead of peeling an epilogue: measured 4.6 cycles per row in
+// this shape against 5.3-5.9 for the peeled shapes and 6.9 for eight rows per trip.
 template <int KIND>
 __device__ __forceinline__ float walk_rows(const float* __restrict__ vcol, int nrows, float acc, unsigned& cnt, float mean, bool upperLane)
 {
-    int i = 0;
-    if (nrows >= 16)
+    const int trips = nrows >> 4;
+    if (trips > 0)
     {
         const float4* __restrict__ p = reinterpret_cast<const float4*>(vcol);
         float4 a = p[0], b = p[1], c = p[2], d = p[3];
-        for (; i + 32 <= nrows; i += 16)
+        for (int t = 0; t < trips; ++t)
         {
-            const float4* __restrict__ q = p + (i >> 2) + 4;
-            const float4 na = q[0], nb = q[1], nc = q[2], nd = q[3];
+            const int nx = (t + 1 < trips) ? (t + 1) * 4 : t * 4;
+            const float4 na = p[nx], nb = p[nx + 1], nc = p[nx + 2], nd = p[nx + 3];
             walk_step4<KIND>(acc, cnt, a, mean, upperLane);
             walk_step4<KIND>(acc, cnt, b, mean, upperLane);
             walk_step4<KIND>(acc, cnt, c, mean, upperLane);
@@ -265,13 +266,8 @@ __device__ __forceinline__ float walk_rows(const float* __restrict__ vcol, int n
             c = nc;
             d = nd;
         }
-        walk_step4<KIND>(acc, cnt, a, mean, upperLane);
-        walk_step4<KIND>(acc, cnt, b, mean, upperLane);
-        walk_step4<KIND>(acc, cnt, c, mean, upperLane);
-        walk_step4<KIND>(acc, cnt, d, mean, upperLane);
-        i += 16;
     }
-    for (; i < nrows; ++i)
+    for (int i = trips << 4; i < nrows; ++i)
         walk_step<KIND>(acc, cnt, vcol[i], mean, upperLane);
     return acc;
 }
@@ -311,8 +307,11 @@ __device__ __forceinline__ void fill_dense(const QTensor& T, int col0, int nc, i
     const bool vec = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(g) & 15) == 0) && ((reinterpret_cast<uintptr_t>(r) & 15) == 0);
     if (vec)
     {
-        // warp task = 32 lanes x UNR float4 of ONE column: all loads of a task are issued before any is used
-        constexpr int UNR = 4;
+        // warp task = 32 lanes x UNR float4 of ONE column.  The gradient goes global -> shared by cp.async (no registers,
+        // every copy of the item in flight at once); the residual goes through registers, UNR loads in flight per lane.
+        // A lane adds the residual only to the 16-byte slots it copied itself, so waiting for its own copy group is
+        // all the synchronisation the two passes need.
+        constexpr int UNR = 8;
         const int M4 = M >> 2;
         const int nch = (M4 + 32 * UNR - 1) / (32 * UNR);
         const int ntasks = nc * nch;
@@ -321,19 +320,40 @@ __device__ __forceinline__ void fill_dense(const QTensor& T, int col0, int nc, i
             const int col = task / nch;
             const int ch = task - col * nch;
             const float4* __restrict__ g4 = reinterpret_cast<const float4*>(g + (size_t) col * M);
-            const float4* __restrict__ r4 = reinterpret_cast<const float4*>(r + (size_t) col * M);
             float4* __restrict__ v4 = reinterpret_cast<float4*>(smem + (size_t) col * stride);
             const int base = ch * 32 * UNR + lane;
-            float4 a[UNR], b[UNR];
 #pragma unroll
             for (int u = 0; u < UNR; ++u)
             {
                 const int idx = base + 32 * u;
                 if (idx < M4)
                 {
-                    a[u] = __ldcs(g4 + idx);
-                    b[u] = __ldcs(r4 + idx);
+                    const unsigned dst = (unsigned) __cvta_generic_to_shared(v4 + idx);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(g4 + idx) : "memory");
                 }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        bool waited = false;
+        for (int task = warp; task < ntasks; task += NWARPS)
+        {
+            const int col = task / nch;
+            const int ch = task - col * nch;
+            const float4* __restrict__ r4 = reinterpret_cast<const float4*>(r + (size_t) col * M);
+            float4* __restrict__ v4 = reinterpret_cast<float4*>(smem + (size_t) col * stride);
+            const int base = ch * 32 * UNR + lane;
+            float4 b[UNR];
+#pragma unroll
+            for (int u = 0; u < UNR; ++u)
+            {
+                const int idx = base + 32 * u;
+                if (idx < M4)
+                    b[u] = __ldcs(r4 + idx);
+            }
+            if (!waited)
+            {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                waited = true;
             }
             unsigned cnt = 0, nan = 0;
 #pragma unroll
@@ -342,11 +362,12 @@ __device__ __forceinline__ void fill_dense(const QTensor& T, int col0, int nc, i
                 const int idx = base + 32 * u;
                 if (idx < M4)
                 {
+                    const float4 a = v4[idx];
                     float4 v;
-                    v.x = __fadd_rn(a[u].x, b[u].x);
-                    v.y = __fadd_rn(a[u].y, b[u].y);
-                    v.z = __fadd_rn(a[u].z, b[u].z);
-                    v.w = __fadd_rn(a[u].w, b[u].w);
+                    v.x = __fadd_rn(a.x, b[u].x);
+                    v.y = __fadd_rn(a.y, b[u].y);
+                    v.z = __fadd_rn(a.z, b[u].z);
+                    v.w = __fadd_rn(a.w, b[u].w);
                     v4[idx] = v;
                     count4<MODE>(v, cnt, nan);
                 }
@@ -364,6 +385,8 @@ __device__ __forceinline__ void fill_dense(const QTensor& T, int col0, int nc, i
                 }
             }
         }
+        if (!waited)
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     else
     {
@@ -885,9 +908,8 @@ __global__ void __launch_bounds__(NT, 3) k_colquant(const QTensor single, const 
 // =================================================================================================================
 // Unquantize kernel (UnquantizeOneQWord, ColumnQuantizer.h:150-203).  Per work item the per-column constants
 // are computed once into shared memory; then, depending on the shape,
-//   words-major  (Q % 4 == 0): thread <-> four adjacent packed words, one float4 store per bit position;
-//   rows-major   (M % 4 == 0): thread <-> four consecutive rows (one float4 store), words fetched through L1;
-//   scalar       otherwise   : thread <-> one packed word, 4-byte stores.
+//   Q % 4 == 0 and 16-byte aligned rows: thread <-> four adjacent packed words, one float4 store per bit position;
+//   otherwise                          : thread <-> one packed word, the warp stores 32 consecutive rows per bit position.
 // =================================================================================================================
 template <bool ADD>
 __device__ __forceinline__ void store_out4(float* p, float4 v)
@@ -1005,49 +1027,39 @@ __global__ void __launch_bounds__(NT) k_unquantize(const QTensor single, const Q
                 }
             }
         }
-        else if (aligned && Q >= 4)
-        {
-            const int M4 = M >> 2;
-            const int total = nc * M4;
-            for (int t = threadIdx.x; t < total; t += NT)
-            {
-                const int col = t / M4;
-                const int row = (t - col * M4) * 4;
-                int k = row / Q;
-                int w = row - k * Q;
-                const unsigned* __restrict__ words = sWords[col];
-                const float ca = sA[col], cb = sB[col];
-                float v[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                {
-                    v[i] = unq_fast(bits, (__ldg(words + w) >> (k * bits)) & mask, ca, cb);
-                    if (++w == Q)
-                    {
-                        w = 0;
-                        ++k;
-                    }
-                }
-                store_out4<ADD>(out0 + (size_t) col * M + row, make_float4(v[0], v[1], v[2], v[3]));
-            }
-        }
         else
         {
-            const long long total = (long long) nc * Q;
-            for (long long t = threadIdx.x; t < total; t += NT)
+            // thread <-> one packed word: for each bit position the warp writes 32 consecutive rows (128 bytes)
+            const int total = nc * Q;
+            for (int t = threadIdx.x; t < total; t += NT)
             {
-                const int col = (int) (t / Q);
-                const int w = (int) (t - (long long) col * Q);
+                const int col = t / Q;
+                const int w = t - col * Q;
                 const unsigned word = __ldg(sWords[col] + w);
                 const float ca = sA[col], cb = sB[col];
                 float* __restrict__ op = out0 + (size_t) col * M + w;
                 const int nk = min(vpw, (M - w + Q - 1) / Q);
-                for (int k = 0; k < nk; ++k)
+                if (bits == 1)
                 {
-                    float val = unq_fast(bits, (word >> (k * bits)) & mask, ca, cb);
-                    if (ADD)
-                        val = __fadd_rn(val, op[(size_t) k * Q]);
-                    op[(size_t) k * Q] = val;
+#pragma unroll 8
+                    for (int k = 0; k < nk; ++k)
+                    {
+                        float val = ((word >> k) & 1u) ? cb : ca;
+                        if (ADD)
+                            val = __fadd_rn(val, op[k * Q]);
+                        op[k * Q] = val;
+                    }
+                }
+                else
+                {
+#pragma unroll 4
+                    for (int k = 0; k < nk; ++k)
+                    {
+                        float val = unq_fast(bits, (word >> (k * bits)) & mask, ca, cb);
+                        if (ADD)
+                            val = __fadd_rn(val, op[k * Q]);
+                        op[k * Q] = val;
+                    }
                 }
             }
         }

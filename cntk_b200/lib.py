@@ -17,6 +17,7 @@ UNIQUE_ID_BYTES = 128
 EXPORTS = [
     "qagg_last_error", "qagg_abi_version", "qagg_packed_col_bytes", "qagg_packed_bytes", "qagg_stripe",
     "qagg_quantize", "qagg_unquantize", "qagg_reduce_requantize", "qagg_quantize_to_host", "qagg_unquantize_from_host",
+    "qagg_plan_create", "qagg_plan_region_bytes", "qagg_plan_tensor_offset", "qagg_plan_gather_slot_bytes", "qagg_plan_destroy",
     "qagg_unique_id", "qagg_comm_create", "qagg_comm_create_local_group", "qagg_comm_rank", "qagg_comm_size",
     "qagg_comm_destroy", "qagg_agg_create", "qagg_agg_step", "qagg_agg_step_group", "qagg_agg_step_host",
     "qagg_agg_reset_residuals", "qagg_agg_residuals", "qagg_agg_copy_residual", "qagg_agg_copy_packed", "qagg_agg_wire_bytes",
@@ -45,6 +46,14 @@ _lib.qagg_unquantize.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
 _lib.qagg_reduce_requantize.argtypes = [c_vp, ctypes.POINTER(c_vp), c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
 _lib.qagg_quantize_to_host.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
 _lib.qagg_unquantize_from_host.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
+_lib.qagg_plan_create.argtypes = [c_int, c_int, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, ctypes.POINTER(c_vp)]
+_lib.qagg_plan_region_bytes.restype = c_i64
+_lib.qagg_plan_region_bytes.argtypes = [c_vp, c_int]
+_lib.qagg_plan_tensor_offset.restype = c_i64
+_lib.qagg_plan_tensor_offset.argtypes = [c_vp, c_int, c_int]
+_lib.qagg_plan_gather_slot_bytes.restype = c_i64
+_lib.qagg_plan_gather_slot_bytes.argtypes = [c_vp]
+_lib.qagg_plan_destroy.argtypes = [c_vp]
 _lib.qagg_unique_id.argtypes = [c_vp]
 _lib.qagg_comm_create.argtypes = [c_vp, c_int, c_int, c_int, ctypes.POINTER(c_vp)]
 _lib.qagg_comm_create_local_group.argtypes = [c_int, c_int, ctypes.POINTER(c_vp)]
@@ -123,6 +132,39 @@ def quantize_to_host(grad_ptr, res_in_ptr, res_out_ptr, dev_scratch_ptr, host_pa
 
 def unquantize_from_host(host_packed_ptr, dev_scratch_ptr, out_ptr, M, N, bits, add=False, stream=0):
     _ok(_lib.qagg_unquantize_from_host(stream, host_packed_ptr, dev_scratch_ptr, out_ptr, M, N, bits, int(bool(add))))
+
+
+class Plan:
+    """Host-only wire layout of rank `rank` of K (qagg_plan_*)."""
+
+    def __init__(self, rank, K, shapes, bits):
+        T = len(shapes)
+        Ms = (c_i64 * T)(*[s[0] for s in shapes])
+        Ns = (c_i64 * T)(*[s[1] for s in shapes])
+        h = c_vp()
+        _ok(_lib.qagg_plan_create(rank, K, T, Ms, Ns, bits, ctypes.byref(h)))
+        self.h, self.rank, self.K, self.shapes, self.bits = h, rank, K, [tuple(s) for s in shapes], bits
+
+    def region_bytes(self, peer):
+        v = int(_lib.qagg_plan_region_bytes(self.h, peer))
+        if v < 0:
+            _ok(v)
+        return v
+
+    def tensor_offset(self, peer, tensor):
+        v = int(_lib.qagg_plan_tensor_offset(self.h, peer, tensor))
+        if v < 0:
+            _ok(v)
+        return v
+
+    @property
+    def gather_slot_bytes(self):
+        return int(_lib.qagg_plan_gather_slot_bytes(self.h))
+
+    def destroy(self):
+        if self.h:
+            _lib.qagg_plan_destroy(self.h)
+            self.h = None
 
 
 def unique_id():

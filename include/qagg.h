@@ -47,6 +47,7 @@ extern "C" {
 
 typedef struct qagg_comm qagg_comm;
 typedef struct qagg_aggregator qagg_aggregator;
+typedef struct qagg_plan qagg_plan;
 
 /* Last error message of the calling thread ("" if none). */
 const char* qagg_last_error(void);
@@ -94,6 +95,18 @@ int qagg_quantize_to_host(void* stream, const float* grad, const float* res_in, 
                           void* host_packed, int64_t M, int64_t N, int bits, int zero_threshold);
 int qagg_unquantize_from_host(void* stream, const void* host_packed, void* dev_scratch, float* out,
                               int64_t M, int64_t N, int bits, int add);
+
+/* ---- wire layout (host arithmetic only; needs no device) ------------------------------------------------
+ * How one rank of K lays the packed stripes out for the exchange.  "Region p" is the concatenation, tensor after
+ * tensor (each block padded to 16 bytes), of the packed stripes that rank p owns: the one message this rank sends to p
+ * where the reference posts one MPI_Isend per tensor and peer (Source/1BitSGD/AllReduceDistGradAggregator.h:336-365),
+ * and rank p's contribution to the all-gather (:486-502).  The stripe of tensor i inside region p starts at
+ * qagg_plan_tensor_offset(p, i) and holds columns GetStripeForNode(N[i], p, K) in the packed column format. */
+int qagg_plan_create(int rank, int num_ranks, int num_tensors, const int64_t* M, const int64_t* N, int bits, qagg_plan** out);
+int64_t qagg_plan_region_bytes(const qagg_plan* p, int peer);
+int64_t qagg_plan_tensor_offset(const qagg_plan* p, int peer, int tensor);
+int64_t qagg_plan_gather_slot_bytes(const qagg_plan* p); /* size of one (padded, equal-sized) all-gather slot */
+int qagg_plan_destroy(qagg_plan* p);
 
 /* ---- communicator ---------------------------------------------------------------------------------
  * Replaces the MPI point-to-point traffic of the reference (Source/1BitSGD/AllReduceDistGradAggregator.h:303-365,
