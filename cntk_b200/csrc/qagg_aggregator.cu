@@ -181,6 +181,43 @@ void make_items(std::vector<QItem>& items, int tensor, int64_t M, int64_t N, int
         items.push_back(QItem{tensor, (int) col0, (int) std::min<int64_t>(c, N - col0)});
 }
 
+// Columns per work item for each matrix of one launch.  Start from as many as shared memory holds; while the launch
+// would not even fill the resident CTA slots once, halve the item of the matrix whose items are the most expensive
+// (rows x columns): a tall column's ordered walk is a fixed latency, so fewer columns per item shortens the launch
+// when there are CTA slots to spare.
+std::vector<int> choose_cols(const std::vector<std::pair<int64_t, int64_t>>& shapes, const LaunchCfg& cfg)
+{
+    std::vector<int> c(shapes.size(), 1);
+    auto items = [&](size_t i) { return shapes[i].second > 0 ? (shapes[i].second + c[i] - 1) / c[i] : 0; };
+    int64_t total = 0;
+    for (size_t i = 0; i < shapes.size(); ++i)
+    {
+        c[i] = cols_per_item(shapes[i].first, shapes[i].second, cfg.smemFloats, nullptr);
+        total += items(i);
+    }
+    const int64_t slots = (int64_t) cfg.numSMs * cfg.ctasPerSM;
+    while (total < slots)
+    {
+        int best = -1;
+        int64_t bestCost = 0;
+        for (size_t i = 0; i < shapes.size(); ++i)
+        {
+            const int64_t cost = shapes[i].first * c[i];
+            if (c[i] > 1 && shapes[i].second > 0 && cost > bestCost)
+            {
+                bestCost = cost;
+                best = (int) i;
+            }
+        }
+        if (best < 0)
+            break;
+        total -= items(best);
+        c[best] = (c[best] + 1) / 2;
+        total += items(best);
+    }
+    return c;
+}
+
 int build_tables(qagg_aggregator* a)
 {
     const int K = a->comm->K, r = a->comm->rank, T = a->T;
@@ -192,6 +229,14 @@ int build_tables(qagg_aggregator* a)
     a->iK2.clear();
     a->iK3.clear();
     std::vector<std::pair<int64_t, QItem>> cost1, cost2;
+    std::vector<std::pair<int64_t, int64_t>> shapes1, shapes2;
+    for (int i = 0; i < T; ++i)
+    {
+        const bool live = a->M[i] > 0 && a->N[i] > 0;
+        shapes1.push_back({a->M[i], live ? a->N[i] : 0});
+        shapes2.push_back({a->M[i], (live && K > 1) ? a->sN[r][i] : 0});
+    }
+    const std::vector<int> c1 = choose_cols(shapes1, a->cfg), c2 = choose_cols(shapes2, a->cfg);
     for (int i = 0; i < T; ++i)
     {
         const int64_t M = a->M[i], N = a->N[i];
@@ -218,8 +263,7 @@ int build_tables(qagg_aggregator* a)
         }
         {
             std::vector<QItem> tmp;
-            const int c = cols_per_item(M, N, a->cfg.smemFloats, nullptr);
-            make_items(tmp, i, M, N, c);
+            make_items(tmp, i, M, N, c1[i]);
             for (auto& it : tmp)
                 cost1.push_back({M * it.ncols, it});
             make_items(a->iK3, i, M, N, unq_cols_per_item(M));
@@ -242,8 +286,7 @@ int build_tables(qagg_aggregator* a)
             a->hK2.push_back(q2);
             a->k2Tensor.push_back(i);
             std::vector<QItem> tmp;
-            const int c = cols_per_item(M, q2.N, a->cfg.smemFloats, nullptr);
-            make_items(tmp, e, M, q2.N, c);
+            make_items(tmp, e, M, q2.N, c2[i]);
             for (auto& it : tmp)
                 cost2.push_back({M * it.ncols, it});
         }

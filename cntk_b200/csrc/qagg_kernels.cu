@@ -418,7 +418,10 @@ __device__ __forceinline__ void fill_dense(const QTensor& T, int col0, int nc, i
     }
 }
 
-// thread <-> (column, packed word): the K sources are added in index order, the raw own stripe (if used) first
+// thread <-> (column, packed word): the K sources are added in index order, the raw own stripe (if used) first, the
+// stripe residual LAST (the reference unquantizes with add = true K-1 times and only then quantizes against the residual,
+// AllReduceDistGradAggregator.h:366-375, 405-435).  The residual is fetched into the column slots by cp.async while the
+// sum of the stripes is built in registers, so no load of this phase waits on another.
 template <int MODE>
 __device__ __forceinline__ void fill_stripes(const QTensor& T, int col0, int nc, int stride, float* __restrict__ smem, const ColStats& S)
 {
@@ -427,70 +430,108 @@ __device__ __forceinline__ void fill_stripes(const QTensor& T, int col0, int nc,
     const int bits = T.bits;
     const int vpw = 32 / bits;
     const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
-    const int total = nc * Q;
-    for (int idx = threadIdx.x; idx < total; idx += NT)
+    const float* __restrict__ r0 = T.res_in + (size_t) col0 * M;
+    const bool async = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(r0) & 15) == 0);
+    if (async)
     {
-        const int col = idx / Q;
-        const int w = idx - col * Q;
-        const int j = col0 + col;
-        float* __restrict__ vcol = smem + (size_t) col * stride + w;
-        const int nk = min(vpw, (M - w + Q - 1) / Q); // rows w, w+Q, ... below M
-        bool first = true;
-        if (T.selfRaw)
+        const int M4 = M >> 2;
+        const int total4 = nc * M4;
+        for (int idx = threadIdx.x; idx < total4; idx += NT)
         {
-            const float* __restrict__ gcol = T.grad + (size_t) j * M + w;
-            for (int k = 0; k < nk; ++k)
-                vcol[k * Q] = gcol[k * Q];
-            first = false;
+            const int col = idx / M4;
+            const int r4 = idx - col * M4;
+            const unsigned dst = (unsigned) __cvta_generic_to_shared(smem + (size_t) col * stride + 4 * r4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(reinterpret_cast<const float4*>(r0) + idx) : "memory");
         }
-        for (int s = T.selfRaw ? 1 : 0; s < T.nsrc; ++s)
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    const int total = nc * Q;
+    {
+        for (int idx0 = 0; idx0 < total; idx0 += NT) // same trip count for every thread: the barrier below is safe
         {
-            const unsigned char* colp = T.src[s] + (size_t) j * T.colBytes;
-            const ValQ q = make_valq(bits, reinterpret_cast<const float*>(colp)[0], reinterpret_cast<const float*>(colp)[1]);
-            const unsigned word = reinterpret_cast<const unsigned*>(colp + 8)[w];
-            if (bits == 1)
+            const int idx = idx0 + threadIdx.x;
+            const bool live = idx < total;
+            const int col = live ? idx / Q : 0;
+            const int w = live ? idx - col * Q : 0;
+            const int j = col0 + col;
+            const int nk = live ? min(vpw, (M - w + Q - 1) / Q) : 0; // rows w, w+Q, ... below M
+            float agg[32];
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+                agg[k] = 0.0f;
+            bool first = true;
+            if (live && T.selfRaw)
             {
-                const float val0 = unquantize_val(q, 1, 0u);
-                const float val1 = unquantize_val(q, 1, 1u);
-                if (first)
+                const float* __restrict__ gcol = T.grad + (size_t) j * M + w;
+#pragma unroll
+                for (int k = 0; k < 32; ++k)
+                    if (k < nk)
+                        agg[k] = gcol[k * Q];
+                first = false;
+            }
+            if (live)
+            {
+                for (int s = T.selfRaw ? 1 : 0; s < T.nsrc; ++s)
                 {
-#pragma unroll 8
-                    for (int k = 0; k < nk; ++k)
-                        vcol[k * Q] = ((word >> k) & 1u) ? val1 : val0;
-                }
-                else
-                {
-#pragma unroll 8
-                    for (int k = 0; k < nk; ++k)
-                        vcol[k * Q] = __fadd_rn(((word >> k) & 1u) ? val1 : val0, vcol[k * Q]);
+                    const unsigned char* colp = T.src[s] + (size_t) j * T.colBytes;
+                    const ValQ q = make_valq(bits, reinterpret_cast<const float*>(colp)[0], reinterpret_cast<const float*>(colp)[1]);
+                    const unsigned word = reinterpret_cast<const unsigned*>(colp + 8)[w];
+                    if (bits == 1)
+                    {
+                        const float val0 = unquantize_val(q, 1, 0u);
+                        const float val1 = unquantize_val(q, 1, 1u);
+#pragma unroll
+                        for (int k = 0; k < 32; ++k)
+                        {
+                            const float val = ((word >> k) & 1u) ? val1 : val0;
+                            agg[k] = first ? val : __fadd_rn(val, agg[k]);
+                        }
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int k = 0; k < 16; ++k)
+                        {
+                            if (k < vpw)
+                            {
+                                const float val = unquantize_val(q, bits, (word >> (k * bits)) & mask);
+                                agg[k] = first ? val : __fadd_rn(val, agg[k]);
+                            }
+                        }
+                    }
+                    first = false;
                 }
             }
-            else
+            if (async && idx0 == 0)
             {
-                for (int k = 0; k < nk; ++k)
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncthreads(); // every thread's share of the residual is in shared memory
+            }
+            if (live)
+            {
+                float* __restrict__ vcol = smem + (size_t) col * stride + w;
+                const float* __restrict__ rcol = T.res_in + (size_t) j * M + w;
+                unsigned cnt = 0;
+#pragma unroll
+                for (int k = 0; k < 32; ++k)
                 {
-                    const float val = unquantize_val(q, bits, (word >> (k * bits)) & mask);
-                    vcol[k * Q] = first ? val : __fadd_rn(val, vcol[k * Q]);
+                    if (k < nk)
+                    {
+                        const float r = async ? vcol[k * Q] : rcol[k * Q];
+                        const float v = __fadd_rn(agg[k], r);
+                        vcol[k * Q] = v;
+                        if (MODE == MODE_ONEBIT_ZERO)
+                        {
+                            cnt += (v < 0.0f);
+                            if (v != v)
+                                S.nan[col] = 1u;
+                        }
+                    }
                 }
-            }
-            first = false;
-        }
-        const float* __restrict__ rcol = T.res_in + (size_t) j * M + w;
-        unsigned cnt = 0;
-#pragma unroll 4
-        for (int k = 0; k < nk; ++k)
-        {
-            const float v = __fadd_rn(first ? 0.0f : vcol[k * Q], rcol[k * Q]);
-            vcol[k * Q] = v;
-            if (MODE == MODE_ONEBIT_ZERO)
-            {
-                cnt += (v < 0.0f);
-                if (v != v)
-                    S.nan[col] = 1u;
+                if (MODE == MODE_ONEBIT_ZERO && cnt)
+                    atomicAdd(&S.n0[col], cnt);
             }
         }
-        if (MODE == MODE_ONEBIT_ZERO && cnt)
-            atomicAdd(&S.n0[col], cnt);
     }
 }
 
