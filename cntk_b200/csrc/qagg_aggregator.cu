@@ -28,6 +28,8 @@ struct qagg_comm
     int device = 0;
     ncclComm_t nccl = nullptr;
     bool local = false; // member of an in-process group (device-to-device copies instead of NCCL)
+    double* scalars = nullptr; // small device buffer for the header all-reduce
+    static const int kMaxScalars = 512;
 };
 
 namespace {
@@ -498,11 +500,44 @@ int qagg_comm_size(const qagg_comm* c)
     return c ? c->K : fail(QAGG_EINVAL, "null communicator");
 }
 
+int qagg_comm_allreduce_f64(qagg_comm* c, double* host_values, int n, void* stream)
+{
+    if (!c || !host_values || n < 0 || n > qagg_comm::kMaxScalars)
+        return fail(QAGG_EINVAL, "qagg_comm_allreduce_f64: bad arguments (at most 512 values)");
+    if (c->K == 1 || n == 0)
+        return QAGG_OK;
+    if (c->local)
+        return fail(QAGG_ESTATE, "qagg_comm_allreduce_f64: not available on an in-process group");
+    cudaStream_t st = (cudaStream_t) stream;
+    int rc = check_cuda(cudaSetDevice(c->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    if (!c->scalars && (rc = check_cuda(cudaMalloc(reinterpret_cast<void**>(&c->scalars), qagg_comm::kMaxScalars * sizeof(double)), "cudaMalloc")))
+        return rc;
+    if ((rc = check_cuda(cudaMemcpyAsync(c->scalars, host_values, n * sizeof(double), cudaMemcpyHostToDevice, st), "header upload")))
+        return rc;
+    if ((rc = check_nccl(ncclAllReduce(c->scalars, c->scalars, (size_t) n, ncclDouble, ncclSum, c->nccl, st), "ncclAllReduce")))
+        return rc;
+    if ((rc = check_cuda(cudaMemcpyAsync(host_values, c->scalars, n * sizeof(double), cudaMemcpyDeviceToHost, st), "header download")))
+        return rc;
+    return check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+}
+
+int qagg_comm_barrier(qagg_comm* c, void* stream)
+{
+    double one = 1.0;
+    if (c && c->local)
+        return QAGG_OK;
+    return qagg_comm_allreduce_f64(c, &one, 1, stream);
+}
+
 int qagg_comm_destroy(qagg_comm* c)
 {
     if (!c)
         return QAGG_OK;
     int rc = QAGG_OK;
+    if (c->scalars)
+        cudaFree(c->scalars);
     if (c->nccl)
         rc = check_nccl(ncclCommDestroy(c->nccl), "ncclCommDestroy");
     delete c;

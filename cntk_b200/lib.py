@@ -18,7 +18,7 @@ EXPORTS = [
     "qagg_last_error", "qagg_abi_version", "qagg_packed_col_bytes", "qagg_packed_bytes", "qagg_stripe",
     "qagg_quantize", "qagg_unquantize", "qagg_reduce_requantize", "qagg_quantize_to_host", "qagg_unquantize_from_host",
     "qagg_plan_create", "qagg_plan_region_bytes", "qagg_plan_tensor_offset", "qagg_plan_gather_slot_bytes", "qagg_plan_destroy",
-    "qagg_unique_id", "qagg_comm_create", "qagg_comm_create_local_group", "qagg_comm_rank", "qagg_comm_size",
+    "qagg_unique_id", "qagg_comm_create", "qagg_comm_create_local_group", "qagg_comm_allreduce_f64", "qagg_comm_barrier", "qagg_comm_rank", "qagg_comm_size",
     "qagg_comm_destroy", "qagg_agg_create", "qagg_agg_step", "qagg_agg_step_group", "qagg_agg_step_host",
     "qagg_agg_reset_residuals", "qagg_agg_residuals", "qagg_agg_copy_residual", "qagg_agg_copy_packed", "qagg_agg_wire_bytes",
     "qagg_agg_launches_per_step", "qagg_agg_set_profiling", "qagg_agg_phase_ms", "qagg_agg_destroy",
@@ -57,6 +57,8 @@ _lib.qagg_plan_destroy.argtypes = [c_vp]
 _lib.qagg_unique_id.argtypes = [c_vp]
 _lib.qagg_comm_create.argtypes = [c_vp, c_int, c_int, c_int, ctypes.POINTER(c_vp)]
 _lib.qagg_comm_create_local_group.argtypes = [c_int, c_int, ctypes.POINTER(c_vp)]
+_lib.qagg_comm_allreduce_f64.argtypes = [c_vp, ctypes.POINTER(ctypes.c_double), c_int, c_vp]
+_lib.qagg_comm_barrier.argtypes = [c_vp, c_vp]
 _lib.qagg_comm_rank.argtypes = [c_vp]
 _lib.qagg_comm_size.argtypes = [c_vp]
 _lib.qagg_comm_destroy.argtypes = [c_vp]
@@ -189,6 +191,14 @@ class Comm:
         arr = (c_vp * K)()
         _ok(_lib.qagg_comm_create_local_group(K, device, arr))
         return [Comm(c_vp(arr[i])) for i in range(K)]
+
+    def allreduce_f64(self, values, stream=0):
+        arr = (ctypes.c_double * len(values))(*values)
+        _ok(_lib.qagg_comm_allreduce_f64(self.h, arr, len(values), stream))
+        return list(arr)
+
+    def barrier(self, stream=0):
+        _ok(_lib.qagg_comm_barrier(self.h, stream))
 
     @property
     def rank(self):

@@ -122,6 +122,12 @@ int qagg_comm_create(const void* unique_id, int rank, int num_ranks, int device,
  * multi-rank GPU tests run (all ranks on GPU 0; Tests/EndToEndTests/Speech/DNN/Parallel1BitQuantization/baseline.gpu.txt).
  * Fills out[0..K-1].  Aggregators built on these must be stepped with qagg_agg_step_group. */
 int qagg_comm_create_local_group(int num_ranks, int device, qagg_comm** out);
+/* Sum `n` (<= 512) doubles in HOST memory over all ranks, in place, and wait for the result: the DistGradHeader / loss
+ * scalars of a step (the reference gathers headers on rank 0 and sends the sum back, AllReduceDistGradAggregator.h:324-333,
+ * 380-383, 440-457, 504-514; the V2 path all-reduces them, V2AllReduceDistGradAggregator.h:222-248). */
+int qagg_comm_allreduce_f64(qagg_comm* c, double* host_values, int n, void* stream);
+/* IDistGradAggregator::WaitAll / DistributedCommunicator::Barrier. */
+int qagg_comm_barrier(qagg_comm* c, void* stream);
 int qagg_comm_rank(const qagg_comm* c);
 int qagg_comm_size(const qagg_comm* c);
 int qagg_comm_destroy(qagg_comm* c);

@@ -1,0 +1,80 @@
+"""The C++ mirror of the reference interfaces (cntk_b200/csrc/cntk_compat) driven as the reference's own callers drive
+them: tests/cpp/compat_check.cpp is compiled with g++ against libqagg.so, run on the GPU, and its dumps are compared
+bit for bit with the CPU oracle."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import make_golden as mg  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def exe(tmp_path_factory):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from cntk_b200 import build
+    build.build()
+    out = str(tmp_path_factory.mktemp("compat") / "compat_check")
+    libdir = os.path.join(ROOT, "cntk_b200")
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = ["g++", "-std=c++17", "-O1", f"-I{cuda}/include", os.path.join(ROOT, "tests", "cpp", "compat_check.cpp"), "-o", out,
+           "-L", libdir, "-l:libqagg.so", f"-L{cuda}/lib64", "-lcudart", f"-Wl,-rpath,{libdir}", f"-Wl,-rpath,{cuda}/lib64"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    return out
+
+
+def run(exe, tmp_path, mode, inputs, M, N, bits, zero_thr):
+    fin, fout = str(tmp_path / "in.bin"), str(tmp_path / "out.bin")
+    np.concatenate([a.reshape(-1) for a in inputs]).astype(np.float32).tofile(fin)
+    res = subprocess.run([exe, mode, fin, fout, str(M), str(N), str(bits), str(int(zero_thr)), str(len(inputs))], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "compat ok" in res.stdout, (res.returncode, res.stdout, res.stderr)
+    return np.fromfile(fout, dtype=np.uint8)
+
+
+@pytest.mark.parametrize("M,N,bits,zero_thr", [(489, 1, 1, True), (100, 50, 1, False), (89, 23, 4, True), (2048, 64, 1, True)])
+def test_matrix_quantizer_impl_like_the_reference_unit_test(exe, tmp_path, oracle_port, M, N, bits, zero_thr):
+    iters = 5
+    inputs = [mg.uniform_input(M, N, -0.5, 0.5, 2515 + it) for it in range(iters)]
+    dump = run(exe, tmp_path, "quantizer", inputs, M, N, bits, zero_thr)
+    C = oracle_port.packed_col_bytes(M, bits)
+    res = np.zeros((N, M), np.float32)
+    out = np.zeros((N, M), np.float32)
+    off = 0
+    for it in range(iters):
+        packed = np.zeros(N * C, np.uint8)
+        oracle_port.quantize(inputs[it], res, res, packed, bits, zero_thr)
+        oracle_port.unquantize(packed, out, bits, add=(it > 0))
+        for name, ref in (("packed", packed), ("residual", res.view(np.uint8).reshape(-1)), ("output", out.view(np.uint8).reshape(-1))):
+            got = dump[off:off + ref.size]
+            off += ref.size
+            assert np.array_equal(got, ref), f"iteration {it}: {name} differs"
+    assert off == dump.size
+
+
+def test_aggregator_and_v2_communicator_single_rank(exe, tmp_path, oracle_port):
+    M, N, bits, iters = 256, 40, 1, 2
+    inputs = [mg.normal_input(M, N, 1e-3, 77 + it) for it in range(iters)]
+    dump = run(exe, tmp_path, "aggregator", inputs, M, N, bits, True)
+    C = oracle_port.packed_col_bytes(M, bits)
+    res0 = np.zeros((N, M), np.float32)
+    res1 = np.zeros((1, M), np.float32)
+    off = 0
+    for it in range(iters):
+        for g, res in ((inputs[it].copy(), res0), (inputs[it][:1].copy(), res1)):
+            n = g.shape[0]
+            packed = np.zeros(n * C, np.uint8)
+            oracle_port.quantize(g, res, res, packed, bits, True)
+            oracle_port.unquantize(packed, g, bits, add=False)
+            ref = g.view(np.uint8).reshape(-1)
+            assert np.array_equal(dump[off:off + ref.size], ref), f"step {it}: aggregate differs"
+            off += ref.size
+    assert off == dump.size
