@@ -16,7 +16,7 @@ UNIQUE_ID_BYTES = 128
 
 EXPORTS = [
     "qagg_last_error", "qagg_abi_version", "qagg_packed_col_bytes", "qagg_packed_bytes", "qagg_stripe",
-    "qagg_quantize", "qagg_unquantize", "qagg_reduce_requantize", "qagg_quantize_to_host", "qagg_unquantize_from_host",
+    "qagg_quantize", "qagg_unquantize", "qagg_reduce_requantize", "qagg_quantize_batch_noalloc", "qagg_quantize_to_host", "qagg_unquantize_from_host",
     "qagg_plan_create", "qagg_plan_region_bytes", "qagg_plan_tensor_offset", "qagg_plan_gather_slot_bytes", "qagg_plan_destroy",
     "qagg_unique_id", "qagg_comm_create", "qagg_comm_create_local_group", "qagg_comm_allreduce_f64", "qagg_comm_barrier", "qagg_comm_rank", "qagg_comm_size",
     "qagg_comm_destroy", "qagg_agg_create", "qagg_agg_step", "qagg_agg_step_group", "qagg_agg_step_host",
@@ -44,6 +44,8 @@ _lib.qagg_stripe.argtypes = [c_i64, c_int, c_int, ctypes.POINTER(c_i64), ctypes.
 _lib.qagg_quantize.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
 _lib.qagg_unquantize.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
 _lib.qagg_reduce_requantize.argtypes = [c_vp, ctypes.POINTER(c_vp), c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
+_lib.qagg_quantize_batch_noalloc.argtypes = [c_vp, c_int, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), ctypes.POINTER(c_vp),
+                                             ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, c_int]
 _lib.qagg_quantize_to_host.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
 _lib.qagg_unquantize_from_host.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
 _lib.qagg_plan_create.argtypes = [c_int, c_int, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, ctypes.POINTER(c_vp)]
@@ -125,6 +127,16 @@ def reduce_requantize(stripe_ptrs, self_raw_ptr, sres_in_ptr, sres_out_ptr, pack
     arr = (c_vp * K)(*[c_vp(p) if p else c_vp(None) for p in stripe_ptrs])
     _ok(_lib.qagg_reduce_requantize(stream, arr, K, self_raw_ptr, sres_in_ptr, sres_out_ptr, packed_out_ptr, M, n, bits,
                                     int(bool(zero_thr))))
+
+
+def quantize_batch_noalloc(grad_ptrs, res_in_ptrs, res_out_ptrs, packed_ptrs, shapes, bits, zero_thr=True, stream=0):
+    """qagg_quantize_batch_noalloc: one launch over several matrices, scratch in the library's fixed array (no allocation)."""
+    n = len(shapes)
+    arr = lambda ps: (c_vp * n)(*[c_vp(p) for p in ps])
+    Ms = (c_i64 * n)(*[s[0] for s in shapes])
+    Ns = (c_i64 * n)(*[s[1] for s in shapes])
+    _ok(_lib.qagg_quantize_batch_noalloc(stream, n, arr(grad_ptrs), arr(res_in_ptrs), arr(res_out_ptrs), arr(packed_ptrs), Ms, Ns, bits,
+                                         int(bool(zero_thr))))
 
 
 def quantize_to_host(grad_ptr, res_in_ptr, res_out_ptr, dev_scratch_ptr, host_packed_ptr, M, N, bits, zero_thr=True, stream=0):

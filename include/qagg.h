@@ -86,6 +86,23 @@ int qagg_reduce_requantize(void* stream, const void* const* stripes, int K, cons
                            const float* sres_in, float* sres_out, void* packed_out,
                            int64_t M, int64_t n, int bits, int zero_threshold);
 
+/* Batched qagg_quantize that allocates nothing.  It has no counterpart in the reference.
+ * For callers that must not allocate device memory at call time -- a plugin whose host framework owns the rest of the
+ * card, a step that cannot afford the device-wide stall of cudaMalloc, a component with a memory budget fixed at start-up.
+ * One launch quantizes `num_matrices` matrices (same rules and results as qagg_quantize on each; all arrays are HOST
+ * arrays of device pointers / sizes).  The kernel's descriptor tables and work-queue counters live in a fixed 64 KB array
+ * inside the library image (every GPU that loads the library holds it until the process exits), hence the limits:
+ * at most QAGG_NOALLOC_MAX_MATRICES matrices and QAGG_NOALLOC_MAX_ITEMS work items (groups of adjacent columns; a
+ * 2048-row matrix uses one item per 9 columns) per call -- beyond that the call fails with QAGG_EINVAL and launches nothing.
+ * The first call on each device also looks up the array's address and clears its counters: make that call before any
+ * stream capture.  Every call reuses the same array, so two calls whose kernels may overlap on the GPU race; calls on one
+ * stream are ordered and safe.  Calls no cudaMalloc / cudaFree. */
+#define QAGG_NOALLOC_MAX_MATRICES 32
+#define QAGG_NOALLOC_MAX_ITEMS 4096
+int qagg_quantize_batch_noalloc(void* stream, int num_matrices, const float* const* grads, const float* const* res_in,
+                                float* const* res_out, void* const* packed, const int64_t* M, const int64_t* N, int bits,
+                                int zero_threshold);
+
 /* ---- single-matrix quantizer, packed buffer on the HOST ---------------------------------------- */
 
 /* As the reference's GPU quantizer is driven (packed QuantizedMatrix on the CPU, Source/Math/MatrixQuantizerGPU.cu:243,
