@@ -46,7 +46,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except Exception:
@@ -193,17 +193,19 @@ def run_ours(args):
         for g, p in zip(grads, pool[s % POOL]):
             g.copy_(p)
 
+    # clocks are sampled from the warm-up to the end of the host-buffer loop: the timed region alone lasts a few
+    # milliseconds, shorter than one nvidia-smi polling period
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for s in range(args.warmup):
         refresh(s)
         agg.step(ptrs, stream)
     torch.cuda.synchronize()
 
     agg.set_profiling(True)
-    sampler = ClockSampler(local_rank)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
     torch.cuda.synchronize()
-    sampler.start()
     t0 = time.perf_counter()
     for s in range(args.steps):
         refresh(args.warmup + s)
@@ -213,7 +215,6 @@ def run_ours(args):
     torch.cuda.synchronize()
     barrier()
     wall = time.perf_counter() - t0
-    clocks = sampler.stop()
     step_ms = [a.elapsed_time(b) for a, b in ev]
     phases = agg.phase_ms()
     agg.set_profiling(False)
@@ -241,6 +242,7 @@ def run_ours(args):
         if s >= 2:
             e2e_t.append(dt)
     e2e_ms = sum(e2e_t) / len(e2e_t) * 1e3
+    clocks = sampler.stop()
     te = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
     if K > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
