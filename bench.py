@@ -84,6 +84,11 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the quantize kernel, from the ncu capture
+# summarised in profiles/k_colquant_speech_dnn_1bit.md (same build, same workload); None where no capture exists
+NCU_TRAFFIC_BYTES = {"speech_dnn": 490.05e6}
+
+
 def get_shapes(name):
     from cntk_b200 import workloads as w
     table = {"speech_dnn": (w.speech_dnn, 1), "resnet50": (w.resnet50, 4), "lstm_lm": (w.lstm_lm, 1), "round_trip_2048": (w.round_trip_2048, 1)}
@@ -266,7 +271,7 @@ def run_ours(args):
             "phases_ms": {"quantize": phases[0], "scatter": phases[1], "reduce_requantize": phases[2], "all_gather": phases[3],
                           "unquantize": phases[4]},
             "roofline": {"bound": "hbm", "kernel": "k_colquant (quantize: stats + pack + residual)", "achieved": k1_gbs, "peak": peak,
-                         "unit": "GB/s", "frac": k1_gbs / peak, "peak_kind": peak_kind, "traffic": None,
+                         "unit": "GB/s", "frac": k1_gbs / peak, "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                          "algorithmic_bytes_per_launch": alg["quantize"],
                          "all_kernels": {"algorithmic_bytes": alg["total"], "ms": kern_ms,
                                          "frac": alg["total"] / (kern_ms * 1e-3) / 1e9 / peak if kern_ms > 0 else None}},

@@ -21,7 +21,7 @@ namespace qagg {
 constexpr int NT = 256;     // threads per CTA
 constexpr int NWARPS = NT / 32;
 constexpr int CMAX = 128;   // most columns in one work item
-constexpr int UNQ_CMAX = 512;
+constexpr int UNQ_CMAX = 4096;
 
 // optional phase timers for development builds (-DQAGG_PROBE); they expand to nothing in the product
 #ifdef QAGG_PROBE
@@ -947,10 +947,11 @@ __global__ void __launch_bounds__(NT, 3) k_colquant(const QTensor single, const 
 }
 
 // =================================================================================================================
-// Unquantize kernel (UnquantizeOneQWord, ColumnQuantizer.h:150-203).  Per work item the per-column constants
-// are computed once into shared memory; then, depending on the shape,
-//   Q % 4 == 0 and 16-byte aligned rows: thread <-> four adjacent packed words, one float4 store per bit position;
-//   otherwise                          : thread <-> one packed word, the warp stores 32 consecutive rows per bit position.
+// Unquantize kernel (UnquantizeOneQWord, ColumnQuantizer.h:150-203).  Every thread fetches the header and the packed
+// words of several tasks before it uses any of them (the loads of a task depend on nothing but its index), then
+// expands them:
+//   Q % 4 == 0 and 16-byte aligned rows: task = four adjacent packed words, one float4 store per bit position;
+//   otherwise                          : task = one packed word, the warp stores 32 consecutive rows per bit position.
 // =================================================================================================================
 template <bool ADD>
 __device__ __forceinline__ void store_out4(float* p, float4 v)
@@ -970,9 +971,24 @@ __device__ __forceinline__ void store_out4(float* p, float4 v)
     }
 }
 
+// the two constants unquantizing needs: 1 bit -> the two level values; else -> (ufactor, quantimin)
+__device__ __forceinline__ void unq_consts(int bits, float lower, float upper, float& ca, float& cb)
+{
+    const ValQ q = make_valq(bits, lower, upper);
+    if (bits == 1)
+    {
+        ca = unquantize_val(q, 1, 0u);
+        cb = unquantize_val(q, 1, 1u);
+    }
+    else
+    {
+        ca = q.ufactor;
+        cb = q.qmin;
+    }
+}
+
 __device__ __forceinline__ float unq_fast(int bits, unsigned field, float ca, float cb)
 {
-    // 1 bit: ca / cb are the two level values.  else: ca = ufactor, cb = quantimin.
     if (bits == 1)
         return field ? cb : ca;
     if (bits == 32)
@@ -981,14 +997,12 @@ __device__ __forceinline__ float unq_fast(int bits, unsigned field, float ca, fl
 }
 
 template <bool ADD, bool TABLE>
-__global__ void __launch_bounds__(NT) k_unquantize(const QTensor single, const QTensor* __restrict__ tensors,
+__global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, const QTensor* __restrict__ tensors,
                                                    const QItem* __restrict__ items, int nItems, int colsPerItem,
                                                    unsigned* __restrict__ counters)
 {
     __shared__ QTensor sT;
     __shared__ int sIt;
-    __shared__ const unsigned* sWords[UNQ_CMAX];
-    __shared__ float sA[UNQ_CMAX], sB[UNQ_CMAX];
     for (int iter = 0;; ++iter)
     {
         __syncthreads();
@@ -1023,83 +1037,117 @@ __global__ void __launch_bounds__(NT) k_unquantize(const QTensor single, const Q
         const int bits = T.bits;
         const int vpw = 32 / bits;
         const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
-        for (int col = threadIdx.x; col < nc; col += NT)
-        {
-            const unsigned char* colp = packed_col(T, col0 + col);
-            const ValQ q = make_valq(bits, reinterpret_cast<const float*>(colp)[0], reinterpret_cast<const float*>(colp)[1]);
-            sWords[col] = reinterpret_cast<const unsigned*>(colp + 8);
-            if (bits == 1)
-            {
-                sA[col] = unquantize_val(q, 1, 0u);
-                sB[col] = unquantize_val(q, 1, 1u);
-            }
-            else
-            {
-                sA[col] = q.ufactor;
-                sB[col] = q.qmin;
-            }
-        }
-        __syncthreads();
         float* __restrict__ out0 = T.out + (size_t) col0 * M;
         const bool aligned = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(T.out) & 15) == 0);
         if (aligned && ((Q & 3) == 0))
         {
+            constexpr int U = 2;
             const int Q4 = Q >> 2;
             const int total = nc * Q4;
-            for (int t = threadIdx.x; t < total; t += NT)
+            for (int t0 = threadIdx.x; t0 < total; t0 += NT * U)
             {
-                const int col = t / Q4;
-                const int w = (t - col * Q4) * 4;
-                const unsigned* __restrict__ words = sWords[col] + w;
-                const unsigned w0 = __ldg(words), w1 = __ldg(words + 1), w2 = __ldg(words + 2), w3 = __ldg(words + 3);
-                const float ca = sA[col], cb = sB[col];
-                float* __restrict__ op = out0 + (size_t) col * M + w;
-                const int nk = min(vpw, (M - w + Q - 1) / Q);
-#pragma unroll 4
-                for (int k = 0; k < nk; ++k)
+                unsigned wd[U][4];
+                float lo[U], up[U];
+                int colU[U], wU[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
                 {
-                    const int sh = k * bits;
-                    float4 v;
-                    v.x = unq_fast(bits, (w0 >> sh) & mask, ca, cb);
-                    v.y = unq_fast(bits, (w1 >> sh) & mask, ca, cb);
-                    v.z = unq_fast(bits, (w2 >> sh) & mask, ca, cb);
-                    v.w = unq_fast(bits, (w3 >> sh) & mask, ca, cb);
-                    store_out4<ADD>(op + k * Q, v);
+                    const int t = t0 + u * NT;
+                    if (t < total)
+                    {
+                        colU[u] = t / Q4;
+                        wU[u] = (t - colU[u] * Q4) * 4;
+                        const unsigned char* colp = packed_col(T, col0 + colU[u]);
+                        lo[u] = __ldg(reinterpret_cast<const float*>(colp));
+                        up[u] = __ldg(reinterpret_cast<const float*>(colp) + 1);
+                        const unsigned* words = reinterpret_cast<const unsigned*>(colp + 8) + wU[u];
+                        wd[u][0] = __ldg(words);
+                        wd[u][1] = __ldg(words + 1);
+                        wd[u][2] = __ldg(words + 2);
+                        wd[u][3] = __ldg(words + 3);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                {
+                    const int t = t0 + u * NT;
+                    if (t < total)
+                    {
+                        float ca, cb;
+                        unq_consts(bits, lo[u], up[u], ca, cb);
+                        float* __restrict__ op = out0 + (size_t) colU[u] * M + wU[u];
+                        const int nk = min(vpw, (M - wU[u] + Q - 1) / Q);
+#pragma unroll 4
+                        for (int k = 0; k < nk; ++k)
+                        {
+                            const int sh = k * bits;
+                            float4 v;
+                            v.x = unq_fast(bits, (wd[u][0] >> sh) & mask, ca, cb);
+                            v.y = unq_fast(bits, (wd[u][1] >> sh) & mask, ca, cb);
+                            v.z = unq_fast(bits, (wd[u][2] >> sh) & mask, ca, cb);
+                            v.w = unq_fast(bits, (wd[u][3] >> sh) & mask, ca, cb);
+                            store_out4<ADD>(op + k * Q, v);
+                        }
+                    }
                 }
             }
         }
         else
         {
-            // thread <-> one packed word: for each bit position the warp writes 32 consecutive rows (128 bytes)
+            constexpr int U = 4;
             const int total = nc * Q;
-            for (int t = threadIdx.x; t < total; t += NT)
+            for (int t0 = threadIdx.x; t0 < total; t0 += NT * U)
             {
-                const int col = t / Q;
-                const int w = t - col * Q;
-                const unsigned word = __ldg(sWords[col] + w);
-                const float ca = sA[col], cb = sB[col];
-                float* __restrict__ op = out0 + (size_t) col * M + w;
-                const int nk = min(vpw, (M - w + Q - 1) / Q);
-                if (bits == 1)
+                unsigned wd[U];
+                float lo[U], up[U];
+                int colU[U], wU[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
                 {
-#pragma unroll 8
-                    for (int k = 0; k < nk; ++k)
+                    const int t = t0 + u * NT;
+                    if (t < total)
                     {
-                        float val = ((word >> k) & 1u) ? cb : ca;
-                        if (ADD)
-                            val = __fadd_rn(val, op[k * Q]);
-                        op[k * Q] = val;
+                        colU[u] = t / Q;
+                        wU[u] = t - colU[u] * Q;
+                        const unsigned char* colp = packed_col(T, col0 + colU[u]);
+                        lo[u] = __ldg(reinterpret_cast<const float*>(colp));
+                        up[u] = __ldg(reinterpret_cast<const float*>(colp) + 1);
+                        wd[u] = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + wU[u]);
                     }
                 }
-                else
+#pragma unroll
+                for (int u = 0; u < U; ++u)
                 {
-#pragma unroll 4
-                    for (int k = 0; k < nk; ++k)
+                    const int t = t0 + u * NT;
+                    if (t < total)
                     {
-                        float val = unq_fast(bits, (word >> (k * bits)) & mask, ca, cb);
-                        if (ADD)
-                            val = __fadd_rn(val, op[k * Q]);
-                        op[k * Q] = val;
+                        float ca, cb;
+                        unq_consts(bits, lo[u], up[u], ca, cb);
+                        float* __restrict__ op = out0 + (size_t) colU[u] * M + wU[u];
+                        const int nk = min(vpw, (M - wU[u] + Q - 1) / Q);
+                        const unsigned word = wd[u];
+                        if (bits == 1)
+                        {
+#pragma unroll 8
+                            for (int k = 0; k < nk; ++k)
+                            {
+                                float val = ((word >> k) & 1u) ? cb : ca;
+                                if (ADD)
+                                    val = __fadd_rn(val, op[k * Q]);
+                                op[k * Q] = val;
+                            }
+                        }
+                        else
+                        {
+#pragma unroll 4
+                            for (int k = 0; k < nk; ++k)
+                            {
+                                float val = unq_fast(bits, (word >> (k * bits)) & mask, ca, cb);
+                                if (ADD)
+                                    val = __fadd_rn(val, op[k * Q]);
+                                op[k * Q] = val;
+                            }
+                        }
                     }
                 }
             }
@@ -1200,9 +1248,10 @@ cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, 
 {
     if (nItems <= 0)
         return cudaSuccess;
-    int grid = cfg.numSMs * 8;
-    if (grid > nItems)
-        grid = nItems;
+    // one CTA per work item: the items are uniform and short, so the hardware block scheduler balances them better
+    // than a software queue whose every fetch costs a global round trip
+    int grid = nItems;
+    counters = nullptr;
     static const QTensor zero = {};
     const QTensor& s = single ? *single : zero;
     if (single)
