@@ -135,7 +135,18 @@ struct qagg_aggregator
     std::vector<int64_t> sendOff;     // offset of region p in the send buffer
     int64_t slotBytes = 0;            // regionBytes[rank], padded: size of one receive slot
     int64_t gatherSlot = 0;           // max region, padded: size of one gather slot
-    DevBuf sendbuf, recvbuf, gatherbuf, resAll, sresAll, tables, hostStage;
+    // "window": [flags][receive slots][gather slots] in ONE allocation, so that a single IPC handle exposes to the
+    // peers everything they write into this rank's memory
+    DevBuf sendbuf, window, resAll, sresAll, tables, hostStage;
+    static const int64_t kFlagBytes = 512; // scatter flags [0, K), gather flags [64, 64 + K), status word at [127]
+    unsigned char* recvbuf = nullptr;
+    unsigned char* gatherbuf = nullptr;
+    // peer-memory exchange (off until qagg_agg_enable_peer): packed columns are stored straight into the peers' windows
+    bool peer = false;
+    unsigned char* peerWin[QAGG_MAXK] = {};
+    bool peerOpened[QAGG_MAXK] = {};
+    unsigned stepNo = 0;
+    long long waitPolls = 20000000; // bounded device-side waits (about two seconds of polling)
     std::vector<float*> res, sres;
     // device tables and their host mirrors
     std::vector<QTensor> hK1, hK2, hK3;
@@ -159,6 +170,9 @@ struct qagg_aggregator
 
     ~qagg_aggregator()
     {
+        for (int p = 0; p < QAGG_MAXK; ++p)
+            if (peerOpened[p])
+                cudaIpcCloseMemHandle(peerWin[p]);
         for (auto& slot : ev)
             for (auto& e : slot)
                 if (e)
@@ -171,8 +185,18 @@ struct qagg_aggregator
         return check_cuda(cudaEventRecord(ev[profSteps % kProfSlots][i], st), "cudaEventRecord");
     }
     unsigned char* send_region(int p) const { return static_cast<unsigned char*>(sendbuf.p) + sendOff[p]; }
-    unsigned char* recv_slot(int src) const { return static_cast<unsigned char*>(recvbuf.p) + (int64_t) src * slotBytes; }
-    unsigned char* gather_slot(int p) const { return static_cast<unsigned char*>(gatherbuf.p) + (int64_t) p * gatherSlot; }
+    unsigned char* recv_slot(int src) const { return recvbuf + (int64_t) src * slotBytes; }
+    unsigned char* gather_slot(int p) const { return gatherbuf + (int64_t) p * gatherSlot; }
+    unsigned* flag_words() const { return static_cast<unsigned*>(window.p); }
+    unsigned* status_word() const { return static_cast<unsigned*>(window.p) + 127; }
+    // the same places inside peer p's window (its receive slots have ITS region size)
+    int64_t peer_slot_bytes(int p) const { return align_up(regionBytes[p], 256); }
+    unsigned char* peer_recv_slot(int p, int src) const { return peerWin[p] + kFlagBytes + (int64_t) src * peer_slot_bytes(p); }
+    unsigned char* peer_gather_slot(int p, int slot) const
+    {
+        return peerWin[p] + kFlagBytes + peer_slot_bytes(p) * comm->K + (int64_t) slot * gatherSlot;
+    }
+    unsigned* peer_flags(int p) const { return reinterpret_cast<unsigned*>(peerWin[p]); }
 };
 
 namespace {
@@ -259,8 +283,12 @@ int build_tables(qagg_aggregator* a)
         {
             if (K == 1)
                 q1.pk[p] = a->gather_slot(0) + a->tOff[0][i];
+            else if (p == r)
+                q1.pk[p] = a->recv_slot(r) + a->tOff[p][i];
+            else if (a->peer)
+                q1.pk[p] = a->peer_recv_slot(p, r) + a->tOff[p][i]; // straight into the owner's receive slot over NVLink
             else
-                q1.pk[p] = (p == r ? a->recv_slot(r) : a->send_region(p)) + a->tOff[p][i];
+                q1.pk[p] = a->send_region(p) + a->tOff[p][i];
             q3.pk[p] = a->gather_slot(p) + a->tOff[p][i];
         }
         {
@@ -284,6 +312,8 @@ int build_tables(qagg_aggregator* a)
                 if (src != r)
                     q2.src[s++] = a->recv_slot(src) + a->tOff[r][i];
             q2.pk[0] = a->gather_slot(r) + a->tOff[r][i];
+            q2.bcast = a->peer ? 1 : 0; // also into slot r of every peer's gather buffer
+            q2.bcastOff = a->tOff[r][i];
             const int e = (int) a->hK2.size();
             a->hK2.push_back(q2);
             a->k2Tensor.push_back(i);
@@ -373,15 +403,40 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
     return QAGG_OK;
 }
 
+// peer mode: which flag words (one per peer, indexed by this rank) the kernel releases when it is done
+Signal make_signal(const qagg_aggregator* a, bool gatherPhase)
+{
+    Signal sg = {};
+    if (!a->peer)
+        return sg;
+    const int K = a->comm->K, r = a->comm->rank;
+    for (int p = 0; p < K; ++p)
+    {
+        if (p == r)
+            continue;
+        sg.flag[sg.n++] = a->peer_flags(p) + (gatherPhase ? 64 : 0) + r;
+        if (gatherPhase)
+            sg.bcastBase[sg.nbcast++] = a->peer_gather_slot(p, r);
+    }
+    sg.value = a->stepNo;
+    return sg;
+}
 int launch_k1(qagg_aggregator* a, cudaStream_t st)
 {
+    const Signal sg = make_signal(a, false);
     return check_cuda(launch_colquant(st, false, a->mode, nullptr, a->dK1, a->dI1, (int) a->iK1.size(), 0, a->cfg,
-                                      static_cast<unsigned*>(a->queue.p)), "quantize launch");
+                                      static_cast<unsigned*>(a->queue.p), &sg), "quantize launch");
 }
 int launch_k2(qagg_aggregator* a, cudaStream_t st)
 {
+    const Signal sg = make_signal(a, true);
     return check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg,
-                                      static_cast<unsigned*>(a->queue.p) + QAGG_COUNTER_UINTS), "reduce-requantize launch");
+                                      static_cast<unsigned*>(a->queue.p) + QAGG_COUNTER_UINTS, &sg), "reduce-requantize launch");
+}
+int wait_peers(qagg_aggregator* a, bool gatherPhase, cudaStream_t st)
+{
+    return check_cuda(launch_wait_flags(st, a->flag_words() + (gatherPhase ? 64 : 0), a->comm->K, a->comm->rank, a->stepNo, a->waitPolls,
+                                        a->status_word()), "flag wait launch");
 }
 int launch_k3(qagg_aggregator* a, cudaStream_t st)
 {
@@ -597,10 +652,10 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
 
     if ((rc = a->sendbuf.alloc((size_t) sendTotal, true)))
         return rc;
-    if ((rc = a->recvbuf.alloc((size_t) (a->slotBytes * K), true)))
+    if ((rc = a->window.alloc((size_t) (qagg_aggregator::kFlagBytes + a->slotBytes * K + a->gatherSlot * K), true)))
         return rc;
-    if ((rc = a->gatherbuf.alloc((size_t) (a->gatherSlot * K), true)))
-        return rc;
+    a->recvbuf = static_cast<unsigned char*>(a->window.p) + qagg_aggregator::kFlagBytes;
+    a->gatherbuf = a->recvbuf + a->slotBytes * K;
     if ((rc = a->resAll.alloc((size_t) resFloats * 4, true)))
         return rc;
     if ((rc = a->sresAll.alloc((size_t) sresFloats * 4, true)))
@@ -648,7 +703,7 @@ static int exchange_scatter(qagg_aggregator* a, cudaStream_t st)
 static int exchange_gather(qagg_aggregator* a, cudaStream_t st)
 {
     const int r = a->comm->rank;
-    return check_nccl(ncclAllGather(a->gather_slot(r), a->gatherbuf.p, (size_t) a->gatherSlot, ncclChar, a->comm->nccl, st), "ncclAllGather");
+    return check_nccl(ncclAllGather(a->gather_slot(r), a->gatherbuf, (size_t) a->gatherSlot, ncclChar, a->comm->nccl, st), "ncclAllGather");
 }
 
 int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream)
@@ -665,6 +720,7 @@ int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream)
         return rc;
     if ((rc = bind_grads(a, grads, st)))
         return rc;
+    a->stepNo++;
     if ((rc = a->mark(0, st)))
         return rc;
     if ((rc = launch_k1(a, st)))
@@ -673,7 +729,7 @@ int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream)
         return rc;
     if (a->comm->K > 1)
     {
-        if ((rc = exchange_scatter(a, st)))
+        if ((rc = a->peer ? wait_peers(a, false, st) : exchange_scatter(a, st)))
             return rc;
         if ((rc = a->mark(2, st)))
             return rc;
@@ -681,7 +737,7 @@ int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream)
             return rc;
         if ((rc = a->mark(3, st)))
             return rc;
-        if ((rc = exchange_gather(a, st)))
+        if ((rc = a->peer ? wait_peers(a, true, st) : exchange_gather(a, st)))
             return rc;
     }
     else
@@ -765,14 +821,33 @@ int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* cons
     int rc = check_cuda(cudaSetDevice(aggs[0]->comm->device), "cudaSetDevice");
     if (rc)
         return rc;
+    const bool peer = aggs[0]->peer;
+    for (int r = 0; r < K; ++r)
+        if (aggs[r]->peer != peer)
+            return fail(QAGG_ESTATE, "qagg_agg_step_group: peer mode must be enabled on all ranks or on none");
     for (int r = 0; r < K; ++r)
     {
         if ((rc = bind_grads(aggs[r], grads[r], st)))
             return rc;
+        aggs[r]->stepNo++;
         if ((rc = launch_k1(aggs[r], st)))
             return rc;
     }
-    if (K > 1)
+    if (K > 1 && peer)
+    {
+        // every rank's kernels run one after the other on this one stream, so each flag is already set when its
+        // waiter starts: the waits check the protocol, they never actually spin here
+        for (int r = 0; r < K; ++r)
+            if ((rc = wait_peers(aggs[r], false, st)))
+                return rc;
+        for (int r = 0; r < K; ++r)
+            if ((rc = launch_k2(aggs[r], st)))
+                return rc;
+        for (int r = 0; r < K; ++r)
+            if ((rc = wait_peers(aggs[r], true, st)))
+                return rc;
+    }
+    else if (K > 1)
     {
         // scatter: region p of rank r's send buffer -> receive slot r of rank p
         for (int r = 0; r < K; ++r)
@@ -796,6 +871,107 @@ int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* cons
         if ((rc = launch_k3(aggs[r], st)))
             return rc;
     return QAGG_OK;
+}
+
+int qagg_agg_peer_handle(qagg_aggregator* a, void* out)
+{
+    if (!a || !out)
+        return fail(QAGG_EINVAL, "qagg_agg_peer_handle: bad arguments");
+    static_assert(sizeof(cudaIpcMemHandle_t) <= QAGG_PEER_HANDLE_BYTES, "IPC handle does not fit");
+    int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    std::memset(out, 0, QAGG_PEER_HANDLE_BYTES);
+    if (a->comm->local)
+    {
+        // ranks of an in-process group share an address space: the "handle" is the window's address
+        std::memcpy(out, &a->window.p, sizeof(void*));
+        return QAGG_OK;
+    }
+    cudaIpcMemHandle_t h;
+    if ((rc = check_cuda(cudaIpcGetMemHandle(&h, a->window.p), "cudaIpcGetMemHandle")))
+        return rc;
+    std::memcpy(out, &h, sizeof(h));
+    return QAGG_OK;
+}
+
+int qagg_agg_enable_peer(qagg_aggregator* a, const void* handles)
+{
+    if (!a || !handles)
+        return fail(QAGG_EINVAL, "qagg_agg_enable_peer: bad arguments");
+    if (a->peer)
+        return fail(QAGG_ESTATE, "qagg_agg_enable_peer: already enabled");
+    const int K = a->comm->K, r = a->comm->rank;
+    if (K == 1)
+        return QAGG_OK;
+    int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    const unsigned char* hb = static_cast<const unsigned char*>(handles);
+    for (int p = 0; p < K; ++p)
+    {
+        if (p == r)
+        {
+            a->peerWin[p] = static_cast<unsigned char*>(a->window.p);
+            continue;
+        }
+        if (a->comm->local)
+        {
+            void* q = nullptr;
+            std::memcpy(&q, hb + (size_t) p * QAGG_PEER_HANDLE_BYTES, sizeof(void*));
+            a->peerWin[p] = static_cast<unsigned char*>(q);
+        }
+        else
+        {
+            cudaIpcMemHandle_t h;
+            std::memcpy(&h, hb + (size_t) p * QAGG_PEER_HANDLE_BYTES, sizeof(h));
+            void* q = nullptr;
+            if ((rc = check_cuda(cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")))
+                return rc;
+            a->peerWin[p] = static_cast<unsigned char*>(q);
+            a->peerOpened[p] = true;
+        }
+        if (!a->peerWin[p])
+            return fail(QAGG_EINVAL, "qagg_agg_enable_peer: null peer window");
+    }
+    a->peer = true;
+    // the routing of the packed columns changes: rebuild and re-upload the tables on the next step
+    if ((rc = build_tables(a)))
+        return rc;
+    a->boundGrads.clear();
+    return QAGG_OK;
+}
+
+int qagg_agg_set_wait_limit(qagg_aggregator* a, long long max_polls)
+{
+    if (!a || max_polls < 1)
+        return fail(QAGG_EINVAL, "qagg_agg_set_wait_limit: bad arguments");
+    a->waitPolls = max_polls;
+    return QAGG_OK;
+}
+
+int qagg_agg_check(qagg_aggregator* a, void* stream)
+{
+    if (!a)
+        return fail(QAGG_EINVAL, "null aggregator");
+    int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    unsigned st = 0;
+    if ((rc = check_cuda(cudaMemcpyAsync(&st, a->status_word(), sizeof(st), cudaMemcpyDeviceToHost, (cudaStream_t) stream), "status read")))
+        return rc;
+    if ((rc = check_cuda(cudaStreamSynchronize((cudaStream_t) stream), "cudaStreamSynchronize")))
+        return rc;
+    if (st & 1u)
+        return fail(QAGG_ETIMEOUT, "a device-side wait for a peer's flag ran out: a peer did not reach the step (results of that step are invalid)");
+    return QAGG_OK;
+}
+
+int qagg_wait_flags(void* stream, const unsigned* flags_dev, int n, int skip, unsigned value, long long max_polls, unsigned* status_dev)
+{
+    if (!flags_dev || !status_dev || n < 1 || n > 32 || max_polls < 1)
+        return fail(QAGG_EINVAL, "qagg_wait_flags: bad arguments");
+    return check_cuda(launch_wait_flags((cudaStream_t) stream, flags_dev, n, skip, value, max_polls, status_dev), "flag wait launch");
 }
 
 int qagg_agg_step_host(qagg_aggregator* a, float* const* host_grads, void* stream)

@@ -31,6 +31,20 @@ struct QTensor
     int nsrc;                           // reduce: number of packed sources
     int selfRaw;                        // reduce: 1 = start from `grad` instead of src[0]
     const unsigned char* src[QAGG_MAXK]; // reduce: packed sources, M x N each, summed in index order
+    int bcast;                           // 1 = every packed column is also written to the launch's broadcast bases
+    int pad_;
+    long long bcastOff;                  // offset of this matrix's block from a broadcast base (K == 1 routing only)
+};
+
+// Flags that the last CTA of a kernel writes (release, system scope) after all of the kernel's stores: one word in each
+// peer's memory, set to `value`.  n == 0: no signalling.
+struct Signal
+{
+    unsigned* flag[QAGG_MAXK];
+    int n;
+    unsigned value;
+    unsigned char* bcastBase[QAGG_MAXK]; // broadcast copies (peer gather slots) for matrices with bcast == 1
+    int nbcast;
 };
 
 struct QItem
@@ -73,7 +87,11 @@ int cols_per_item(long long M, long long N, int smemFloats, bool* resident);
 // switches the kernel from static striding over the items to a shared work queue: [0] next item, [1] CTAs finished
 // (both re-zeroed by the kernel before it ends), [8 + smid] per-SM tickets that spread the walking warps.
 cudaError_t launch_colquant(cudaStream_t st, bool stripes, int mode, const QTensor* single, const QTensor* tensors,
-                            const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters = nullptr);
+                            const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters = nullptr,
+                            const Signal* signal = nullptr);
+// one warp polls flags[i] (i < n, i != skip) until each is >= value (wrap-safe) or maxPolls polls have passed; on
+// give-up it ORs 1 into *status and returns: the context stays usable and the host reads the status later
+cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status);
 cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, const QTensor* tensors,
                               const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters = nullptr);
 cudaError_t get_launch_cfg(int device, LaunchCfg* cfg);

@@ -648,8 +648,27 @@ __device__ __forceinline__ void store_header(unsigned char* dst, float lower, fl
     reinterpret_cast<float*>(dst)[1] = upper;
 }
 
+// a packed column's words (and, from the thread that owns word 0, its header) go to the owner's buffer and to every
+// broadcast copy: with peer pointers in pk[] / bcast[] these stores ARE the scatter / all-gather traffic over NVLink
+__device__ __forceinline__ void store_words(const QTensor& T, const Signal& sg, int j, int w, const unsigned* words, int nw, float lower, float upper)
+{
+    unsigned char* dst = packed_col(T, j);
+    const size_t off = (size_t) (dst - T.pk[0]) + (size_t) T.bcastOff; // used only when T.bcast is set (K == 1 routing)
+    const int nb = T.bcast ? sg.nbcast : 0;
+    for (int b = -1; b < nb; ++b)
+    {
+        unsigned char* d = (b < 0) ? dst : sg.bcastBase[b] + off;
+        unsigned* pw = reinterpret_cast<unsigned*>(d + 8) + w;
+        for (int i = 0; i < nw; ++i)
+            pw[i] = words[i];
+        if (w == 0)
+            store_header(d, lower, upper);
+    }
+}
+
 template <int MODE>
-__device__ __forceinline__ void quantize_resident(const QTensor& T, int col0, int nc, int stride, const float* __restrict__ smem, const ColStats& S)
+__device__ __forceinline__ void quantize_resident(const QTensor& T, const Signal& sg, int col0, int nc, int stride, const float* __restrict__ smem,
+                                                  const ColStats& S)
 {
     const int M = (int) T.M;
     const int Q = T.Q;
@@ -685,14 +704,8 @@ __device__ __forceinline__ void quantize_resident(const QTensor& T, int col0, in
                 w3 |= quant_one<MODE>(q, bits, val0, val1, v.w, r.w) << sh;
                 __stcs(reinterpret_cast<float4*>(rp + k * Q), r);
             }
-            unsigned char* dst = packed_col(T, j);
-            unsigned* words = reinterpret_cast<unsigned*>(dst + 8) + w;
-            words[0] = w0;
-            words[1] = w1;
-            words[2] = w2;
-            words[3] = w3;
-            if (w == 0)
-                store_header(dst, lower, upper);
+            const unsigned ws[4] = {w0, w1, w2, w3};
+            store_words(T, sg, j, w, ws, 4, lower, upper);
         }
     }
     else
@@ -717,17 +730,14 @@ __device__ __forceinline__ void quantize_resident(const QTensor& T, int col0, in
                 word |= quant_one<MODE>(q, bits, val0, val1, vp[k * Q], r) << (k * bits);
                 rp[k * Q] = r;
             }
-            unsigned char* dst = packed_col(T, j);
-            reinterpret_cast<unsigned*>(dst + 8)[w] = word;
-            if (w == 0)
-                store_header(dst, lower, upper);
+            store_words(T, sg, j, w, &word, 1, lower, upper);
         }
     }
 }
 
 // same, for streamed columns: the values are recomputed from the inputs
 template <int MODE, bool STRIPES>
-__device__ __forceinline__ void quantize_streamed(const QTensor& T, int col0, int nc, const ColStats& S)
+__device__ __forceinline__ void quantize_streamed(const QTensor& T, const Signal& sg, int col0, int nc, const ColStats& S)
 {
     const int M = (int) T.M;
     const int Q = T.Q;
@@ -751,10 +761,7 @@ __device__ __forceinline__ void quantize_streamed(const QTensor& T, int col0, in
             word |= quant_one<MODE>(q, bits, val0, val1, load_v<STRIPES>(T, j, (long long) w + (long long) k * Q), r) << (k * bits);
             rp[(size_t) k * Q] = r;
         }
-        unsigned char* dst = packed_col(T, j);
-        reinterpret_cast<unsigned*>(dst + 8)[w] = word;
-        if (w == 0)
-            store_header(dst, lower, upper);
+        store_words(T, sg, j, w, &word, 1, lower, upper);
     }
 }
 
@@ -770,7 +777,7 @@ __device__ __forceinline__ void quantize_streamed(const QTensor& T, int col0, in
 template <bool STRIPES, int MODE, bool TABLE>
 __global__ void __launch_bounds__(NT, 3) k_colquant(const QTensor single, const QTensor* __restrict__ tensors,
                                                     const QItem* __restrict__ items, int nItems, int colsPerItem, int smemFloats,
-                                                    int numSMs, unsigned* __restrict__ counters)
+                                                    int numSMs, unsigned* __restrict__ counters, const Signal signal)
 {
     extern __shared__ __align__(16) float smem[];
     __shared__ QTensor sT;
@@ -873,7 +880,7 @@ __global__ void __launch_bounds__(NT, 3) k_colquant(const QTensor single, const 
                 __syncthreads();
             }
             PROBE_MARK(t2);
-            quantize_resident<MODE>(T, col0, nc, stride, smem, S);
+            quantize_resident<MODE>(T, signal, col0, nc, stride, smem, S);
             PROBE_MARK(t3);
             PROBE_ADD(0, t0, t1);
             PROBE_ADD(1, t1, t2);
@@ -929,21 +936,51 @@ __global__ void __launch_bounds__(NT, 3) k_colquant(const QTensor single, const 
                 S.upper[lane] = up;
             }
             __syncthreads();
-            quantize_streamed<MODE, STRIPES>(T, col0, nc, S);
+            quantize_streamed<MODE, STRIPES>(T, signal, col0, nc, S);
         }
     }
-    // the last CTA to leave re-arms the work counter for the next launch
+    // The last CTA to leave re-arms the work counter for the next launch and, if asked to, tells the peers that every
+    // store of this kernel (theirs included: packed columns written straight into peer memory) has been issued:
+    // each CTA's stores are ordered before its arrival by barrier + system-scope fence, the last arrival observes all
+    // of them and releases the flags.
     if (counters && threadIdx.x == 0)
     {
-        __threadfence();
+        __threadfence_system();
         const unsigned done = atomicAdd(&counters[1], 1u);
         if (done == gridDim.x - 1)
         {
             counters[0] = 0;
             counters[1] = 0;
-            __threadfence();
+            __threadfence_system();
+            for (int i = 0; i < signal.n; ++i)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
         }
     }
+}
+
+// One warp waits for the peers' flags.  Every wait is bounded: after maxPolls polls the lane gives up, records it in
+// *status and the kernel ends normally.
+__global__ void k_wait_flags(const unsigned* __restrict__ flags, int n, int skip, unsigned value, long long maxPolls, unsigned* __restrict__ status)
+{
+    const int i = threadIdx.x;
+    if (i < n && i != skip)
+    {
+        long long polls = 0;
+        for (;;)
+        {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
+            if ((int) (v - value) >= 0)
+                break;
+            if (++polls >= maxPolls)
+            {
+                atomicOr(status, 1u);
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    __threadfence_system();
 }
 
 // =================================================================================================================
@@ -1203,7 +1240,7 @@ int unq_cols_per_item(long long M)
 
 template <bool STRIPES, int MODE, bool TABLE>
 static cudaError_t launch_cq(cudaStream_t st, const QTensor* single, const QTensor* tensors, const QItem* items,
-                             int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters)
+                             int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters, const Signal& signal)
 {
     auto kern = k_colquant<STRIPES, MODE, TABLE>;
     const size_t smemBytes = (size_t) cfg.smemFloats * sizeof(float);
@@ -1214,19 +1251,44 @@ static cudaError_t launch_cq(cudaStream_t st, const QTensor* single, const QTens
     if (grid > nItems)
         grid = nItems;
     static const QTensor zero = {};
-    kern<<<grid, NT, smemBytes, st>>>(single ? *single : zero, tensors, items, nItems, colsPerItem, cfg.smemFloats, cfg.numSMs, counters);
+    kern<<<grid, NT, smemBytes, st>>>(single ? *single : zero, tensors, items, nItems, colsPerItem, cfg.smemFloats, cfg.numSMs, counters, signal);
+    return cudaGetLastError();
+}
+
+__global__ void k_signal_only(const Signal signal)
+{
+    __threadfence_system();
+    for (int i = 0; i < signal.n; ++i)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
+}
+
+cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status)
+{
+    if (n > 32)
+        return cudaErrorInvalidValue;
+    k_wait_flags<<<1, 32, 0, st>>>(flags, n, skip, value, maxPolls, status);
     return cudaGetLastError();
 }
 
 cudaError_t launch_colquant(cudaStream_t st, bool stripes, int mode, const QTensor* single, const QTensor* tensors,
-                            const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters)
+                            const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters, const Signal* signalp)
 {
+    static const Signal none = {};
+    const Signal& signal = signalp ? *signalp : none;
     if (nItems <= 0)
+    {
+        // nothing to compute, but the peers still wait for this rank's flags
+        if (signal.n > 0)
+        {
+            k_signal_only<<<1, 1, 0, st>>>(signal);
+            return cudaGetLastError();
+        }
         return cudaSuccess;
+    }
     const bool table = (single == nullptr);
 #define QAGG_CASE(S, MD, TB) \
     if (stripes == S && mode == MD && table == TB) \
-        return launch_cq<S, MD, TB>(st, single, tensors, items, nItems, colsPerItem, cfg, counters);
+        return launch_cq<S, MD, TB>(st, single, tensors, items, nItems, colsPerItem, cfg, counters, signal);
     QAGG_CASE(false, MODE_ONEBIT_ZERO, false)
     QAGG_CASE(false, MODE_ONEBIT_MEAN, false)
     QAGG_CASE(false, MODE_MULTIBIT, false)

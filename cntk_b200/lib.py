@@ -13,6 +13,7 @@ ZERO_THRESHOLD = 1
 SELF_QUANTIZED = 2
 V2_IDENTITY_K1 = 4
 UNIQUE_ID_BYTES = 128
+PEER_HANDLE_BYTES = 64
 
 EXPORTS = [
     "qagg_last_error", "qagg_abi_version", "qagg_packed_col_bytes", "qagg_packed_bytes", "qagg_stripe",
@@ -21,7 +22,8 @@ EXPORTS = [
     "qagg_unique_id", "qagg_comm_create", "qagg_comm_create_local_group", "qagg_comm_allreduce_f64", "qagg_comm_barrier", "qagg_comm_rank", "qagg_comm_size",
     "qagg_comm_destroy", "qagg_agg_create", "qagg_agg_step", "qagg_agg_step_group", "qagg_agg_step_host",
     "qagg_agg_reset_residuals", "qagg_agg_residuals", "qagg_agg_copy_residual", "qagg_agg_copy_packed", "qagg_agg_wire_bytes",
-    "qagg_agg_launches_per_step", "qagg_agg_set_profiling", "qagg_agg_phase_ms", "qagg_agg_destroy",
+    "qagg_agg_launches_per_step", "qagg_agg_peer_handle", "qagg_agg_enable_peer", "qagg_agg_set_wait_limit", "qagg_agg_check", "qagg_wait_flags",
+    "qagg_agg_set_profiling", "qagg_agg_phase_ms", "qagg_agg_destroy",
 ]
 
 
@@ -75,6 +77,11 @@ _lib.qagg_agg_copy_packed.argtypes = [c_vp, c_int, c_vp, c_vp]
 _lib.qagg_agg_wire_bytes.restype = c_i64
 _lib.qagg_agg_wire_bytes.argtypes = [c_vp]
 _lib.qagg_agg_launches_per_step.argtypes = [c_vp]
+_lib.qagg_agg_peer_handle.argtypes = [c_vp, c_vp]
+_lib.qagg_agg_enable_peer.argtypes = [c_vp, c_vp]
+_lib.qagg_agg_set_wait_limit.argtypes = [c_vp, ctypes.c_longlong]
+_lib.qagg_agg_check.argtypes = [c_vp, c_vp]
+_lib.qagg_wait_flags.argtypes = [c_vp, c_vp, c_int, c_int, ctypes.c_uint, ctypes.c_longlong, c_vp]
 _lib.qagg_agg_set_profiling.argtypes = [c_vp, c_int]
 _lib.qagg_agg_phase_ms.argtypes = [c_vp, ctypes.POINTER(ctypes.c_float)]
 _lib.qagg_agg_destroy.argtypes = [c_vp]
@@ -181,6 +188,10 @@ class Plan:
             self.h = None
 
 
+def wait_flags(flags_ptr, n, skip, value, max_polls, status_ptr, stream=0):
+    _ok(_lib.qagg_wait_flags(stream, flags_ptr, n, skip, value, max_polls, status_ptr))
+
+
 def unique_id():
     buf = ctypes.create_string_buffer(UNIQUE_ID_BYTES)
     _ok(_lib.qagg_unique_id(buf))
@@ -260,6 +271,23 @@ class Aggregator:
 
     def copy_packed(self, tensor, dst_ptr, stream=0):
         _ok(_lib.qagg_agg_copy_packed(self.h, tensor, dst_ptr, stream))
+
+    def peer_handle(self):
+        buf = ctypes.create_string_buffer(PEER_HANDLE_BYTES)
+        _ok(_lib.qagg_agg_peer_handle(self.h, buf))
+        return buf.raw
+
+    def enable_peer(self, handles):
+        """handles: the K peer handles (bytes), in rank order."""
+        blob = b"".join(handles)
+        assert len(blob) == PEER_HANDLE_BYTES * len(handles)
+        _ok(_lib.qagg_agg_enable_peer(self.h, ctypes.create_string_buffer(blob, len(blob))))
+
+    def set_wait_limit(self, max_polls):
+        _ok(_lib.qagg_agg_set_wait_limit(self.h, max_polls))
+
+    def check(self, stream=0):
+        _ok(_lib.qagg_agg_check(self.h, stream))
 
     def set_profiling(self, enabled):
         _ok(_lib.qagg_agg_set_profiling(self.h, int(bool(enabled))))

@@ -176,6 +176,25 @@ int qagg_agg_copy_residual(qagg_aggregator* a, int tensor, int which, float* dst
 /* Copy the gathered packed matrix of tensor i (what every rank unquantized from in the last step) into a device
  * buffer of qagg_packed_bytes(M[i], N[i], bits), in the reference's contiguous layout. */
 int qagg_agg_copy_packed(qagg_aggregator* a, int tensor, void* dst_dev, void* stream);
+/* ---- peer-memory exchange (optional; replaces the two NCCL collectives of a step) ------------------------------------
+ * Where the reference moves every stripe GPU -> pinned host -> MPI -> pinned host -> GPU (Source/Math/MatrixQuantizerGPU.cu:126-142,
+ * 313-324; Source/1BitSGD/AllReduceDistGradAggregator.h:303-365, 459-502), the quantize kernel here stores each packed
+ * column straight into its owner's receive slot and the owner's requantize kernel stores its result straight into every
+ * rank's gather slot, over NVLink peer mappings; a step's two "collectives" shrink to two flag hand-shakes.
+ *   1. every rank calls qagg_agg_peer_handle (QAGG_PEER_HANDLE_BYTES bytes out) and the caller all-gathers the handles;
+ *   2. every rank calls qagg_agg_enable_peer with the K handles in rank order (cudaIpcOpenMemHandle on the others').
+ * From then on qagg_agg_step uses the peer path.  Device-side waits are bounded (qagg_agg_set_wait_limit polls, default
+ * about two seconds): a peer that never arrives makes the wait give up and set a status word instead of hanging;
+ * qagg_agg_check synchronises the stream and returns QAGG_ETIMEOUT if that happened since creation. */
+#define QAGG_PEER_HANDLE_BYTES 64
+int qagg_agg_peer_handle(qagg_aggregator* a, void* out);
+int qagg_agg_enable_peer(qagg_aggregator* a, const void* handles);
+int qagg_agg_set_wait_limit(qagg_aggregator* a, long long max_polls);
+int qagg_agg_check(qagg_aggregator* a, void* stream);
+/* The bounded wait on its own: one warp polls flags_dev[i] (i < n <= 32, i != skip) until each is >= value or max_polls
+ * polls have passed; on give-up it ORs 1 into *status_dev.  Never hangs. */
+int qagg_wait_flags(void* stream, const unsigned* flags_dev, int n, int skip, unsigned value, long long max_polls, unsigned* status_dev);
+
 /* Per-phase device timing of the steps that follow (no reference counterpart; the reference only has the wall-clock
  * "Actual gradient aggregation time" trace, AllReduceDistGradAggregator.h:241-246, 560-565).  When enabled, each step records
  * CUDA events on its stream around its five phases.  qagg_agg_phase_ms waits for the recorded steps and returns the mean

@@ -37,9 +37,16 @@ def main():
     dist.broadcast(idt, 0)
     comm = lib.Comm.create(bytes(idt.cpu().numpy().tobytes()), rank, K, local)
     be = backend.OracleBackend()
-    for bits, zero_thr, self_q in ((1, True, True), (1, False, True), (4, True, True), (1, True, False)):
+    for bits, zero_thr, self_q, peer in ((1, True, True, False), (1, False, True, False), (4, True, True, False), (1, True, False, False),
+                                         (1, True, True, True), (4, True, True, True), (1, True, False, True)):
         flags = (lib.ZERO_THRESHOLD if zero_thr else 0) | (lib.SELF_QUANTIZED if self_q else 0)
         agg = lib.Aggregator(comm, SHAPES, bits, flags)
+        if peer:
+            # exchange the IPC handles of the ranks' windows, then switch the aggregator to the peer-memory path
+            mine = torch.frombuffer(bytearray(agg.peer_handle()), dtype=torch.uint8).to(dev)
+            allh = [torch.zeros_like(mine) for _ in range(K)]
+            dist.all_gather(allh, mine)
+            agg.enable_peer([bytes(h.cpu().numpy().tobytes()) for h in allh])
         st = exchange.ExchangeState(SHAPES, K)
         dg = [torch.zeros((N, M), dtype=torch.float32, device=dev) for (M, N) in SHAPES]
         for step in range(4):
@@ -50,7 +57,7 @@ def main():
             agg.step([t.data_ptr() for t in dg], torch.cuda.current_stream().cuda_stream)
             torch.cuda.synchronize()
             for i, (M, N) in enumerate(SHAPES):
-                what = f"bits {bits} zero {zero_thr} self {self_q} step {step} rank {rank} tensor {i}"
+                what = f"bits {bits} zero {zero_thr} self {self_q} peer {peer} step {step} rank {rank} tensor {i}"
                 assert np.array_equal(dg[i].cpu().numpy().view(np.uint32), grads[rank][i].view(np.uint32)), "aggregate: " + what
                 r_ = torch.empty((N, M), dtype=torch.float32, device=dev)
                 agg.copy_residual(i, 0, r_.data_ptr())
@@ -66,6 +73,8 @@ def main():
                 agg.copy_packed(i, pk.data_ptr())
                 torch.cuda.synchronize()
                 assert np.array_equal(pk.cpu().numpy(), packed[rank][i]), "packed words: " + what
+        agg.check()
+        dist.barrier()  # nobody unmaps a window that a peer may still be writing to
         agg.destroy()
     dist.barrier()
     comm.destroy()

@@ -27,11 +27,15 @@ def G():
     return gpu_util
 
 
-def run_group(G, oracle, shapes, K, bits, zero_thr, self_quant, steps, make_inputs, check_every=1, v2_identity=False):
+def run_group(G, oracle, shapes, K, bits, zero_thr, self_quant, steps, make_inputs, check_every=1, v2_identity=False, peer=False):
     from cntk_b200 import lib
     flags = (lib.ZERO_THRESHOLD if zero_thr else 0) | (lib.SELF_QUANTIZED if self_quant else 0) | (lib.V2_IDENTITY_K1 if v2_identity else 0)
     comms = lib.Comm.local_group(K, 0)
     aggs = [lib.Aggregator(c, shapes, bits, flags) for c in comms]
+    if peer:
+        handles = [a.peer_handle() for a in aggs]
+        for a in aggs:
+            a.enable_peer(handles)
     st = ox.ExchangeState(shapes, K)
     dgrads = [[torch.zeros((N, M), dtype=torch.float32, device=G.DEV) for (M, N) in shapes] for _ in range(K)]
     try:
@@ -61,11 +65,44 @@ def run_group(G, oracle, shapes, K, bits, zero_thr, self_quant, steps, make_inpu
                         pk = torch.zeros(lib.packed_bytes(M, N, bits), dtype=torch.uint8, device=G.DEV)
                         aggs[r].copy_packed(i, pk.data_ptr())
                         G.assert_same_bits(G.host(pk), packed[r][i], f"step {step} rank {r} tensor {i} gathered packed words")
+        for a in aggs:
+            a.check()  # no bounded wait gave up
     finally:
         for a in aggs:
             a.destroy()
         for c in comms:
             c.destroy()
+
+
+@pytest.mark.parametrize("K", [2, 3, 8])
+@pytest.mark.parametrize("bits,zero_thr,self_quant", [(1, True, True), (1, True, False), (4, True, True)])
+def test_peer_memory_exchange_bit_exact(G, oracle_port, K, bits, zero_thr, self_quant):
+    """The exchange without collectives: the quantize kernel stores packed columns straight into their owner's receive
+    slot and the owner's kernel stores its result into every rank's gather slot (here all windows are on one device, so
+    the "peer" pointers are ordinary ones and the flag waits never spin: this checks routing, offsets and the protocol's
+    bookkeeping; tests/test_gpu_multi.py runs it across GPUs)."""
+    run_group(G, oracle_port, mg.EXCHANGE_SHAPES, K, bits, zero_thr, self_quant, 4, mg.exchange_inputs, peer=True)
+
+
+def test_peer_memory_exchange_speech_shaped(G, oracle_port):
+    run_group(G, oracle_port, SPEECH_SMALL, 4, 1, True, True, 12, speech_inputs, check_every=6, peer=True)
+
+
+def test_bounded_wait_gives_up_and_reports(G):
+    """Failure detection without a GPU fault: a wait on a flag that nothing sets runs out of polls, records it in the
+    status word and returns; the context stays usable and a later wait on flags that ARE set passes."""
+    from cntk_b200 import lib
+    flags = torch.zeros(8, dtype=torch.int32, device=G.DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=G.DEV)
+    lib.wait_flags(flags.data_ptr(), 4, 1, 1, 2000, status.data_ptr())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1
+    status.zero_()
+    flags.fill_(7)
+    lib.wait_flags(flags.data_ptr(), 4, 1, 7, 2000, status.data_ptr())
+    lib.wait_flags(flags.data_ptr(), 4, 1, 5, 2000, status.data_ptr())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
 
 
 @pytest.mark.parametrize("K", [1, 2, 3, 4, 8])
