@@ -15,6 +15,7 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <vector>
@@ -147,6 +148,9 @@ struct qagg_aggregator
     bool peerOpened[QAGG_MAXK] = {};
     unsigned stepNo = 0;
     long long waitPolls = 20000000; // bounded device-side waits (about two seconds of polling)
+    // peer mode, all-gather half: true = the requantize kernel writes locally and a small copy kernel pushes the finished
+    // region to the peers; false = the requantize kernel itself stores every packed word K times
+    bool pushGather = true;
     std::vector<float*> res, sres;
     // device tables and their host mirrors
     std::vector<QTensor> hK1, hK2, hK3;
@@ -312,7 +316,7 @@ int build_tables(qagg_aggregator* a)
                 if (src != r)
                     q2.src[s++] = a->recv_slot(src) + a->tOff[r][i];
             q2.pk[0] = a->gather_slot(r) + a->tOff[r][i];
-            q2.bcast = a->peer ? 1 : 0; // also into slot r of every peer's gather buffer
+            q2.bcast = (a->peer && !a->pushGather) ? 1 : 0; // also into slot r of every peer's gather buffer
             q2.bcastOff = a->tOff[r][i];
             const int e = (int) a->hK2.size();
             a->hK2.push_back(q2);
@@ -430,6 +434,16 @@ int launch_k1(qagg_aggregator* a, cudaStream_t st)
 int launch_k2(qagg_aggregator* a, cudaStream_t st)
 {
     const Signal sg = make_signal(a, true);
+    if (a->peer && a->pushGather)
+    {
+        int rc = check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg,
+                                            static_cast<unsigned*>(a->queue.p) + QAGG_COUNTER_UINTS, nullptr), "reduce-requantize launch");
+        if (rc)
+            return rc;
+        const int r = a->comm->rank;
+        return check_cuda(launch_push(st, a->gather_slot(r), (size_t) a->regionBytes[r], sg, static_cast<unsigned*>(a->queue.p) + 3 * QAGG_COUNTER_UINTS,
+                                      a->cfg.numSMs), "gather push launch");
+    }
     return check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg,
                                       static_cast<unsigned*>(a->queue.p) + QAGG_COUNTER_UINTS, &sg), "reduce-requantize launch");
 }
@@ -619,6 +633,8 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
     a->mode = mode_of(bits, flags & QAGG_ZERO_THRESHOLD);
     const int K = comm->K, r = comm->rank;
     a->identity = (K == 1) && (flags & QAGG_V2_IDENTITY_K1);
+    if (const char* e = std::getenv("QAGG_PUSH_GATHER")) // tuning knob: 0 = requantize kernel stores to the peers itself
+        a->pushGather = (e[0] != '0');
     rc = check_cuda(get_launch_cfg(comm->device, &a->cfg), "cudaGetDeviceProperties");
     if (rc)
         return rc;
@@ -674,7 +690,7 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
         return rc;
     if ((rc = a->tables.alloc(table_bytes(a.get()), true)))
         return rc;
-    if ((rc = a->queue.alloc(3 * QAGG_COUNTER_UINTS * sizeof(unsigned), true)))
+    if ((rc = a->queue.alloc(4 * QAGG_COUNTER_UINTS * sizeof(unsigned), true)))
         return rc;
     *out = a.release();
     return QAGG_OK;
@@ -1092,7 +1108,9 @@ int qagg_agg_launches_per_step(const qagg_aggregator* a)
         return fail(QAGG_EINVAL, "null aggregator");
     if (a->identity || a->totalValues == 0)
         return 0;
-    return (a->comm->K > 1 && !a->iK2.empty()) ? 3 : 2;
+    if (a->comm->K == 1)
+        return 2;
+    return 3 + (a->peer ? 2 + (a->pushGather ? 1 : 0) : 0); // + two flag waits (+ the gather push) in peer mode
 }
 
 int qagg_agg_destroy(qagg_aggregator* a)

@@ -89,6 +89,8 @@ int cols_per_item(long long M, long long N, int smemFloats, bool* resident);
 cudaError_t launch_colquant(cudaStream_t st, bool stripes, int mode, const QTensor* single, const QTensor* tensors,
                             const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters = nullptr,
                             const Signal* signal = nullptr);
+// copies `bytes` (rounded up to 16) from local `src` to the same offset of every signal.bcastBase[], then releases signal.flag[]
+cudaError_t launch_push(cudaStream_t st, const void* src, size_t bytes, const Signal& signal, unsigned* counters, int numSMs);
 // one warp polls flags[i] (i < n, i != skip) until each is >= value (wrap-safe) or maxPolls polls have passed; on
 // give-up it ORs 1 into *status and returns: the context stays usable and the host reads the status later
 cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status);

@@ -1262,6 +1262,43 @@ __global__ void k_signal_only(const Signal signal)
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
 }
 
+// Broadcast of a finished region: every CTA copies 16-byte words from local memory into the same offset of each
+// destination (peer gather slots), then the last CTA releases the flags (same hand-shake as at the end of k_colquant).
+__global__ void __launch_bounds__(256) k_push(const uint4* __restrict__ src, size_t n16, const Signal signal, unsigned* __restrict__ counters)
+{
+    for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t) gridDim.x * blockDim.x)
+    {
+        const uint4 v = __ldg(src + i);
+        for (int b = 0; b < signal.nbcast; ++b)
+            reinterpret_cast<uint4*>(signal.bcastBase[b])[i] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        __threadfence_system();
+        const unsigned done = atomicAdd(&counters[1], 1u);
+        if (done == gridDim.x - 1)
+        {
+            counters[1] = 0;
+            __threadfence_system();
+            for (int i = 0; i < signal.n; ++i)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
+        }
+    }
+}
+
+cudaError_t launch_push(cudaStream_t st, const void* src, size_t bytes, const Signal& signal, unsigned* counters, int numSMs)
+{
+    const size_t n16 = (bytes + 15) / 16;
+    int grid = (int) ((n16 + 255) / 256);
+    if (grid > numSMs)
+        grid = numSMs;
+    if (grid < 1)
+        grid = 1;
+    k_push<<<grid, 256, 0, st>>>(static_cast<const uint4*>(src), n16, signal, counters);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status)
 {
     if (n > 32)
