@@ -257,7 +257,14 @@ def run_ours(args):
     t_step = float(tt[0])
     phases = [float(x) for x in tt[1:]]
 
-    # end to end through the host-buffer entry point: pinned host gradients in, aggregated gradients back out
+    # end to end through the host-buffer entry point: pinned host gradients in, aggregated gradients back out, chunks of
+    # tensors pipelined over streams inside the library (upload / kernels / download of different chunks overlap)
+    hagg = lib.HostAggregator(comm, shapes, bits, chunks=args.e2e_chunks)
+    if K > 1 and exchange.startswith("peer"):
+        mine = torch.frombuffer(bytearray(hagg.peer_handles()), dtype=torch.uint8).to(dev)
+        allh = [torch.zeros_like(mine) for _ in range(K)]
+        dist.all_gather(allh, mine)
+        hagg.enable_peer([bytes(h.cpu().numpy().tobytes()) for h in allh])
     hpool = [torch.empty((n, m), dtype=torch.float32).normal_(0, 1e-3).pin_memory() for (m, n) in shapes]
     hgrads = [torch.empty((n, m), dtype=torch.float32).pin_memory() for (m, n) in shapes]
     hptrs = [h.data_ptr() for h in hgrads]
@@ -269,7 +276,7 @@ def run_ours(args):
         barrier()
         torch.cuda.synchronize()
         t1 = time.perf_counter()
-        agg.step_host(hptrs, stream)  # returns after the results are back in host memory
+        hagg.step(hptrs)  # returns after the results are back in host memory
         dt = time.perf_counter() - t1
         if s >= 2:
             e2e_t.append(dt)
@@ -279,6 +286,10 @@ def run_ours(args):
     if K > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_ms = float(te[0])
+    hagg.check()
+    e2e_launches = e2e_steps * hagg.chunks * agg.launches_per_step
+    barrier()
+    hagg.destroy()
 
     if rank == 0:
         peak, peak_kind = load_peaks()
@@ -305,8 +316,9 @@ def run_ours(args):
             "wire": {"bytes_per_step_per_gpu_each_way": agg.wire_bytes,
                      "nvlink_frac_of_770GBs": (agg.wire_bytes / ((phases[1] + phases[3]) * 1e-3) / 770e9) if K > 1 and (phases[1] + phases[3]) > 0 else None},
             "e2e": {"value": 4.0 * V * K / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": 4 * V, "d2h_bytes_per_step": 4 * V, "steps": e2e_steps},
-            "gpu_launches": agg.launches_per_step * args.steps,
+                    "h2d_bytes_per_step": 4 * V, "d2h_bytes_per_step": 4 * V, "steps": e2e_steps,
+                    "chunks": args.e2e_chunks, "api": "qagg_hagg_step (pinned host buffers, chunk-pipelined)"},
+            "gpu_launches": agg.launches_per_step * args.steps, "gpu_launches_e2e": e2e_launches,
             "clocks": clocks, "wall_ms_per_step_including_refresh": wall / args.steps * 1e3,
         }
         if K == 1 and not args.no_cpu_baseline:
@@ -329,6 +341,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="speech_dnn", choices=["speech_dnn", "resnet50", "lstm_lm", "round_trip_2048"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=6, help="tensor chunks pipelined by the host-buffer entry point")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="multi-GPU transport of the packed stripes")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -1030,6 +1030,197 @@ int qagg_agg_step_host(qagg_aggregator* a, float* const* host_grads, void* strea
     return check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
 }
 
+// =====================================================================================================================
+// Host-buffer aggregator: the same step for callers whose gradients live in host memory.  A tensor's aggregate depends
+// on that tensor only, so the gradient set is cut into chunks of consecutive tensors, each with its own aggregator, and
+// the chunks are software-pipelined over a few streams: while chunk c computes, chunk c+1 uploads and chunk c-1
+// downloads (PCIe is full duplex).  With more than one rank the chunks overlap only in peer mode (each chunk has its
+// own window and flags); on the NCCL path they run one after the other on a single stream, because one communicator
+// must see its collectives in one order.
+// =====================================================================================================================
+struct qagg_host_aggregator
+{
+    qagg_comm* comm = nullptr;
+    int T = 0;
+    std::vector<qagg_aggregator*> kids;
+    std::vector<int> first;   // first tensor of each chunk; first[chunks] == T
+    std::vector<int64_t> elems; // elements per tensor
+    std::vector<cudaStream_t> streams;
+    std::vector<DevBuf> dev;  // one device gradient buffer per chunk
+    std::vector<std::vector<float*>> devPtr;
+    std::vector<int> order;   // chunks in the order they are issued: largest first, so that the longest upload is not
+                              // left without anything to overlap with
+    bool peer = false;
+    ~qagg_host_aggregator()
+    {
+        for (auto* k : kids)
+            qagg_agg_destroy(k);
+        for (auto s : streams)
+            cudaStreamDestroy(s);
+    }
+};
+
+int qagg_hagg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, int bits, int flags, int num_chunks,
+                     qagg_host_aggregator** out)
+{
+    if (!comm || !out || num_tensors < 1 || !M || !N || num_chunks < 1)
+        return fail(QAGG_EINVAL, "qagg_hagg_create: bad arguments");
+    int rc = check_cuda(cudaSetDevice(comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    std::unique_ptr<qagg_host_aggregator> h(new qagg_host_aggregator);
+    h->comm = comm;
+    h->T = num_tensors;
+    int64_t total = 0;
+    for (int i = 0; i < num_tensors; ++i)
+    {
+        if (M[i] < 0 || N[i] < 0)
+            return fail(QAGG_EINVAL, "qagg_hagg_create: bad tensor shape");
+        h->elems.push_back(M[i] * N[i]);
+        total += M[i] * N[i];
+    }
+    if (num_chunks > num_tensors)
+        num_chunks = num_tensors;
+    // consecutive tensors, about equal bytes per chunk
+    h->first.push_back(0);
+    int64_t acc = 0;
+    for (int i = 0; i < num_tensors; ++i)
+    {
+        acc += h->elems[i];
+        const int done = (int) h->first.size();
+        if (done < num_chunks && acc * num_chunks >= total * done && i + 1 < num_tensors)
+            h->first.push_back(i + 1);
+    }
+    h->first.push_back(num_tensors);
+    const int chunks = (int) h->first.size() - 1;
+    h->dev.resize(chunks);
+    h->devPtr.resize(chunks);
+    for (int c = 0; c < chunks; ++c)
+    {
+        const int i0 = h->first[c], i1 = h->first[c + 1];
+        qagg_aggregator* kid = nullptr;
+        if ((rc = qagg_agg_create(comm, i1 - i0, M + i0, N + i0, bits, flags, &kid)))
+            return rc;
+        h->kids.push_back(kid);
+        int64_t floats = 0;
+        for (int i = i0; i < i1; ++i)
+            floats += align_up(h->elems[i], 4);
+        if ((rc = h->dev[c].alloc((size_t) floats * 4, false)))
+            return rc;
+        int64_t o = 0;
+        for (int i = i0; i < i1; ++i)
+        {
+            h->devPtr[c].push_back(static_cast<float*>(h->dev[c].p) + o);
+            o += align_up(h->elems[i], 4);
+        }
+    }
+    std::vector<int64_t> chunkElems(chunks, 0);
+    for (int c = 0; c < chunks; ++c)
+        for (int i = h->first[c]; i < h->first[c + 1]; ++i)
+            chunkElems[c] += h->elems[i];
+    for (int c = 0; c < chunks; ++c)
+        h->order.push_back(c);
+    std::stable_sort(h->order.begin(), h->order.end(), [&](int x, int y) { return chunkElems[x] > chunkElems[y]; });
+    const int nStreams = std::min(chunks, 3);
+    for (int s = 0; s < nStreams; ++s)
+    {
+        cudaStream_t st;
+        if ((rc = check_cuda(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking), "cudaStreamCreate")))
+            return rc;
+        h->streams.push_back(st);
+    }
+    *out = h.release();
+    return QAGG_OK;
+}
+
+int qagg_hagg_chunks(const qagg_host_aggregator* h)
+{
+    return h ? (int) h->kids.size() : fail(QAGG_EINVAL, "null host aggregator");
+}
+
+int qagg_hagg_peer_handles(qagg_host_aggregator* h, void* out)
+{
+    if (!h || !out)
+        return fail(QAGG_EINVAL, "qagg_hagg_peer_handles: bad arguments");
+    for (size_t c = 0; c < h->kids.size(); ++c)
+    {
+        int rc = qagg_agg_peer_handle(h->kids[c], static_cast<unsigned char*>(out) + c * QAGG_PEER_HANDLE_BYTES);
+        if (rc)
+            return rc;
+    }
+    return QAGG_OK;
+}
+
+int qagg_hagg_enable_peer(qagg_host_aggregator* h, const void* handles)
+{
+    if (!h || !handles)
+        return fail(QAGG_EINVAL, "qagg_hagg_enable_peer: bad arguments");
+    const int K = h->comm->K;
+    const size_t chunks = h->kids.size();
+    std::vector<unsigned char> one((size_t) K * QAGG_PEER_HANDLE_BYTES);
+    for (size_t c = 0; c < chunks; ++c)
+    {
+        for (int p = 0; p < K; ++p) // rank-major input: rank p's handles for chunks 0..chunks-1
+            std::memcpy(one.data() + (size_t) p * QAGG_PEER_HANDLE_BYTES,
+                        static_cast<const unsigned char*>(handles) + ((size_t) p * chunks + c) * QAGG_PEER_HANDLE_BYTES, QAGG_PEER_HANDLE_BYTES);
+        int rc = qagg_agg_enable_peer(h->kids[c], one.data());
+        if (rc)
+            return rc;
+    }
+    h->peer = true;
+    return QAGG_OK;
+}
+
+int qagg_hagg_step(qagg_host_aggregator* h, float* const* host_grads)
+{
+    if (!h || !host_grads)
+        return fail(QAGG_EINVAL, "qagg_hagg_step: bad arguments");
+    int rc = check_cuda(cudaSetDevice(h->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    const bool overlap = (h->comm->K == 1) || h->peer;
+    const size_t chunks = h->kids.size();
+    for (size_t k = 0; k < chunks; ++k)
+    {
+        const int c = h->order[k];
+        cudaStream_t st = h->streams[overlap ? k % h->streams.size() : 0];
+        const int i0 = h->first[c], i1 = h->first[c + 1];
+        for (int i = i0; i < i1; ++i)
+            if (h->elems[i] && (rc = check_cuda(cudaMemcpyAsync(h->devPtr[c][i - i0], host_grads[i], (size_t) h->elems[i] * 4, cudaMemcpyHostToDevice, st),
+                                                "gradient upload")))
+                return rc;
+        if ((rc = qagg_agg_step(h->kids[c], h->devPtr[c].data(), st)))
+            return rc;
+        for (int i = i0; i < i1; ++i)
+            if (h->elems[i] && (rc = check_cuda(cudaMemcpyAsync(host_grads[i], h->devPtr[c][i - i0], (size_t) h->elems[i] * 4, cudaMemcpyDeviceToHost, st),
+                                                "gradient download")))
+                return rc;
+    }
+    for (auto st : h->streams)
+        if ((rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize")))
+            return rc;
+    return QAGG_OK;
+}
+
+int qagg_hagg_check(qagg_host_aggregator* h)
+{
+    if (!h)
+        return fail(QAGG_EINVAL, "null host aggregator");
+    for (auto* k : h->kids)
+    {
+        int rc = qagg_agg_check(k, nullptr);
+        if (rc)
+            return rc;
+    }
+    return QAGG_OK;
+}
+
+int qagg_hagg_destroy(qagg_host_aggregator* h)
+{
+    delete h;
+    return QAGG_OK;
+}
+
 int qagg_agg_reset_residuals(qagg_aggregator* a, void* stream)
 {
     if (!a)

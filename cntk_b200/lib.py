@@ -23,7 +23,8 @@ EXPORTS = [
     "qagg_comm_destroy", "qagg_agg_create", "qagg_agg_step", "qagg_agg_step_group", "qagg_agg_step_host",
     "qagg_agg_reset_residuals", "qagg_agg_residuals", "qagg_agg_copy_residual", "qagg_agg_copy_packed", "qagg_agg_wire_bytes",
     "qagg_agg_launches_per_step", "qagg_agg_peer_handle", "qagg_agg_enable_peer", "qagg_agg_set_wait_limit", "qagg_agg_check", "qagg_wait_flags",
-    "qagg_agg_set_profiling", "qagg_agg_phase_ms", "qagg_agg_destroy",
+    "qagg_hagg_create", "qagg_hagg_chunks", "qagg_hagg_peer_handles", "qagg_hagg_enable_peer", "qagg_hagg_step", "qagg_hagg_check",
+    "qagg_hagg_destroy", "qagg_agg_set_profiling", "qagg_agg_phase_ms", "qagg_agg_destroy",
 ]
 
 
@@ -82,6 +83,13 @@ _lib.qagg_agg_enable_peer.argtypes = [c_vp, c_vp]
 _lib.qagg_agg_set_wait_limit.argtypes = [c_vp, ctypes.c_longlong]
 _lib.qagg_agg_check.argtypes = [c_vp, c_vp]
 _lib.qagg_wait_flags.argtypes = [c_vp, c_vp, c_int, c_int, ctypes.c_uint, ctypes.c_longlong, c_vp]
+_lib.qagg_hagg_create.argtypes = [c_vp, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, c_int, c_int, ctypes.POINTER(c_vp)]
+_lib.qagg_hagg_chunks.argtypes = [c_vp]
+_lib.qagg_hagg_peer_handles.argtypes = [c_vp, c_vp]
+_lib.qagg_hagg_enable_peer.argtypes = [c_vp, c_vp]
+_lib.qagg_hagg_step.argtypes = [c_vp, ctypes.POINTER(c_vp)]
+_lib.qagg_hagg_check.argtypes = [c_vp]
+_lib.qagg_hagg_destroy.argtypes = [c_vp]
 _lib.qagg_agg_set_profiling.argtypes = [c_vp, c_int]
 _lib.qagg_agg_phase_ms.argtypes = [c_vp, ctypes.POINTER(ctypes.c_float)]
 _lib.qagg_agg_destroy.argtypes = [c_vp]
@@ -309,6 +317,39 @@ class Aggregator:
     def destroy(self):
         if self.h:
             _ok(_lib.qagg_agg_destroy(self.h))
+            self.h = None
+
+
+class HostAggregator:
+    """qagg_host_aggregator: aggregation of gradients held in host memory, chunk-pipelined over PCIe."""
+
+    def __init__(self, comm, shapes, bits, flags=ZERO_THRESHOLD | SELF_QUANTIZED, chunks=6):
+        T = len(shapes)
+        Ms = (c_i64 * T)(*[s[0] for s in shapes])
+        Ns = (c_i64 * T)(*[s[1] for s in shapes])
+        h = c_vp()
+        _ok(_lib.qagg_hagg_create(comm.h, T, Ms, Ns, bits, flags, chunks, ctypes.byref(h)))
+        self.h, self.T = h, T
+        self.chunks = int(_lib.qagg_hagg_chunks(h))
+
+    def peer_handles(self):
+        buf = ctypes.create_string_buffer(PEER_HANDLE_BYTES * self.chunks)
+        _ok(_lib.qagg_hagg_peer_handles(self.h, buf))
+        return buf.raw
+
+    def enable_peer(self, handles_per_rank):
+        blob = b"".join(handles_per_rank)
+        _ok(_lib.qagg_hagg_enable_peer(self.h, ctypes.create_string_buffer(blob, len(blob))))
+
+    def step(self, host_grad_ptrs):
+        _ok(_lib.qagg_hagg_step(self.h, (c_vp * len(host_grad_ptrs))(*[c_vp(p) for p in host_grad_ptrs])))
+
+    def check(self):
+        _ok(_lib.qagg_hagg_check(self.h))
+
+    def destroy(self):
+        if self.h:
+            _ok(_lib.qagg_hagg_destroy(self.h))
             self.h = None
 
 

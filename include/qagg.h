@@ -48,6 +48,7 @@ extern "C" {
 typedef struct qagg_comm qagg_comm;
 typedef struct qagg_aggregator qagg_aggregator;
 typedef struct qagg_plan qagg_plan;
+typedef struct qagg_host_aggregator qagg_host_aggregator;
 
 /* Last error message of the calling thread ("" if none). */
 const char* qagg_last_error(void);
@@ -176,6 +177,24 @@ int qagg_agg_copy_residual(qagg_aggregator* a, int tensor, int which, float* dst
 /* Copy the gathered packed matrix of tensor i (what every rank unquantized from in the last step) into a device
  * buffer of qagg_packed_bytes(M[i], N[i], bits), in the reference's contiguous layout. */
 int qagg_agg_copy_packed(qagg_aggregator* a, int tensor, void* dst_dev, void* stream);
+/* ---- aggregation from host buffers, software-pipelined ---------------------------------------------------------------
+ * For gradients that live in (pinned) host memory -- the situation of the reference's CPU-device runs and of its GPU runs'
+ * packed buffers, which always cross PCIe (Source/Math/MatrixQuantizerGPU.cu:126-142, 313-324).  The gradient set is cut
+ * into `num_chunks` runs of consecutive tensors with about equal bytes; each chunk is uploaded, aggregated and downloaded on
+ * its own stream so that the upload of one chunk, the kernels of another and the download of a third overlap.
+ * qagg_hagg_step returns when all results are back in host_grads.  Residuals live inside the object.
+ * Peer mode: qagg_hagg_peer_handles writes chunks * QAGG_PEER_HANDLE_BYTES bytes; qagg_hagg_enable_peer takes the
+ * handles of all ranks, rank-major (K * chunks * QAGG_PEER_HANDLE_BYTES bytes).  Without peer mode and with more than one
+ * rank the chunks run one after the other (one NCCL communicator needs one order of collectives). */
+int qagg_hagg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, int bits, int flags, int num_chunks,
+                     qagg_host_aggregator** out);
+int qagg_hagg_chunks(const qagg_host_aggregator* h);
+int qagg_hagg_peer_handles(qagg_host_aggregator* h, void* out);
+int qagg_hagg_enable_peer(qagg_host_aggregator* h, const void* handles);
+int qagg_hagg_step(qagg_host_aggregator* h, float* const* host_grads);
+int qagg_hagg_check(qagg_host_aggregator* h);
+int qagg_hagg_destroy(qagg_host_aggregator* h);
+
 /* ---- peer-memory exchange (optional; replaces the two NCCL collectives of a step) ------------------------------------
  * Where the reference moves every stripe GPU -> pinned host -> MPI -> pinned host -> GPU (Source/Math/MatrixQuantizerGPU.cu:126-142,
  * 313-324; Source/1BitSGD/AllReduceDistGradAggregator.h:303-365, 459-502), the quantize kernel here stores each packed

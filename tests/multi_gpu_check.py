@@ -76,6 +76,25 @@ def main():
         agg.check()
         dist.barrier()  # nobody unmaps a window that a peer may still be writing to
         agg.destroy()
+    # host-buffer aggregator, chunks pipelined over streams, peer-memory exchange per chunk
+    hagg = lib.HostAggregator(comm, SHAPES, 1, chunks=3)
+    mine = torch.frombuffer(bytearray(hagg.peer_handles()), dtype=torch.uint8).to(dev)
+    allh = [torch.zeros_like(mine) for _ in range(K)]
+    dist.all_gather(allh, mine)
+    hagg.enable_peer([bytes(h.cpu().numpy().tobytes()) for h in allh])
+    st = exchange.ExchangeState(SHAPES, K)
+    host = [torch.empty((N, M), dtype=torch.float32).pin_memory() for (M, N) in SHAPES]
+    for step in range(3):
+        grads = inputs(K, step)
+        for t, a in zip(host, grads[rank]):
+            t.copy_(torch.from_numpy(a))
+        exchange.aggregate_step(be, st, grads, 1)
+        hagg.step([t.data_ptr() for t in host])
+        for i in range(len(SHAPES)):
+            assert np.array_equal(host[i].numpy().view(np.uint32), grads[rank][i].view(np.uint32)), f"host aggregator: step {step} rank {rank} tensor {i}"
+    hagg.check()
+    dist.barrier()
+    hagg.destroy()
     dist.barrier()
     comm.destroy()
     dist.destroy_process_group()

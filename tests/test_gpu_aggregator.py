@@ -88,6 +88,31 @@ def test_peer_memory_exchange_speech_shaped(G, oracle_port):
     run_group(G, oracle_port, SPEECH_SMALL, 4, 1, True, True, 12, speech_inputs, check_every=6, peer=True)
 
 
+@pytest.mark.parametrize("chunks", [1, 3, 16])
+def test_host_buffer_aggregator_pipelined(G, oracle_port, chunks):
+    """qagg_hagg_*: gradients in pinned host memory, chunks of tensors pipelined over streams; one rank (V1 round trip).
+    Results and the carried residuals (three steps) must equal the oracle's bit for bit, whatever the chunking."""
+    from cntk_b200 import lib
+    comm = lib.Comm.create(None, 0, 1, 0)
+    h = lib.HostAggregator(comm, SPEECH_SMALL, 1, chunks=chunks)
+    assert 1 <= h.chunks <= min(chunks, len(SPEECH_SMALL))
+    st = ox.ExchangeState(SPEECH_SMALL, 1)
+    host = [torch.empty((N, M), dtype=torch.float32).pin_memory() for (M, N) in SPEECH_SMALL]
+    try:
+        for step in range(3):
+            grads = speech_inputs(1, step)
+            for t, a in zip(host, grads[0]):
+                t.copy_(torch.from_numpy(a))
+            ox.aggregate_step(oracle_port, st, grads, 1)
+            h.step([t.data_ptr() for t in host])
+            for i in range(len(SPEECH_SMALL)):
+                G.assert_same_bits(host[i].numpy(), grads[0][i], f"chunks {chunks} step {step} tensor {i}")
+        h.check()
+    finally:
+        h.destroy()
+        comm.destroy()
+
+
 def test_bounded_wait_gives_up_and_reports(G):
     """Failure detection without a GPU fault: a wait on a flag that nothing sets runs out of polls, records it in the
     status word and returns; the context stays usable and a later wait on flags that ARE set passes."""
