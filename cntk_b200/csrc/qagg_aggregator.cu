@@ -215,14 +215,15 @@ void make_items(std::vector<QItem>& items, int tensor, int64_t M, int64_t N, int
 // would not even fill the resident CTA slots once, halve the item of the matrix whose items are the most expensive
 // (rows x columns): a tall column's ordered walk is a fixed latency, so fewer columns per item shortens the launch
 // when there are CTA slots to spare.
-std::vector<int> choose_cols(const std::vector<std::pair<int64_t, int64_t>>& shapes, const LaunchCfg& cfg)
+std::vector<int> choose_cols(const std::vector<std::pair<int64_t, int64_t>>& shapes, const LaunchCfg& cfg, int bits = 1, int packedSources = 0)
 {
     std::vector<int> c(shapes.size(), 1);
     auto items = [&](size_t i) { return shapes[i].second > 0 ? (shapes[i].second + c[i] - 1) / c[i] : 0; };
     int64_t total = 0;
     for (size_t i = 0; i < shapes.size(); ++i)
     {
-        c[i] = cols_per_item(shapes[i].first, shapes[i].second, cfg.smemFloats, nullptr);
+        const int colWords = 2 + (int) ((shapes[i].first * bits + 31) / 32);
+        c[i] = cols_per_item(shapes[i].first, shapes[i].second, cfg.smemFloats, nullptr, packedSources * colWords);
         total += items(i);
     }
     const int64_t slots = (int64_t) cfg.numSMs * cfg.ctasPerSM;

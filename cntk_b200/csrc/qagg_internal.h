@@ -79,7 +79,9 @@ struct LaunchCfg
 
 // cols per work item for a matrix of M rows under a given shared-memory budget; *resident tells whether whole
 // columns fit (else the kernel streams the column through shared memory in chunks and reads its inputs twice)
-int cols_per_item(long long M, long long N, int smemFloats, bool* resident);
+// extraFloatsPerCol: further shared memory a column needs (the reduce kernel stages its K packed source columns:
+// K * colBytes / 4)
+int cols_per_item(long long M, long long N, int smemFloats, bool* resident, int extraFloatsPerCol = 0);
 
 // launchers (qagg_kernels.cu).  `single` != nullptr: one matrix described by value, items derived from the block index.
 // otherwise `tensors`/`items` are device tables.

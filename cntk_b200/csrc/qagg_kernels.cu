@@ -418,20 +418,24 @@ __device__ __forceinline__ void fill_dense(const QTensor& T, int col0, int nc, i
     }
 }
 
-// thread <-> (column, packed word): the K sources are added in index order, the raw own stripe (if used) first, the
-// stripe residual LAST (the reference unquantizes with add = true K-1 times and only then quantizes against the residual,
-// AllReduceDistGradAggregator.h:366-375, 405-435).  The residual is fetched into the column slots by cp.async while the
-// sum of the stripes is built in registers, so no load of this phase waits on another.
+// The K sources are added in index order, the raw own stripe (if used) first, the stripe residual LAST (the reference
+// unquantizes with add = true K-1 times and only then quantizes against the residual, AllReduceDistGradAggregator.h:366-375,
+// 405-435).  `pks` is shared-memory staging for the item's packed columns (nsrc x nc x (colBytes / 4) words), or null
+// when that does not fit: then headers and words are read from global memory.
 template <int MODE>
-__device__ __forceinline__ void fill_stripes(const QTensor& T, int col0, int nc, int stride, float* __restrict__ smem, const ColStats& S)
+__device__ __forceinline__ void fill_stripes(const QTensor& T, int col0, int nc, int stride, float* __restrict__ smem, const ColStats& S,
+                                             unsigned* __restrict__ pks)
 {
     const int M = (int) T.M;
     const int Q = T.Q;
     const int bits = T.bits;
     const int vpw = 32 / bits;
     const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
+    const int colWords = T.colBytes >> 2; // header (2 words) + Q packed words
     const float* __restrict__ r0 = T.res_in + (size_t) col0 * M;
     const bool async = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(r0) & 15) == 0);
+    // 1. everything this item reads goes into flight at once: the stripe residual (16-byte copies into the column slots)
+    //    and the item's packed columns of all K sources (4-byte copies: packed columns are only 4-byte aligned)
     if (async)
     {
         const int M4 = M >> 2;
@@ -443,95 +447,116 @@ __device__ __forceinline__ void fill_stripes(const QTensor& T, int col0, int nc,
             const unsigned dst = (unsigned) __cvta_generic_to_shared(smem + (size_t) col * stride + 4 * r4);
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(reinterpret_cast<const float4*>(r0) + idx) : "memory");
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    const int total = nc * Q;
+    if (pks)
     {
-        for (int idx0 = 0; idx0 < total; idx0 += NT) // same trip count for every thread: the barrier below is safe
+        const int perSrc = nc * colWords;
+        const int totalW = T.nsrc * perSrc;
+        for (int idx = threadIdx.x; idx < totalW; idx += NT)
         {
-            const int idx = idx0 + threadIdx.x;
-            const bool live = idx < total;
-            const int col = live ? idx / Q : 0;
-            const int w = live ? idx - col * Q : 0;
-            const int j = col0 + col;
-            const int nk = live ? min(vpw, (M - w + Q - 1) / Q) : 0; // rows w, w+Q, ... below M
-            float agg[32];
+            const int s = idx / perSrc;
+            const int rem = idx - s * perSrc;
+            if (s == 0 && T.selfRaw)
+                continue;
+            const unsigned* src = reinterpret_cast<const unsigned*>(T.src[s] + (size_t) col0 * T.colBytes) + rem;
+            const unsigned dst = (unsigned) __cvta_generic_to_shared(pks + idx);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    bool landed = false;
+    if (pks)
+    {
+        // the sums below read the staged packed columns: everything must have landed first
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        landed = true;
+    }
+
+    // 2. thread <-> (column, packed word): sum of the K sources in registers, in index order, then the residual.
+    //    Every thread runs the same number of trips, so the barrier inside the loop is safe.
+    const int total = nc * Q;
+    for (int idx0 = 0; idx0 < total; idx0 += NT)
+    {
+        const int idx = idx0 + threadIdx.x;
+        const bool live = idx < total;
+        const int col = live ? idx / Q : 0;
+        const int w = live ? idx - col * Q : 0;
+        const int j = col0 + col;
+        const int nk = live ? min(vpw, (M - w + Q - 1) / Q) : 0; // rows w, w+Q, ... below M
+        float agg[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+            agg[k] = 0.0f;
+        bool first = true;
+        if (live && T.selfRaw)
+        {
+            const float* __restrict__ gcol = T.grad + (size_t) j * M + w;
 #pragma unroll
             for (int k = 0; k < 32; ++k)
-                agg[k] = 0.0f;
-            bool first = true;
-            if (live && T.selfRaw)
+                if (k < nk)
+                    agg[k] = gcol[k * Q];
+            first = false;
+        }
+        for (int s = T.selfRaw ? 1 : 0; live && s < T.nsrc; ++s)
+        {
+            const unsigned* colp = pks ? pks + ((size_t) s * nc + col) * colWords
+                                       : reinterpret_cast<const unsigned*>(T.src[s] + (size_t) j * T.colBytes);
+            const ValQ q = make_valq(bits, __uint_as_float(colp[0]), __uint_as_float(colp[1]));
+            const unsigned word = colp[2 + w];
+            if (bits == 1)
             {
-                const float* __restrict__ gcol = T.grad + (size_t) j * M + w;
-#pragma unroll
-                for (int k = 0; k < 32; ++k)
-                    if (k < nk)
-                        agg[k] = gcol[k * Q];
-                first = false;
-            }
-            if (live)
-            {
-                for (int s = T.selfRaw ? 1 : 0; s < T.nsrc; ++s)
-                {
-                    const unsigned char* colp = T.src[s] + (size_t) j * T.colBytes;
-                    const ValQ q = make_valq(bits, reinterpret_cast<const float*>(colp)[0], reinterpret_cast<const float*>(colp)[1]);
-                    const unsigned word = reinterpret_cast<const unsigned*>(colp + 8)[w];
-                    if (bits == 1)
-                    {
-                        const float val0 = unquantize_val(q, 1, 0u);
-                        const float val1 = unquantize_val(q, 1, 1u);
-#pragma unroll
-                        for (int k = 0; k < 32; ++k)
-                        {
-                            const float val = ((word >> k) & 1u) ? val1 : val0;
-                            agg[k] = first ? val : __fadd_rn(val, agg[k]);
-                        }
-                    }
-                    else
-                    {
-#pragma unroll
-                        for (int k = 0; k < 16; ++k)
-                        {
-                            if (k < vpw)
-                            {
-                                const float val = unquantize_val(q, bits, (word >> (k * bits)) & mask);
-                                agg[k] = first ? val : __fadd_rn(val, agg[k]);
-                            }
-                        }
-                    }
-                    first = false;
-                }
-            }
-            if (async && idx0 == 0)
-            {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-                __syncthreads(); // every thread's share of the residual is in shared memory
-            }
-            if (live)
-            {
-                float* __restrict__ vcol = smem + (size_t) col * stride + w;
-                const float* __restrict__ rcol = T.res_in + (size_t) j * M + w;
-                unsigned cnt = 0;
+                const float val0 = unquantize_val(q, 1, 0u);
+                const float val1 = unquantize_val(q, 1, 1u);
 #pragma unroll
                 for (int k = 0; k < 32; ++k)
                 {
-                    if (k < nk)
+                    const float val = ((word >> k) & 1u) ? val1 : val0;
+                    agg[k] = first ? val : __fadd_rn(val, agg[k]);
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int k = 0; k < 16; ++k)
+                {
+                    if (k < vpw)
                     {
-                        const float r = async ? vcol[k * Q] : rcol[k * Q];
-                        const float v = __fadd_rn(agg[k], r);
-                        vcol[k * Q] = v;
-                        if (MODE == MODE_ONEBIT_ZERO)
-                        {
-                            cnt += (v < 0.0f);
-                            if (v != v)
-                                S.nan[col] = 1u;
-                        }
+                        const float val = unquantize_val(q, bits, (word >> (k * bits)) & mask);
+                        agg[k] = first ? val : __fadd_rn(val, agg[k]);
                     }
                 }
-                if (MODE == MODE_ONEBIT_ZERO && cnt)
-                    atomicAdd(&S.n0[col], cnt);
+            }
+            first = false;
+        }
+        if (!landed)
+        {
+            // the residual copies were in flight while the first sums were built from global memory
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+            landed = true;
+        }
+        float* __restrict__ vcol = smem + (size_t) col * stride + w;
+        const float* __restrict__ rcol = T.res_in + (size_t) j * M + w;
+        unsigned cnt = 0;
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+        {
+            if (k < nk)
+            {
+                const float r = async ? vcol[k * Q] : rcol[k * Q];
+                const float v = __fadd_rn(agg[k], r);
+                vcol[k * Q] = v;
+                if (MODE == MODE_ONEBIT_ZERO)
+                {
+                    cnt += (v < 0.0f);
+                    if (v != v)
+                        S.nan[col] = 1u;
+                }
             }
         }
+        if (MODE == MODE_ONEBIT_ZERO && cnt)
+            atomicAdd(&S.n0[col], cnt);
     }
 }
 
@@ -835,8 +860,14 @@ __global__ void __launch_bounds__(NT, 3) k_colquant(const QTensor single, const 
             if (threadIdx.x == 0)
                 sT = single;
         }
-        const int strideGuess = smem_stride(TABLE ? tensors[items[it].tensor].M : single.M);
+        const QTensor* gT = TABLE ? (tensors + items[it].tensor) : &single;
+        const int strideGuess = smem_stride(gT->M);
+        // floats of shared memory per column: staged values + per-column scratch (+ the K packed source columns)
+        const int extraPerCol = STRIPES ? gT->nsrc * (gT->colBytes >> 2) : 0;
         const bool resident = ((long long) nc * (strideGuess + COLSTAT_FLOATS) <= (long long) smemFloats);
+        // the K packed source columns are staged in shared memory too when that fits next to the values; else the reduce
+        // kernel reads them from global memory
+        const bool stagePacked = STRIPES && ((long long) nc * (strideGuess + COLSTAT_FLOATS + extraPerCol) <= (long long) smemFloats);
         // per-column scratch sits behind the staged values (resident) or behind the chunk ring (streamed)
         ColStats S;
         {
@@ -861,7 +892,8 @@ __global__ void __launch_bounds__(NT, 3) k_colquant(const QTensor single, const 
         {
             PROBE_MARK(t0);
             if (STRIPES)
-                fill_stripes<MODE>(T, col0, nc, stride, smem, S);
+                fill_stripes<MODE>(T, col0, nc, stride, smem, S,
+                                   stagePacked ? reinterpret_cast<unsigned*>(smem + (size_t) nc * (stride + COLSTAT_FLOATS)) : nullptr);
             else
                 fill_dense<MODE>(T, col0, nc, stride, smem, S);
             __syncthreads();
@@ -1205,10 +1237,10 @@ __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, cons
 
 // ---- host side ------------------------------------------------------------------------------------------------
 
-int cols_per_item(long long M, long long N, int smemFloats, bool* resident)
+int cols_per_item(long long M, long long N, int smemFloats, bool* resident, int extraFloatsPerCol)
 {
     const int stride = smem_stride(M);
-    long long c = smemFloats / (stride + COLSTAT_FLOATS);
+    long long c = smemFloats / (stride + COLSTAT_FLOATS + extraFloatsPerCol);
     bool res = true;
     if (c < 1)
     {
