@@ -150,7 +150,7 @@ struct qagg_aggregator
     long long waitPolls = 20000000; // bounded device-side waits (about two seconds of polling)
     // peer mode, all-gather half: true = the requantize kernel writes locally and a small copy kernel pushes the finished
     // region to the peers; false = the requantize kernel itself stores every packed word K times
-    bool pushGather = true;
+    bool pushGather = false;
     std::vector<float*> res, sres;
     // device tables and their host mirrors
     std::vector<QTensor> hK1, hK2, hK3;

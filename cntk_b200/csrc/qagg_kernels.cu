@@ -71,6 +71,17 @@ __device__ __forceinline__ float unquantize_val(const ValQ& q, int bits, unsigne
     return __fadd_rn(__fmul_rn(__fadd_rn((float) u, 0.5f), q.ufactor), q.qmin);
 }
 
+// The two reconstruction values of a 1-bit column, Unquantize(0) and Unquantize(1) (ValueQuantizer.h:131-141 with
+// Nbits = 1): there rangeend = usedrangeend = 2, so ufactor = (upper - lower) / 2.  Halving a normal float is exact
+// (the range is at least 1e-36 here), so the divide is replaced by a multiplication by 0.5 with the same result.
+__device__ __forceinline__ void levels_1bit(float lower, float upper, float& val0, float& val1)
+{
+    const float range = __fsub_rn(upper, lower);
+    const float ufactor = (range < 1e-36f) ? 0.0f : __fmul_rn(0.5f, range);
+    val0 = __fadd_rn(__fmul_rn(0.5f, ufactor), lower);
+    val1 = __fadd_rn(__fmul_rn(1.5f, ufactor), lower);
+}
+
 __device__ __forceinline__ unsigned quantize_multibit(const ValQ& q, int bits, float v)
 {
     if (bits == 32)
@@ -473,27 +484,34 @@ __device__ __forceinline__ void fill_stripes(const QTensor& T, int col0, int nc,
         landed = true;
     }
 
-    // 2. thread <-> (column, packed word): sum of the K sources in registers, in index order, then the residual.
-    //    Every thread runs the same number of trips, so the barrier inside the loop is safe.
-    const int total = nc * Q;
+    // 2. thread <-> (column, packed word, half of the word's bit positions): sum of the K sources in registers, in
+    //    index order, then the residual.  Splitting a word's positions over two threads doubles the number of tasks, which
+    //    matters for tall columns (a 9304-row column has only 291 words for 256 threads).  Every thread runs the same
+    //    number of trips, so the barrier inside the loop is safe.
+    const int H = (bits == 1) ? 2 : 1;     // tasks per word
+    const int KH = 32 / H;                 // bit positions (of the 1-bit layout) per task; multi-bit: all vpw <= 16 in one
+    const int total = nc * Q * H;
     for (int idx0 = 0; idx0 < total; idx0 += NT)
     {
         const int idx = idx0 + threadIdx.x;
         const bool live = idx < total;
-        const int col = live ? idx / Q : 0;
-        const int w = live ? idx - col * Q : 0;
+        const int cw = live ? idx / H : 0;
+        const int kLo = live ? (idx - cw * H) * KH : 0;
+        const int col = cw / Q;
+        const int w = cw - col * Q;
         const int j = col0 + col;
-        const int nk = live ? min(vpw, (M - w + Q - 1) / Q) : 0; // rows w, w+Q, ... below M
-        float agg[32];
+        const int nkAll = live ? min(vpw, (M - w + Q - 1) / Q) : 0; // rows w, w+Q, ... below M
+        const int nk = max(0, min(nkAll - kLo, KH));               // this task's share: positions kLo .. kLo + nk - 1
+        float agg[16];
 #pragma unroll
-        for (int k = 0; k < 32; ++k)
+        for (int k = 0; k < 16; ++k)
             agg[k] = 0.0f;
         bool first = true;
         if (live && T.selfRaw)
         {
-            const float* __restrict__ gcol = T.grad + (size_t) j * M + w;
+            const float* __restrict__ gcol = T.grad + (size_t) j * M + w + (size_t) kLo * Q;
 #pragma unroll
-            for (int k = 0; k < 32; ++k)
+            for (int k = 0; k < 16; ++k)
                 if (k < nk)
                     agg[k] = gcol[k * Q];
             first = false;
@@ -502,21 +520,22 @@ __device__ __forceinline__ void fill_stripes(const QTensor& T, int col0, int nc,
         {
             const unsigned* colp = pks ? pks + ((size_t) s * nc + col) * colWords
                                        : reinterpret_cast<const unsigned*>(T.src[s] + (size_t) j * T.colBytes);
-            const ValQ q = make_valq(bits, __uint_as_float(colp[0]), __uint_as_float(colp[1]));
             const unsigned word = colp[2 + w];
             if (bits == 1)
             {
-                const float val0 = unquantize_val(q, 1, 0u);
-                const float val1 = unquantize_val(q, 1, 1u);
+                float val0, val1;
+                levels_1bit(__uint_as_float(colp[0]), __uint_as_float(colp[1]), val0, val1);
+                const unsigned part = word >> kLo;
 #pragma unroll
-                for (int k = 0; k < 32; ++k)
+                for (int k = 0; k < 16; ++k)
                 {
-                    const float val = ((word >> k) & 1u) ? val1 : val0;
+                    const float val = ((part >> k) & 1u) ? val1 : val0;
                     agg[k] = first ? val : __fadd_rn(val, agg[k]);
                 }
             }
             else
             {
+                const ValQ q = make_valq(bits, __uint_as_float(colp[0]), __uint_as_float(colp[1]));
 #pragma unroll
                 for (int k = 0; k < 16; ++k)
                 {
@@ -536,11 +555,11 @@ __device__ __forceinline__ void fill_stripes(const QTensor& T, int col0, int nc,
             __syncthreads();
             landed = true;
         }
-        float* __restrict__ vcol = smem + (size_t) col * stride + w;
-        const float* __restrict__ rcol = T.res_in + (size_t) j * M + w;
+        float* __restrict__ vcol = smem + (size_t) col * stride + w + (size_t) kLo * Q;
+        const float* __restrict__ rcol = T.res_in + (size_t) j * M + w + (size_t) kLo * Q;
         unsigned cnt = 0;
 #pragma unroll
-        for (int k = 0; k < 32; ++k)
+        for (int k = 0; k < 16; ++k)
         {
             if (k < nk)
             {
@@ -711,8 +730,15 @@ __device__ __forceinline__ void quantize_resident(const QTensor& T, const Signal
             const int w = (t - col * Q4) * 4;
             const int j = col0 + col;
             const float lower = S.lower[col], upper = S.upper[col];
-            const ValQ q = make_valq(bits, lower, upper);
-            const float val0 = unquantize_val(q, 1, 0u), val1 = unquantize_val(q, 1, 1u);
+            ValQ q;
+            float val0 = 0.0f, val1 = 0.0f;
+            if (MODE == MODE_MULTIBIT)
+                q = make_valq(bits, lower, upper);
+            else
+            {
+                q.qmid = __fmul_rn(0.5f, __fadd_rn(upper, lower));
+                levels_1bit(lower, upper, val0, val1);
+            }
             const float* __restrict__ vp = smem + (size_t) col * stride + w;
             float* __restrict__ rp = T.res_out + (size_t) j * M + w;
             const int nk = min(vpw, (M - w + Q - 1) / Q);
@@ -742,8 +768,15 @@ __device__ __forceinline__ void quantize_resident(const QTensor& T, const Signal
             const int w = t - col * Q;
             const int j = col0 + col;
             const float lower = S.lower[col], upper = S.upper[col];
-            const ValQ q = make_valq(bits, lower, upper);
-            const float val0 = unquantize_val(q, 1, 0u), val1 = unquantize_val(q, 1, 1u);
+            ValQ q;
+            float val0 = 0.0f, val1 = 0.0f;
+            if (MODE == MODE_MULTIBIT)
+                q = make_valq(bits, lower, upper);
+            else
+            {
+                q.qmid = __fmul_rn(0.5f, __fadd_rn(upper, lower));
+                levels_1bit(lower, upper, val0, val1);
+            }
             const float* __restrict__ vp = smem + (size_t) col * stride + w;
             float* __restrict__ rp = T.res_out + (size_t) j * M + w;
             const int nk = min(vpw, (M - w + Q - 1) / Q);
@@ -1043,14 +1076,13 @@ __device__ __forceinline__ void store_out4(float* p, float4 v)
 // the two constants unquantizing needs: 1 bit -> the two level values; else -> (ufactor, quantimin)
 __device__ __forceinline__ void unq_consts(int bits, float lower, float upper, float& ca, float& cb)
 {
-    const ValQ q = make_valq(bits, lower, upper);
     if (bits == 1)
     {
-        ca = unquantize_val(q, 1, 0u);
-        cb = unquantize_val(q, 1, 1u);
+        levels_1bit(lower, upper, ca, cb);
     }
     else
     {
+        const ValQ q = make_valq(bits, lower, upper);
         ca = q.ufactor;
         cb = q.qmin;
     }
