@@ -50,6 +50,7 @@ int check_nccl(ncclResult_t r, const char* what)
 struct DevBuf
 {
     void* p = nullptr;
+    size_t bytes = 0;
     ~DevBuf()
     {
         if (p)
@@ -59,6 +60,7 @@ struct DevBuf
     {
         if (bytes == 0)
             bytes = 16;
+        this->bytes = bytes;
         int rc = check_cuda(cudaMalloc(&p, bytes), "cudaMalloc");
         if (rc)
             return rc;
@@ -152,6 +154,11 @@ struct qagg_aggregator
     // region to the peers; false = the requantize kernel itself stores every packed word K times
     bool pushGather = false;
     std::vector<float*> res, sres;
+    // 1 bit with threshold 0 runs the streaming kernels, which keep both residual sets in deferred form: the buffers above
+    // hold the quantized values v, and lv / slv each column's two reconstruction values (see qagg_internal.h)
+    bool deferred = false;
+    DevBuf lvAll, slvAll;
+    std::vector<float*> lv, slv;
     // device tables and their host mirrors
     std::vector<QTensor> hK1, hK2, hK3;
     std::vector<QItem> iK1, iK2, iK3;
@@ -268,6 +275,7 @@ int build_tables(qagg_aggregator* a)
         shapes2.push_back({a->M[i], (live && K > 1) ? a->sN[r][i] : 0});
     }
     const std::vector<int> c1 = choose_cols(shapes1, a->cfg), c2 = choose_cols(shapes2, a->cfg);
+    std::vector<std::pair<long long, long long>> k2Shapes; // streaming kernels: (rows, columns) per entry of the owner table
     for (int i = 0; i < T; ++i)
     {
         const int64_t M = a->M[i], N = a->N[i];
@@ -277,6 +285,7 @@ int build_tables(qagg_aggregator* a)
         fill_layout(&q1, M, N, a->bits);
         q1.res_in = a->res[i];
         q1.res_out = a->res[i];
+        q1.lv = a->deferred ? a->lv[i] : nullptr;
         q1.K = K;
         q1.per = N / K;
         q1.rem = N % K;
@@ -284,6 +293,7 @@ int build_tables(qagg_aggregator* a)
         q3 = q1;
         q3.res_in = nullptr;
         q3.res_out = nullptr;
+        q3.lv = nullptr;
         for (int p = 0; p < K; ++p)
         {
             if (K == 1)
@@ -309,6 +319,7 @@ int build_tables(qagg_aggregator* a)
             fill_layout(&q2, M, a->sN[r][i], a->bits);
             q2.res_in = a->sres[i];
             q2.res_out = a->sres[i];
+            q2.lv = a->deferred ? a->slv[i] : nullptr;
             q2.selfRaw = (a->flags & QAGG_SELF_QUANTIZED) ? 0 : 1;
             q2.nsrc = K;
             q2.src[0] = a->recv_slot(r) + a->tOff[r][i];
@@ -321,6 +332,7 @@ int build_tables(qagg_aggregator* a)
             q2.bcastOff = a->tOff[r][i];
             const int e = (int) a->hK2.size();
             a->hK2.push_back(q2);
+            k2Shapes.push_back({M, q2.N});
             a->k2Tensor.push_back(i);
             std::vector<QItem> tmp;
             make_items(tmp, e, M, q2.N, c2[i]);
@@ -336,6 +348,15 @@ int build_tables(qagg_aggregator* a)
         a->iK1.push_back(c.second);
     for (auto& c : cost2)
         a->iK2.push_back(c.second);
+    if (a->deferred)
+    {
+        // the streaming kernels size and order their own work items
+        std::vector<std::pair<long long, long long>> k1Shapes;
+        for (int i = 0; i < T; ++i)
+            k1Shapes.push_back({a->M[i], (a->M[i] > 0 && a->N[i] > 0) ? a->N[i] : 0});
+        stream_make_items(k1Shapes, a->cfg.numSMs, a->bits, 0, a->iK1);
+        stream_make_items(k2Shapes, a->cfg.numSMs, a->bits, (a->flags & QAGG_SELF_QUANTIZED) ? K : K - 1, a->iK2);
+    }
     return QAGG_OK;
 }
 
@@ -429,24 +450,31 @@ Signal make_signal(const qagg_aggregator* a, bool gatherPhase)
 int launch_k1(qagg_aggregator* a, cudaStream_t st)
 {
     const Signal sg = make_signal(a, false);
+    if (a->deferred)
+        return check_cuda(launch_stream1(st, false, a->dK1, a->dI1, (int) a->iK1.size(), a->cfg, static_cast<unsigned*>(a->queue.p), &sg),
+                          "quantize launch");
     return check_cuda(launch_colquant(st, false, a->mode, nullptr, a->dK1, a->dI1, (int) a->iK1.size(), 0, a->cfg,
                                       static_cast<unsigned*>(a->queue.p), &sg), "quantize launch");
 }
 int launch_k2(qagg_aggregator* a, cudaStream_t st)
 {
     const Signal sg = make_signal(a, true);
+    unsigned* q2 = static_cast<unsigned*>(a->queue.p) + QAGG_COUNTER_UINTS;
     if (a->peer && a->pushGather)
     {
-        int rc = check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg,
-                                            static_cast<unsigned*>(a->queue.p) + QAGG_COUNTER_UINTS, nullptr), "reduce-requantize launch");
+        int rc = check_cuda(a->deferred ? launch_stream1(st, true, a->dK2, a->dI2, (int) a->iK2.size(), a->cfg, q2, nullptr)
+                                        : launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg, q2, nullptr),
+                            "reduce-requantize launch");
         if (rc)
             return rc;
         const int r = a->comm->rank;
         return check_cuda(launch_push(st, a->gather_slot(r), (size_t) a->regionBytes[r], sg, static_cast<unsigned*>(a->queue.p) + 3 * QAGG_COUNTER_UINTS,
                                       a->cfg.numSMs), "gather push launch");
     }
-    return check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg,
-                                      static_cast<unsigned*>(a->queue.p) + QAGG_COUNTER_UINTS, &sg), "reduce-requantize launch");
+    if (a->deferred)
+        return check_cuda(launch_stream1(st, true, a->dK2, a->dI2, (int) a->iK2.size(), a->cfg, q2, &sg), "reduce-requantize launch");
+    return check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg, q2, &sg),
+                      "reduce-requantize launch");
 }
 int wait_peers(qagg_aggregator* a, bool gatherPhase, cudaStream_t st)
 {
@@ -636,6 +664,15 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
     a->identity = (K == 1) && (flags & QAGG_V2_IDENTITY_K1);
     if (const char* e = std::getenv("QAGG_PUSH_GATHER")) // tuning knob: 0 = requantize kernel stores to the peers itself
         a->pushGather = (e[0] != '0');
+    // 1 bit, threshold 0: streaming kernels with deferred residuals, unless a column is too tall for them
+    // (QAGG_STREAM=0 keeps the resident-column kernels, for comparison)
+    a->deferred = (a->mode == MODE_ONEBIT_ZERO);
+    for (int i = 0; i < num_tensors; ++i)
+        if (M[i] > 0 && N[i] > 0 && stream_max_cols((M[i] * bits + 31) / 32) < 1)
+            a->deferred = false;
+    if (const char* e = std::getenv("QAGG_STREAM"))
+        if (e[0] == '0')
+            a->deferred = false;
     rc = check_cuda(get_launch_cfg(comm->device, &a->cfg), "cudaGetDeviceProperties");
     if (rc)
         return rc;
@@ -679,13 +716,35 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
         return rc;
     a->res.resize(num_tensors);
     a->sres.resize(num_tensors);
-    int64_t ro = 0, so = 0;
+    a->lv.assign(num_tensors, nullptr);
+    a->slv.assign(num_tensors, nullptr);
+    if (a->deferred)
+    {
+        int64_t cols = 0, scols = 0;
+        for (int i = 0; i < num_tensors; ++i)
+        {
+            cols += N[i];
+            scols += a->sN[r][i];
+        }
+        if ((rc = a->lvAll.alloc((size_t) cols * 8, true)))
+            return rc;
+        if ((rc = a->slvAll.alloc((size_t) scols * 8, true)))
+            return rc;
+    }
+    int64_t ro = 0, so = 0, lo = 0, slo = 0;
     for (int i = 0; i < num_tensors; ++i)
     {
         a->res[i] = static_cast<float*>(a->resAll.p) + ro;
         ro += align_up(M[i] * N[i], 4);
         a->sres[i] = (a->sN[r][i] > 0 && K > 1) ? static_cast<float*>(a->sresAll.p) + so : nullptr;
         so += align_up(M[i] * a->sN[r][i], 4);
+        if (a->deferred)
+        {
+            a->lv[i] = static_cast<float*>(a->lvAll.p) + lo;
+            a->slv[i] = static_cast<float*>(a->slvAll.p) + slo;
+            lo += 2 * N[i];
+            slo += 2 * a->sN[r][i];
+        }
     }
     if ((rc = build_tables(a.get())))
         return rc;
@@ -1237,6 +1296,14 @@ int qagg_agg_reset_residuals(qagg_aggregator* a, void* stream)
     int rc = check_cuda(cudaMemsetAsync(a->resAll.p, 0, (size_t) std::max<int64_t>(resFloats, 1) * 4, st), "cudaMemsetAsync");
     if (rc)
         return rc;
+    if (a->deferred)
+    {
+        // an all-zero deferred state is a zero residual
+        if ((rc = check_cuda(cudaMemsetAsync(a->lvAll.p, 0, a->lvAll.bytes, st), "cudaMemsetAsync")))
+            return rc;
+        if ((rc = check_cuda(cudaMemsetAsync(a->slvAll.p, 0, a->slvAll.bytes, st), "cudaMemsetAsync")))
+            return rc;
+    }
     return check_cuda(cudaMemsetAsync(a->sresAll.p, 0, (size_t) std::max<int64_t>(sresFloats, 1) * 4, st), "cudaMemsetAsync");
 }
 
@@ -1244,6 +1311,27 @@ int qagg_agg_residuals(qagg_aggregator* a, int tensor, float** residual, float**
 {
     if (!a || tensor < 0 || tensor >= a->T)
         return fail(QAGG_EINVAL, "qagg_agg_residuals: bad arguments");
+    if (a->deferred)
+    {
+        // turn this tensor's deferred state into plain residuals in place (with zero reconstruction values the state means
+        // the same), so that the caller sees residuals; runs on the default stream and waits
+        const int r = a->comm->rank;
+        int rc = check_cuda(launch_materialize(nullptr, a->res[tensor], a->lv[tensor], a->res[tensor], a->M[tensor], a->N[tensor], a->cfg.numSMs),
+                            "residual export");
+        if (!rc && a->N[tensor] > 0)
+            rc = check_cuda(cudaMemsetAsync(a->lv[tensor], 0, (size_t) a->N[tensor] * 8, nullptr), "cudaMemsetAsync");
+        if (!rc && a->sres[tensor])
+        {
+            rc = check_cuda(launch_materialize(nullptr, a->sres[tensor], a->slv[tensor], a->sres[tensor], a->M[tensor], a->sN[r][tensor], a->cfg.numSMs),
+                            "residual export");
+            if (!rc)
+                rc = check_cuda(cudaMemsetAsync(a->slv[tensor], 0, (size_t) a->sN[r][tensor] * 8, nullptr), "cudaMemsetAsync");
+        }
+        if (!rc)
+            rc = check_cuda(cudaStreamSynchronize(nullptr), "cudaStreamSynchronize");
+        if (rc)
+            return rc;
+    }
     if (residual)
         *residual = a->res[tensor];
     if (stripe_residual)
@@ -1260,6 +1348,9 @@ int qagg_agg_copy_residual(qagg_aggregator* a, int tensor, int which, float* dst
     const int64_t n = a->M[tensor] * (which ? a->sN[r][tensor] : a->N[tensor]);
     if (n == 0 || !src)
         return QAGG_OK;
+    if (a->deferred)
+        return check_cuda(launch_materialize((cudaStream_t) stream, src, which ? a->slv[tensor] : a->lv[tensor], dst_dev, a->M[tensor],
+                                             which ? a->sN[r][tensor] : a->N[tensor], a->cfg.numSMs), "residual export");
     return check_cuda(cudaMemcpyAsync(dst_dev, src, (size_t) n * 4, cudaMemcpyDeviceToDevice, (cudaStream_t) stream), "residual copy");
 }
 

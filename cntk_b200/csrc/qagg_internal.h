@@ -5,6 +5,8 @@
 #include <stdint.h>
 
 #include <string>
+#include <utility>
+#include <vector>
 
 #define QAGG_MAXK 16 // most ranks in one group (one 8-GPU box needs 8)
 #define QAGG_COUNTER_UINTS 272
@@ -34,6 +36,8 @@ struct QTensor
     int bcast;                           // 1 = every packed column is also written to the launch's broadcast bases
     int pad_;
     long long bcastOff;                  // offset of this matrix's block from a broadcast base (K == 1 routing only)
+    float* lv;                           // streaming kernel only: the two reconstruction values of each column's previous
+                                         // quantization (2 floats per column), read at the start and rewritten at the end
 };
 
 // Flags that the last CTA of a kernel writes (release, system scope) after all of the kernel's stores: one word in each
@@ -99,6 +103,36 @@ cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int
 cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, const QTensor* tensors,
                               const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters = nullptr);
 cudaError_t get_launch_cfg(int device, LaunchCfg* cfg);
+// releases the flags of `signal` from a one-thread kernel (a rank with nothing to compute still has to tell its peers)
+cudaError_t launch_signal_only(cudaStream_t st, const Signal& signal);
+
+// ---- streaming kernel for 1 bit with threshold 0 (qagg_stream.cu) --------------------------------------------------
+// It keeps the error-feedback state of a matrix in DEFERRED form: the buffer holds v (the value that was quantized:
+// gradient + residual) and `lv` holds each column's two reconstruction values; the residual proper,
+// v - (v >= 0 ? lv[1] : lv[0]), is formed with the same single subtraction when the state is next read.  All-zero
+// buffers are a zero residual.  Columns stream through shared memory in row chunks, so column height is limited only
+// by the shared-memory copy of a work item's packed words: nc * Q <= QAGG_STREAM_PKWORDS.
+#define QAGG_STREAM_PKWORDS 4096
+#define QAGG_STREAM_CMAX 32
+// most columns per work item for columns of Q packed words (0: the column is too tall for this kernel); the owner
+// kernel also stages the item's columns of its `packedSources` packed inputs, header included
+inline int stream_max_cols(long long Q, int packedSources = 0)
+{
+    if (Q <= 0)
+        return QAGG_STREAM_CMAX;
+    const long long c = QAGG_STREAM_PKWORDS / (Q + (long long) packedSources * (Q + 2));
+    return (int) (c > QAGG_STREAM_CMAX ? QAGG_STREAM_CMAX : c);
+}
+// Work items of one launch of the streaming kernel, in queue order.  shapes[t] = (rows, columns) of table entry t.
+// Items are sized for about (all values) / (3 x resident CTAs) values each, ordered longest first; the items in the last
+// quarter of the queue are cut into four, so that the launch ends with short items and all CTAs finish together.
+void stream_make_items(const std::vector<std::pair<long long, long long>>& shapes, int numSMs, int bits, int packedSources,
+                       std::vector<QItem>& out);
+// always table-driven with a work queue (`counters` as for launch_colquant, required)
+cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors, const QItem* items, int nItems,
+                           const LaunchCfg& cfg, unsigned* counters, const Signal* signal = nullptr);
+// dst[i, j] = buf[i, j] - (buf[i, j] >= 0 ? lv[2j + 1] : lv[2j]): the residual proper of a deferred state (dst may be buf)
+cudaError_t launch_materialize(cudaStream_t st, const float* buf, const float* lv, float* dst, long long M, long long N, int numSMs);
 int unq_cols_per_item(long long M);
 
 // error plumbing (qagg_capi.cu)
