@@ -154,9 +154,11 @@ struct qagg_aggregator
     // region to the peers; false = the requantize kernel itself stores every packed word K times
     bool pushGather = false;
     std::vector<float*> res, sres;
-    // 1 bit with threshold 0 runs the streaming kernels, which keep both residual sets in deferred form: the buffers above
-    // hold the quantized values v, and lv / slv each column's two reconstruction values (see qagg_internal.h)
-    bool deferred = false;
+    // 1 bit with threshold 0: the quantize kernel (and optionally the owner's reduce-requantize kernel) is the streaming
+    // kernel, which keeps its residual set in deferred form: the buffer above holds the quantized values v, and lv (slv)
+    // each column's two reconstruction values (see qagg_internal.h)
+    bool deferred = false;      // quantize kernel: residuals `res`
+    bool deferredOwner = false; // owner kernel: stripe residuals `sres`
     DevBuf lvAll, slvAll;
     std::vector<float*> lv, slv;
     // device tables and their host mirrors
@@ -319,7 +321,7 @@ int build_tables(qagg_aggregator* a)
             fill_layout(&q2, M, a->sN[r][i], a->bits);
             q2.res_in = a->sres[i];
             q2.res_out = a->sres[i];
-            q2.lv = a->deferred ? a->slv[i] : nullptr;
+            q2.lv = a->deferredOwner ? a->slv[i] : nullptr;
             q2.selfRaw = (a->flags & QAGG_SELF_QUANTIZED) ? 0 : 1;
             q2.nsrc = K;
             q2.src[0] = a->recv_slot(r) + a->tOff[r][i];
@@ -355,7 +357,8 @@ int build_tables(qagg_aggregator* a)
         for (int i = 0; i < T; ++i)
             k1Shapes.push_back({a->M[i], (a->M[i] > 0 && a->N[i] > 0) ? a->N[i] : 0});
         stream_make_items(k1Shapes, a->cfg.numSMs, a->bits, 0, a->iK1);
-        stream_make_items(k2Shapes, a->cfg.numSMs, a->bits, (a->flags & QAGG_SELF_QUANTIZED) ? K : K - 1, a->iK2);
+        if (a->deferredOwner)
+            stream_make_items(k2Shapes, a->cfg.numSMs, a->bits, (a->flags & QAGG_SELF_QUANTIZED) ? K : K - 1, a->iK2);
     }
     return QAGG_OK;
 }
@@ -451,7 +454,7 @@ int launch_k1(qagg_aggregator* a, cudaStream_t st)
 {
     const Signal sg = make_signal(a, false);
     if (a->deferred)
-        return check_cuda(launch_stream1(st, false, a->dK1, a->dI1, (int) a->iK1.size(), a->cfg, static_cast<unsigned*>(a->queue.p), &sg),
+        return check_cuda(launch_stream1(st, false, a->dK1, a->dI1, (int) a->iK1.size(), a->cfg, static_cast<unsigned*>(a->queue.p), &sg, a->status_word()),
                           "quantize launch");
     return check_cuda(launch_colquant(st, false, a->mode, nullptr, a->dK1, a->dI1, (int) a->iK1.size(), 0, a->cfg,
                                       static_cast<unsigned*>(a->queue.p), &sg), "quantize launch");
@@ -462,7 +465,7 @@ int launch_k2(qagg_aggregator* a, cudaStream_t st)
     unsigned* q2 = static_cast<unsigned*>(a->queue.p) + QAGG_COUNTER_UINTS;
     if (a->peer && a->pushGather)
     {
-        int rc = check_cuda(a->deferred ? launch_stream1(st, true, a->dK2, a->dI2, (int) a->iK2.size(), a->cfg, q2, nullptr)
+        int rc = check_cuda(a->deferredOwner ? launch_stream1(st, true, a->dK2, a->dI2, (int) a->iK2.size(), a->cfg, q2, nullptr, a->status_word())
                                         : launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg, q2, nullptr),
                             "reduce-requantize launch");
         if (rc)
@@ -471,8 +474,8 @@ int launch_k2(qagg_aggregator* a, cudaStream_t st)
         return check_cuda(launch_push(st, a->gather_slot(r), (size_t) a->regionBytes[r], sg, static_cast<unsigned*>(a->queue.p) + 3 * QAGG_COUNTER_UINTS,
                                       a->cfg.numSMs), "gather push launch");
     }
-    if (a->deferred)
-        return check_cuda(launch_stream1(st, true, a->dK2, a->dI2, (int) a->iK2.size(), a->cfg, q2, &sg), "reduce-requantize launch");
+    if (a->deferredOwner)
+        return check_cuda(launch_stream1(st, true, a->dK2, a->dI2, (int) a->iK2.size(), a->cfg, q2, &sg, a->status_word()), "reduce-requantize launch");
     return check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg, q2, &sg),
                       "reduce-requantize launch");
 }
@@ -664,15 +667,19 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
     a->identity = (K == 1) && (flags & QAGG_V2_IDENTITY_K1);
     if (const char* e = std::getenv("QAGG_PUSH_GATHER")) // tuning knob: 0 = requantize kernel stores to the peers itself
         a->pushGather = (e[0] != '0');
-    // 1 bit, threshold 0: streaming kernels with deferred residuals, unless a column is too tall for them
-    // (QAGG_STREAM=0 keeps the resident-column kernels, for comparison)
+    // 1 bit, threshold 0: the quantize kernel streams with a deferred residual, unless a column is too tall for that.
+    // Tuning knob QAGG_STREAM: 0 = resident-column kernels only, 1 = quantize kernel streams (default), 2 = the owner's
+    // reduce-requantize kernel streams too (it is the slower of the two owner kernels on the shapes measured so far).
     a->deferred = (a->mode == MODE_ONEBIT_ZERO);
     for (int i = 0; i < num_tensors; ++i)
         if (M[i] > 0 && N[i] > 0 && stream_max_cols((M[i] * bits + 31) / 32) < 1)
             a->deferred = false;
     if (const char* e = std::getenv("QAGG_STREAM"))
+    {
         if (e[0] == '0')
             a->deferred = false;
+        a->deferredOwner = a->deferred && (e[0] == '2');
+    }
     rc = check_cuda(get_launch_cfg(comm->device, &a->cfg), "cudaGetDeviceProperties");
     if (rc)
         return rc;
@@ -1040,6 +1047,8 @@ int qagg_agg_check(qagg_aggregator* a, void* stream)
         return rc;
     if (st & 1u)
         return fail(QAGG_ETIMEOUT, "a device-side wait for a peer's flag ran out: a peer did not reach the step (results of that step are invalid)");
+    if (st & 2u)
+        return fail(QAGG_ETIMEOUT, "a device-side wait for a copy into shared memory ran out (results of that step are invalid)");
     return QAGG_OK;
 }
 
@@ -1320,7 +1329,7 @@ int qagg_agg_residuals(qagg_aggregator* a, int tensor, float** residual, float**
                             "residual export");
         if (!rc && a->N[tensor] > 0)
             rc = check_cuda(cudaMemsetAsync(a->lv[tensor], 0, (size_t) a->N[tensor] * 8, nullptr), "cudaMemsetAsync");
-        if (!rc && a->sres[tensor])
+        if (!rc && a->sres[tensor] && a->deferredOwner)
         {
             rc = check_cuda(launch_materialize(nullptr, a->sres[tensor], a->slv[tensor], a->sres[tensor], a->M[tensor], a->sN[r][tensor], a->cfg.numSMs),
                             "residual export");
@@ -1348,7 +1357,7 @@ int qagg_agg_copy_residual(qagg_aggregator* a, int tensor, int which, float* dst
     const int64_t n = a->M[tensor] * (which ? a->sN[r][tensor] : a->N[tensor]);
     if (n == 0 || !src)
         return QAGG_OK;
-    if (a->deferred)
+    if (which ? a->deferredOwner : a->deferred)
         return check_cuda(launch_materialize((cudaStream_t) stream, src, which ? a->slv[tensor] : a->lv[tensor], dst_dev, a->M[tensor],
                                              which ? a->sN[r][tensor] : a->N[tensor], a->cfg.numSMs), "residual export");
     return check_cuda(cudaMemcpyAsync(dst_dev, src, (size_t) n * 4, cudaMemcpyDeviceToDevice, (cudaStream_t) stream), "residual copy");

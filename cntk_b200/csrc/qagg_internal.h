@@ -112,7 +112,7 @@ cudaError_t launch_signal_only(cudaStream_t st, const Signal& signal);
 // v - (v >= 0 ? lv[1] : lv[0]), is formed with the same single subtraction when the state is next read.  All-zero
 // buffers are a zero residual.  Columns stream through shared memory in row chunks, so column height is limited only
 // by the shared-memory copy of a work item's packed words: nc * Q <= QAGG_STREAM_PKWORDS.
-#define QAGG_STREAM_PKWORDS 4096
+#define QAGG_STREAM_PKWORDS 3968
 #define QAGG_STREAM_CMAX 32
 // most columns per work item for columns of Q packed words (0: the column is too tall for this kernel); the owner
 // kernel also stages the item's columns of its `packedSources` packed inputs, header included
@@ -128,9 +128,10 @@ inline int stream_max_cols(long long Q, int packedSources = 0)
 // quarter of the queue are cut into four, so that the launch ends with short items and all CTAs finish together.
 void stream_make_items(const std::vector<std::pair<long long, long long>>& shapes, int numSMs, int bits, int packedSources,
                        std::vector<QItem>& out);
-// always table-driven with a work queue (`counters` as for launch_colquant, required)
+// always table-driven with a work queue (`counters` as for launch_colquant, required).  The kernel's waits for copies in
+// flight are bounded: if one runs out, bit 1 of *status is set and the kernel ends normally (results invalid)
 cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors, const QItem* items, int nItems,
-                           const LaunchCfg& cfg, unsigned* counters, const Signal* signal = nullptr);
+                           const LaunchCfg& cfg, unsigned* counters, const Signal* signal = nullptr, unsigned* status = nullptr);
 // dst[i, j] = buf[i, j] - (buf[i, j] >= 0 ? lv[2j + 1] : lv[2j]): the residual proper of a deferred state (dst may be buf)
 cudaError_t launch_materialize(cudaStream_t st, const float* buf, const float* lv, float* dst, long long M, long long N, int numSMs);
 int unq_cols_per_item(long long M);

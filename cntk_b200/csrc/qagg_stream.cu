@@ -10,15 +10,21 @@
 // to stay resident: columns stream through shared memory in row chunks, every input and output crosses HBM once, and
 // the number of add chains in flight is no longer tied to the column height.
 //
-// One work item = nc <= 32 adjacent columns of one matrix, processed in chunks of R rows (nc * R <= 1536 values):
-//   * six "element" warps copy the chunk's inputs global -> shared with cp.async (two chunks ahead), then form
+// One work item = nc <= 32 adjacent columns of one matrix, processed in chunks of R rows (nc * R <= 1536 values) that
+// pass through a ring of chunk tiles in shared memory.  The CTA's nine warps have three roles:
+//   * one "producer" warp fetches work items from the queue and brings every chunk's inputs global -> shared as bulk
+//     asynchronous copies (one per column segment; an mbarrier per ring slot counts the bytes), as far ahead as the
+//     ring has free slots -- across item boundaries too, so the consumers never wait for a pipeline to refill;
+//   * six "element" warps form
 //       v = gradient + (prev - level(prev))                                   (quantize), or
 //       v = sum over the K packed stripes in source order + (prev - level(prev))   (owner's reduce-requantize),
 //     store v to global memory and to the chunk tile, and OR the bit (v >= 0) into the item's packed words, which
 //     live in shared memory until the item ends;
 //   * two "walker" warps (one per level, lane = column) add min(v, 0) resp. max(v, 0) of the previous chunk to their
-//     running sums, in row order;
+//     running sums, in row order, and hand the tile back to the producer;
 //   * at the end the ranges and the new reconstruction values are derived and the packed columns go to their owners.
+// Every wait on an mbarrier is bounded: if one runs out, the CTA stops waiting altogether, bit 1 of the status word
+// is set and the kernel ends normally (the results of that launch are then invalid).
 #include "qagg_device.cuh"
 
 #include <algorithm>
@@ -38,8 +44,7 @@ constexpr int ST_ETHREADS = NT - 32 * ST_WALK_WARPS; // 192 element threads
 #endif
 constexpr int ST_U = QAGG_ST_U;                      // 16-byte positions per element thread and chunk
 constexpr int ST_TILE_VALUES = 4 * ST_U * ST_ETHREADS; // 1536 values per chunk
-constexpr int ST_STAGES = QAGG_ST_STAGES;                         // chunk tiles in the ring: 1 walked, 1 formed, 2 in flight
-constexpr int ST_DIST = ST_STAGES - 2;               // how many chunks ahead the copies run
+constexpr int ST_STAGES = QAGG_ST_STAGES;            // chunk tiles in the ring: 1 walked, 1 formed, the others in flight
 constexpr int ST_TILE_FLOATS = ST_TILE_VALUES + 4 * QAGG_STREAM_CMAX; // room for the 4-float pad of every column
 constexpr int ST_CTAS_PER_SM = QAGG_ST_CTAS;
 constexpr size_t ST_SMEM_BYTES = (size_t) (2 * ST_STAGES * ST_TILE_FLOATS + QAGG_STREAM_PKWORDS) * 4;
@@ -51,15 +56,65 @@ __device__ __forceinline__ int stream_rows(int nc)
     return ((ST_TILE_VALUES / nc) >> 5) << 5;
 }
 
-__device__ __forceinline__ void cp_async16(float* dstShared, const float* src)
+constexpr int ST_DESC = 4; // work items whose descriptors may be fetched ahead of the consumers
+
+// ---- mbarriers and bulk asynchronous copies (addresses and sizes are multiples of 16 bytes) -----------------------------
+__device__ __forceinline__ unsigned smem_addr(const void* p)
 {
-    const unsigned dst = (unsigned) __cvta_generic_to_shared(dstShared);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    return (unsigned) __cvta_generic_to_shared(p);
 }
-__device__ __forceinline__ void cp_async4(float* dstShared, const float* src)
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count)
 {
-    const unsigned dst = (unsigned) __cvta_generic_to_shared(dstShared);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+// one non-blocking test: has the phase with this parity completed?
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity)
+{
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smem_addr(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// Bounded wait for the phase of `bar` with the given parity to complete.  After ST_WAIT_TRIES tries it gives up: the
+// CTA-wide flag *broken makes every later wait return at once, and bit 1 of *status tells the host.
+constexpr int ST_WAIT_TRIES = 1 << 22;
+__device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity, unsigned* broken, unsigned* status)
+{
+    if (mbar_try_wait(bar, parity))
+        return;
+    if (*reinterpret_cast<volatile unsigned*>(broken))
+        return;
+    // not there yet: poll with the warp asleep in between, so that the waiting costs the other warps no issue slots
+    for (int tries = 0; tries < ST_WAIT_TRIES; ++tries)
+    {
+        __nanosleep(128);
+        if (mbar_try_wait(bar, parity))
+            return;
+    }
+    *reinterpret_cast<volatile unsigned*>(broken) = 1u;
+    if (status)
+        atomicOr(status, 2u);
+}
+__device__ __forceinline__ void bulk_load(float* dstShared, const float* src, unsigned bytes, unsigned long long* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dstShared)), "l"(src),
+                 "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+// barrier of the eight consumer warps (the producer warp does not take part)
+__device__ __forceinline__ void consumer_sync()
+{
+    asm volatile("bar.sync 1, 256;" ::: "memory");
 }
 
 __device__ __forceinline__ float deferred_residual(float prev, float lv0, float lv1)
@@ -68,7 +123,7 @@ __device__ __forceinline__ float deferred_residual(float prev, float lv0, float 
 }
 
 // optional phase timers for development builds (-DQAGG_PROBE; the array is defined in qagg_kernels.cu)
-#ifdef QAGG_PROBE
+#ifdef QAGG_PROBE_PHASES
 #define ST_MARK(var) const long long var = clock64()
 #define ST_ADD(i, a, b)  \
     if (et == 0 && !isWalker) \
@@ -78,11 +133,9 @@ __device__ __forceinline__ float deferred_residual(float prev, float lv0, float 
 #define ST_ADD(i, a, b)
 #endif
 
-static_assert(sizeof(QTensor) % 16 == 0 && sizeof(QTensor) <= 32 * 16, "a warp copies one descriptor with 16-byte cp.async");
-
 template <bool STRIPES>
-__global__ void __launch_bounds__(NT, ST_CTAS_PER_SM) k_stream1(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
-                                                                unsigned* __restrict__ counters, const Signal signal)
+__global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
+                                                                     unsigned* __restrict__ counters, const Signal signal, unsigned* __restrict__ status)
 {
     extern __shared__ __align__(16) float dsm[];
     float* const tileG = dsm;                               // gradient (or raw own stripe), replaced in place by v
@@ -90,11 +143,15 @@ __global__ void __launch_bounds__(NT, ST_CTAS_PER_SM) k_stream1(const QTensor* _
     // the item's packed words (nc x Q), then -- owner kernel -- its packed source columns, headers included
     // ([source][column][2 + Q] words)
     unsigned* const pkw = reinterpret_cast<unsigned*>(dsm + 2 * ST_STAGES * ST_TILE_FLOATS);
-    // descriptor, work item and previous reconstruction values are double-buffered: while one item streams, the next
-    // one's are fetched
-    __shared__ __align__(16) QTensor sT[2];
-    __shared__ QItem sItem[2];
-    __shared__ int sIt[2];
+    // work items in flight: buffer (n % ST_DESC) holds the CTA's n-th item: its queue index (>= nItems: the queue is
+    // empty), the item and its matrix descriptor
+    __shared__ QTensor sT[ST_DESC];
+    __shared__ QItem sItem[ST_DESC];
+    __shared__ int sIt[ST_DESC];
+    // sFull[slot]: the chunk's inputs have landed (producer's arrival + byte count).  sEmpty[slot]: both walkers are done
+    // with the tile.  sMetaFull[b]: buffer b describes the next item.  sMetaEmpty[b]: the consumers are done with it.
+    __shared__ __align__(8) unsigned long long sFull[ST_STAGES], sEmpty[ST_STAGES], sMetaFull[ST_DESC], sMetaEmpty[ST_DESC];
+    __shared__ unsigned sBroken;
     __shared__ int sWalker;
     __shared__ float sLv0[QAGG_STREAM_CMAX], sLv1[QAGG_STREAM_CMAX], sA0[QAGG_STREAM_CMAX], sA1[QAGG_STREAM_CMAX];
     __shared__ float sLower[QAGG_STREAM_CMAX], sUpper[QAGG_STREAM_CMAX];
@@ -118,426 +175,498 @@ __global__ void __launch_bounds__(NT, ST_CTAS_PER_SM) k_stream1(const QTensor* _
         sIt[0] = first;
         if (first < nItems)
             sItem[0] = items[first];
+        for (int i = 0; i < ST_STAGES; ++i)
+        {
+            mbar_init(&sFull[i], 1u);
+            mbar_init(&sEmpty[i], (unsigned) ST_WALK_WARPS);
+        }
+        for (int i = 0; i < ST_DESC; ++i)
+        {
+            mbar_init(&sMetaFull[i], 1u);
+            mbar_init(&sMetaEmpty[i], 1u);
+        }
+        sBroken = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    const int ww = sWalker;
-    const bool isWalker = (warp == ww) || (warp == ww + 1);
-    const int et = ((warp > ww) ? warp - ST_WALK_WARPS : warp) * 32 + lane; // index among the element threads
-    bool more = sIt[0] < nItems;
-    if (more)
+    if (sIt[0] < nItems)
     {
         const int* srcw = reinterpret_cast<const int*>(tensors + sItem[0].tensor);
         int* dstw = reinterpret_cast<int*>(&sT[0]);
-        for (int i = tid; i < (int) (sizeof(QTensor) / sizeof(int)); i += NT)
+        for (int i = tid; i < (int) (sizeof(QTensor) / sizeof(int)); i += NT + 32)
             dstw[i] = srcw[i];
     }
     __syncthreads();
+    if (tid == 0)
+        mbar_arrive(&sMetaFull[0]); // the first item is published like every later one
 
-    // ---- the item being streamed: geometry (uniform) and this thread's positions ----------------------------------------
-    const QTensor* Tp = &sT[0];
-    int M = 1, Q = 1, nc = 1, col0 = 0, R = 32, stride = 36, nchunks = 0;
-    bool hasG = true, vec = false;
-    const float* gbase = nullptr;
-    const float* pbase = nullptr;
-    float* obase = nullptr;
-    unsigned advK = 0, advW = 0;
-    unsigned ring = 0;                  // ring slot of the item's chunk 0
-    float lvReg0 = 0.0f, lvReg1 = 0.0f; // thread c < nc: the previous reconstruction values of column c, loaded ahead
-    // An element thread owns the same ST_U 16-byte positions (column, four rows) of every chunk.  Row i of a column is
-    // bit i / Q of packed word i % Q; the position's (word, bit) pair moves by a fixed step from chunk to chunk.
-    bool pv[ST_U];
-    int sofs[ST_U], pcol[ST_U], prow[ST_U];
-    size_t gofs[ST_U];
-    unsigned pw[ST_U], pk[ST_U], nanf[ST_U];
-
-    // element threads: the inputs of chunk q, 16 bytes per position (4 bytes per value for unaligned matrices)
-    auto issue = [&](int q) {
-        if (q < nchunks)
-        {
-            const int slotOff = (int) ((ring + (unsigned) q) % ST_STAGES) * ST_TILE_FLOATS;
-            const int row0 = q * R;
-#pragma unroll
-            for (int u = 0; u < ST_U; ++u)
-            {
-                const int row = row0 + prow[u];
-                if (!pv[u] || row >= M)
-                    continue;
-                const int so = slotOff + sofs[u];
-                const size_t go = gofs[u] + (size_t) row0;
-                if (vec)
-                {
-                    if (hasG)
-                        cp_async16(tileG + so, gbase + go);
-                    cp_async16(tileP + so, pbase + go);
-                }
-                else
-                {
-                    for (int i = 0; i < 4 && row + i < M; ++i)
-                    {
-                        if (hasG)
-                            cp_async4(tileG + so + i, gbase + go + i);
-                        cp_async4(tileP + so + i, pbase + go + i);
-                    }
-                }
-            }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-
-    // take over the item described by sT[b] / sItem[b] and put its first chunks into flight (every tile must be free of
-    // readers and writers of the generic proxy: call after a barrier that follows the last walk)
-    auto adopt = [&](int b, unsigned chunksBefore) {
-        Tp = &sT[b];
-        const QTensor& T = *Tp;
-        ring = (ring + chunksBefore) % ST_STAGES;
-        M = (int) T.M;
-        Q = T.Q;
-        nc = sItem[b].ncols;
-        col0 = sItem[b].col0;
-        R = stream_rows(nc);
-        stride = R + 4;
-        nchunks = (M + R - 1) / R;
-        hasG = !STRIPES || T.selfRaw;
-        gbase = T.grad;
-        pbase = T.res_in;
-        obase = T.res_out;
-        vec = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(pbase) & 15) == 0) && ((reinterpret_cast<uintptr_t>(obase) & 15) == 0) &&
-              (!hasG || (reinterpret_cast<uintptr_t>(gbase) & 15) == 0);
-        advK = (unsigned) R / (unsigned) Q;
-        advW = (unsigned) R - advK * (unsigned) Q;
-        const int R4 = R >> 2;
-#pragma unroll
-        for (int u = 0; u < ST_U; ++u)
-        {
-            const int f = et + ST_ETHREADS * u;
-            pv[u] = !isWalker && f < nc * R4;
-            const int c = pv[u] ? f / R4 : 0;
-            const int r = pv[u] ? 4 * (f - c * R4) : 0;
-            pcol[u] = c;
-            prow[u] = r;
-            sofs[u] = c * stride + r;
-            gofs[u] = (size_t) (col0 + c) * (size_t) M + (size_t) r;
-            pk[u] = (unsigned) r / (unsigned) Q;
-            pw[u] = (unsigned) r - pk[u] * (unsigned) Q;
-            nanf[u] = 0u;
-        }
-        if (!isWalker)
-            for (int q = 0; q < ST_DIST; ++q)
-                issue(q);
-        if (tid < nc)
-        {
-            lvReg0 = T.lv[2 * (size_t) (col0 + tid)];
-            lvReg1 = T.lv[2 * (size_t) (col0 + tid) + 1];
-        }
-    };
-
-    int par = 0;
-    if (more)
-        adopt(0, 0u);
-
-    while (more)
+    if (warp == NWARPS)
     {
-        ST_MARK(tItem0);
-        const QTensor& T = *Tp;
-        const int nsrc = STRIPES ? T.nsrc : 0;
-        const int firstPacked = hasG ? 1 : 0;      // owner kernel: sources firstPacked .. nsrc - 1 are packed
-        const int colWords = Q + 2;
-        unsigned* const srcw = pkw + nc * Q;       // staged packed sources
-
-        // ---- per-item state --------------------------------------------------------------------------------------------
-        for (int i = tid; i < nc * Q; i += NT)
-            pkw[i] = 0u;
-        if (tid < nc)
+        // =============================================== producer warp ===============================================
+        unsigned pos = 0; // ring position of the current item's chunk 0
+        for (unsigned itemNo = 0;; ++itemNo)
         {
-            sLv0[tid] = lvReg0;
-            sLv1[tid] = lvReg1;
-            sNan[tid] = 0u;
-            sDst[tid] = packed_col(T, col0 + tid);
-        }
-        // owner kernel: the item's columns of every packed source are staged in shared memory when they fit next to the
-        // item's own packed words (one contiguous block of nc * (2 + Q) words per source); else they are read in place
-        const bool staged = STRIPES && (nc * Q + (nsrc - firstPacked) * nc * colWords <= QAGG_STREAM_PKWORDS);
-        if (STRIPES)
-        {
-            if (staged)
-            {
-                const int blockWords = nc * colWords;
-                for (int s = firstPacked; s < nsrc; ++s)
+            const int b = (int) (itemNo % ST_DESC);
+            if (sIt[b] >= nItems || *reinterpret_cast<volatile unsigned*>(&sBroken))
+                break;
+            const QTensor& T = sT[b];
+            const int M = (int) T.M, nc = sItem[b].ncols, col0 = sItem[b].col0;
+            const int R = stream_rows(nc), stride = R + 4, nchunks = (M + R - 1) / R;
+            const bool hasG = !STRIPES || T.selfRaw;
+            const float* const gbase = T.grad;
+            const float* const pbase = T.res_in;
+            const bool vec = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(pbase) & 15) == 0) && ((reinterpret_cast<uintptr_t>(T.res_out) & 15) == 0) &&
+                             (!hasG || (reinterpret_cast<uintptr_t>(gbase) & 15) == 0);
+            int issued = 0;
+            // bring chunks [issued, upto) on their way, each as soon as its ring slot is free
+            auto pump = [&](int upto) {
+                for (; issued < upto; ++issued)
                 {
-                    const unsigned* src = reinterpret_cast<const unsigned*>(T.src[s] + (size_t) col0 * T.colBytes);
-                    unsigned* dst = srcw + (s - firstPacked) * blockWords;
-                    for (int i = tid; i < blockWords; i += NT)
-                        dst[i] = __ldg(src + i);
+                    const unsigned p = pos + (unsigned) issued;
+                    const unsigned slot = p % ST_STAGES;
+                    if (p >= ST_STAGES)
+                        mbar_wait(&sEmpty[slot], ((p / ST_STAGES) - 1u) & 1u, &sBroken, status);
+                    if (*reinterpret_cast<volatile unsigned*>(&sBroken))
+                        return; // a wait ran out: nothing more is put in flight
+                    const int nrows = min(R, M - issued * R);
+                    if (lane == 0)
+                        mbar_arrive_expect_tx(&sFull[slot], (unsigned) ((hasG ? 2 : 1) * nc * nrows * 4));
+                    __syncwarp();
+                    if (lane < nc)
+                    {
+                        const size_t go = (size_t) (col0 + lane) * (size_t) M + (size_t) issued * R;
+                        const int so = (int) slot * ST_TILE_FLOATS + lane * stride;
+                        if (hasG)
+                            bulk_load(tileG + so, gbase + go, (unsigned) nrows * 4u, &sFull[slot]);
+                        bulk_load(tileP + so, pbase + go, (unsigned) nrows * 4u, &sFull[slot]);
+                    }
                 }
-                __syncthreads();
-            }
-            for (int i = tid; i < (nsrc - firstPacked) * nc; i += NT)
+            };
+            if (vec)
+                pump(min(nchunks, 2));
+            // the item after this one: its queue index, the item and its descriptor (this warp may block on global
+            // memory here -- the chunks above keep the consumers busy meanwhile)
             {
-                const int sp = i / nc, c = i - sp * nc;
-                const unsigned* hdr = staged ? srcw + (sp * nc + c) * colWords
-                                             : reinterpret_cast<const unsigned*>(T.src[sp + firstPacked] + (size_t) (col0 + c) * T.colBytes);
-                float v0, v1;
-                levels_1bit(__uint_as_float(hdr[0]), __uint_as_float(hdr[1]), v0, v1);
-                sSrc0[STRIPES ? sp : 0][c] = v0;
-                sSrc1[STRIPES ? sp : 0][c] = v1;
+                const unsigned n1 = itemNo + 1u;
+                const int b1 = (int) (n1 % ST_DESC);
+                if (n1 >= ST_DESC)
+                    mbar_wait(&sMetaEmpty[b1], ((n1 / ST_DESC) - 1u) & 1u, &sBroken, status);
+                int nx = 0;
+                if (lane == 0)
+                    nx = (int) atomicAdd(&counters[0], 1u);
+                nx = __shfl_sync(0xffffffffu, nx, 0);
+                if (lane == 0)
+                    sIt[b1] = nx;
+                if (nx < nItems)
+                {
+                    const int word = (lane < 3) ? reinterpret_cast<const int*>(items + nx)[lane] : 0;
+                    if (lane < 3)
+                        reinterpret_cast<int*>(&sItem[b1])[lane] = word;
+                    const int tIdx = __shfl_sync(0xffffffffu, word, 0);
+                    const int* srcw = reinterpret_cast<const int*>(tensors + tIdx);
+                    int* dstw = reinterpret_cast<int*>(&sT[b1]);
+                    for (int i = lane; i < (int) (sizeof(QTensor) / sizeof(int)); i += 32)
+                        dstw[i] = srcw[i];
+                }
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&sMetaFull[b1]);
+            }
+            if (vec)
+            {
+                pump(nchunks);
+                pos += (unsigned) nchunks;
             }
         }
-        __syncthreads();
+    }
+    else
+    {
+        // ========================================= consumer warps (element + walker) =========================================
+        const int ww = sWalker;
+        const bool isWalker = (warp == ww) || (warp == ww + 1);
+        const int et = ((warp > ww) ? warp - ST_WALK_WARPS : warp) * 32 + lane; // index among the element threads
 
-        auto form = [&](int q) {
-            const int slotOff = (int) ((ring + (unsigned) q) % ST_STAGES) * ST_TILE_FLOATS;
-            const int row0 = q * R;
+        // ---- the item being streamed: geometry (uniform) and this thread's positions ----------------------------------------
+        const QTensor* Tp = &sT[0];
+        int M = 1, Q = 1, nc = 1, col0 = 0, R = 32, stride = 36, nchunks = 0;
+        bool hasG = true, vec = false;
+        const float* gbase = nullptr;
+        const float* pbase = nullptr;
+        float* obase = nullptr;
+        unsigned advK = 0, advW = 0;
+        unsigned pos = 0;                   // ring position of the item's chunk 0
+        float lvReg0 = 0.0f, lvReg1 = 0.0f; // thread c < nc: the previous reconstruction values of column c, loaded ahead
+        // An element thread owns the same ST_U 16-byte positions (column, four rows) of every chunk.  Row i of a column is
+        // bit i / Q of packed word i % Q; the position's (word, bit) pair moves by a fixed step from chunk to chunk.
+        bool pv[ST_U];
+        int sofs[ST_U], pcol[ST_U], prow[ST_U];
+        size_t gofs[ST_U];
+        unsigned pw[ST_U], pk[ST_U], nanf[ST_U];
+
+        // wait for the CTA's n-th item to be described, and take it over unless the queue was empty
+        auto adopt = [&](unsigned n) -> bool {
+            const int b = (int) (n % ST_DESC);
+            mbar_wait(&sMetaFull[b], (n / ST_DESC) & 1u, &sBroken, status);
+            if (sIt[b] >= nItems || *reinterpret_cast<volatile unsigned*>(&sBroken))
+                return false;
+            Tp = &sT[b];
+            const QTensor& T = *Tp;
+            M = (int) T.M;
+            Q = T.Q;
+            nc = sItem[b].ncols;
+            col0 = sItem[b].col0;
+            R = stream_rows(nc);
+            stride = R + 4;
+            nchunks = (M + R - 1) / R;
+            hasG = !STRIPES || T.selfRaw;
+            gbase = T.grad;
+            pbase = T.res_in;
+            obase = T.res_out;
+            vec = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(pbase) & 15) == 0) && ((reinterpret_cast<uintptr_t>(obase) & 15) == 0) &&
+                  (!hasG || (reinterpret_cast<uintptr_t>(gbase) & 15) == 0);
+            advK = (unsigned) R / (unsigned) Q;
+            advW = (unsigned) R - advK * (unsigned) Q;
+            const int R4 = R >> 2;
 #pragma unroll
             for (int u = 0; u < ST_U; ++u)
             {
-                const int row = row0 + prow[u];
-                if (pv[u] && row < M)
+                const int f = et + ST_ETHREADS * u;
+                pv[u] = !isWalker && f < nc * R4;
+                const int c = pv[u] ? f / R4 : 0;
+                const int r = pv[u] ? 4 * (f - c * R4) : 0;
+                pcol[u] = c;
+                prow[u] = r;
+                sofs[u] = c * stride + r;
+                gofs[u] = (size_t) (col0 + c) * (size_t) M + (size_t) r;
+                pk[u] = (unsigned) r / (unsigned) Q;
+                pw[u] = (unsigned) r - pk[u] * (unsigned) Q;
+                nanf[u] = 0u;
+            }
+            if (tid < nc)
+            {
+                lvReg0 = T.lv[2 * (size_t) (col0 + tid)];
+                lvReg1 = T.lv[2 * (size_t) (col0 + tid) + 1];
+            }
+            return true;
+        };
+
+        unsigned itemNo = 0;
+        bool more = adopt(0u);
+        while (more)
+        {
+            ST_MARK(tItem0);
+            const QTensor& T = *Tp;
+            const int nsrc = STRIPES ? T.nsrc : 0;
+            const int firstPacked = hasG ? 1 : 0;      // owner kernel: sources firstPacked .. nsrc - 1 are packed
+            const int colWords = Q + 2;
+            unsigned* const srcw = pkw + nc * Q;       // staged packed sources
+
+            // ---- per-item state ----------------------------------------------------------------------------------------
+            for (int i = tid; i < nc * Q; i += NT)
+                pkw[i] = 0u;
+            if (tid < nc)
+            {
+                sLv0[tid] = lvReg0;
+                sLv1[tid] = lvReg1;
+                sNan[tid] = 0u;
+                sDst[tid] = packed_col(T, col0 + tid);
+            }
+            // owner kernel: the item's columns of every packed source are staged in shared memory when they fit next to
+            // the item's own packed words (one contiguous block of nc * (2 + Q) words per source); else they are read in place
+            const bool staged = STRIPES && (nc * Q + (nsrc - firstPacked) * nc * colWords <= QAGG_STREAM_PKWORDS);
+            if (STRIPES)
+            {
+                if (staged)
                 {
-                    const int c = pcol[u];
-                    const int so = slotOff + sofs[u];
-                    const int nv = vec ? 4 : min(4, M - row);
-                    float prev[4];
-                    float agg[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    const int blockWords = nc * colWords;
+                    for (int s = firstPacked; s < nsrc; ++s)
                     {
-                        const float4 p4 = *reinterpret_cast<const float4*>(tileP + so);
-                        prev[0] = p4.x;
-                        prev[1] = p4.y;
-                        prev[2] = p4.z;
-                        prev[3] = p4.w;
-                        if (hasG)
-                        {
-                            const float4 g4 = *reinterpret_cast<const float4*>(tileG + so);
-                            agg[0] = g4.x;
-                            agg[1] = g4.y;
-                            agg[2] = g4.z;
-                            agg[3] = g4.w;
-                        }
+                        const unsigned* src = reinterpret_cast<const unsigned*>(T.src[s] + (size_t) col0 * T.colBytes);
+                        unsigned* dst = srcw + (s - firstPacked) * blockWords;
+                        for (int i = tid; i < blockWords; i += NT)
+                            dst[i] = __ldg(src + i);
                     }
-                    const float lv0 = sLv0[c], lv1 = sLv1[c];
-                    // the usual case: the four rows are the same bit of four adjacent words
-                    const bool flat = (nv == 4) && (pw[u] + 3u < (unsigned) Q);
-                    if (STRIPES)
-                    {
-                        // (word, bit) of the four rows
-                        unsigned wi[4], ki[4];
+                    consumer_sync();
+                }
+                for (int i = tid; i < (nsrc - firstPacked) * nc; i += NT)
+                {
+                    const int sp = i / nc, c = i - sp * nc;
+                    const unsigned* hdr = staged ? srcw + (sp * nc + c) * colWords
+                                                 : reinterpret_cast<const unsigned*>(T.src[sp + firstPacked] + (size_t) (col0 + c) * T.colBytes);
+                    float v0, v1;
+                    levels_1bit(__uint_as_float(hdr[0]), __uint_as_float(hdr[1]), v0, v1);
+                    sSrc0[STRIPES ? sp : 0][c] = v0;
+                    sSrc1[STRIPES ? sp : 0][c] = v1;
+                }
+            }
+            consumer_sync();
+
+            auto form = [&](int q) {
+                const int slotOff = (int) ((pos + (unsigned) q) % ST_STAGES) * ST_TILE_FLOATS;
+                const int row0 = q * R;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
+                for (int u = 0; u < ST_U; ++u)
+                {
+                    const int row = row0 + prow[u];
+                    if (pv[u] && row < M)
+                    {
+                        const int c = pcol[u];
+                        const int so = slotOff + sofs[u];
+                        const int nv = vec ? 4 : min(4, M - row);
+                        float prev[4];
+                        float agg[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if (vec)
                         {
-                            const unsigned w = pw[u] + i;
-                            const unsigned over = flat ? 0u : w / (unsigned) Q;
-                            ki[i] = pk[u] + over;
-                            wi[i] = w - over * (unsigned) Q;
+                            const float4 p4 = *reinterpret_cast<const float4*>(tileP + so);
+                            prev[0] = p4.x;
+                            prev[1] = p4.y;
+                            prev[2] = p4.z;
+                            prev[3] = p4.w;
+                            if (hasG)
+                            {
+                                const float4 g4 = *reinterpret_cast<const float4*>(tileG + so);
+                                agg[0] = g4.x;
+                                agg[1] = g4.y;
+                                agg[2] = g4.z;
+                                agg[3] = g4.w;
+                            }
                         }
-                        // the K sources in index order (the own stripe first), the residual last
-                        // (AllReduceDistGradAggregator.h:366-375, 405-435)
-                        bool first = !hasG;
-                        for (int sp = 0; sp < nsrc - firstPacked; ++sp)
+                        else
                         {
-                            const float s0 = sSrc0[STRIPES ? sp : 0][c], s1 = sSrc1[STRIPES ? sp : 0][c];
-                            const unsigned* words = staged ? srcw + (sp * nc + c) * colWords + 2
-                                                           : reinterpret_cast<const unsigned*>(T.src[sp + firstPacked] + (size_t) (col0 + c) * T.colBytes) + 2;
+                            // matrices whose columns are not 16-byte aligned take no bulk copies: plain loads
 #pragma unroll
                             for (int i = 0; i < 4; ++i)
                             {
-                                if (i < nv)
-                                {
-                                    const unsigned word = staged ? words[wi[i]] : __ldg(words + wi[i]);
-                                    const float val = ((word >> ki[i]) & 1u) ? s1 : s0;
-                                    agg[i] = first ? val : __fadd_rn(val, agg[i]);
-                                }
+                                prev[i] = (i < nv) ? pbase[gofs[u] + (size_t) row0 + i] : 0.0f;
+                                if (hasG)
+                                    agg[i] = (i < nv) ? gbase[gofs[u] + (size_t) row0 + i] : 0.0f;
                             }
-                            first = false;
                         }
-                    }
-                    float v[4];
+                        const float lv0 = sLv0[c], lv1 = sLv1[c];
+                        // the usual case: the four rows are the same bit of four adjacent words
+                        const bool flat = (nv == 4) && (pw[u] + 3u < (unsigned) Q);
+                        if (STRIPES)
+                        {
+                            // (word, bit) of the four rows
+                            unsigned wi[4], ki[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        v[i] = __fadd_rn(agg[i], deferred_residual(prev[i], lv0, lv1));
-                    unsigned* const myWords = pkw + c * Q;
-                    if (flat)
-                    {
-                        unsigned* const wp = myWords + pw[u];
-                        const unsigned m = 1u << pk[u];
-                        nanf[u] |= ((v[0] != v[0]) | (v[1] != v[1]) | (v[2] != v[2]) | (v[3] != v[3])) ? 1u : 0u;
+                            for (int i = 0; i < 4; ++i)
+                            {
+                                const unsigned w = pw[u] + i;
+                                const unsigned over = flat ? 0u : w / (unsigned) Q;
+                                ki[i] = pk[u] + over;
+                                wi[i] = w - over * (unsigned) Q;
+                            }
+                            // the K sources in index order (the own stripe first), the residual last
+                            // (AllReduceDistGradAggregator.h:366-375, 405-435)
+                            bool first = !hasG;
+                            for (int sp = 0; sp < nsrc - firstPacked; ++sp)
+                            {
+                                const float s0 = sSrc0[STRIPES ? sp : 0][c], s1 = sSrc1[STRIPES ? sp : 0][c];
+                                const unsigned* words = staged ? srcw + (sp * nc + c) * colWords + 2
+                                                               : reinterpret_cast<const unsigned*>(T.src[sp + firstPacked] + (size_t) (col0 + c) * T.colBytes) + 2;
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                {
+                                    if (i < nv)
+                                    {
+                                        const unsigned word = staged ? words[wi[i]] : __ldg(words + wi[i]);
+                                        const float val = ((word >> ki[i]) & 1u) ? s1 : s0;
+                                        agg[i] = first ? val : __fadd_rn(val, agg[i]);
+                                    }
+                                }
+                                first = false;
+                            }
+                        }
+                        float v[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
-#ifndef QAGG_ST_NO_ATOM
-                            if (v[i] >= 0.0f)
-#else
-                            if (v[i] == 123.0f)
-#endif
-                                atomicOr(wp + i, m);
-                    }
-                    else
-                    {
-                        for (int i = 0; i < nv; ++i)
+                            v[i] = __fadd_rn(agg[i], deferred_residual(prev[i], lv0, lv1));
+                        unsigned* const myWords = pkw + c * Q;
+                        if (flat)
                         {
-                            const unsigned w = pw[u] + i;
-                            const unsigned over = w / (unsigned) Q;
-                            nanf[u] |= (v[i] != v[i]) ? 1u : 0u;
-                            if (v[i] >= 0.0f)
-                                atomicOr(myWords + (w - over * (unsigned) Q), 1u << (pk[u] + over));
+                            unsigned* const wp = myWords + pw[u];
+                            const unsigned m = 1u << pk[u];
+                            nanf[u] |= ((v[0] != v[0]) | (v[1] != v[1]) | (v[2] != v[2]) | (v[3] != v[3])) ? 1u : 0u;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+#ifndef QAGG_ST_NO_ATOM
+                                if (v[i] >= 0.0f)
+#else
+                                if (v[i] == 123.0f)
+#endif
+                                    atomicOr(wp + i, m);
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                            {
+                                const unsigned w = pw[u] + i;
+                                const unsigned over = w / (unsigned) Q;
+                                if (i < nv)
+                                {
+                                    nanf[u] |= (v[i] != v[i]) ? 1u : 0u;
+                                    if (v[i] >= 0.0f)
+                                        atomicOr(myWords + (w - over * (unsigned) Q), 1u << (pk[u] + over));
+                                }
+                            }
+                        }
+                        const float4 v4 = make_float4(v[0], v[1], v[2], v[3]);
+                        *reinterpret_cast<float4*>(tileG + so) = v4;
+                        float* gout = obase + gofs[u] + (size_t) row0;
+                        if (vec)
+                        {
+                            *reinterpret_cast<float4*>(gout) = v4;
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                if (i < nv)
+                                    gout[i] = v[i];
                         }
                     }
-                    const float4 v4 = make_float4(v[0], v[1], v[2], v[3]);
-                    *reinterpret_cast<float4*>(tileG + so) = v4;
-                    float* gout = obase + gofs[u] + (size_t) row0;
-                    if (vec)
-                        *reinterpret_cast<float4*>(gout) = v4;
-                    else
-                        for (int i = 0; i < nv; ++i)
-                            gout[i] = v[i];
+                    // on to the next chunk's rows
+                    pw[u] += advW;
+                    pk[u] += advK;
+                    if (pw[u] >= (unsigned) Q)
+                    {
+                        pw[u] -= (unsigned) Q;
+                        ++pk[u];
+                    }
                 }
-                // on to the next chunk's rows
-                pw[u] += advW;
-                pk[u] += advK;
-                if (pw[u] >= (unsigned) Q)
-                {
-                    pw[u] -= (unsigned) Q;
-                    ++pk[u];
-                }
-            }
-        };
+            };
 
-        // ---- the chunk loop ----------------------------------------------------------------------------------------------
-        // iteration q: chunk q's values are formed, chunk q - 1 is walked and on its way to global memory, the inputs of
-        // chunks q + 1 .. q + ST_DIST are in flight
-        float acc = 0.0f; // a walker lane's running sum of its column
-        ST_MARK(tLoop0);
-        ST_ADD(0, tItem0, tLoop0);
-        for (int q = 0; q <= nchunks; ++q)
-        {
-            ST_MARK(tq0);
-            if (!isWalker)
+            // ---- the chunk loop: in iteration q, chunk q's values are formed and chunk q - 1 is walked -----------------------
+            float acc = 0.0f; // a walker lane's running sum of its column
+            ST_MARK(tLoop0);
+            ST_ADD(0, tItem0, tLoop0);
+            for (int q = 0; q <= nchunks; ++q)
             {
-                issue(q + ST_DIST); // into the tile of chunk q - 2, which was walked before the last barrier
-                ST_MARK(tq1);
-                ST_ADD(1, tq0, tq1);
-                // all but the ST_DIST newest copy groups have landed: chunk q is complete, and this thread forms exactly
-                // the positions it copied itself
-                asm volatile("cp.async.wait_group %0;" ::"n"(ST_DIST) : "memory");
-                ST_MARK(tq2);
-                ST_ADD(2, tq1, tq2);
-                if (q < nchunks)
-                    form(q);
-                ST_MARK(tq3);
-                ST_ADD(3, tq2, tq3);
+                ST_MARK(tq0);
+                if (!isWalker)
+                {
+                    if (q < nchunks)
+                    {
+                        if (vec)
+                        {
+                            const unsigned p = pos + (unsigned) q;
+                            mbar_wait(&sFull[p % ST_STAGES], (p / ST_STAGES) & 1u, &sBroken, status);
+                        }
+                        ST_MARK(tq2);
+                        ST_ADD(2, tq0, tq2);
+#ifndef QAGG_ST_NO_FORM
+                        form(q);
+#endif
+                        ST_MARK(tq3);
+                        ST_ADD(3, tq2, tq3);
+                    }
+                }
+                else if (q >= 1)
+                {
+                    const int qq = q - 1;
+                    const unsigned slot = (pos + (unsigned) qq) % ST_STAGES;
+#ifdef QAGG_ST_NO_WALK
+                    if (q == 1 && lane < nc)
+#else
+                    if (lane < nc)
+#endif
+                    {
+                        const int nrows = min(R, M - qq * R);
+                        const float* vcol = tileG + (int) slot * ST_TILE_FLOATS + lane * stride;
+                        unsigned dummy = 0;
+                        if (warp == ww)
+                            acc = walk_rows<WALK_MIN0>(vcol, nrows, acc, dummy, 0.0f, false);
+                        else
+                            acc = walk_rows<WALK_MAX0>(vcol, nrows, acc, dummy, 0.0f, true);
+                    }
+                    if (vec)
+                    {
+                        // this warp is done with the tile (the element warps were before the last barrier)
+                        __syncwarp();
+                        if (lane == 0)
+                            mbar_arrive(&sEmpty[slot]);
+                    }
+                }
+                ST_MARK(tq4);
+                consumer_sync(); // chunk q is formed (next: walked), chunk q - 1 is walked
+                ST_MARK(tq5);
+                ST_ADD(4, tq4, tq5);
+                ST_ADD(6, 0, 1);
+            }
+            ST_MARK(tLoop1);
+
+            // ---- finish ------------------------------------------------------------------------------------------------------
+            if (isWalker)
+            {
+                if (lane < nc)
+                    (warp == ww ? sA0 : sA1)[lane] = acc;
             }
             else
             {
-                if (q == 0 && warp == ww)
-                {
-                    // nothing to walk yet: fetch the index of this CTA's next item, the item and (asynchronously) its
-                    // descriptor; they are read after the loop's last barrier
-                    int nx = 0;
-                    if (lane == 0)
-                        nx = (int) atomicAdd(&counters[0], 1u);
-                    nx = __shfl_sync(0xffffffffu, nx, 0);
-                    if (lane == 0)
-                        sIt[par ^ 1] = nx;
-                    if (nx < nItems)
-                    {
-                        const int word = (lane < 3) ? reinterpret_cast<const int*>(items + nx)[lane] : 0;
-                        if (lane < 3)
-                            reinterpret_cast<int*>(&sItem[par ^ 1])[lane] = word;
-                        const int tIdx = __shfl_sync(0xffffffffu, word, 0);
-                        if (lane < (int) (sizeof(QTensor) / 16))
-                            cp_async16(reinterpret_cast<float*>(&sT[par ^ 1]) + 4 * lane, reinterpret_cast<const float*>(tensors + tIdx) + 4 * lane);
-                    }
-                    asm volatile("cp.async.commit_group;" ::: "memory");
-                }
-#ifdef QAGG_ST_NO_WALK
-                if (q == 1 && lane < nc)
-#else
-                if (q >= 1 && lane < nc)
-#endif
-                {
-                    const int qq = q - 1;
-                    const int nrows = min(R, M - qq * R);
-                    const float* vcol = tileG + (int) ((ring + (unsigned) qq) % ST_STAGES) * ST_TILE_FLOATS + lane * stride;
-                    unsigned dummy = 0;
-                    if (warp == ww)
-                        acc = walk_rows<WALK_MIN0>(vcol, nrows, acc, dummy, 0.0f, false);
-                    else
-                        acc = walk_rows<WALK_MAX0>(vcol, nrows, acc, dummy, 0.0f, true);
-                }
-                if (q == nchunks && warp == ww)
-                    asm volatile("cp.async.wait_group 0;" ::: "memory");
-            }
-            ST_MARK(tq4);
-            __syncthreads(); // chunk q is formed (next: walked and stored), chunk q - 1 is walked
-            ST_MARK(tq5);
-            ST_ADD(4, tq4, tq5);
-            ST_ADD(6, 0, 1);
-        }
-        ST_MARK(tLoop1);
-
-        // ---- finish: the next item's first chunks go into flight first (every tile is free now) ------------------------------
-        if (isWalker)
-        {
-            if (lane < nc)
-                (warp == ww ? sA0 : sA1)[lane] = acc;
-        }
-        else
-        {
 #pragma unroll
-            for (int u = 0; u < ST_U; ++u)
-                if (pv[u] && nanf[u])
-                    sNan[pcol[u]] = 1u;
-        }
-        const int fnc = nc, fQ = Q, fcol0 = col0; // the finishing item's geometry
-        const unsigned used = (unsigned) nchunks; // ring slots this item went through
-        more = sIt[par ^ 1] < nItems;
-        if (more)
-            adopt(par ^ 1, used);
-        __syncthreads();
-        // rows below the threshold = rows whose bit is 0 (a NaN row has bit 0 too, but then the range is NaN whatever the count)
-        for (int c = warp; c < fnc; c += NWARPS)
-        {
-            unsigned ones = 0;
-            for (int w = lane; w < fQ; w += 32)
-                ones += __popc(pkw[c * fQ + w]);
-            ones = __reduce_add_sync(0xffffffffu, ones);
-            if (lane == 0)
-                sN0[c] = (unsigned) T.M - ones;
-        }
-        __syncthreads();
-        if (tid < fnc)
-        {
-            // min/max drop a NaN where the reference adds it to the upper sum: put it back
-            float lo, up, v0, v1;
-            finalize_range<MODE_ONEBIT_ZERO>(sA0[tid], sNan[tid] ? __int_as_float(0x7fc00000) : sA1[tid], sN0[tid], 0.0f, T.M, lo, up);
-            sLower[tid] = lo;
-            sUpper[tid] = up;
-            levels_1bit(lo, up, v0, v1);
-            T.lv[2 * (size_t) (fcol0 + tid)] = v0;
-            T.lv[2 * (size_t) (fcol0 + tid) + 1] = v1;
-        }
-        __syncthreads();
-        // packed columns to their owners (and to the broadcast copies): warp <-> column, lane <-> word
-        {
-            const int nb = T.bcast ? signal.nbcast : 0;
+                for (int u = 0; u < ST_U; ++u)
+                    if (pv[u] && nanf[u])
+                        sNan[pcol[u]] = 1u;
+            }
+            const int fnc = nc, fQ = Q, fcol0 = col0; // the finishing item's geometry
+            if (vec)
+                pos += (unsigned) nchunks;
+            // the next item's geometry and previous reconstruction values are fetched before this item's last steps
+            more = adopt(itemNo + 1u);
+            consumer_sync();
+            // rows below the threshold = rows whose bit is 0 (a NaN row has bit 0 too, but then the range is NaN whatever the count)
             for (int c = warp; c < fnc; c += NWARPS)
             {
-                unsigned char* const dst = sDst[c];
-                const size_t off = (size_t) (dst - T.pk[0]) + (size_t) T.bcastOff;
-                for (int b = -1; b < nb; ++b)
+                unsigned ones = 0;
+                for (int w = lane; w < fQ; w += 32)
+                    ones += __popc(pkw[c * fQ + w]);
+                ones = __reduce_add_sync(0xffffffffu, ones);
+                if (lane == 0)
+                    sN0[c] = (unsigned) T.M - ones;
+            }
+            consumer_sync();
+            if (tid < fnc)
+            {
+                // min/max drop a NaN where the reference adds it to the upper sum: put it back
+                float lo, up, v0, v1;
+                finalize_range<MODE_ONEBIT_ZERO>(sA0[tid], sNan[tid] ? __int_as_float(0x7fc00000) : sA1[tid], sN0[tid], 0.0f, T.M, lo, up);
+                sLower[tid] = lo;
+                sUpper[tid] = up;
+                levels_1bit(lo, up, v0, v1);
+                T.lv[2 * (size_t) (fcol0 + tid)] = v0;
+                T.lv[2 * (size_t) (fcol0 + tid) + 1] = v1;
+            }
+            consumer_sync();
+            // packed columns to their owners (and to the broadcast copies): warp <-> column, lane <-> word
+            {
+                const int nb = T.bcast ? signal.nbcast : 0;
+                for (int c = warp; c < fnc; c += NWARPS)
                 {
-                    unsigned char* d = (b < 0) ? dst : signal.bcastBase[b] + off;
-                    unsigned* out = reinterpret_cast<unsigned*>(d + 8);
-                    for (int w = lane; w < fQ; w += 32)
-                        out[w] = pkw[c * fQ + w];
-                    if (lane == 0)
-                        store_header(d, sLower[c], sUpper[c]);
+                    unsigned char* const dst = sDst[c];
+                    const size_t off = (size_t) (dst - T.pk[0]) + (size_t) T.bcastOff;
+                    for (int b = -1; b < nb; ++b)
+                    {
+                        unsigned char* d = (b < 0) ? dst : signal.bcastBase[b] + off;
+                        unsigned* out = reinterpret_cast<unsigned*>(d + 8);
+                        for (int w = lane; w < fQ; w += 32)
+                            out[w] = pkw[c * fQ + w];
+                        if (lane == 0)
+                            store_header(d, sLower[c], sUpper[c]);
+                    }
                 }
             }
+            consumer_sync(); // the item is done with its shared-memory state and with its descriptor buffer
+            if (tid == 0)
+                mbar_arrive(&sMetaEmpty[itemNo % ST_DESC]);
+            ST_MARK(tItem1);
+            ST_ADD(5, tLoop1, tItem1);
+            ST_ADD(7, 0, 1);
+            ++itemNo;
         }
-        __syncthreads(); // the item is done with its shared-memory state
-        ST_MARK(tItem1);
-        ST_ADD(5, tLoop1, tItem1);
-        ST_ADD(7, 0, 1);
-        par ^= 1;
     }
+    __syncthreads();
 
 #ifdef QAGG_PROBE
     if (tid == 0)
@@ -656,7 +785,7 @@ void stream_make_items(const std::vector<std::pair<long long, long long>>& shape
 }
 
 cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors, const QItem* items, int nItems,
-                           const LaunchCfg& cfg, unsigned* counters, const Signal* signalp)
+                           const LaunchCfg& cfg, unsigned* counters, const Signal* signalp, unsigned* status)
 {
     static const Signal none = {};
     const Signal& signal = signalp ? *signalp : none;
@@ -673,14 +802,14 @@ cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors
         e = cudaFuncSetAttribute(k_stream1<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ST_SMEM_BYTES);
         if (e != cudaSuccess)
             return e;
-        k_stream1<true><<<grid, NT, ST_SMEM_BYTES, st>>>(tensors, items, nItems, counters, signal);
+        k_stream1<true><<<grid, NT + 32, ST_SMEM_BYTES, st>>>(tensors, items, nItems, counters, signal, status);
     }
     else
     {
         e = cudaFuncSetAttribute(k_stream1<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ST_SMEM_BYTES);
         if (e != cudaSuccess)
             return e;
-        k_stream1<false><<<grid, NT, ST_SMEM_BYTES, st>>>(tensors, items, nItems, counters, signal);
+        k_stream1<false><<<grid, NT + 32, ST_SMEM_BYTES, st>>>(tensors, items, nItems, counters, signal, status);
     }
     return cudaGetLastError();
 }
