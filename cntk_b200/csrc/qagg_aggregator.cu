@@ -159,6 +159,8 @@ struct qagg_aggregator
     // each column's two reconstruction values (see qagg_internal.h)
     bool deferred = false;      // quantize kernel: residuals `res`
     bool deferredOwner = false; // owner kernel: stripe residuals `sres`
+    DevBuf tmaps;                        // tensor maps of the streaming descriptors (QAGG_STREAM_MAP_BYTES each)
+    std::vector<unsigned char> hostMaps; // their host mirror: quantize table entries first, then owner table entries
     DevBuf lvAll, slvAll;
     std::vector<float*> lv, slv;
     // device tables and their host mirrors
@@ -356,9 +358,23 @@ int build_tables(qagg_aggregator* a)
         std::vector<std::pair<long long, long long>> k1Shapes;
         for (int i = 0; i < T; ++i)
             k1Shapes.push_back({a->M[i], (a->M[i] > 0 && a->N[i] > 0) ? a->N[i] : 0});
-        stream_make_items(k1Shapes, a->cfg.numSMs, a->bits, 0, a->iK1);
+        std::vector<std::pair<int, int>> box;
+        stream_make_items(k1Shapes, a->cfg.numSMs, a->bits, 0, a->iK1, box);
+        for (int i = 0; i < T; ++i)
+        {
+            a->hK1[i].boxCols[0] = box[i].first;
+            a->hK1[i].boxCols[1] = box[i].second;
+        }
         if (a->deferredOwner)
-            stream_make_items(k2Shapes, a->cfg.numSMs, a->bits, (a->flags & QAGG_SELF_QUANTIZED) ? K : K - 1, a->iK2);
+        {
+            stream_make_items(k2Shapes, a->cfg.numSMs, a->bits, (a->flags & QAGG_SELF_QUANTIZED) ? K : K - 1, a->iK2, box);
+            for (size_t e = 0; e < a->hK2.size(); ++e)
+            {
+                a->hK2[e].boxCols[0] = box[e].first;
+                a->hK2[e].boxCols[1] = box[e].second;
+            }
+        }
+        a->hostMaps.assign((a->hK1.size() + a->hK2.size()) * (size_t) QAGG_STREAM_MAP_BYTES, 0);
     }
     return QAGG_OK;
 }
@@ -425,6 +441,22 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
     int rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
     if (rc)
         return rc;
+    if (a->deferred)
+    {
+        // the streaming kernels fetch gradient and residual tiles through tensor maps, which hold the base addresses
+        unsigned char* dev = static_cast<unsigned char*>(a->tmaps.p);
+        for (size_t i = 0; i < a->hK1.size(); ++i)
+            stream_set_maps(&a->hK1[i], false, a->hostMaps.data() + i * QAGG_STREAM_MAP_BYTES, dev + i * QAGG_STREAM_MAP_BYTES);
+        if (a->deferredOwner)
+            for (size_t e = 0; e < a->hK2.size(); ++e)
+            {
+                const size_t slot = a->hK1.size() + e;
+                stream_set_maps(&a->hK2[e], true, a->hostMaps.data() + slot * QAGG_STREAM_MAP_BYTES, dev + slot * QAGG_STREAM_MAP_BYTES);
+            }
+        if (!a->hostMaps.empty())
+            if ((rc = check_cuda(cudaMemcpy(dev, a->hostMaps.data(), a->hostMaps.size(), cudaMemcpyHostToDevice), "tensor map upload")))
+                return rc;
+    }
     rc = upload_tables(a);
     if (rc)
         return rc;
@@ -757,6 +789,9 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
         return rc;
     if ((rc = a->tables.alloc(table_bytes(a.get()), true)))
         return rc;
+    if (a->deferred)
+        if ((rc = a->tmaps.alloc(a->hostMaps.size() + 128, true)))
+            return rc;
     if ((rc = a->queue.alloc(4 * QAGG_COUNTER_UINTS * sizeof(unsigned), true)))
         return rc;
     *out = a.release();

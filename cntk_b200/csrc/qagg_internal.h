@@ -38,6 +38,11 @@ struct QTensor
     long long bcastOff;                  // offset of this matrix's block from a broadcast base (K == 1 routing only)
     float* lv;                           // streaming kernel only: the two reconstruction values of each column's previous
                                          // quantization (2 floats per column), read at the start and rewritten at the end
+    // streaming kernel only: tensor maps (device addresses of 128-byte CUtensorMap objects) through which the chunk tiles of
+    // `grad` ([g][0]) and `res_in` ([g][1]) are fetched, for two tile geometries: items of up to boxCols[0] columns and
+    // items of up to boxCols[1] < boxCols[0] columns (0: no such items).  All null: the matrix is fetched with plain loads.
+    const void* tm[2][2];
+    int boxCols[2];
 };
 
 // Flags that the last CTA of a kernel writes (release, system scope) after all of the kernel's stores: one word in each
@@ -112,7 +117,7 @@ cudaError_t launch_signal_only(cudaStream_t st, const Signal& signal);
 // v - (v >= 0 ? lv[1] : lv[0]), is formed with the same single subtraction when the state is next read.  All-zero
 // buffers are a zero residual.  Columns stream through shared memory in row chunks, so column height is limited only
 // by the shared-memory copy of a work item's packed words: nc * Q <= QAGG_STREAM_PKWORDS.
-#define QAGG_STREAM_PKWORDS 3968
+#define QAGG_STREAM_PKWORDS 2560
 #define QAGG_STREAM_CMAX 32
 // most columns per work item for columns of Q packed words (0: the column is too tall for this kernel); the owner
 // kernel also stages the item's columns of its `packedSources` packed inputs, header included
@@ -124,10 +129,17 @@ inline int stream_max_cols(long long Q, int packedSources = 0)
     return (int) (c > QAGG_STREAM_CMAX ? QAGG_STREAM_CMAX : c);
 }
 // Work items of one launch of the streaming kernel, in queue order.  shapes[t] = (rows, columns) of table entry t.
-// Items are sized for about (all values) / (3 x resident CTAs) values each, ordered longest first; the items in the last
-// quarter of the queue are cut into four, so that the launch ends with short items and all CTAs finish together.
+// Items are sized for about (all values) / (2 x resident CTAs) values each, ordered longest first; the items in the last
+// quarter of the queue are cut into three, so that the launch ends with short items and all CTAs finish together.
+// boxCols[t] = {columns of a full item, columns of a cut item or 0} for matrix t.
 void stream_make_items(const std::vector<std::pair<long long, long long>>& shapes, int numSMs, int bits, int packedSources,
-                       std::vector<QItem>& out);
+                       std::vector<QItem>& out, std::vector<std::pair<int, int>>& boxCols);
+// Encodes the tensor maps of one streaming descriptor whose grad / res_in / res_out / M / N / selfRaw / boxCols are set:
+// writes up to four maps to hostMaps (512 bytes, to be copied to devMaps, 128-byte aligned) and sets t->tm[][] to their
+// device addresses -- or to null if the matrix cannot be fetched through tensor maps (rows not a multiple of 4, or
+// buffers not 16-byte aligned), in which case the kernel uses plain loads for it.  `stripes`: owner-kernel descriptor.
+void stream_set_maps(QTensor* t, bool stripes, unsigned char* hostMaps, unsigned char* devMaps);
+#define QAGG_STREAM_MAP_BYTES 512
 // always table-driven with a work queue (`counters` as for launch_colquant, required).  The kernel's waits for copies in
 // flight are bounded: if one runs out, bit 1 of *status is set and the kernel ends normally (results invalid)
 cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors, const QItem* items, int nItems,

@@ -10,50 +10,58 @@
 // to stay resident: columns stream through shared memory in row chunks, every input and output crosses HBM once, and
 // the number of add chains in flight is no longer tied to the column height.
 //
-// One work item = nc <= 32 adjacent columns of one matrix, processed in chunks of R rows (nc * R <= 1536 values) that
-// pass through a ring of chunk tiles in shared memory.  The CTA's nine warps have three roles:
-//   * one "producer" warp fetches work items from the queue and brings every chunk's inputs global -> shared as bulk
-//     asynchronous copies (one per column segment; an mbarrier per ring slot counts the bytes), as far ahead as the
-//     ring has free slots -- across item boundaries too, so the consumers never wait for a pipeline to refill;
+// One work item = nc <= 32 adjacent columns of one matrix, processed in chunks of R rows (nc * R <= 1536 values).
+// The CTA's nine warps have three roles:
+//   * one "producer" warp fetches work items from the queue and brings every chunk's inputs global -> shared with ONE
+//     tensor copy per input (cp.async.bulk.tensor through a tensor map of the matrix: box = R rows x nc columns; an
+//     mbarrier per ring slot counts the bytes), as far ahead as the input ring has free slots -- across item
+//     boundaries too, so the consumers never wait for a pipeline to refill;
 //   * six "element" warps form
 //       v = gradient + (prev - level(prev))                                   (quantize), or
 //       v = sum over the K packed stripes in source order + (prev - level(prev))   (owner's reduce-requantize),
-//     store v to global memory and to the chunk tile, and OR the bit (v >= 0) into the item's packed words, which
-//     live in shared memory until the item ends;
+//     store v to global memory and to a padded tile for the walkers, and OR the bit (v >= 0) into the item's packed
+//     words, which live in shared memory until the item ends;
 //   * two "walker" warps (one per level, lane = column) add min(v, 0) resp. max(v, 0) of the previous chunk to their
-//     running sums, in row order, and hand the tile back to the producer;
+//     running sums, in row order;
 //   * at the end the ranges and the new reconstruction values are derived and the packed columns go to their owners.
 // Every wait on an mbarrier is bounded: if one runs out, the CTA stops waiting altogether, bit 1 of the status word
 // is set and the kernel ends normally (the results of that launch are then invalid).
+// Matrices whose columns are not 16-byte aligned have no tensor maps; their chunks are fetched with plain loads.
 #include "qagg_device.cuh"
 
+#include <cuda.h>
+
 #include <algorithm>
+#include <cstring>
 
 namespace qagg {
 
 constexpr int ST_WALK_WARPS = 2;
-constexpr int ST_ETHREADS = NT - 32 * ST_WALK_WARPS; // 192 element threads
-#ifndef QAGG_ST_U
-#define QAGG_ST_U 2
-#endif
-#ifndef QAGG_ST_STAGES
-#define QAGG_ST_STAGES 4
-#endif
+constexpr int ST_ETHREADS = NT - 32 * ST_WALK_WARPS;   // 192 element threads
+constexpr int ST_U = 2;                                // 16-byte positions per element thread and chunk
+constexpr int ST_TILE_VALUES = 4 * ST_U * ST_ETHREADS; // 1536 values per chunk
+constexpr int ST_IN_FLOATS = ST_TILE_VALUES;           // input tile: dense box, column stride R
+constexpr int ST_V_FLOATS = ST_TILE_VALUES + 4 * QAGG_STREAM_CMAX; // walkers' tile: column stride R + 4
 #ifndef QAGG_ST_CTAS
 #define QAGG_ST_CTAS 3
 #endif
-constexpr int ST_U = QAGG_ST_U;                      // 16-byte positions per element thread and chunk
-constexpr int ST_TILE_VALUES = 4 * ST_U * ST_ETHREADS; // 1536 values per chunk
-constexpr int ST_STAGES = QAGG_ST_STAGES;            // chunk tiles in the ring: 1 walked, 1 formed, the others in flight
-constexpr int ST_TILE_FLOATS = ST_TILE_VALUES + 4 * QAGG_STREAM_CMAX; // room for the 4-float pad of every column
 constexpr int ST_CTAS_PER_SM = QAGG_ST_CTAS;
-constexpr size_t ST_SMEM_BYTES = (size_t) (2 * ST_STAGES * ST_TILE_FLOATS + QAGG_STREAM_PKWORDS) * 4;
-
-// rows per chunk for an item of nc columns: a multiple of 32, so that the tile's column stride R + 4 is 4 mod 32 and
-// the walkers' 128-bit reads of neighbouring columns fall into distinct banks
-__device__ __forceinline__ int stream_rows(int nc)
+// input ring slots: 1 being formed, the others in flight (the owner kernel has less shared memory to spare)
+__host__ __device__ constexpr int stream_in_stages(bool stripes)
 {
-    return ((ST_TILE_VALUES / nc) >> 5) << 5;
+    return stripes ? 3 : 4;
+}
+__host__ __device__ constexpr size_t stream_smem_bytes(bool stripes)
+{
+    return (size_t) (2 * stream_in_stages(stripes) * ST_IN_FLOATS + 2 * ST_V_FLOATS + QAGG_STREAM_PKWORDS) * 4;
+}
+
+// rows per chunk for a tile geometry of `boxCols` columns: a multiple of 32 (so that the walkers' tile, whose column
+// stride is R + 4, spreads the 128-bit reads of neighbouring columns over distinct banks), at most 256 (tensor copy box)
+__host__ __device__ __forceinline__ int stream_rows(int boxCols)
+{
+    const int r = ((ST_TILE_VALUES / boxCols) >> 5) << 5;
+    return r > 256 ? 256 : r;
 }
 
 constexpr int ST_DESC = 4; // work items whose descriptors may be fetched ahead of the consumers
@@ -105,16 +113,59 @@ __device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned pari
     if (status)
         atomicOr(status, 2u);
 }
-__device__ __forceinline__ void bulk_load(float* dstShared, const float* src, unsigned bytes, unsigned long long* bar)
+// box (rows x0 .., columns x1 ..) of the matrix behind `tmap` -> dense tile [column][row]
+__device__ __forceinline__ void tensor_load_2d(float* dstShared, const void* tmap, int x0, int x1, unsigned long long* bar)
 {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dstShared)), "l"(src),
-                 "r"(bytes), "r"(smem_addr(bar))
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_addr(dstShared)),
+                 "l"(tmap), "r"(smem_addr(bar)), "r"(x0), "r"(x1)
                  : "memory");
 }
 // barrier of the eight consumer warps (the producer warp does not take part)
 __device__ __forceinline__ void consumer_sync()
 {
     asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+
+// Ordered walk over the rows of one chunk (a multiple of 4, usually of 32): thirty-two rows per loop trip in two
+// register sets of sixteen, each set reloaded while the other is being added, so the loop carries no register moves.
+template <int KIND>
+__device__ __forceinline__ float walk_chunk(const float* __restrict__ vcol, int nrows, float acc)
+{
+    const float4* __restrict__ p = reinterpret_cast<const float4*>(vcol);
+    const int n16 = nrows >> 4;
+    unsigned dummy = 0;
+    if (n16 > 0)
+    {
+        float4 a0 = p[0], a1 = p[1], a2 = p[2], a3 = p[3];
+        int t = 0;
+        for (; t + 2 <= n16; t += 2)
+        {
+            const float4 b0 = p[4 * t + 4], b1 = p[4 * t + 5], b2 = p[4 * t + 6], b3 = p[4 * t + 7];
+            walk_step4<KIND>(acc, dummy, a0, 0.0f, false);
+            walk_step4<KIND>(acc, dummy, a1, 0.0f, false);
+            walk_step4<KIND>(acc, dummy, a2, 0.0f, false);
+            walk_step4<KIND>(acc, dummy, a3, 0.0f, false);
+            const int nx = 4 * min(t + 2, n16 - 1); // the last trip reloads rows it will not use
+            a0 = p[nx];
+            a1 = p[nx + 1];
+            a2 = p[nx + 2];
+            a3 = p[nx + 3];
+            walk_step4<KIND>(acc, dummy, b0, 0.0f, false);
+            walk_step4<KIND>(acc, dummy, b1, 0.0f, false);
+            walk_step4<KIND>(acc, dummy, b2, 0.0f, false);
+            walk_step4<KIND>(acc, dummy, b3, 0.0f, false);
+        }
+        if (t < n16)
+        {
+            walk_step4<KIND>(acc, dummy, a0, 0.0f, false);
+            walk_step4<KIND>(acc, dummy, a1, 0.0f, false);
+            walk_step4<KIND>(acc, dummy, a2, 0.0f, false);
+            walk_step4<KIND>(acc, dummy, a3, 0.0f, false);
+        }
+    }
+    for (int i = n16 << 4; i < nrows; ++i)
+        walk_step<KIND>(acc, dummy, vcol[i], 0.0f, false);
+    return acc;
 }
 
 __device__ __forceinline__ float deferred_residual(float prev, float lv0, float lv1)
@@ -133,24 +184,32 @@ __device__ __forceinline__ float deferred_residual(float prev, float lv0, float 
 #define ST_ADD(i, a, b)
 #endif
 
+// which of a descriptor's two tile geometries an item of `ncols` columns uses (the same answer on both sides of the ring)
+__device__ __forceinline__ int stream_geometry(const QTensor& T, int ncols)
+{
+    return (T.boxCols[1] > 0 && ncols <= T.boxCols[1]) ? 1 : 0;
+}
+
 template <bool STRIPES>
 __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
                                                                      unsigned* __restrict__ counters, const Signal signal, unsigned* __restrict__ status)
 {
-    extern __shared__ __align__(16) float dsm[];
-    float* const tileG = dsm;                               // gradient (or raw own stripe), replaced in place by v
-    float* const tileP = dsm + ST_STAGES * ST_TILE_FLOATS;   // previous state
+    constexpr int SIN = stream_in_stages(STRIPES);
+    extern __shared__ __align__(128) float dsm[];
+    float* const inG = dsm;                                  // input ring: gradient (or raw own stripe) boxes
+    float* const inP = dsm + SIN * ST_IN_FLOATS;             // input ring: previous-state boxes
+    float* const vt = dsm + 2 * SIN * ST_IN_FLOATS;          // the formed values of two chunks: one being walked, one being written
     // the item's packed words (nc x Q), then -- owner kernel -- its packed source columns, headers included
     // ([source][column][2 + Q] words)
-    unsigned* const pkw = reinterpret_cast<unsigned*>(dsm + 2 * ST_STAGES * ST_TILE_FLOATS);
+    unsigned* const pkw = reinterpret_cast<unsigned*>(dsm + 2 * SIN * ST_IN_FLOATS + 2 * ST_V_FLOATS);
     // work items in flight: buffer (n % ST_DESC) holds the CTA's n-th item: its queue index (>= nItems: the queue is
     // empty), the item and its matrix descriptor
     __shared__ QTensor sT[ST_DESC];
     __shared__ QItem sItem[ST_DESC];
     __shared__ int sIt[ST_DESC];
-    // sFull[slot]: the chunk's inputs have landed (producer's arrival + byte count).  sEmpty[slot]: both walkers are done
-    // with the tile.  sMetaFull[b]: buffer b describes the next item.  sMetaEmpty[b]: the consumers are done with it.
-    __shared__ __align__(8) unsigned long long sFull[ST_STAGES], sEmpty[ST_STAGES], sMetaFull[ST_DESC], sMetaEmpty[ST_DESC];
+    // sFull[slot]: the chunk's inputs have landed (producer's arrival + byte count).  sEmpty[slot]: the element warps have
+    // formed the chunk.  sMetaFull[b]: buffer b describes the next item.  sMetaEmpty[b]: the consumers are done with it.
+    __shared__ __align__(8) unsigned long long sFull[SIN], sEmpty[SIN], sMetaFull[ST_DESC], sMetaEmpty[ST_DESC];
     __shared__ unsigned sBroken;
     __shared__ int sWalker;
     __shared__ float sLv0[QAGG_STREAM_CMAX], sLv1[QAGG_STREAM_CMAX], sA0[QAGG_STREAM_CMAX], sA1[QAGG_STREAM_CMAX];
@@ -175,10 +234,10 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
         sIt[0] = first;
         if (first < nItems)
             sItem[0] = items[first];
-        for (int i = 0; i < ST_STAGES; ++i)
+        for (int i = 0; i < SIN; ++i)
         {
             mbar_init(&sFull[i], 1u);
-            mbar_init(&sEmpty[i], (unsigned) ST_WALK_WARPS);
+            mbar_init(&sEmpty[i], 1u);
         }
         for (int i = 0; i < ST_DESC; ++i)
         {
@@ -210,40 +269,37 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
             if (sIt[b] >= nItems || *reinterpret_cast<volatile unsigned*>(&sBroken))
                 break;
             const QTensor& T = sT[b];
-            const int M = (int) T.M, nc = sItem[b].ncols, col0 = sItem[b].col0;
-            const int R = stream_rows(nc), stride = R + 4, nchunks = (M + R - 1) / R;
+            const int M = (int) T.M, col0 = sItem[b].col0;
+            const int geo = stream_geometry(T, sItem[b].ncols);
+            const int boxCols = T.boxCols[geo];
             const bool hasG = !STRIPES || T.selfRaw;
-            const float* const gbase = T.grad;
-            const float* const pbase = T.res_in;
-            const bool vec = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(pbase) & 15) == 0) && ((reinterpret_cast<uintptr_t>(T.res_out) & 15) == 0) &&
-                             (!hasG || (reinterpret_cast<uintptr_t>(gbase) & 15) == 0);
+            const void* const tmG = T.tm[geo][0];
+            const void* const tmP = T.tm[geo][1];
+            const bool vec = tmP != nullptr && (!hasG || tmG != nullptr);
+            const int R = vec ? stream_rows(boxCols) : 1;
+            const int nchunks = vec ? (M + R - 1) / R : 0;
             int issued = 0;
             // bring chunks [issued, upto) on their way, each as soon as its ring slot is free
             auto pump = [&](int upto) {
                 for (; issued < upto; ++issued)
                 {
                     const unsigned p = pos + (unsigned) issued;
-                    const unsigned slot = p % ST_STAGES;
-                    if (p >= ST_STAGES)
-                        mbar_wait(&sEmpty[slot], ((p / ST_STAGES) - 1u) & 1u, &sBroken, status);
+                    const unsigned slot = p % SIN;
+                    if (p >= (unsigned) SIN)
+                        mbar_wait(&sEmpty[slot], ((p / SIN) - 1u) & 1u, &sBroken, status);
                     if (*reinterpret_cast<volatile unsigned*>(&sBroken))
                         return; // a wait ran out: nothing more is put in flight
-                    const int nrows = min(R, M - issued * R);
                     if (lane == 0)
-                        mbar_arrive_expect_tx(&sFull[slot], (unsigned) ((hasG ? 2 : 1) * nc * nrows * 4));
-                    __syncwarp();
-                    if (lane < nc)
                     {
-                        const size_t go = (size_t) (col0 + lane) * (size_t) M + (size_t) issued * R;
-                        const int so = (int) slot * ST_TILE_FLOATS + lane * stride;
+                        // the whole box counts, whether or not part of it lies outside the matrix (that part is zero-filled)
+                        mbar_arrive_expect_tx(&sFull[slot], (unsigned) ((hasG ? 2 : 1) * boxCols * R * 4));
                         if (hasG)
-                            bulk_load(tileG + so, gbase + go, (unsigned) nrows * 4u, &sFull[slot]);
-                        bulk_load(tileP + so, pbase + go, (unsigned) nrows * 4u, &sFull[slot]);
+                            tensor_load_2d(inG + slot * ST_IN_FLOATS, tmG, issued * R, col0, &sFull[slot]);
+                        tensor_load_2d(inP + slot * ST_IN_FLOATS, tmP, issued * R, col0, &sFull[slot]);
                     }
                 }
             };
-            if (vec)
-                pump(min(nchunks, 2));
+            pump(min(nchunks, 2));
             // the item after this one: its queue index, the item and its descriptor (this warp may block on global
             // memory here -- the chunks above keep the consumers busy meanwhile)
             {
@@ -272,11 +328,8 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
                 if (lane == 0)
                     mbar_arrive(&sMetaFull[b1]);
             }
-            if (vec)
-            {
-                pump(nchunks);
-                pos += (unsigned) nchunks;
-            }
+            pump(nchunks);
+            pos += (unsigned) nchunks;
         }
     }
     else
@@ -284,11 +337,12 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
         // ========================================= consumer warps (element + walker) =========================================
         const int ww = sWalker;
         const bool isWalker = (warp == ww) || (warp == ww + 1);
+        const int firstElementWarp = (ww == 0) ? ST_WALK_WARPS : 0;
         const int et = ((warp > ww) ? warp - ST_WALK_WARPS : warp) * 32 + lane; // index among the element threads
 
         // ---- the item being streamed: geometry (uniform) and this thread's positions ----------------------------------------
         const QTensor* Tp = &sT[0];
-        int M = 1, Q = 1, nc = 1, col0 = 0, R = 32, stride = 36, nchunks = 0;
+        int M = 1, Q = 1, nc = 1, col0 = 0, R = 32, nchunks = 0;
         bool hasG = true, vec = false;
         const float* gbase = nullptr;
         const float* pbase = nullptr;
@@ -299,7 +353,7 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
         // An element thread owns the same ST_U 16-byte positions (column, four rows) of every chunk.  Row i of a column is
         // bit i / Q of packed word i % Q; the position's (word, bit) pair moves by a fixed step from chunk to chunk.
         bool pv[ST_U];
-        int sofs[ST_U], pcol[ST_U], prow[ST_U];
+        int iofs[ST_U], vofs[ST_U], pcol[ST_U], prow[ST_U];
         size_t gofs[ST_U];
         unsigned pw[ST_U], pk[ST_U], nanf[ST_U];
 
@@ -315,15 +369,14 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
             Q = T.Q;
             nc = sItem[b].ncols;
             col0 = sItem[b].col0;
-            R = stream_rows(nc);
-            stride = R + 4;
-            nchunks = (M + R - 1) / R;
+            const int geo = stream_geometry(T, nc);
             hasG = !STRIPES || T.selfRaw;
+            vec = T.tm[geo][1] != nullptr && (!hasG || T.tm[geo][0] != nullptr);
+            R = stream_rows(vec ? T.boxCols[geo] : nc);
+            nchunks = (M + R - 1) / R;
             gbase = T.grad;
             pbase = T.res_in;
             obase = T.res_out;
-            vec = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(pbase) & 15) == 0) && ((reinterpret_cast<uintptr_t>(obase) & 15) == 0) &&
-                  (!hasG || (reinterpret_cast<uintptr_t>(gbase) & 15) == 0);
             advK = (unsigned) R / (unsigned) Q;
             advW = (unsigned) R - advK * (unsigned) Q;
             const int R4 = R >> 2;
@@ -336,7 +389,8 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
                 const int r = pv[u] ? 4 * (f - c * R4) : 0;
                 pcol[u] = c;
                 prow[u] = r;
-                sofs[u] = c * stride + r;
+                iofs[u] = c * R + r;       // in the dense input box
+                vofs[u] = c * (R + 4) + r; // in the walkers' tile
                 gofs[u] = (size_t) (col0 + c) * (size_t) M + (size_t) r;
                 pk[u] = (unsigned) r / (unsigned) Q;
                 pw[u] = (unsigned) r - pk[u] * (unsigned) Q;
@@ -359,6 +413,7 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
             const int nsrc = STRIPES ? T.nsrc : 0;
             const int firstPacked = hasG ? 1 : 0;      // owner kernel: sources firstPacked .. nsrc - 1 are packed
             const int colWords = Q + 2;
+            const int vstride = R + 4;
             unsigned* const srcw = pkw + nc * Q;       // staged packed sources
 
             // ---- per-item state ----------------------------------------------------------------------------------------
@@ -402,7 +457,8 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
             consumer_sync();
 
             auto form = [&](int q) {
-                const int slotOff = (int) ((pos + (unsigned) q) % ST_STAGES) * ST_TILE_FLOATS;
+                const int inOff = (int) ((pos + (unsigned) q) % SIN) * ST_IN_FLOATS;
+                float* const vtile = vt + (q & 1) * ST_V_FLOATS;
                 const int row0 = q * R;
 #pragma unroll
                 for (int u = 0; u < ST_U; ++u)
@@ -411,20 +467,19 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
                     if (pv[u] && row < M)
                     {
                         const int c = pcol[u];
-                        const int so = slotOff + sofs[u];
                         const int nv = vec ? 4 : min(4, M - row);
                         float prev[4];
                         float agg[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                         if (vec)
                         {
-                            const float4 p4 = *reinterpret_cast<const float4*>(tileP + so);
+                            const float4 p4 = *reinterpret_cast<const float4*>(inP + inOff + iofs[u]);
                             prev[0] = p4.x;
                             prev[1] = p4.y;
                             prev[2] = p4.z;
                             prev[3] = p4.w;
                             if (hasG)
                             {
-                                const float4 g4 = *reinterpret_cast<const float4*>(tileG + so);
+                                const float4 g4 = *reinterpret_cast<const float4*>(inG + inOff + iofs[u]);
                                 agg[0] = g4.x;
                                 agg[1] = g4.y;
                                 agg[2] = g4.z;
@@ -433,7 +488,7 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
                         }
                         else
                         {
-                            // matrices whose columns are not 16-byte aligned take no bulk copies: plain loads
+                            // matrices without tensor maps: plain loads
 #pragma unroll
                             for (int i = 0; i < 4; ++i)
                             {
@@ -513,7 +568,7 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
                             }
                         }
                         const float4 v4 = make_float4(v[0], v[1], v[2], v[3]);
-                        *reinterpret_cast<float4*>(tileG + so) = v4;
+                        *reinterpret_cast<float4*>(vtile + vofs[u]) = v4;
                         float* gout = obase + gofs[u] + (size_t) row0;
                         if (vec)
                         {
@@ -547,12 +602,20 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
                 ST_MARK(tq0);
                 if (!isWalker)
                 {
+                    if (vec && q >= 1 && warp == firstElementWarp && lane == 0)
+                    {
+                        // every element warp passed the last barrier: the input slot of chunk q - 1 may be refilled
+                        mbar_arrive(&sEmpty[(pos + (unsigned) (q - 1)) % SIN]);
+                    }
                     if (q < nchunks)
                     {
                         if (vec)
                         {
+                            // one warp watches the mbarrier, the other element warps sleep at a hardware barrier meanwhile
                             const unsigned p = pos + (unsigned) q;
-                            mbar_wait(&sFull[p % ST_STAGES], (p / ST_STAGES) & 1u, &sBroken, status);
+                            if (warp == firstElementWarp)
+                                mbar_wait(&sFull[p % SIN], (p / SIN) & 1u, &sBroken, status);
+                            asm volatile("bar.sync 2, %0;" ::"n"(ST_ETHREADS) : "memory");
                         }
                         ST_MARK(tq2);
                         ST_ADD(2, tq0, tq2);
@@ -565,32 +628,23 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
                 }
                 else if (q >= 1)
                 {
-                    const int qq = q - 1;
-                    const unsigned slot = (pos + (unsigned) qq) % ST_STAGES;
 #ifdef QAGG_ST_NO_WALK
                     if (q == 1 && lane < nc)
 #else
                     if (lane < nc)
 #endif
                     {
+                        const int qq = q - 1;
                         const int nrows = min(R, M - qq * R);
-                        const float* vcol = tileG + (int) slot * ST_TILE_FLOATS + lane * stride;
-                        unsigned dummy = 0;
+                        const float* vcol = vt + (qq & 1) * ST_V_FLOATS + lane * vstride;
                         if (warp == ww)
-                            acc = walk_rows<WALK_MIN0>(vcol, nrows, acc, dummy, 0.0f, false);
+                            acc = walk_chunk<WALK_MIN0>(vcol, nrows, acc);
                         else
-                            acc = walk_rows<WALK_MAX0>(vcol, nrows, acc, dummy, 0.0f, true);
-                    }
-                    if (vec)
-                    {
-                        // this warp is done with the tile (the element warps were before the last barrier)
-                        __syncwarp();
-                        if (lane == 0)
-                            mbar_arrive(&sEmpty[slot]);
+                            acc = walk_chunk<WALK_MAX0>(vcol, nrows, acc);
                     }
                 }
                 ST_MARK(tq4);
-                consumer_sync(); // chunk q is formed (next: walked), chunk q - 1 is walked
+                consumer_sync(); // chunk q is formed (next: walked), chunk q - 1 is walked (its tile may be overwritten)
                 ST_MARK(tq5);
                 ST_ADD(4, tq4, tq5);
                 ST_ADD(6, 0, 1);
@@ -734,13 +788,14 @@ static int nice_cols(double want, int most)
 }
 
 void stream_make_items(const std::vector<std::pair<long long, long long>>& shapes, int numSMs, int bits, int packedSources,
-                       std::vector<QItem>& out)
+                       std::vector<QItem>& out, std::vector<std::pair<int, int>>& boxCols)
 {
+    boxCols.assign(shapes.size(), std::pair<int, int>(0, 0));
     long long total = 0;
     for (auto& sh : shapes)
         total += sh.first * sh.second;
     const long long slots = (long long) numSMs * ST_CTAS_PER_SM;
-    long long target = total / (3 * slots > 0 ? 3 * slots : 1);
+    long long target = total / (2 * slots > 0 ? 2 * slots : 1);
     target = target < 4096 ? 4096 : (target > 49152 ? 49152 : target);
     struct Cand
     {
@@ -759,7 +814,11 @@ void stream_make_items(const std::vector<std::pair<long long, long long>>& shape
         int fit = stream_max_cols(Q, packedSources);
         if (fit < 1)
             fit = stream_max_cols(Q);
-        const long long c = nice_cols((double) target / (double) M, (int) std::min<long long>(fit, N));
+        // at least eight columns where the matrix has them: with fewer, a chunk has so many rows that the walkers' add
+        // chains, not the memory system, set the pace
+        const int most = (int) std::min<long long>(fit, N);
+        const long long c = std::max(nice_cols((double) target / (double) M, most), std::min(8, most));
+        boxCols[t].first = (int) c;
         for (long long c0 = 0; c0 < N; c0 += c)
         {
             const int n = (int) (c < N - c0 ? c : N - c0);
@@ -771,16 +830,86 @@ void stream_make_items(const std::vector<std::pair<long long, long long>>& shape
     long long done = 0;
     for (const Cand& cd : cand)
     {
-        const bool split = done * 4 >= total * 3 && cd.item.ncols >= 2;
+        const bool split = done * 4 >= total * 3 && cd.item.ncols >= 16;
         done += cd.cost;
         if (!split)
         {
             out.push_back(cd.item);
             continue;
         }
-        const int piece = nice_cols(cd.item.ncols / 4.0, cd.item.ncols);
+        // one piece size per matrix (its items were all cut from full ones of the same width, but for the last)
+        int piece = boxCols[cd.item.tensor].second;
+        if (piece == 0)
+        {
+            piece = std::max(8, nice_cols(boxCols[cd.item.tensor].first / 3.0, boxCols[cd.item.tensor].first));
+            if (piece >= boxCols[cd.item.tensor].first)
+            {
+                out.push_back(cd.item);
+                continue;
+            }
+            boxCols[cd.item.tensor].second = piece;
+        }
         for (int c0 = 0; c0 < cd.item.ncols; c0 += piece)
             out.push_back(QItem{cd.item.tensor, cd.item.col0 + c0, piece < cd.item.ncols - c0 ? piece : cd.item.ncols - c0});
+    }
+}
+
+// ---- tensor maps ---------------------------------------------------------------------------------------------------------
+// cuTensorMapEncodeTiled is a driver entry point; it is looked up at run time so that the library needs no link-time
+// dependency on the driver library.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn tensor_map_encoder()
+{
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// map of a column-major M x N fp32 matrix with a box of boxRows rows x boxCols columns; false if it cannot be encoded
+static bool encode_map(void* out128, const float* base, long long M, long long N, int boxRows, int boxCols)
+{
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc || !base || M <= 0 || N <= 0 || (M & 3) || (reinterpret_cast<uintptr_t>(base) & 15) || boxRows < 1 || boxRows > 256 || boxCols < 1 ||
+        boxCols > 256)
+        return false;
+    const cuuint64_t dims[2] = {(cuuint64_t) M, (cuuint64_t) N};
+    const cuuint64_t strides[1] = {(cuuint64_t) M * 4};
+    const cuuint32_t box[2] = {(cuuint32_t) boxRows, (cuuint32_t) boxCols};
+    const cuuint32_t estr[2] = {1, 1};
+    alignas(64) CUtensorMap m;
+    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return false;
+    static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+    std::memcpy(out128, &m, 128);
+    return true;
+}
+
+void stream_set_maps(QTensor* t, bool stripes, unsigned char* hostMaps, unsigned char* devMaps)
+{
+    const bool hasG = !stripes || t->selfRaw;
+    bool ok = (reinterpret_cast<uintptr_t>(t->res_out) & 15) == 0 && (reinterpret_cast<uintptr_t>(devMaps) & 127) == 0;
+    for (int g = 0; g < 2 && ok; ++g)
+    {
+        if (t->boxCols[g] <= 0)
+            continue;
+        const int R = stream_rows(t->boxCols[g]);
+        if (hasG)
+            ok = ok && encode_map(hostMaps + (2 * g) * 128, t->grad, t->M, t->N, R, t->boxCols[g]);
+        ok = ok && encode_map(hostMaps + (2 * g + 1) * 128, t->res_in, t->M, t->N, R, t->boxCols[g]);
+    }
+    for (int g = 0; g < 2; ++g)
+    {
+        const bool have = ok && t->boxCols[g] > 0;
+        t->tm[g][0] = (have && hasG) ? devMaps + (2 * g) * 128 : nullptr;
+        t->tm[g][1] = have ? devMaps + (2 * g + 1) * 128 : nullptr;
     }
 }
 
@@ -799,17 +928,17 @@ cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors
     cudaError_t e;
     if (stripes)
     {
-        e = cudaFuncSetAttribute(k_stream1<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ST_SMEM_BYTES);
+        e = cudaFuncSetAttribute(k_stream1<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) stream_smem_bytes(true));
         if (e != cudaSuccess)
             return e;
-        k_stream1<true><<<grid, NT + 32, ST_SMEM_BYTES, st>>>(tensors, items, nItems, counters, signal, status);
+        k_stream1<true><<<grid, NT + 32, stream_smem_bytes(true), st>>>(tensors, items, nItems, counters, signal, status);
     }
     else
     {
-        e = cudaFuncSetAttribute(k_stream1<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ST_SMEM_BYTES);
+        e = cudaFuncSetAttribute(k_stream1<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) stream_smem_bytes(false));
         if (e != cudaSuccess)
             return e;
-        k_stream1<false><<<grid, NT + 32, ST_SMEM_BYTES, st>>>(tensors, items, nItems, counters, signal, status);
+        k_stream1<false><<<grid, NT + 32, stream_smem_bytes(false), st>>>(tensors, items, nItems, counters, signal, status);
     }
     return cudaGetLastError();
 }
