@@ -85,8 +85,8 @@ class ClockSampler:
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the quantize kernel, from the ncu capture
-# summarised in profiles/k_colquant_speech_dnn_1bit.md (same build, same workload); None where no capture exists
-NCU_TRAFFIC_BYTES = {"speech_dnn": 490.05e6}
+# summarised in profiles/k_stream1_speech_dnn_1bit.md (same build, same workload); None where no capture exists
+NCU_TRAFFIC_BYTES = {"speech_dnn": 502.62e6}
 
 
 def get_shapes(name):
@@ -308,7 +308,7 @@ def run_ours(args):
                        "timing": "CUDA events around each step on the launch stream, mean over steps, max over ranks"},
             "phases_ms": {"quantize": phases[0], "scatter": phases[1], "reduce_requantize": phases[2], "all_gather": phases[3],
                           "unquantize": phases[4]},
-            "roofline": {"bound": "hbm", "kernel": "k_colquant (quantize: stats + pack + residual)", "achieved": k1_gbs, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "k_stream1 (quantize: level sums + pack + deferred residual)", "achieved": k1_gbs, "peak": peak,
                          "unit": "GB/s", "frac": k1_gbs / peak, "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                          "algorithmic_bytes_per_launch": alg["quantize"],
                          "all_kernels": {"algorithmic_bytes": alg["total"], "ms": kern_ms,

@@ -117,7 +117,8 @@ cudaError_t launch_signal_only(cudaStream_t st, const Signal& signal);
 // v - (v >= 0 ? lv[1] : lv[0]), is formed with the same single subtraction when the state is next read.  All-zero
 // buffers are a zero residual.  Columns stream through shared memory in row chunks, so column height is limited only
 // by the shared-memory copy of a work item's packed words: nc * Q <= QAGG_STREAM_PKWORDS.
-#define QAGG_STREAM_PKWORDS 2560
+#define QAGG_STREAM_PKWORDS 2560       /* quantize kernel */
+#define QAGG_STREAM_PKWORDS_OWNER 4480 /* owner kernel: its input ring is one slot shorter */
 #define QAGG_STREAM_CMAX 32
 // most columns per work item for columns of Q packed words (0: the column is too tall for this kernel); the owner
 // kernel also stages the item's columns of its `packedSources` packed inputs, header included
@@ -125,7 +126,7 @@ inline int stream_max_cols(long long Q, int packedSources = 0)
 {
     if (Q <= 0)
         return QAGG_STREAM_CMAX;
-    const long long c = QAGG_STREAM_PKWORDS / (Q + (long long) packedSources * (Q + 2));
+    const long long c = (packedSources > 0 ? QAGG_STREAM_PKWORDS_OWNER : QAGG_STREAM_PKWORDS) / (Q + (long long) packedSources * (Q + 2));
     return (int) (c > QAGG_STREAM_CMAX ? QAGG_STREAM_CMAX : c);
 }
 // Work items of one launch of the streaming kernel, in queue order.  shapes[t] = (rows, columns) of table entry t.

@@ -53,7 +53,7 @@ __host__ __device__ constexpr int stream_in_stages(bool stripes)
 }
 __host__ __device__ constexpr size_t stream_smem_bytes(bool stripes)
 {
-    return (size_t) (2 * stream_in_stages(stripes) * ST_IN_FLOATS + 2 * ST_V_FLOATS + QAGG_STREAM_PKWORDS) * 4;
+    return (size_t) (2 * stream_in_stages(stripes) * ST_IN_FLOATS + 2 * ST_V_FLOATS + (stripes ? QAGG_STREAM_PKWORDS_OWNER : QAGG_STREAM_PKWORDS)) * 4;
 }
 
 // rows per chunk for a tile geometry of `boxCols` columns: a multiple of 32 (so that the walkers' tile, whose column
@@ -428,7 +428,7 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
             }
             // owner kernel: the item's columns of every packed source are staged in shared memory when they fit next to
             // the item's own packed words (one contiguous block of nc * (2 + Q) words per source); else they are read in place
-            const bool staged = STRIPES && (nc * Q + (nsrc - firstPacked) * nc * colWords <= QAGG_STREAM_PKWORDS);
+            const bool staged = STRIPES && (nc * Q + (nsrc - firstPacked) * nc * colWords <= QAGG_STREAM_PKWORDS_OWNER);
             if (STRIPES)
             {
                 if (staged)
@@ -819,14 +819,19 @@ void stream_make_items(const std::vector<std::pair<long long, long long>>& shape
         const int most = (int) std::min<long long>(fit, N);
         const long long c = std::max(nice_cols((double) target / (double) M, most), std::min(8, most));
         boxCols[t].first = (int) c;
+        // an item takes about as long as it has chunks, whatever its width: a single tall column is a long item
+        const long long chunks = (M + stream_rows((int) c) - 1) / stream_rows((int) c);
         for (long long c0 = 0; c0 < N; c0 += c)
         {
             const int n = (int) (c < N - c0 ? c : N - c0);
-            cand.push_back(Cand{M * n, QItem{(int) t, (int) c0, n}, fit});
+            cand.push_back(Cand{chunks, QItem{(int) t, (int) c0, n}, fit});
         }
     }
     std::stable_sort(cand.begin(), cand.end(), [](const Cand& x, const Cand& y) { return x.cost > y.cost; });
     out.clear();
+    total = 0;
+    for (const Cand& cd : cand)
+        total += cd.cost;
     long long done = 0;
     for (const Cand& cd : cand)
     {
