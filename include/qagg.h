@@ -169,10 +169,13 @@ int qagg_agg_step_host(qagg_aggregator* a, float* const* host_grads, void* strea
  * Source/1BitSGD/QuantizedDataParallelDistributedLearner.h:73-91). */
 int qagg_agg_reset_residuals(qagg_aggregator* a, void* stream);
 /* Device pointers to internal state, for inspection: the M x N residual and the M x n stripe residual of tensor i
- * (stripe pointer NULL when this rank owns no column of it). */
+ * (stripe pointer NULL when this rank owns no column of it).  For 1 bit with threshold 0 the aggregator keeps the
+ * residual in a deferred form (the quantized value plus the column's two reconstruction values; the subtraction is done
+ * when the state is next read -- the same arithmetic as the reference's, later); this call first turns tensor i's state
+ * into plain residuals in place, on the default stream, and waits for that. */
 int qagg_agg_residuals(qagg_aggregator* a, int tensor, float** residual, float** stripe_residual);
 /* Copy the residual (which = 0, M x N floats) or the stripe residual (which = 1, M x n floats) of tensor i into a
- * device buffer, on `stream`. */
+ * device buffer, on `stream`: always plain residuals, bit-identical to the reference's GetResidualMatrix. */
 int qagg_agg_copy_residual(qagg_aggregator* a, int tensor, int which, float* dst_dev, void* stream);
 /* Copy the gathered packed matrix of tensor i (what every rank unquantized from in the last step) into a device
  * buffer of qagg_packed_bytes(M[i], N[i], bits), in the reference's contiguous layout. */
@@ -204,7 +207,8 @@ int qagg_hagg_destroy(qagg_host_aggregator* h);
  *   2. every rank calls qagg_agg_enable_peer with the K handles in rank order (cudaIpcOpenMemHandle on the others').
  * From then on qagg_agg_step uses the peer path.  Device-side waits are bounded (qagg_agg_set_wait_limit polls, default
  * about two seconds): a peer that never arrives makes the wait give up and set a status word instead of hanging;
- * qagg_agg_check synchronises the stream and returns QAGG_ETIMEOUT if that happened since creation. */
+ * qagg_agg_check synchronises the stream and returns QAGG_ETIMEOUT if that happened since creation -- or if a bounded
+ * wait inside the streaming quantize kernel (for a copy into shared memory) ever ran out. */
 #define QAGG_PEER_HANDLE_BYTES 64
 int qagg_agg_peer_handle(qagg_aggregator* a, void* out);
 int qagg_agg_enable_peer(qagg_aggregator* a, const void* handles);
