@@ -565,6 +565,34 @@ int qagg_plan_destroy(qagg_plan* p)
     return QAGG_OK;
 }
 
+int64_t qagg_plan_stream_items(int num_tensors, const int64_t* M, const int64_t* N, int bits, int num_sms, int packed_sources,
+                               int32_t* items, int64_t capacity)
+{
+    if (num_tensors < 0 || (num_tensors > 0 && (!M || !N)) || !bits_ok(bits) || num_sms < 1 || packed_sources < 0 || packed_sources > QAGG_MAXK ||
+        capacity < 0 || (capacity > 0 && !items))
+        return fail(QAGG_EINVAL, "qagg_plan_stream_items: bad arguments");
+    std::vector<std::pair<long long, long long>> shapes;
+    for (int i = 0; i < num_tensors; ++i)
+    {
+        if (M[i] < 0 || N[i] < 0 || M[i] > 0x3fffffffLL || N[i] > 0x7fffffffLL)
+            return fail(QAGG_EINVAL, "qagg_plan_stream_items: bad tensor shape");
+        const long long Q = (M[i] * bits + 31) / 32;
+        if (M[i] > 0 && N[i] > 0 && stream_max_cols(Q) < 1)
+            return fail(QAGG_EINVAL, "qagg_plan_stream_items: a column is too tall for the streaming kernel");
+        shapes.push_back({M[i], (M[i] > 0 && N[i] > 0) ? N[i] : 0});
+    }
+    std::vector<QItem> out;
+    std::vector<std::pair<int, int>> box;
+    stream_make_items(shapes, num_sms, bits, packed_sources, out, box);
+    for (size_t k = 0; k < out.size() && (int64_t) k < capacity; ++k)
+    {
+        items[3 * k] = out[k].tensor;
+        items[3 * k + 1] = out[k].col0;
+        items[3 * k + 2] = out[k].ncols;
+    }
+    return (int64_t) out.size();
+}
+
 int qagg_unique_id(void* out)
 {
     if (!out)

@@ -173,7 +173,8 @@ __device__ __forceinline__ float deferred_residual(float prev, float lv0, float 
     return __fsub_rn(prev, (prev >= 0.0f) ? lv1 : lv0);
 }
 
-// optional phase timers for development builds (-DQAGG_PROBE; the array is defined in qagg_kernels.cu)
+// optional timers for development builds: -DQAGG_PROBE records CTA lifetimes, -DQAGG_PROBE_PHASES also per-phase cycle
+// counts of one element thread per CTA (the counter array is defined in qagg_kernels.cu); nothing in the product
 #ifdef QAGG_PROBE_PHASES
 #define ST_MARK(var) const long long var = clock64()
 #define ST_ADD(i, a, b)  \
@@ -545,11 +546,7 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
                             nanf[u] |= ((v[0] != v[0]) | (v[1] != v[1]) | (v[2] != v[2]) | (v[3] != v[3])) ? 1u : 0u;
 #pragma unroll
                             for (int i = 0; i < 4; ++i)
-#ifndef QAGG_ST_NO_ATOM
                                 if (v[i] >= 0.0f)
-#else
-                                if (v[i] == 123.0f)
-#endif
                                     atomicOr(wp + i, m);
                         }
                         else
@@ -619,20 +616,14 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
                         }
                         ST_MARK(tq2);
                         ST_ADD(2, tq0, tq2);
-#ifndef QAGG_ST_NO_FORM
                         form(q);
-#endif
                         ST_MARK(tq3);
                         ST_ADD(3, tq2, tq3);
                     }
                 }
                 else if (q >= 1)
                 {
-#ifdef QAGG_ST_NO_WALK
-                    if (q == 1 && lane < nc)
-#else
                     if (lane < nc)
-#endif
                     {
                         const int qq = q - 1;
                         const int nrows = min(R, M - qq * R);
