@@ -170,7 +170,18 @@ struct qagg_aggregator
     QItem *dI1 = nullptr, *dI2 = nullptr, *dI3 = nullptr;
     DevBuf queue; // three pairs of work-queue counters (one pair per kernel), zero when no kernel is running
     std::vector<int> k2Tensor; // tensor index of each K2 table entry
-    std::vector<float*> boundGrads;
+    // The device tables (and tensor maps) hold the gradient pointers.  Two sets are kept, each bound to one array of
+    // gradient pointers, so that a caller that alternates between two gradient buffer sets (double-buffered aggregation)
+    // pays for the table upload only twice.
+    struct Binding
+    {
+        std::vector<float*> grads;
+        QTensor *dK1 = nullptr, *dK2 = nullptr, *dK3 = nullptr;
+        QItem *dI1 = nullptr, *dI2 = nullptr, *dI3 = nullptr;
+    };
+    Binding bindings[2];
+    int curBinding = 0;
+    size_t tableBytes = 0; // size of one set of tables
     LaunchCfg cfg;
     int64_t totalValues = 0;
     bool identity = false;
@@ -385,10 +396,10 @@ size_t table_bytes(const qagg_aggregator* a)
            (a->iK1.size() + a->iK2.size() + a->iK3.size()) * sizeof(QItem) + 256;
 }
 
-// copies the host tables to the device (synchronously: only when the bound gradient pointers change)
-int upload_tables(qagg_aggregator* a)
+// copies the host tables to table set `slot` on the device (synchronously: only when a new array of gradient pointers is bound)
+int upload_tables(qagg_aggregator* a, int slot)
 {
-    unsigned char* base = static_cast<unsigned char*>(a->tables.p);
+    unsigned char* base = static_cast<unsigned char*>(a->tables.p) + (size_t) slot * a->tableBytes;
     size_t off = 0;
     auto put = [&](const void* src, size_t bytes, void** devp) -> int {
         *devp = base + off;
@@ -419,11 +430,26 @@ int upload_tables(qagg_aggregator* a)
 
 int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
 {
-    bool same = (a->boundGrads.size() == (size_t) a->T);
-    for (int i = 0; same && i < a->T; ++i)
-        same = (a->boundGrads[i] == grads[i]);
-    if (same)
-        return QAGG_OK;
+    for (int s = 0; s < 2; ++s)
+    {
+        const qagg_aggregator::Binding& b = a->bindings[s];
+        bool same = (b.grads.size() == (size_t) a->T) && b.dK3 != nullptr;
+        for (int i = 0; same && i < a->T; ++i)
+            same = (b.grads[i] == grads[i]);
+        if (same)
+        {
+            a->curBinding = s;
+            a->dK1 = b.dK1;
+            a->dK2 = b.dK2;
+            a->dK3 = b.dK3;
+            a->dI1 = b.dI1;
+            a->dI2 = b.dI2;
+            a->dI3 = b.dI3;
+            return QAGG_OK;
+        }
+    }
+    // not bound yet: take the set that is not the current one (the first call takes set 0)
+    const int slot = a->bindings[a->curBinding].dK3 ? (a->curBinding ^ 1) : a->curBinding;
     for (int i = 0; i < a->T; ++i)
     {
         if (!grads[i] && a->M[i] * a->N[i] > 0)
@@ -437,14 +463,14 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
         const int i = a->k2Tensor[e];
         a->hK2[e].grad = grads[i] + a->sStart[r][i] * a->M[i];
     }
-    // an earlier step may still be reading the old tables
+    // an earlier step may still be reading the tables of that set
     int rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
     if (rc)
         return rc;
     if (a->deferred)
     {
         // the streaming kernels fetch gradient and residual tiles through tensor maps, which hold the base addresses
-        unsigned char* dev = static_cast<unsigned char*>(a->tmaps.p);
+        unsigned char* dev = static_cast<unsigned char*>(a->tmaps.p) + (size_t) slot * align_up((int64_t) a->hostMaps.size(), 128);
         for (size_t i = 0; i < a->hK1.size(); ++i)
             stream_set_maps(&a->hK1[i], false, a->hostMaps.data() + i * QAGG_STREAM_MAP_BYTES, dev + i * QAGG_STREAM_MAP_BYTES);
         if (a->deferredOwner)
@@ -457,10 +483,18 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
             if ((rc = check_cuda(cudaMemcpy(dev, a->hostMaps.data(), a->hostMaps.size(), cudaMemcpyHostToDevice), "tensor map upload")))
                 return rc;
     }
-    rc = upload_tables(a);
+    rc = upload_tables(a, slot);
     if (rc)
         return rc;
-    a->boundGrads.assign(grads, grads + a->T);
+    qagg_aggregator::Binding& b = a->bindings[slot];
+    b.grads.assign(grads, grads + a->T);
+    b.dK1 = a->dK1;
+    b.dK2 = a->dK2;
+    b.dK3 = a->dK3;
+    b.dI1 = a->dI1;
+    b.dI2 = a->dI2;
+    b.dI3 = a->dI3;
+    a->curBinding = slot;
     return QAGG_OK;
 }
 
@@ -815,10 +849,11 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
     }
     if ((rc = build_tables(a.get())))
         return rc;
-    if ((rc = a->tables.alloc(table_bytes(a.get()), true)))
+    a->tableBytes = (size_t) align_up((int64_t) table_bytes(a.get()), 256);
+    if ((rc = a->tables.alloc(2 * a->tableBytes, true)))
         return rc;
     if (a->deferred)
-        if ((rc = a->tmaps.alloc(a->hostMaps.size() + 128, true)))
+        if ((rc = a->tmaps.alloc(2 * (size_t) align_up((int64_t) a->hostMaps.size(), 128) + 128, true)))
             return rc;
     if ((rc = a->queue.alloc(4 * QAGG_COUNTER_UINTS * sizeof(unsigned), true)))
         return rc;
@@ -1084,7 +1119,9 @@ int qagg_agg_enable_peer(qagg_aggregator* a, const void* handles)
     // the routing of the packed columns changes: rebuild and re-upload the tables on the next step
     if ((rc = build_tables(a)))
         return rc;
-    a->boundGrads.clear();
+    for (auto& b : a->bindings)
+        b = qagg_aggregator::Binding();
+    a->curBinding = 0;
     return QAGG_OK;
 }
 

@@ -3,6 +3,7 @@
 //   mode "quantizer": the loop of TestRunQuantization (Tests/UnitTests/MathTests/MatrixQuantizerTests.cpp:268-316):
 //       MatrixQuantizerImpl::Create, QuantizeAsync(in, residue, CPU QuantizedMatrix, residue), UnquantizeAsync(add = it > 0)
 //   mode "aggregator": AllReduceDistGradAggregator::AggregateGradients on one rank (SGD.cpp:1376), two calls
+//   mode "aggregator_async": the same with useAsyncAggregation = true (one-step-stale results, AllReduceDistGradAggregator.h:156-229)
 // usage: compat_check <mode> <in.bin> <out.bin> M N bits zeroThr iters
 #include <cstdio>
 #include <cstdlib>
@@ -100,6 +101,44 @@ int main(int argc, char** argv)
             auto v = download(*view);
             if (memcmp(v.data(), in.data(), in.size() * 4) != 0)
                 return 9;
+        }
+        else if (mode == "aggregator_async")
+        {
+            // useAsyncAggregation = true (AllReduceDistGradAggregator.h:156-229): every call hands back the aggregate of the
+            // PREVIOUS call's gradients (zeros after the reset) and launches the aggregation of the ones it received
+            auto mpi = std::make_shared<MPIWrapper>(std::string(), 0, 1, 0);
+            AllReduceDistGradAggregator<float> agg(mpi, bits, zeroThr != 0, true, true, 0, 0);
+            Matrix<float> g0(M, N, 0), g1(M, 1, 0);
+            std::vector<Matrix<float>*> grads{&g0, &g1};
+            DistGradHeader* hdr = DistGradHeader::Create(1);
+            for (int it = 0; it <= iters; ++it)
+            {
+                hdr->Clear();
+                if (it < iters)
+                {
+                    if (fread(in.data(), 4, in.size(), fi) != in.size())
+                        return 4;
+                    cudaMemcpy(g0.Data(), in.data(), in.size() * 4, cudaMemcpyHostToDevice);
+                    cudaMemcpy(g1.Data(), in.data(), M * 4, cudaMemcpyHostToDevice);
+                    hdr->numSamples = 7;
+                    hdr->criterion = 1.5;
+                }
+                const bool any = agg.AggregateGradients(grads, hdr, it == 0);
+                if (!any)
+                    return 7;
+                // the header that comes back is the previous call's, aggregated (cleared after the reset)
+                if (it == 0 ? (hdr->numSamples != 0) : (hdr->numSamples != 7 || hdr->criterion != 1.5))
+                    return 8;
+                auto a = download(g0), b = download(g1);
+                fwrite(a.data(), 4, a.size(), fo);
+                fwrite(b.data(), 4, b.size(), fo);
+            }
+            // resetting the state while an aggregation is pending is a logic error
+            bool threw = false;
+            try { agg.AggregateGradients(grads, hdr, true); } catch (const std::logic_error&) { threw = true; }
+            if (!threw)
+                return 11;
+            DistGradHeader::Destroy(hdr);
         }
         else
             return 2;

@@ -78,3 +78,28 @@ def test_aggregator_and_v2_communicator_single_rank(exe, tmp_path, oracle_port):
             assert np.array_equal(dump[off:off + ref.size], ref), f"step {it}: aggregate differs"
             off += ref.size
     assert off == dump.size
+
+
+def test_aggregator_buffered_async_hands_back_the_previous_aggregate(exe, tmp_path, oracle_port):
+    """useAsyncAggregation = true (Source/1BitSGD/AllReduceDistGradAggregator.h:156-229): call t returns the aggregate of the
+    gradients given to call t - 1 (zeros after the reset); the residual chain is the same as without buffering."""
+    M, N, bits, iters = 256, 40, 1, 3
+    inputs = [mg.normal_input(M, N, 1e-3, 177 + it) for it in range(iters)]
+    dump = run(exe, tmp_path, "aggregator_async", inputs, M, N, bits, True)
+    C = oracle_port.packed_col_bytes(M, bits)
+    res0 = np.zeros((N, M), np.float32)
+    res1 = np.zeros((1, M), np.float32)
+    per_call = (N * M + M) * 4
+    assert dump.size == (iters + 1) * per_call
+    assert not dump[:per_call].any(), "the first call must hand back zeros"
+    off = per_call
+    for it in range(iters):
+        for g, res in ((inputs[it].copy(), res0), (inputs[it][:1].copy(), res1)):
+            n = g.shape[0]
+            packed = np.zeros(n * C, np.uint8)
+            oracle_port.quantize(g, res, res, packed, bits, True)
+            oracle_port.unquantize(packed, g, bits, add=False)
+            ref = g.view(np.uint8).reshape(-1)
+            assert np.array_equal(dump[off:off + ref.size], ref), f"call {it + 1}: aggregate of step {it} differs"
+            off += ref.size
+    assert off == dump.size
