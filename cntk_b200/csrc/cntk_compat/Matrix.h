@@ -28,7 +28,7 @@ public:
         if (cudaSetDevice(deviceId) != cudaSuccess)
             RuntimeError("Matrix: cudaSetDevice(%d) failed", deviceId);
         void* p = nullptr;
-        const size_t bytes = (numRows * numCols ? numRows * numCols : 1) * sizeof(ElemType);
+        const size_t bytes = (numRows * numCols != 0 ? numRows * numCols : 1) * sizeof(ElemType);
         if (cudaMalloc(&p, bytes) != cudaSuccess)
             RuntimeError("Matrix: cudaMalloc of %zu bytes failed", bytes);
         cudaMemset(p, 0, bytes); // CNTK matrices start zeroed (the residual relies on it, 1BitSGD/MatrixQuantizer.h:27-30)

@@ -30,7 +30,7 @@ public:
         if (c < 0)
             LogicError("QuantizedMatrix: nbits=%zu must be a power of two dividing the 32-bit word", nbits); // QuantizedMatrix.cpp:12-15
         m_qColSize = (size_t) c;
-        const size_t bytes = m_qColSize * numCols ? m_qColSize * numCols : 1;
+        const size_t bytes = m_qColSize * numCols != 0 ? m_qColSize * numCols : 1;
         void* p = nullptr;
         if (deviceId == CPUDEVICE)
         {

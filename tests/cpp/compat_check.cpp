@@ -11,6 +11,8 @@
 #include <vector>
 
 #include "../../cntk_b200/csrc/cntk_compat/AllReduceDistGradAggregator.h"
+#include "../../cntk_b200/csrc/cntk_compat/QuantizedDataParallelDistributedLearner.h"
+#include "../../cntk_b200/csrc/cntk_compat/V2AllReduceDistGradAggregator.h"
 #include "../../cntk_b200/csrc/cntk_compat/MatrixQuantizer.h"
 #include "../../cntk_b200/csrc/cntk_compat/QuantizedDistributedCommunicator.h"
 
@@ -101,6 +103,77 @@ int main(int argc, char** argv)
             auto v = download(*view);
             if (memcmp(v.data(), in.data(), in.size() * 4) != 0)
                 return 9;
+
+            // V2AllReduceDistGradAggregator: the IDistGradAggregator face of the V2 communicator (one worker: identity)
+            {
+                V2AllReduceDistGradAggregator<float> v2agg(comm, false, 0, 0);
+                std::vector<Matrix<float>*> vg{view.get()};
+                DistGradHeader* h2 = DistGradHeader::Create(1);
+                h2->Clear();
+                h2->numSamples = 5;
+                h2->criterion = 0.25;
+                if (!v2agg.AggregateGradients(vg, h2, true) || h2->numSamples != 5 || h2->criterion != 0.25)
+                    return 12;
+                v = download(*view);
+                if (memcmp(v.data(), in.data(), in.size() * 4) != 0)
+                    return 13;
+                h2->Clear(); // a worker without samples: zero gradients, "nothing processed"
+                if (v2agg.AggregateGradients(vg, h2, false))
+                    return 14;
+                v = download(*view);
+                for (float x : v)
+                    if (x != 0.0f)
+                        return 15;
+                DistGradHeader::Destroy(h2);
+                bool threwAsync = false;
+                try { V2AllReduceDistGradAggregator<float> bad(comm, true, 0, 0); } catch (const std::logic_error&) { threwAsync = true; }
+                if (!threwAsync)
+                    return 16;
+            }
+            // QuantizedDataParallelDistributedLearner: warm-start threshold, aggregated sample count, empty minibatch, checkpoint
+            {
+                struct CountingLearner : ::CNTK::Learner
+                {
+                    int calls = 0;
+                    size_t lastCount = 0;
+                    bool Update(std::vector<::CNTK::NDArrayViewPtr>&, size_t n, bool) override
+                    {
+                        ++calls;
+                        lastCount = n;
+                        return true;
+                    }
+                };
+                auto learner = std::make_shared<CountingLearner>();
+                auto dl = ::CNTK::CreateQuantizedDataParallelDistributedLearner(comm, learner, /*distributeAfterSamples=*/10);
+                cudaMemcpy(view->Data(), in.data(), in.size() * 4, cudaMemcpyHostToDevice);
+                ::CNTK::MinibatchInfo info;
+                for (int step = 0; step < 3; ++step) // steps 0 and 1 run before the threshold, step 2 after it
+                {
+                    info.numberOfSamples = 6;
+                    info.trainingLossValue = 2.0;
+                    info.evalCriterionValue = 0.5;
+                    if (!dl->Update(vals, info) || info.numberOfSamples != 6 || learner->lastCount != 6)
+                        return 17;
+                }
+                if (learner->calls != 3 || dl->TotalNumberOfSamplesSeen() != 18)
+                    return 18;
+                v = download(*view);
+                if (memcmp(v.data(), in.data(), in.size() * 4) != 0) // one worker: gradients untouched
+                    return 19;
+                info = ::CNTK::MinibatchInfo(); // empty minibatch: zero gradients, no local update
+                if (dl->Update(vals, info) || learner->calls != 3)
+                    return 20;
+                v = download(*view);
+                for (float x : v)
+                    if (x != 0.0f)
+                        return 21;
+                if (dl->CreateCheckpoint() != 18)
+                    return 22;
+                bool threwAsync = false;
+                try { ::CNTK::CreateQuantizedDataParallelDistributedLearner(comm, learner, 0, true); } catch (const std::logic_error&) { threwAsync = true; }
+                if (!threwAsync)
+                    return 23;
+            }
         }
         else if (mode == "aggregator_async")
         {
