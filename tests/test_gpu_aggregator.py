@@ -224,3 +224,14 @@ def lstm_inputs(K, step):
 def test_lstm_shaped_set_ragged(G, oracle_port, K):
     """Tall embedding with 90% all-zero columns, wide softmax, bias vectors; 1 bit, 10 steps."""
     run_group(G, oracle_port, LSTM_SMALL, K, 1, True, True, 10, lstm_inputs, check_every=5)
+
+
+@pytest.mark.parametrize("stream_knob", ["0", "2"])
+def test_kernel_choice_knob_changes_no_result(G, oracle_port, stream_knob, monkeypatch):
+    """QAGG_STREAM is a tuning knob read when an aggregator is created: 0 = resident-column kernels only (plain residuals),
+    2 = streaming kernel also for the owner's reduce-requantize (deferred stripe residuals).  Either way aggregates,
+    both residual sets and the gathered packed words stay bit-identical to the oracle (the default, 1, is what every
+    other 1-bit zero-threshold test in this file runs)."""
+    monkeypatch.setenv("QAGG_STREAM", stream_knob)
+    run_group(G, oracle_port, SPEECH_SMALL, 3, 1, True, True, 6, speech_inputs, check_every=3)
+    run_group(G, oracle_port, mg.EXCHANGE_SHAPES, 2, 1, True, False, 4, mg.exchange_inputs, peer=True)
