@@ -1152,6 +1152,13 @@ int qagg_agg_check(qagg_aggregator* a, void* stream)
     return QAGG_OK;
 }
 
+int qagg_stream_wait_selftest(void* stream, int max_tries, unsigned* status_dev, long long* cycles_dev)
+{
+    if (!status_dev || max_tries < 1 || max_tries > (1 << 22))
+        return fail(QAGG_EINVAL, "qagg_stream_wait_selftest: bad arguments");
+    return check_cuda(launch_stream_wait_selftest((cudaStream_t) stream, max_tries, status_dev, cycles_dev), "wait self-test launch");
+}
+
 int qagg_wait_flags(void* stream, const unsigned* flags_dev, int n, int skip, unsigned value, long long max_polls, unsigned* status_dev)
 {
     if (!flags_dev || !status_dev || n < 1 || n > 32 || max_polls < 1)

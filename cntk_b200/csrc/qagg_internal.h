@@ -145,6 +145,8 @@ void stream_set_maps(QTensor* t, bool stripes, unsigned char* hostMaps, unsigned
 // flight are bounded: if one runs out, bit 1 of *status is set and the kernel ends normally (results invalid)
 cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors, const QItem* items, int nItems,
                            const LaunchCfg& cfg, unsigned* counters, const Signal* signal = nullptr, unsigned* status = nullptr);
+// runs the streaming kernel's bounded mbarrier wait on a barrier that nothing completes (see qagg_stream_wait_selftest)
+cudaError_t launch_stream_wait_selftest(cudaStream_t st, int maxTries, unsigned* status, long long* cycles);
 // dst[i, j] = buf[i, j] - (buf[i, j] >= 0 ? lv[2j + 1] : lv[2j]): the residual proper of a deferred state (dst may be buf)
 cudaError_t launch_materialize(cudaStream_t st, const float* buf, const float* lv, float* dst, long long M, long long N, int numSMs);
 int unq_cols_per_item(long long M);

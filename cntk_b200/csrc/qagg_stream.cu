@@ -42,10 +42,7 @@ constexpr int ST_U = 2;                                // 16-byte positions per 
 constexpr int ST_TILE_VALUES = 4 * ST_U * ST_ETHREADS; // 1536 values per chunk
 constexpr int ST_IN_FLOATS = ST_TILE_VALUES;           // input tile: dense box, column stride R
 constexpr int ST_V_FLOATS = ST_TILE_VALUES + 4 * QAGG_STREAM_CMAX; // walkers' tile: column stride R + 4
-#ifndef QAGG_ST_CTAS
-#define QAGG_ST_CTAS 3
-#endif
-constexpr int ST_CTAS_PER_SM = QAGG_ST_CTAS;
+constexpr int ST_CTAS_PER_SM = 3;
 // input ring slots: 1 being formed, the others in flight (the owner kernel has less shared memory to spare)
 __host__ __device__ constexpr int stream_in_stages(bool stripes)
 {
@@ -96,14 +93,14 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
 // Bounded wait for the phase of `bar` with the given parity to complete.  After ST_WAIT_TRIES tries it gives up: the
 // CTA-wide flag *broken makes every later wait return at once, and bit 1 of *status tells the host.
 constexpr int ST_WAIT_TRIES = 1 << 22;
-__device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity, unsigned* broken, unsigned* status)
+__device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity, unsigned* broken, unsigned* status, int maxTries = ST_WAIT_TRIES)
 {
     if (mbar_try_wait(bar, parity))
         return;
     if (*reinterpret_cast<volatile unsigned*>(broken))
         return;
     // not there yet: poll with the warp asleep in between, so that the waiting costs the other warps no issue slots
-    for (int tries = 0; tries < ST_WAIT_TRIES; ++tries)
+    for (int tries = 0; tries < maxTries; ++tries)
     {
         __nanosleep(128);
         if (mbar_try_wait(bar, parity))
@@ -741,6 +738,38 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
                 asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
         }
     }
+}
+
+// One warp waits, with the streaming kernel's own bounded wait, for an mbarrier phase that nothing completes: the wait
+// runs out after `maxTries` polls, sets bit 1 of *status, and the kernel ends normally.  A second wait then returns at
+// once (the CTA-wide "broken" flag).  polls[0] / polls[1] receive the clock cycles the two waits took.
+__global__ void k_stream_wait_selftest(int maxTries, unsigned* __restrict__ status, long long* __restrict__ cycles)
+{
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ unsigned broken;
+    if (threadIdx.x == 0)
+    {
+        mbar_init(&bar, 1u);
+        broken = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const long long t0 = clock64();
+    mbar_wait(&bar, 0u, &broken, status, maxTries);
+    const long long t1 = clock64();
+    mbar_wait(&bar, 0u, &broken, status, maxTries);
+    const long long t2 = clock64();
+    if (threadIdx.x == 0 && cycles)
+    {
+        cycles[0] = t1 - t0;
+        cycles[1] = t2 - t1;
+    }
+}
+
+cudaError_t launch_stream_wait_selftest(cudaStream_t st, int maxTries, unsigned* status, long long* cycles)
+{
+    k_stream_wait_selftest<<<1, 32, 0, st>>>(maxTries, status, cycles);
+    return cudaGetLastError();
 }
 
 // the residual proper of a deferred state, element by element (export, checkpoint, tests)

@@ -18,7 +18,7 @@ PEER_HANDLE_BYTES = 64
 EXPORTS = [
     "qagg_last_error", "qagg_abi_version", "qagg_packed_col_bytes", "qagg_packed_bytes", "qagg_stripe",
     "qagg_quantize", "qagg_unquantize", "qagg_reduce_requantize", "qagg_quantize_batch_noalloc", "qagg_quantize_to_host", "qagg_unquantize_from_host",
-    "qagg_plan_create", "qagg_plan_stream_items", "qagg_plan_region_bytes", "qagg_plan_tensor_offset", "qagg_plan_gather_slot_bytes", "qagg_plan_destroy",
+    "qagg_plan_create", "qagg_plan_stream_items", "qagg_stream_wait_selftest", "qagg_plan_region_bytes", "qagg_plan_tensor_offset", "qagg_plan_gather_slot_bytes", "qagg_plan_destroy",
     "qagg_unique_id", "qagg_comm_create", "qagg_comm_create_local_group", "qagg_comm_allreduce_f64", "qagg_comm_barrier", "qagg_comm_rank", "qagg_comm_size",
     "qagg_comm_destroy", "qagg_agg_create", "qagg_agg_step", "qagg_agg_step_group", "qagg_agg_step_host",
     "qagg_agg_reset_residuals", "qagg_agg_residuals", "qagg_agg_copy_residual", "qagg_agg_copy_packed", "qagg_agg_wire_bytes",
@@ -59,6 +59,7 @@ _lib.qagg_plan_tensor_offset.argtypes = [c_vp, c_int, c_int]
 _lib.qagg_plan_gather_slot_bytes.restype = c_i64
 _lib.qagg_plan_gather_slot_bytes.argtypes = [c_vp]
 _lib.qagg_plan_destroy.argtypes = [c_vp]
+_lib.qagg_stream_wait_selftest.argtypes = [c_vp, c_int, c_vp, c_vp]
 _lib.qagg_plan_stream_items.restype = c_i64
 _lib.qagg_plan_stream_items.argtypes = [c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, c_int, c_int, ctypes.POINTER(ctypes.c_int32), c_i64]
 _lib.qagg_unique_id.argtypes = [c_vp]
@@ -212,6 +213,10 @@ def stream_items(shapes, bits=1, num_sms=148, packed_sources=0):
     if n2 < 0:
         _ok(n2)
     return [(buf[3 * k], buf[3 * k + 1], buf[3 * k + 2]) for k in range(n)]
+
+
+def stream_wait_selftest(max_tries, status_ptr, cycles_ptr=0, stream=0):
+    _ok(_lib.qagg_stream_wait_selftest(stream, max_tries, status_ptr, cycles_ptr))
 
 
 def wait_flags(flags_ptr, n, skip, value, max_polls, status_ptr, stream=0):

@@ -222,6 +222,11 @@ int qagg_agg_peer_handle(qagg_aggregator* a, void* out);
 int qagg_agg_enable_peer(qagg_aggregator* a, const void* handles);
 int qagg_agg_set_wait_limit(qagg_aggregator* a, long long max_polls);
 int qagg_agg_check(qagg_aggregator* a, void* stream);
+/* Failure detection of the streaming quantize kernel, exercised without a fault: one warp runs the kernel's own bounded
+ * wait on an mbarrier phase that nothing will ever complete.  After `max_tries` polls the wait gives up, ORs 2 into
+ * *status_dev and the kernel ends normally; a second wait in the same kernel returns at once.  cycles_dev (2 x int64,
+ * may be NULL) receives the clock cycles each wait took.  No reference counterpart. */
+int qagg_stream_wait_selftest(void* stream, int max_tries, unsigned* status_dev, long long* cycles_dev);
 /* The bounded wait on its own: one warp polls flags_dev[i] (i < n <= 32, i != skip) until each is >= value or max_polls
  * polls have passed; on give-up it ORs 1 into *status_dev.  Never hangs. */
 int qagg_wait_flags(void* stream, const unsigned* flags_dev, int n, int skip, unsigned value, long long max_polls, unsigned* status_dev);

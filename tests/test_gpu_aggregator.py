@@ -130,6 +130,23 @@ def test_bounded_wait_gives_up_and_reports(G):
     assert int(status.item()) == 0
 
 
+def test_streaming_kernel_wait_gives_up_and_reports(G):
+    """The streaming quantize kernel waits on mbarriers for its copies into shared memory; every such wait is bounded.
+    Here the kernel's own wait runs on a barrier that nothing completes: it gives up after the given number of polls, sets
+    bit 1 of the status word and returns; a second wait in the same kernel returns at once; the context stays usable."""
+    from cntk_b200 import lib
+    status = torch.zeros(1, dtype=torch.int32, device=G.DEV)
+    cycles = torch.zeros(2, dtype=torch.int64, device=G.DEV)
+    lib.stream_wait_selftest(200, status.data_ptr(), cycles.data_ptr())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 2
+    first, second = [int(x) for x in cycles.tolist()]
+    assert first > 200 * 100, "200 polls with a sleep in between take a while"
+    assert second < first // 20, "once a wait has run out, later waits do not wait again"
+    # the device is fine afterwards
+    assert int((torch.ones(4, device=G.DEV) * 2).sum().item()) == 8
+
+
 @pytest.mark.parametrize("K", [1, 2, 3, 4, 8])
 @pytest.mark.parametrize("bits,zero_thr", [(1, True), (1, False), (2, True), (4, True)])
 @pytest.mark.parametrize("self_quant", [True, False])
