@@ -49,6 +49,10 @@ def test_bad_arguments(lib):
     with pytest.raises(lib.QaggError):
         lib.quantize(16, 16, 16, 16, 8, 8, 5, True)
     assert "power of two" in lib.last_error()
+    with pytest.raises(lib.QaggError):
+        lib.stream_wait_selftest(10, 0)        # no status word
+    with pytest.raises(lib.QaggError):
+        lib.stream_wait_selftest(0, 16)        # at least one poll
 
 
 def test_no_cpu_fallback(lib):
@@ -60,3 +64,6 @@ def test_no_cpu_fallback(lib):
     assert "qagg error -2" in str(e.value)
     with pytest.raises(lib.QaggError):
         lib.Comm.create(None, 0, 1, 0)
+    with pytest.raises(lib.QaggError) as e:
+        lib.stream_wait_selftest(10, 16)       # valid arguments, but no device to launch on
+    assert "qagg error -2" in str(e.value)
