@@ -42,7 +42,13 @@ constexpr int ST_U = 2;                                // 16-byte positions per 
 constexpr int ST_TILE_VALUES = 4 * ST_U * ST_ETHREADS; // 1536 values per chunk
 constexpr int ST_IN_FLOATS = ST_TILE_VALUES;           // input tile: dense box, column stride R
 constexpr int ST_V_FLOATS = ST_TILE_VALUES + 4 * QAGG_STREAM_CMAX; // walkers' tile: column stride R + 4
-constexpr int ST_CTAS_PER_SM = 3;
+// resident CTAs per SM: three for the quantize kernel; two for the owner kernel, whose element warps need more than the 72
+// registers that three CTAs of 288 threads leave (spilled registers are costly here: with this much shared memory in use
+// the L1 cache that backs them is almost gone)
+__host__ __device__ constexpr int stream_ctas_per_sm(bool stripes)
+{
+    return stripes ? 2 : 3;
+}
 // input ring slots: 1 being formed, the others in flight (the owner kernel has less shared memory to spare)
 __host__ __device__ constexpr int stream_in_stages(bool stripes)
 {
@@ -189,7 +195,7 @@ __device__ __forceinline__ int stream_geometry(const QTensor& T, int ncols)
 }
 
 template <bool STRIPES>
-__global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
+__global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream1(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
                                                                      unsigned* __restrict__ counters, const Signal signal, unsigned* __restrict__ status)
 {
     constexpr int SIN = stream_in_stages(STRIPES);
@@ -814,7 +820,7 @@ void stream_make_items(const std::vector<std::pair<long long, long long>>& shape
     long long total = 0;
     for (auto& sh : shapes)
         total += sh.first * sh.second;
-    const long long slots = (long long) numSMs * ST_CTAS_PER_SM;
+    const long long slots = (long long) numSMs * stream_ctas_per_sm(packedSources > 0);
     long long target = total / (2 * slots > 0 ? 2 * slots : 1);
     target = target < 4096 ? 4096 : (target > 49152 ? 49152 : target);
     struct Cand
@@ -947,7 +953,7 @@ cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors
         return cudaErrorInvalidValue;
     if (nItems <= 0)
         return signal.n > 0 ? launch_signal_only(st, signal) : cudaSuccess;
-    int grid = cfg.numSMs * ST_CTAS_PER_SM;
+    int grid = cfg.numSMs * stream_ctas_per_sm(stripes);
     if (grid > nItems)
         grid = nItems;
     cudaError_t e;
