@@ -165,9 +165,10 @@ struct qagg_aggregator
     std::vector<float*> lv, slv;
     // device tables and their host mirrors
     std::vector<QTensor> hK1, hK2, hK3;
-    std::vector<QItem> iK1, iK2, iK3;
+    std::vector<QItem> iK1, iK2;
+    long long k3Units = 0; // work units of the unquantize launch
     QTensor *dK1 = nullptr, *dK2 = nullptr, *dK3 = nullptr;
-    QItem *dI1 = nullptr, *dI2 = nullptr, *dI3 = nullptr;
+    QItem *dI1 = nullptr, *dI2 = nullptr;
     DevBuf queue; // three pairs of work-queue counters (one pair per kernel), zero when no kernel is running
     std::vector<int> k2Tensor; // tensor index of each K2 table entry
     // The device tables (and tensor maps) hold the gradient pointers.  Two sets are kept, each bound to one array of
@@ -177,7 +178,7 @@ struct qagg_aggregator
     {
         std::vector<float*> grads;
         QTensor *dK1 = nullptr, *dK2 = nullptr, *dK3 = nullptr;
-        QItem *dI1 = nullptr, *dI2 = nullptr, *dI3 = nullptr;
+        QItem *dI1 = nullptr, *dI2 = nullptr;
     };
     Binding bindings[2];
     int curBinding = 0;
@@ -276,11 +277,17 @@ int build_tables(qagg_aggregator* a)
     const int K = a->comm->K, r = a->comm->rank, T = a->T;
     a->hK1.assign(T, QTensor{});
     a->hK3.assign(T, QTensor{});
+    a->k3Units = 0;
+    for (int i = 0; i < T; ++i)
+    {
+        // every entry, empty matrices included, carries the running unit count (the kernel searches this column)
+        a->hK3[i].unit0 = a->k3Units;
+        a->k3Units += unq_units(a->M[i], a->N[i]);
+    }
     a->hK2.clear();
     a->k2Tensor.clear();
     a->iK1.clear();
     a->iK2.clear();
-    a->iK3.clear();
     std::vector<std::pair<int64_t, QItem>> cost1, cost2;
     std::vector<std::pair<int64_t, int64_t>> shapes1, shapes2;
     for (int i = 0; i < T; ++i)
@@ -305,7 +312,9 @@ int build_tables(qagg_aggregator* a)
         q1.per = N / K;
         q1.rem = N % K;
         QTensor& q3 = a->hK3[i];
+        const long long unit0 = q3.unit0;
         q3 = q1;
+        q3.unit0 = unit0;
         q3.res_in = nullptr;
         q3.res_out = nullptr;
         q3.lv = nullptr;
@@ -326,7 +335,6 @@ int build_tables(qagg_aggregator* a)
             make_items(tmp, i, M, N, c1[i]);
             for (auto& it : tmp)
                 cost1.push_back({M * it.ncols, it});
-            make_items(a->iK3, i, M, N, unq_cols_per_item(M));
         }
         if (K > 1 && a->sN[r][i] > 0)
         {
@@ -393,7 +401,7 @@ int build_tables(qagg_aggregator* a)
 size_t table_bytes(const qagg_aggregator* a)
 {
     return (a->hK1.size() + a->hK2.size() + a->hK3.size()) * sizeof(QTensor) +
-           (a->iK1.size() + a->iK2.size() + a->iK3.size()) * sizeof(QItem) + 256;
+           (a->iK1.size() + a->iK2.size()) * sizeof(QItem) + 256;
 }
 
 // copies the host tables to table set `slot` on the device (synchronously: only when a new array of gradient pointers is bound)
@@ -423,8 +431,6 @@ int upload_tables(qagg_aggregator* a, int slot)
         return rc;
     if ((rc = put(a->iK2.data(), a->iK2.size() * sizeof(QItem), (void**) &a->dI2)))
         return rc;
-    if ((rc = put(a->iK3.data(), a->iK3.size() * sizeof(QItem), (void**) &a->dI3)))
-        return rc;
     return QAGG_OK;
 }
 
@@ -444,7 +450,6 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
             a->dK3 = b.dK3;
             a->dI1 = b.dI1;
             a->dI2 = b.dI2;
-            a->dI3 = b.dI3;
             return QAGG_OK;
         }
     }
@@ -493,7 +498,6 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
     b.dK3 = a->dK3;
     b.dI1 = a->dI1;
     b.dI2 = a->dI2;
-    b.dI3 = a->dI3;
     a->curBinding = slot;
     return QAGG_OK;
 }
@@ -552,8 +556,7 @@ int wait_peers(qagg_aggregator* a, bool gatherPhase, cudaStream_t st)
 }
 int launch_k3(qagg_aggregator* a, cudaStream_t st)
 {
-    return check_cuda(launch_unquantize(st, false, nullptr, a->dK3, a->dI3, (int) a->iK3.size(), 0, a->cfg,
-                                        static_cast<unsigned*>(a->queue.p) + 2 * QAGG_COUNTER_UINTS), "unquantize launch");
+    return check_cuda(launch_unquantize(st, false, nullptr, a->dK3, (int) a->hK3.size(), a->k3Units, a->cfg), "unquantize launch");
 }
 
 } // namespace
@@ -1006,12 +1009,15 @@ int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* cons
     for (int r = 0; r < K; ++r)
         if (aggs[r]->peer != peer)
             return fail(QAGG_ESTATE, "qagg_agg_step_group: peer mode must be enabled on all ranks or on none");
+    // Per-phase timing (qagg_agg_set_profiling) on a local group: the events bracket each rank's own three kernels, so
+    // phases 0, 2 and 4 (quantize, reduce-requantize, unquantize) are that rank's kernel times; phases 1 and 3 then span
+    // the other ranks' kernels and mean nothing here.
     for (int r = 0; r < K; ++r)
     {
         if ((rc = bind_grads(aggs[r], grads[r], st)))
             return rc;
         aggs[r]->stepNo++;
-        if ((rc = launch_k1(aggs[r], st)))
+        if ((rc = aggs[r]->mark(0, st)) || (rc = launch_k1(aggs[r], st)) || (rc = aggs[r]->mark(1, st)))
             return rc;
     }
     if (K > 1 && peer)
@@ -1022,7 +1028,7 @@ int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* cons
             if ((rc = wait_peers(aggs[r], false, st)))
                 return rc;
         for (int r = 0; r < K; ++r)
-            if ((rc = launch_k2(aggs[r], st)))
+            if ((rc = aggs[r]->mark(2, st)) || (rc = launch_k2(aggs[r], st)) || (rc = aggs[r]->mark(3, st)))
                 return rc;
         for (int r = 0; r < K; ++r)
             if ((rc = wait_peers(aggs[r], true, st)))
@@ -1038,7 +1044,7 @@ int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* cons
                                                          cudaMemcpyDeviceToDevice, st), "stripe copy")))
                         return rc;
         for (int r = 0; r < K; ++r)
-            if ((rc = launch_k2(aggs[r], st)))
+            if ((rc = aggs[r]->mark(2, st)) || (rc = launch_k2(aggs[r], st)) || (rc = aggs[r]->mark(3, st)))
                 return rc;
         // all-gather: gather slot r of rank r -> gather slot r of every other rank
         for (int r = 0; r < K; ++r)
@@ -1049,8 +1055,14 @@ int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* cons
                         return rc;
     }
     for (int r = 0; r < K; ++r)
-        if ((rc = launch_k3(aggs[r], st)))
+    {
+        if (K == 1 && ((rc = aggs[r]->mark(2, st)) || (rc = aggs[r]->mark(3, st))))
             return rc;
+        if ((rc = aggs[r]->mark(4, st)) || (rc = launch_k3(aggs[r], st)) || (rc = aggs[r]->mark(5, st)))
+            return rc;
+        if (aggs[r]->profiling)
+            aggs[r]->profSteps++;
+    }
     return QAGG_OK;
 }
 

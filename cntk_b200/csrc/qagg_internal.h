@@ -43,6 +43,7 @@ struct QTensor
     // items of up to boxCols[1] < boxCols[0] columns (0: no such items).  All null: the matrix is fetched with plain loads.
     const void* tm[2][2];
     int boxCols[2];
+    long long unit0; // unquantize kernel only: number of work units of the table entries before this one
 };
 
 // Flags that the last CTA of a kernel writes (release, system scope) after all of the kernel's stores: one word in each
@@ -105,8 +106,11 @@ cudaError_t launch_push(cudaStream_t st, const void* src, size_t bytes, const Si
 // one warp polls flags[i] (i < n, i != skip) until each is >= value (wrap-safe) or maxPolls polls have passed; on
 // give-up it ORs 1 into *status and returns: the context stays usable and the host reads the status later
 cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status);
-cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, const QTensor* tensors,
-                              const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters = nullptr);
+// unquantize (qagg_unquantize.cu): `single` != nullptr: one matrix described by value; otherwise `tensors` is a device table
+// of nTensors entries whose unit0 fields are the running sums of unq_units() (entry order = unit order)
+cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, const QTensor* tensors, int nTensors, long long totalUnits,
+                              const LaunchCfg& cfg);
+long long unq_units(long long M, long long N); // work units of an M x N matrix in the unquantize kernel
 cudaError_t get_launch_cfg(int device, LaunchCfg* cfg);
 // releases the flags of `signal` from a one-thread kernel (a rank with nothing to compute still has to tell its peers)
 cudaError_t launch_signal_only(cudaStream_t st, const Signal& signal);
@@ -149,7 +153,6 @@ cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors
 cudaError_t launch_stream_wait_selftest(cudaStream_t st, int maxTries, unsigned* status, long long* cycles);
 // dst[i, j] = buf[i, j] - (buf[i, j] >= 0 ? lv[2j + 1] : lv[2j]): the residual proper of a deferred state (dst may be buf)
 cudaError_t launch_materialize(cudaStream_t st, const float* buf, const float* lv, float* dst, long long M, long long N, int numSMs);
-int unq_cols_per_item(long long M);
 
 // error plumbing (qagg_capi.cu)
 int fail(int code, const std::string& msg);

@@ -19,20 +19,6 @@
 namespace qagg {
 
 constexpr int CMAX = 128;   // most columns in one work item
-constexpr int UNQ_CMAX = 4096;
-
-// optional phase timers for development builds (-DQAGG_PROBE); they expand to nothing in the product
-#ifdef QAGG_PROBE
-__device__ unsigned long long g_probe[16];
-__device__ int g_walkerForce = -1;
-#define PROBE_MARK(var) const long long var = clock64()
-#define PROBE_ADD(i, a, b) \
-    if (threadIdx.x == 0)  \
-    atomicAdd(&g_probe[i], (unsigned long long) ((b) - (a)))
-#else
-#define PROBE_MARK(var)
-#define PROBE_ADD(i, a, b)
-#endif
 
 // per-item scratch that lives behind the staged columns in dynamic shared memory
 struct ColStats
@@ -374,13 +360,7 @@ __device__ __forceinline__ void walk_resident(const QTensor& T, int nc, int stri
             const float* vcol = smem + (size_t) col * stride;
             if (warp == wl)
             {
-                PROBE_MARK(w0);
                 S.a0[col] = walk_rows<WALK_MIN0>(vcol, M, 0.0f, cnt, 0.0f, false);
-                PROBE_MARK(w1);
-#ifdef QAGG_PROBE
-                if (lane == 0)
-                    atomicAdd(&g_probe[4], (unsigned long long) (w1 - w0));
-#endif
             }
             else
             {
@@ -588,10 +568,6 @@ __global__ void __launch_bounds__(NT, QAGG_CTAS_PER_SM) k_colquant(const QTensor
             ticket = blockIdx.x / (unsigned) max(numSMs, 1);
         }
         sWalker = (int) (ticket & 3u);
-#ifdef QAGG_PROBE
-        if (g_walkerForce >= 0)
-            sWalker = g_walkerForce;
-#endif
     }
     __syncthreads();
     const int walkerWarp = sWalker;
@@ -653,14 +629,12 @@ __global__ void __launch_bounds__(NT, QAGG_CTAS_PER_SM) k_colquant(const QTensor
 
         if (resident)
         {
-            PROBE_MARK(t0);
             if (STRIPES)
                 fill_stripes<MODE>(T, col0, nc, stride, smem, S,
                                    stagePacked ? reinterpret_cast<unsigned*>(smem + (size_t) nc * (stride + COLSTAT_FLOATS)) : nullptr);
             else
                 fill_dense<MODE>(T, col0, nc, stride, smem, S);
             __syncthreads();
-            PROBE_MARK(t1);
             walk_resident<MODE>(T, nc, stride, smem, S, walkerWarp);
             __syncthreads();
             if (MODE == MODE_ONEBIT_ZERO)
@@ -674,13 +648,7 @@ __global__ void __launch_bounds__(NT, QAGG_CTAS_PER_SM) k_colquant(const QTensor
                 }
                 __syncthreads();
             }
-            PROBE_MARK(t2);
             quantize_resident<MODE>(T, signal, col0, nc, stride, smem, S);
-            PROBE_MARK(t3);
-            PROBE_ADD(0, t0, t1);
-            PROBE_ADD(1, t1, t2);
-            PROBE_ADD(2, t2, t3);
-            PROBE_ADD(3, 0, 1);
         }
         else
         {
@@ -778,225 +746,6 @@ __global__ void k_wait_flags(const unsigned* __restrict__ flags, int n, int skip
     __threadfence_system();
 }
 
-// =================================================================================================================
-// Unquantize kernel (UnquantizeOneQWord, ColumnQuantizer.h:150-203).  Every thread fetches the header and the packed
-// words of several tasks before it uses any of them (the loads of a task depend on nothing but its index), then
-// expands them:
-//   Q % 4 == 0 and 16-byte aligned rows: task = four adjacent packed words, one float4 store per bit position;
-//   otherwise                          : task = one packed word, the warp stores 32 consecutive rows per bit position.
-// =================================================================================================================
-template <bool ADD>
-__device__ __forceinline__ void store_out4(float* p, float4 v)
-{
-    if (ADD)
-    {
-        const float4 o = *reinterpret_cast<const float4*>(p);
-        v.x = __fadd_rn(v.x, o.x);
-        v.y = __fadd_rn(v.y, o.y);
-        v.z = __fadd_rn(v.z, o.z);
-        v.w = __fadd_rn(v.w, o.w);
-        *reinterpret_cast<float4*>(p) = v;
-    }
-    else
-    {
-        __stcs(reinterpret_cast<float4*>(p), v);
-    }
-}
-
-// the two constants unquantizing needs: 1 bit -> the two level values; else -> (ufactor, quantimin)
-__device__ __forceinline__ void unq_consts(int bits, float lower, float upper, float& ca, float& cb)
-{
-    if (bits == 1)
-    {
-        levels_1bit(lower, upper, ca, cb);
-    }
-    else
-    {
-        const ValQ q = make_valq(bits, lower, upper);
-        ca = q.ufactor;
-        cb = q.qmin;
-    }
-}
-
-__device__ __forceinline__ float unq_fast(int bits, unsigned field, float ca, float cb)
-{
-    if (bits == 1)
-        return field ? cb : ca;
-    if (bits == 32)
-        return __uint_as_float(field);
-    return __fadd_rn(__fmul_rn(__fadd_rn((float) field, 0.5f), ca), cb);
-}
-
-template <bool ADD, bool TABLE>
-__global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, const QTensor* __restrict__ tensors,
-                                                   const QItem* __restrict__ items, int nItems, int colsPerItem,
-                                                   unsigned* __restrict__ counters)
-{
-    __shared__ QTensor sT;
-    __shared__ int sIt;
-    for (int iter = 0;; ++iter)
-    {
-        __syncthreads();
-        if (threadIdx.x == 0)
-            sIt = counters ? (int) atomicAdd(&counters[0], 1u) : (int) (blockIdx.x + (unsigned) iter * gridDim.x);
-        __syncthreads();
-        const int it = sIt;
-        if (it >= nItems)
-            break;
-        int col0, nc;
-        if (TABLE)
-        {
-            const QItem item = items[it];
-            col0 = item.col0;
-            nc = item.ncols;
-            const int* srcw = reinterpret_cast<const int*>(tensors + item.tensor);
-            int* dstw = reinterpret_cast<int*>(&sT);
-            for (int i = threadIdx.x; i < (int) (sizeof(QTensor) / sizeof(int)); i += NT)
-                dstw[i] = srcw[i];
-        }
-        else
-        {
-            col0 = it * colsPerItem;
-            nc = (int) min((long long) colsPerItem, single.N - col0);
-            if (threadIdx.x == 0)
-                sT = single;
-        }
-        __syncthreads();
-        const QTensor& T = sT;
-        const int M = (int) T.M;
-        const int Q = T.Q;
-        const int bits = T.bits;
-        const int vpw = 32 / bits;
-        const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
-        float* __restrict__ out0 = T.out + (size_t) col0 * M;
-        const bool aligned = ((M & 3) == 0) && ((reinterpret_cast<uintptr_t>(T.out) & 15) == 0);
-        if (aligned && ((Q & 3) == 0))
-        {
-            constexpr int U = 2;
-            const int Q4 = Q >> 2;
-            const int total = nc * Q4;
-            for (int t0 = threadIdx.x; t0 < total; t0 += NT * U)
-            {
-                unsigned wd[U][4];
-                float lo[U], up[U];
-                int colU[U], wU[U];
-#pragma unroll
-                for (int u = 0; u < U; ++u)
-                {
-                    const int t = t0 + u * NT;
-                    if (t < total)
-                    {
-                        colU[u] = t / Q4;
-                        wU[u] = (t - colU[u] * Q4) * 4;
-                        const unsigned char* colp = packed_col(T, col0 + colU[u]);
-                        lo[u] = __ldg(reinterpret_cast<const float*>(colp));
-                        up[u] = __ldg(reinterpret_cast<const float*>(colp) + 1);
-                        const unsigned* words = reinterpret_cast<const unsigned*>(colp + 8) + wU[u];
-                        wd[u][0] = __ldg(words);
-                        wd[u][1] = __ldg(words + 1);
-                        wd[u][2] = __ldg(words + 2);
-                        wd[u][3] = __ldg(words + 3);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < U; ++u)
-                {
-                    const int t = t0 + u * NT;
-                    if (t < total)
-                    {
-                        float ca, cb;
-                        unq_consts(bits, lo[u], up[u], ca, cb);
-                        float* __restrict__ op = out0 + (size_t) colU[u] * M + wU[u];
-                        const int nk = min(vpw, (M - wU[u] + Q - 1) / Q);
-#pragma unroll 4
-                        for (int k = 0; k < nk; ++k)
-                        {
-                            const int sh = k * bits;
-                            float4 v;
-                            v.x = unq_fast(bits, (wd[u][0] >> sh) & mask, ca, cb);
-                            v.y = unq_fast(bits, (wd[u][1] >> sh) & mask, ca, cb);
-                            v.z = unq_fast(bits, (wd[u][2] >> sh) & mask, ca, cb);
-                            v.w = unq_fast(bits, (wd[u][3] >> sh) & mask, ca, cb);
-                            store_out4<ADD>(op + k * Q, v);
-                        }
-                    }
-                }
-            }
-        }
-        else
-        {
-            constexpr int U = 4;
-            const int total = nc * Q;
-            for (int t0 = threadIdx.x; t0 < total; t0 += NT * U)
-            {
-                unsigned wd[U];
-                float lo[U], up[U];
-                int colU[U], wU[U];
-#pragma unroll
-                for (int u = 0; u < U; ++u)
-                {
-                    const int t = t0 + u * NT;
-                    if (t < total)
-                    {
-                        colU[u] = t / Q;
-                        wU[u] = t - colU[u] * Q;
-                        const unsigned char* colp = packed_col(T, col0 + colU[u]);
-                        lo[u] = __ldg(reinterpret_cast<const float*>(colp));
-                        up[u] = __ldg(reinterpret_cast<const float*>(colp) + 1);
-                        wd[u] = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + wU[u]);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < U; ++u)
-                {
-                    const int t = t0 + u * NT;
-                    if (t < total)
-                    {
-                        float ca, cb;
-                        unq_consts(bits, lo[u], up[u], ca, cb);
-                        float* __restrict__ op = out0 + (size_t) colU[u] * M + wU[u];
-                        const int nk = min(vpw, (M - wU[u] + Q - 1) / Q);
-                        const unsigned word = wd[u];
-                        if (bits == 1)
-                        {
-#pragma unroll 8
-                            for (int k = 0; k < nk; ++k)
-                            {
-                                float val = ((word >> k) & 1u) ? cb : ca;
-                                if (ADD)
-                                    val = __fadd_rn(val, op[k * Q]);
-                                op[k * Q] = val;
-                            }
-                        }
-                        else
-                        {
-#pragma unroll 4
-                            for (int k = 0; k < nk; ++k)
-                            {
-                                float val = unq_fast(bits, (word >> (k * bits)) & mask, ca, cb);
-                                if (ADD)
-                                    val = __fadd_rn(val, op[k * Q]);
-                                op[k * Q] = val;
-                            }
-                        }
-                    }
-                }
-            }
-        }
-    }
-    if (counters && threadIdx.x == 0)
-    {
-        __threadfence();
-        const unsigned done = atomicAdd(&counters[1], 1u);
-        if (done == gridDim.x - 1)
-        {
-            counters[0] = 0;
-            counters[1] = 0;
-            __threadfence();
-        }
-    }
-}
-
 // ---- host side ------------------------------------------------------------------------------------------------
 
 int cols_per_item(long long M, long long N, int smemFloats, bool* resident, int extraFloatsPerCol)
@@ -1019,16 +768,6 @@ int cols_per_item(long long M, long long N, int smemFloats, bool* resident, int 
         c = 1;
     if (resident)
         *resident = res;
-    return (int) c;
-}
-
-int unq_cols_per_item(long long M)
-{
-    long long c = 32768 / (M > 0 ? M : 1);
-    if (c < 1)
-        c = 1;
-    if (c > UNQ_CMAX)
-        c = UNQ_CMAX;
     return (int) c;
 }
 
@@ -1140,34 +879,6 @@ cudaError_t launch_colquant(cudaStream_t st, bool stripes, int mode, const QTens
     QAGG_CASE(true, MODE_MULTIBIT, true)
 #undef QAGG_CASE
     return cudaErrorInvalidValue;
-}
-
-cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, const QTensor* tensors,
-                              const QItem* items, int nItems, int colsPerItem, const LaunchCfg& cfg, unsigned* counters)
-{
-    if (nItems <= 0)
-        return cudaSuccess;
-    // one CTA per work item: the items are uniform and short, so the hardware block scheduler balances them better
-    // than a software queue whose every fetch costs a global round trip
-    int grid = nItems;
-    counters = nullptr;
-    static const QTensor zero = {};
-    const QTensor& s = single ? *single : zero;
-    if (single)
-    {
-        if (add)
-            k_unquantize<true, false><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem, counters);
-        else
-            k_unquantize<false, false><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem, counters);
-    }
-    else
-    {
-        if (add)
-            k_unquantize<true, true><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem, counters);
-        else
-            k_unquantize<false, true><<<grid, NT, 0, st>>>(s, tensors, items, nItems, colsPerItem, counters);
-    }
-    return cudaGetLastError();
 }
 
 cudaError_t get_launch_cfg(int device, LaunchCfg* cfg)

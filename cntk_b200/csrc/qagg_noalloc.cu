@@ -14,7 +14,10 @@
 //   * the first call on each device looks up the array's device address and zeroes the counters.  That first call
 //     should be made before any stream capture begins;
 //   * all calls share the one array and it keeps the previous call's tables: two calls whose kernels could overlap
-//     on the GPU (different streams, no dependency between them) race on it.  Calls on one stream are safe.
+//     on the GPU (different streams, no dependency between them) race on it.  Calls on one stream are safe;
+//   * the tables of a call are built in about 62 KB of the calling thread's stack and uploaded from there, so the
+//     call needs that much stack, and a call on a stream that is being captured is refused with QAGG_ESTATE (the
+//     recorded copy would point into a stack frame that no longer exists when the graph runs).
 #include "../../include/qagg.h"
 #include "qagg_internal.h"
 
@@ -94,6 +97,15 @@ extern "C" int qagg_quantize_batch_noalloc(void* stream, int num_matrices, const
     int rc = setup_current_device(&s);
     if (rc)
         return rc;
+    {
+        // the table uploads below read this call's stack frame: they must run now, not when a captured graph is replayed
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if ((rc = check_cuda(cudaStreamIsCapturing((cudaStream_t) stream, &cap), "cudaStreamIsCapturing")))
+            return rc;
+        if (cap != cudaStreamCaptureStatusNone)
+            return fail(QAGG_ESTATE, "qagg_quantize_batch_noalloc: the stream is being captured; this entry point uploads its tables from the "
+                                     "caller's stack and cannot be recorded into a graph");
+    }
 
     // tables are built on the stack: nothing is allocated on the host either
     QTensor tensors[kMaxMatrices];
@@ -110,6 +122,9 @@ extern "C" int qagg_quantize_batch_noalloc(void* stream, int num_matrices, const
             continue;
         if (!grads[i] || !res_in[i] || !res_out[i] || !packed[i])
             return fail(QAGG_EINVAL, "qagg_quantize_batch_noalloc: null pointer");
+        if ((reinterpret_cast<uintptr_t>(packed[i]) & 3) || (reinterpret_cast<uintptr_t>(grads[i]) & 3) || (reinterpret_cast<uintptr_t>(res_in[i]) & 3) ||
+            (reinterpret_cast<uintptr_t>(res_out[i]) & 3))
+            return fail(QAGG_EINVAL, "qagg_quantize_batch_noalloc: buffers must be 4-byte aligned");
         t.grad = grads[i];
         t.res_in = res_in[i];
         t.res_out = res_out[i];

@@ -176,18 +176,6 @@ __device__ __forceinline__ float deferred_residual(float prev, float lv0, float 
     return __fsub_rn(prev, (prev >= 0.0f) ? lv1 : lv0);
 }
 
-// optional timers for development builds: -DQAGG_PROBE records CTA lifetimes, -DQAGG_PROBE_PHASES also per-phase cycle
-// counts of one element thread per CTA (the counter array is defined in qagg_kernels.cu); nothing in the product
-#ifdef QAGG_PROBE_PHASES
-#define ST_MARK(var) const long long var = clock64()
-#define ST_ADD(i, a, b)  \
-    if (et == 0 && !isWalker) \
-    atomicAdd(&g_probe[i], (unsigned long long) ((b) - (a)))
-#else
-#define ST_MARK(var)
-#define ST_ADD(i, a, b)
-#endif
-
 // which of a descriptor's two tile geometries an item of `ncols` columns uses (the same answer on both sides of the ring)
 __device__ __forceinline__ int stream_geometry(const QTensor& T, int ncols)
 {
@@ -223,11 +211,6 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
     __shared__ float sSrc0[STRIPES ? QAGG_MAXK : 1][QAGG_STREAM_CMAX], sSrc1[STRIPES ? QAGG_MAXK : 1][QAGG_STREAM_CMAX];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-#ifdef QAGG_PROBE
-    const long long tKernel0 = clock64();
-    unsigned long long gt0;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0));
-#endif
     if (tid == 0)
     {
         // the walkers of the CTAs that share an SM sit on different warp pairs (a per-SM ticket that only ever grows)
@@ -412,7 +395,6 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
         bool more = adopt(0u);
         while (more)
         {
-            ST_MARK(tItem0);
             const QTensor& T = *Tp;
             const int nsrc = STRIPES ? T.nsrc : 0;
             const int firstPacked = hasG ? 1 : 0;      // owner kernel: sources firstPacked .. nsrc - 1 are packed
@@ -595,11 +577,8 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
 
             // ---- the chunk loop: in iteration q, chunk q's values are formed and chunk q - 1 is walked -----------------------
             float acc = 0.0f; // a walker lane's running sum of its column
-            ST_MARK(tLoop0);
-            ST_ADD(0, tItem0, tLoop0);
             for (int q = 0; q <= nchunks; ++q)
             {
-                ST_MARK(tq0);
                 if (!isWalker)
                 {
                     if (vec && q >= 1 && warp == firstElementWarp && lane == 0)
@@ -617,11 +596,7 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
                                 mbar_wait(&sFull[p % SIN], (p / SIN) & 1u, &sBroken, status);
                             asm volatile("bar.sync 2, %0;" ::"n"(ST_ETHREADS) : "memory");
                         }
-                        ST_MARK(tq2);
-                        ST_ADD(2, tq0, tq2);
                         form(q);
-                        ST_MARK(tq3);
-                        ST_ADD(3, tq2, tq3);
                     }
                 }
                 else if (q >= 1)
@@ -637,13 +612,8 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
                             acc = walk_chunk<WALK_MAX0>(vcol, nrows, acc);
                     }
                 }
-                ST_MARK(tq4);
                 consumer_sync(); // chunk q is formed (next: walked), chunk q - 1 is walked (its tile may be overwritten)
-                ST_MARK(tq5);
-                ST_ADD(4, tq4, tq5);
-                ST_ADD(6, 0, 1);
             }
-            ST_MARK(tLoop1);
 
             // ---- finish ------------------------------------------------------------------------------------------------------
             if (isWalker)
@@ -708,27 +678,11 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
             consumer_sync(); // the item is done with its shared-memory state and with its descriptor buffer
             if (tid == 0)
                 mbar_arrive(&sMetaEmpty[itemNo % ST_DESC]);
-            ST_MARK(tItem1);
-            ST_ADD(5, tLoop1, tItem1);
-            ST_ADD(7, 0, 1);
             ++itemNo;
         }
     }
     __syncthreads();
 
-#ifdef QAGG_PROBE
-    if (tid == 0)
-    {
-        unsigned long long gt1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1));
-        atomicAdd(&g_probe[8], (unsigned long long) (clock64() - tKernel0)); // cycles this CTA lived
-        atomicAdd(&g_probe[9], gt1 - gt0);                                    // nanoseconds this CTA lived
-        atomicAdd(&g_probe[10], 1ull);
-        atomicMin(&g_probe[11], gt0);
-        atomicMax(&g_probe[12], gt1);
-        atomicMax(&g_probe[13], gt1 - gt0);
-    }
-#endif
     // The last CTA to leave re-arms the work counter for the next launch and releases the peers' flags: each CTA's
     // stores (into peer memory too) are ordered before its arrival by barrier + system-scope fence.
     if (tid == 0)

@@ -97,7 +97,9 @@ int qagg_reduce_requantize(void* stream, const void* const* stripes, int K, cons
  * 2048-row matrix uses one item per 9 columns) per call -- beyond that the call fails with QAGG_EINVAL and launches nothing.
  * The first call on each device also looks up the array's address and clears its counters: make that call before any
  * stream capture.  Every call reuses the same array, so two calls whose kernels may overlap on the GPU race; calls on one
- * stream are ordered and safe.  Calls no cudaMalloc / cudaFree. */
+ * stream are ordered and safe.  Calls no cudaMalloc / cudaFree.  The call builds its tables in about 62 KB of the calling
+ * thread's stack (mind small thread stacks) and uploads them from there; for that reason a call on a stream that is
+ * being captured is refused with QAGG_ESTATE. */
 #define QAGG_NOALLOC_MAX_MATRICES 32
 #define QAGG_NOALLOC_MAX_ITEMS 4096
 int qagg_quantize_batch_noalloc(void* stream, int num_matrices, const float* const* grads, const float* const* res_in,

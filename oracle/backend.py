@@ -21,9 +21,20 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _f32p = ctypes.POINTER(ctypes.c_float)
 
 
+def reference_root():
+    """Root of the CNTK checkout the reference-header checker is built from: $QAGG_REFERENCE_ROOT, else a sibling
+    `reference` directory of this repository's parent; None when neither holds the quantizer headers."""
+    cands = [os.environ.get("QAGG_REFERENCE_ROOT"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "Source", "Math", "ColumnQuantizer.h")):
+            return c
+    return None
+
+
 def build(quiet=True):
     """Run oracle/Makefile (gcc only; also builds _ref when the reference checkout exists)."""
-    out = subprocess.run(["make", "-C", _HERE], capture_output=True, text=True)
+    ref = reference_root()
+    out = subprocess.run(["make", "-C", _HERE] + ([f"REF={ref}"] if ref else []), capture_output=True, text=True)
     if out.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + out.stdout + out.stderr)
     if not quiet:
