@@ -158,9 +158,11 @@ struct qagg_aggregator
     // kernel, which keeps its residual set in deferred form: the buffer above holds the quantized values v, and lv (slv)
     // each column's two reconstruction values (see qagg_internal.h)
     bool deferred = false;      // quantize kernel: residuals `res`
-    bool deferredOwner = false; // owner kernel: stripe residuals `sres`
-    DevBuf tmaps;                        // tensor maps of the streaming descriptors (QAGG_STREAM_MAP_BYTES each)
-    std::vector<unsigned char> hostMaps; // their host mirror: quantize table entries first, then owner table entries
+    bool deferredOwner = false; // owner kernels (form + walk): stripe residuals `sres`
+    DevBuf tmaps;                        // tensor maps of the streaming quantize descriptors (QAGG_STREAM_MAP_BYTES each)
+    std::vector<unsigned char> hostMaps; // their host mirror
+    DevBuf ownMaps, ownStats;            // owner kernels: one tensor map per owned stripe; two counters per owned column
+    long long k2Units = 0;               // work units of the owner's form kernel
     DevBuf lvAll, slvAll;
     std::vector<float*> lv, slv;
     // device tables and their host mirrors
@@ -282,12 +284,13 @@ int build_tables(qagg_aggregator* a)
     {
         // every entry, empty matrices included, carries the running unit count (the kernel searches this column)
         a->hK3[i].unit0 = a->k3Units;
-        a->k3Units += unq_units(a->M[i], a->N[i]);
+        a->k3Units += unq_units(a->M[i], a->N[i], a->bits);
     }
     a->hK2.clear();
     a->k2Tensor.clear();
     a->iK1.clear();
     a->iK2.clear();
+    a->k2Units = 0;
     std::vector<std::pair<int64_t, QItem>> cost1, cost2;
     std::vector<std::pair<int64_t, int64_t>> shapes1, shapes2;
     for (int i = 0; i < T; ++i)
@@ -343,6 +346,13 @@ int build_tables(qagg_aggregator* a)
             q2.res_in = a->sres[i];
             q2.res_out = a->sres[i];
             q2.lv = a->deferredOwner ? a->slv[i] : nullptr;
+            if (a->deferredOwner)
+            {
+                // columns of the earlier tensors' stripes come first in the per-column arrays (slv is laid out the same way)
+                q2.stats = static_cast<unsigned*>(a->ownStats.p) + (a->slv[i] - static_cast<float*>(a->slvAll.p));
+                q2.unit0 = a->k2Units;
+                a->k2Units += owner_form_units(M, q2.N);
+            }
             q2.selfRaw = (a->flags & QAGG_SELF_QUANTIZED) ? 0 : 1;
             q2.nsrc = K;
             q2.src[0] = a->recv_slot(r) + a->tOff[r][i];
@@ -378,22 +388,25 @@ int build_tables(qagg_aggregator* a)
         for (int i = 0; i < T; ++i)
             k1Shapes.push_back({a->M[i], (a->M[i] > 0 && a->N[i] > 0) ? a->N[i] : 0});
         std::vector<std::pair<int, int>> box;
-        stream_make_items(k1Shapes, a->cfg.numSMs, a->bits, 0, a->iK1, box);
+        stream_make_items(k1Shapes, a->cfg.numSMs, a->bits, a->iK1, box);
         for (int i = 0; i < T; ++i)
         {
             a->hK1[i].boxCols[0] = box[i].first;
             a->hK1[i].boxCols[1] = box[i].second;
         }
-        if (a->deferredOwner)
-        {
-            stream_make_items(k2Shapes, a->cfg.numSMs, a->bits, (a->flags & QAGG_SELF_QUANTIZED) ? K : K - 1, a->iK2, box);
-            for (size_t e = 0; e < a->hK2.size(); ++e)
-            {
-                a->hK2[e].boxCols[0] = box[e].first;
-                a->hK2[e].boxCols[1] = box[e].second;
-            }
-        }
-        a->hostMaps.assign((a->hK1.size() + a->hK2.size()) * (size_t) QAGG_STREAM_MAP_BYTES, 0);
+        a->hostMaps.assign(a->hK1.size() * (size_t) QAGG_STREAM_MAP_BYTES, 0);
+    }
+    if (a->deferredOwner && !a->hK2.empty())
+    {
+        // the owner kernels: walk items, and one tensor map per owned stripe (it covers the stripe residual, whose address
+        // does not depend on the bound gradients, so it is made and uploaded here)
+        owner_make_items(k2Shapes, a->iK2);
+        std::vector<unsigned char> maps(a->hK2.size() * 128);
+        for (size_t e = 0; e < a->hK2.size(); ++e)
+            owner_set_map(&a->hK2[e], maps.data() + e * 128, static_cast<unsigned char*>(a->ownMaps.p) + e * 128);
+        int rc = check_cuda(cudaMemcpy(a->ownMaps.p, maps.data(), maps.size(), cudaMemcpyHostToDevice), "tensor map upload");
+        if (rc)
+            return rc;
     }
     return QAGG_OK;
 }
@@ -477,13 +490,7 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
         // the streaming kernels fetch gradient and residual tiles through tensor maps, which hold the base addresses
         unsigned char* dev = static_cast<unsigned char*>(a->tmaps.p) + (size_t) slot * align_up((int64_t) a->hostMaps.size(), 128);
         for (size_t i = 0; i < a->hK1.size(); ++i)
-            stream_set_maps(&a->hK1[i], false, a->hostMaps.data() + i * QAGG_STREAM_MAP_BYTES, dev + i * QAGG_STREAM_MAP_BYTES);
-        if (a->deferredOwner)
-            for (size_t e = 0; e < a->hK2.size(); ++e)
-            {
-                const size_t slot = a->hK1.size() + e;
-                stream_set_maps(&a->hK2[e], true, a->hostMaps.data() + slot * QAGG_STREAM_MAP_BYTES, dev + slot * QAGG_STREAM_MAP_BYTES);
-            }
+            stream_set_maps(&a->hK1[i], a->hostMaps.data() + i * QAGG_STREAM_MAP_BYTES, dev + i * QAGG_STREAM_MAP_BYTES);
         if (!a->hostMaps.empty())
             if ((rc = check_cuda(cudaMemcpy(dev, a->hostMaps.data(), a->hostMaps.size(), cudaMemcpyHostToDevice), "tensor map upload")))
                 return rc;
@@ -524,7 +531,7 @@ int launch_k1(qagg_aggregator* a, cudaStream_t st)
 {
     const Signal sg = make_signal(a, false);
     if (a->deferred)
-        return check_cuda(launch_stream1(st, false, a->dK1, a->dI1, (int) a->iK1.size(), a->cfg, static_cast<unsigned*>(a->queue.p), &sg, a->status_word()),
+        return check_cuda(launch_stream1(st, a->dK1, a->dI1, (int) a->iK1.size(), a->cfg, static_cast<unsigned*>(a->queue.p), &sg, a->status_word()),
                           "quantize launch");
     return check_cuda(launch_colquant(st, false, a->mode, nullptr, a->dK1, a->dI1, (int) a->iK1.size(), 0, a->cfg,
                                       static_cast<unsigned*>(a->queue.p), &sg), "quantize launch");
@@ -535,8 +542,9 @@ int launch_k2(qagg_aggregator* a, cudaStream_t st)
     unsigned* q2 = static_cast<unsigned*>(a->queue.p) + QAGG_COUNTER_UINTS;
     if (a->peer && a->pushGather)
     {
-        int rc = check_cuda(a->deferredOwner ? launch_stream1(st, true, a->dK2, a->dI2, (int) a->iK2.size(), a->cfg, q2, nullptr, a->status_word())
-                                        : launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg, q2, nullptr),
+        int rc = check_cuda(a->deferredOwner ? launch_owner(st, a->dK2, (int) a->hK2.size(), a->k2Units, a->dI2, (int) a->iK2.size(), a->cfg, q2, nullptr,
+                                                            a->status_word())
+                                             : launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg, q2, nullptr),
                             "reduce-requantize launch");
         if (rc)
             return rc;
@@ -545,7 +553,8 @@ int launch_k2(qagg_aggregator* a, cudaStream_t st)
                                       a->cfg.numSMs), "gather push launch");
     }
     if (a->deferredOwner)
-        return check_cuda(launch_stream1(st, true, a->dK2, a->dI2, (int) a->iK2.size(), a->cfg, q2, &sg, a->status_word()), "reduce-requantize launch");
+        return check_cuda(launch_owner(st, a->dK2, (int) a->hK2.size(), a->k2Units, a->dI2, (int) a->iK2.size(), a->cfg, q2, &sg, a->status_word()),
+                          "reduce-requantize launch");
     return check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg, q2, &sg),
                       "reduce-requantize launch");
 }
@@ -556,7 +565,7 @@ int wait_peers(qagg_aggregator* a, bool gatherPhase, cudaStream_t st)
 }
 int launch_k3(qagg_aggregator* a, cudaStream_t st)
 {
-    return check_cuda(launch_unquantize(st, false, nullptr, a->dK3, (int) a->hK3.size(), a->k3Units, a->cfg), "unquantize launch");
+    return check_cuda(launch_unquantize(st, false, a->bits, nullptr, a->dK3, (int) a->hK3.size(), a->k3Units, a->cfg), "unquantize launch");
 }
 
 } // namespace
@@ -602,11 +611,9 @@ int qagg_plan_destroy(qagg_plan* p)
     return QAGG_OK;
 }
 
-int64_t qagg_plan_stream_items(int num_tensors, const int64_t* M, const int64_t* N, int bits, int num_sms, int packed_sources,
-                               int32_t* items, int64_t capacity)
+int64_t qagg_plan_stream_items(int num_tensors, const int64_t* M, const int64_t* N, int bits, int num_sms, int32_t* items, int64_t capacity)
 {
-    if (num_tensors < 0 || (num_tensors > 0 && (!M || !N)) || !bits_ok(bits) || num_sms < 1 || packed_sources < 0 || packed_sources > QAGG_MAXK ||
-        capacity < 0 || (capacity > 0 && !items))
+    if (num_tensors < 0 || (num_tensors > 0 && (!M || !N)) || !bits_ok(bits) || num_sms < 1 || capacity < 0 || (capacity > 0 && !items))
         return fail(QAGG_EINVAL, "qagg_plan_stream_items: bad arguments");
     std::vector<std::pair<long long, long long>> shapes;
     for (int i = 0; i < num_tensors; ++i)
@@ -620,7 +627,7 @@ int64_t qagg_plan_stream_items(int num_tensors, const int64_t* M, const int64_t*
     }
     std::vector<QItem> out;
     std::vector<std::pair<int, int>> box;
-    stream_make_items(shapes, num_sms, bits, packed_sources, out, box);
+    stream_make_items(shapes, num_sms, bits, out, box);
     for (size_t k = 0; k < out.size() && (int64_t) k < capacity; ++k)
     {
         items[3 * k] = out[k].tensor;
@@ -765,18 +772,20 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
     if (const char* e = std::getenv("QAGG_PUSH_GATHER")) // tuning knob: 0 = requantize kernel stores to the peers itself
         a->pushGather = (e[0] != '0');
     // 1 bit, threshold 0: the quantize kernel streams with a deferred residual, unless a column is too tall for that.
-    // Tuning knob QAGG_STREAM: 0 = resident-column kernels only, 1 = quantize kernel streams (default), 2 = the owner's
-    // reduce-requantize kernel streams too (it is the slower of the two owner kernels on the shapes measured so far).
+    // The owner's reduce-requantize is then the form + walk kernel pair, which keeps the stripe residuals deferred too.
+    // Tuning knobs (results never change): QAGG_STREAM=0 resident-column kernels only; QAGG_OWNER=0 resident-column kernel
+    // for the owner only.
     a->deferred = (a->mode == MODE_ONEBIT_ZERO);
     for (int i = 0; i < num_tensors; ++i)
         if (M[i] > 0 && N[i] > 0 && stream_max_cols((M[i] * bits + 31) / 32) < 1)
             a->deferred = false;
     if (const char* e = std::getenv("QAGG_STREAM"))
-    {
         if (e[0] == '0')
             a->deferred = false;
-        a->deferredOwner = a->deferred && (e[0] == '2');
-    }
+    a->deferredOwner = a->deferred && K > 1;
+    if (const char* e = std::getenv("QAGG_OWNER"))
+        if (e[0] == '0')
+            a->deferredOwner = false;
     rc = check_cuda(get_launch_cfg(comm->device, &a->cfg), "cudaGetDeviceProperties");
     if (rc)
         return rc;
@@ -833,6 +842,10 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
         if ((rc = a->lvAll.alloc((size_t) cols * 8, true)))
             return rc;
         if ((rc = a->slvAll.alloc((size_t) scols * 8, true)))
+            return rc;
+        if ((rc = a->ownStats.alloc((size_t) scols * 8, true)))
+            return rc;
+        if ((rc = a->ownMaps.alloc((size_t) std::max(num_tensors, 1) * 128, true)))
             return rc;
     }
     int64_t ro = 0, so = 0, lo = 0, slo = 0;
@@ -1521,7 +1534,8 @@ int qagg_agg_launches_per_step(const qagg_aggregator* a)
         return 0;
     if (a->comm->K == 1)
         return 2;
-    return 3 + (a->peer ? 2 + (a->pushGather ? 1 : 0) : 0); // + two flag waits (+ the gather push) in peer mode
+    // quantize, owner (one kernel, or form + walk), unquantize; + two flag waits (+ the gather push) in peer mode
+    return 3 + (a->deferredOwner ? 1 : 0) + (a->peer ? 2 + (a->pushGather ? 1 : 0) : 0);
 }
 
 int qagg_agg_destroy(qagg_aggregator* a)

@@ -43,7 +43,8 @@ struct QTensor
     // items of up to boxCols[1] < boxCols[0] columns (0: no such items).  All null: the matrix is fetched with plain loads.
     const void* tm[2][2];
     int boxCols[2];
-    long long unit0; // unquantize kernel only: number of work units of the table entries before this one
+    long long unit0; // unquantize and owner-form kernels: number of work units of the table entries before this one
+    unsigned* stats; // owner kernels only: two words per column (rows with a set bit, NaN seen), zero between steps
 };
 
 // Flags that the last CTA of a kernel writes (release, system scope) after all of the kernel's stores: one word in each
@@ -107,10 +108,10 @@ cudaError_t launch_push(cudaStream_t st, const void* src, size_t bytes, const Si
 // give-up it ORs 1 into *status and returns: the context stays usable and the host reads the status later
 cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status);
 // unquantize (qagg_unquantize.cu): `single` != nullptr: one matrix described by value; otherwise `tensors` is a device table
-// of nTensors entries whose unit0 fields are the running sums of unq_units() (entry order = unit order)
-cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, const QTensor* tensors, int nTensors, long long totalUnits,
-                              const LaunchCfg& cfg);
-long long unq_units(long long M, long long N); // work units of an M x N matrix in the unquantize kernel
+// of nTensors entries (all of `bits` bits) whose unit0 fields are the running sums of unq_units() (entry order = unit order)
+cudaError_t launch_unquantize(cudaStream_t st, bool add, int bits, const QTensor* single, const QTensor* tensors, int nTensors,
+                              long long totalUnits, const LaunchCfg& cfg);
+long long unq_units(long long M, long long N, int bits); // work units of an M x N matrix in the unquantize kernel
 cudaError_t get_launch_cfg(int device, LaunchCfg* cfg);
 // releases the flags of `signal` from a one-thread kernel (a rank with nothing to compute still has to tell its peers)
 cudaError_t launch_signal_only(cudaStream_t st, const Signal& signal);
@@ -121,34 +122,49 @@ cudaError_t launch_signal_only(cudaStream_t st, const Signal& signal);
 // v - (v >= 0 ? lv[1] : lv[0]), is formed with the same single subtraction when the state is next read.  All-zero
 // buffers are a zero residual.  Columns stream through shared memory in row chunks, so column height is limited only
 // by the shared-memory copy of a work item's packed words: nc * Q <= QAGG_STREAM_PKWORDS.
-#define QAGG_STREAM_PKWORDS 2560       /* quantize kernel */
-#define QAGG_STREAM_PKWORDS_OWNER 4480 /* owner kernel: its input ring is one slot shorter */
+#define QAGG_STREAM_PKWORDS 2560
 #define QAGG_STREAM_CMAX 32
-// most columns per work item for columns of Q packed words (0: the column is too tall for this kernel); the owner
-// kernel also stages the item's columns of its `packedSources` packed inputs, header included
-inline int stream_max_cols(long long Q, int packedSources = 0)
+// most columns per work item for columns of Q packed words (0: the column is too tall for this kernel)
+inline int stream_max_cols(long long Q)
 {
     if (Q <= 0)
         return QAGG_STREAM_CMAX;
-    const long long c = (packedSources > 0 ? QAGG_STREAM_PKWORDS_OWNER : QAGG_STREAM_PKWORDS) / (Q + (long long) packedSources * (Q + 2));
+    const long long c = QAGG_STREAM_PKWORDS / Q;
     return (int) (c > QAGG_STREAM_CMAX ? QAGG_STREAM_CMAX : c);
 }
 // Work items of one launch of the streaming kernel, in queue order.  shapes[t] = (rows, columns) of table entry t.
 // Items are sized for about (all values) / (2 x resident CTAs) values each, ordered longest first; the items in the last
 // quarter of the queue are cut into three, so that the launch ends with short items and all CTAs finish together.
 // boxCols[t] = {columns of a full item, columns of a cut item or 0} for matrix t.
-void stream_make_items(const std::vector<std::pair<long long, long long>>& shapes, int numSMs, int bits, int packedSources,
-                       std::vector<QItem>& out, std::vector<std::pair<int, int>>& boxCols);
+void stream_make_items(const std::vector<std::pair<long long, long long>>& shapes, int numSMs, int bits, std::vector<QItem>& out,
+                       std::vector<std::pair<int, int>>& boxCols);
 // Encodes the tensor maps of one streaming descriptor whose grad / res_in / res_out / M / N / selfRaw / boxCols are set:
 // writes up to four maps to hostMaps (512 bytes, to be copied to devMaps, 128-byte aligned) and sets t->tm[][] to their
 // device addresses -- or to null if the matrix cannot be fetched through tensor maps (rows not a multiple of 4, or
-// buffers not 16-byte aligned), in which case the kernel uses plain loads for it.  `stripes`: owner-kernel descriptor.
-void stream_set_maps(QTensor* t, bool stripes, unsigned char* hostMaps, unsigned char* devMaps);
+// buffers not 16-byte aligned), in which case the kernel uses plain loads for it.
+void stream_set_maps(QTensor* t, unsigned char* hostMaps, unsigned char* devMaps);
+// 128-byte tensor map of a column-major M x N fp32 matrix with a box of boxRows rows x boxCols columns (each <= 256), looked
+// up through the runtime's driver entry point; false if it cannot be encoded (rows not a multiple of 4, base not 16-byte
+// aligned, driver too old)
+bool encode_map_2d(void* out128, const float* base, long long M, long long N, int boxRows, int boxCols);
 #define QAGG_STREAM_MAP_BYTES 512
 // always table-driven with a work queue (`counters` as for launch_colquant, required).  The kernel's waits for copies in
 // flight are bounded: if one runs out, bit 1 of *status is set and the kernel ends normally (results invalid)
-cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors, const QItem* items, int nItems,
-                           const LaunchCfg& cfg, unsigned* counters, const Signal* signal = nullptr, unsigned* status = nullptr);
+cudaError_t launch_stream1(cudaStream_t st, const QTensor* tensors, const QItem* items, int nItems, const LaunchCfg& cfg, unsigned* counters,
+                           const Signal* signal = nullptr, unsigned* status = nullptr);
+
+// ---- the owner's reduce-requantize for 1 bit with threshold 0, two kernels (qagg_owner.cu) -------------------------------
+// Table entries describe the owned stripes: src[] / nsrc / selfRaw / grad (raw own stripe), res_in == res_out (stripe
+// residual in deferred form), lv, stats, pk[0] (this rank's gather slot), bcast / bcastOff, unit0 = running sum of
+// owner_form_units(), tm[0][1] = tensor map of res_out made by owner_set_map (null: plain loads).
+long long owner_form_units(long long M, long long n);
+// walk items (32 adjacent columns of one entry), tallest columns first; shapes[e] = (rows, owned columns) of entry e
+void owner_make_items(const std::vector<std::pair<long long, long long>>& shapes, std::vector<QItem>& out);
+bool owner_set_map(QTensor* t, unsigned char* hostMap, unsigned char* devMap);
+// form kernel, then walk kernel; the walk kernel's last CTA releases signal.flag[] (`counters` as for launch_colquant; only
+// [1] is used).  Its waits for tiles in flight are bounded like the streaming kernel's (bit 1 of *status).
+cudaError_t launch_owner(cudaStream_t st, const QTensor* tensors, int nTensors, long long formUnits, const QItem* items, int nItems,
+                         const LaunchCfg& cfg, unsigned* counters, const Signal* signal = nullptr, unsigned* status = nullptr);
 // runs the streaming kernel's bounded mbarrier wait on a barrier that nothing completes (see qagg_stream_wait_selftest)
 cudaError_t launch_stream_wait_selftest(cudaStream_t st, int maxTries, unsigned* status, long long* cycles);
 // dst[i, j] = buf[i, j] - (buf[i, j] >= 0 ? lv[2j + 1] : lv[2j]): the residual proper of a deferred state (dst may be buf)

@@ -1,0 +1,408 @@
+// qagg_owner.cu -- the stripe owner's reduce-requantize (AllReduceDistGradAggregator.h:366-375, 405-435) for 1 bit with
+// threshold 0, in two phases.
+//
+// For every column the owner has to (a) add the K unpacked stripes in source order, (b) add the stripe residual,
+// (c) take the two level sums IN ROW ORDER to get the column's range, (d) emit bits and the new residual.  With the
+// residual kept in deferred form (qagg_internal.h) neither the bits nor the stored state depend on the range, so only
+// the column's 8-byte header does -- and only step (c) is serial.  The two are therefore separate kernels:
+//
+//   k_owner_form   everything that is parallel.  Thread <-> (column, packed word, half of the word's 32 rows): it reads the
+//                  K source words once, the 16 previous-state values of its rows (rows w + kQ: for a fixed k the warp reads
+//                  128 consecutive bytes), forms v = sum of sources + (prev - level(prev)), stores v, and stores its 16
+//                  result bits as one 16-bit half of the packed word -- straight into this rank's gather slot and into
+//                  every peer's.  No shared memory, no barrier; warps take 32-word units u, u + warps, ...
+//                  It also counts each column's rows with v >= 0 and flags NaNs (integers: no order needed).
+//   k_owner_walk   the serial part, nothing else.  One CTA = a producer warp and two walking warps (one per level); a work
+//                  item is 32 adjacent columns, lane <-> column.  The producer brings tiles of 132 rows x 32 columns of
+//                  the just-written state (mostly still in L2) into a 4-slot ring with one tensor copy each; both walkers
+//                  add min(v, 0) resp. max(v, 0) down their lane's tile column.  All columns of all owned stripes walk
+//                  concurrently, every walking warp has up to 32 active lanes, and the launch lasts as long as the tallest
+//                  column's add chain (about 4.4 cycles per row).  At the end: range, header (to all gather slots), the
+//                  new reconstruction values, and the release of the peers' flags by the last CTA.
+//
+// The kernel this replaces kept whole columns resident in shared memory and walked them with two one-lane warps per CTA
+// while the other 254 threads waited at a barrier; at 8 ranks it ran at 0.09 of the HBM roofline.
+// Other modes (mean threshold, 2..32 bits) cannot defer anything and keep the resident-column kernel.
+#include "qagg_async.cuh"
+
+#include <algorithm>
+
+namespace qagg {
+
+constexpr int OW_HALF = 16;   // rows (field positions) per thread
+constexpr int OW_SRC = 8;     // packed sources fetched per batch
+constexpr int OW_R = 132;     // tile rows: 4 x an odd number, so that the 128-bit reads of neighbouring tile columns fall
+                              // into distinct banks (the tile is dense: column stride = OW_R floats)
+constexpr int OW_C = 32;      // tile columns = lanes of a walking warp
+constexpr int OW_STAGES = 4;  // ring slots
+constexpr int OW_TILE_FLOATS = OW_R * OW_C;
+constexpr int OW_THREADS = 96;
+constexpr size_t OW_SMEM_BYTES = (size_t) OW_STAGES * OW_TILE_FLOATS * 4;
+
+long long owner_form_units(long long M, long long n)
+{
+    if (M <= 0 || n <= 0)
+        return 0;
+    const long long Q = (M + 31) / 32;
+    return 2 * ((n * Q + 31) / 32);
+}
+
+__global__ void __launch_bounds__(NT, 3) k_owner_form(const QTensor* __restrict__ tensors, int nTensors, long long totalUnits, const Signal signal)
+{
+    const unsigned lane = threadIdx.x & 31;
+    const long long gwarp = (long long) blockIdx.x * NWARPS + (threadIdx.x >> 5);
+    const long long nwarps = (long long) gridDim.x * NWARPS;
+    int cur = 0;
+    for (long long u = gwarp; u < totalUnits; u += nwarps)
+    {
+        if (!(tensors[cur].unit0 <= u && (cur + 1 >= nTensors || u < tensors[cur + 1].unit0)))
+        {
+            int lo = 0, hi = nTensors;
+            while (hi - lo > 1)
+            {
+                const int mid = (lo + hi) >> 1;
+                if (tensors[mid].unit0 <= u)
+                    lo = mid;
+                else
+                    hi = mid;
+            }
+            cur = lo;
+        }
+        const QTensor* __restrict__ Tp = tensors + cur;
+        const unsigned M = (unsigned) Tp->M;
+        const unsigned Q = (unsigned) Tp->Q;
+        const unsigned long long local = (unsigned long long) (u - Tp->unit0);
+        const unsigned kb = (unsigned) (local & 1ull) * OW_HALF;  // this unit's rows are field positions kb .. kb + 15
+        const unsigned long long t0 = (local >> 1) * 32ull;       // first word of the unit, columns laid end to end
+        const unsigned long long totalWords = (unsigned long long) Tp->N * Q;
+        unsigned col0, w0;
+        if (totalWords <= 0xffffffffull)
+        {
+            col0 = (unsigned) t0 / Q;
+            w0 = (unsigned) t0 - col0 * Q;
+        }
+        else
+        {
+            col0 = (unsigned) (t0 / Q);
+            w0 = (unsigned) (t0 - (unsigned long long) col0 * Q);
+        }
+        const bool live = t0 + lane < totalWords;
+        const unsigned tl = w0 + lane;
+        const unsigned dc = tl / Q;
+        const unsigned c = live ? col0 + dc : col0;
+        const unsigned w = live ? tl - dc * Q : 0u;
+        unsigned bitsOut = 0u, nan = 0u;
+        if (live)
+        {
+            const size_t colOff = (size_t) c * M + w;
+            const float* __restrict__ prevp = Tp->res_in + colOff;
+            float* __restrict__ outp = Tp->res_out + colOff;
+            const bool selfRaw = Tp->selfRaw != 0;
+            const float* __restrict__ rawp = Tp->grad + colOff; // used only when selfRaw
+            const int nsrc = Tp->nsrc;
+            const size_t colBytes = (size_t) Tp->colBytes;
+            float prev[OW_HALF], agg[OW_HALF];
+#pragma unroll
+            for (int k = 0; k < OW_HALF; ++k)
+            {
+                const unsigned row = w + (kb + k) * Q;
+                prev[k] = (row < M) ? __ldcs(prevp + (size_t) (kb + k) * Q) : 0.0f;
+                agg[k] = (selfRaw && row < M) ? __ldcs(rawp + (size_t) (kb + k) * Q) : 0.0f;
+            }
+            const float lv0 = Tp->lv[2 * (size_t) c], lv1 = Tp->lv[2 * (size_t) c + 1];
+            // the K sources in index order (the own stripe first), the residual last (AllReduceDistGradAggregator.h:366-375, 405-435)
+            int s = selfRaw ? 1 : 0;
+            if (!selfRaw)
+            {
+                // the first packed source starts the sum (the reference unquantizes it with add = false)
+                const unsigned char* colp = Tp->src[0] + (size_t) c * colBytes;
+                float v0, v1;
+                levels_1bit(__ldg(reinterpret_cast<const float*>(colp)), __ldg(reinterpret_cast<const float*>(colp) + 1), v0, v1);
+                const unsigned word = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + w) >> kb;
+#pragma unroll
+                for (int k = 0; k < OW_HALF; ++k)
+                    agg[k] = ((word >> k) & 1u) ? v1 : v0;
+                s = 1;
+            }
+            for (; s < nsrc; s += OW_SRC)
+            {
+                unsigned sw[OW_SRC];
+                float slo[OW_SRC], sup[OW_SRC];
+#pragma unroll
+                for (int j = 0; j < OW_SRC; ++j)
+                {
+                    sw[j] = 0u;
+                    slo[j] = sup[j] = 0.0f;
+                    if (s + j < nsrc)
+                    {
+                        const unsigned char* colp = Tp->src[s + j] + (size_t) c * colBytes;
+                        slo[j] = __ldg(reinterpret_cast<const float*>(colp));
+                        sup[j] = __ldg(reinterpret_cast<const float*>(colp) + 1);
+                        sw[j] = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + w) >> kb;
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < OW_SRC; ++j)
+                {
+                    if (s + j < nsrc)
+                    {
+                        float v0, v1;
+                        levels_1bit(slo[j], sup[j], v0, v1);
+#pragma unroll
+                        for (int k = 0; k < OW_HALF; ++k)
+                            agg[k] = __fadd_rn(((sw[j] >> k) & 1u) ? v1 : v0, agg[k]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < OW_HALF; ++k)
+            {
+                if (w + (kb + k) * Q < M)
+                {
+                    const float v = __fadd_rn(agg[k], deferred_residual(prev[k], lv0, lv1));
+                    outp[(size_t) (kb + k) * Q] = v; // read again by the walk kernel: a plain store, so that it stays in L2
+                    bitsOut |= (v >= 0.0f) ? (1u << k) : 0u;
+                    nan |= (v != v) ? 1u : 0u;
+                }
+            }
+            // this half of the packed word, to this rank's gather slot and to every peer's
+            unsigned char* const dst = Tp->pk[0] + (size_t) c * colBytes;
+            const size_t wordOff = 8 + 4 * (size_t) w + (kb ? 2 : 0);
+            *reinterpret_cast<unsigned short*>(dst + wordOff) = (unsigned short) bitsOut;
+            if (Tp->bcast)
+            {
+                const size_t off = (size_t) (dst - Tp->pk[0]) + (size_t) Tp->bcastOff + wordOff;
+                for (int b = 0; b < signal.nbcast; ++b)
+                    *reinterpret_cast<unsigned short*>(signal.bcastBase[b] + off) = (unsigned short) bitsOut;
+            }
+        }
+        // per-column count of rows with v >= 0: one atomic per warp when the warp lies inside one column
+        const unsigned ones = __popc(bitsOut);
+        unsigned* __restrict__ stats = Tp->stats;
+        const bool oneColumn = __all_sync(0xffffffffu, !live || c == col0);
+        if (oneColumn)
+        {
+            const unsigned tot = __reduce_add_sync(0xffffffffu, ones);
+            if (lane == 0 && tot)
+                atomicAdd(&stats[2 * (size_t) col0], tot);
+        }
+        else if (live && ones)
+        {
+            atomicAdd(&stats[2 * (size_t) c], ones);
+        }
+        if (live && nan)
+            atomicOr(&stats[2 * (size_t) c + 1], 1u);
+    }
+}
+
+__global__ void __launch_bounds__(OW_THREADS, 3) k_owner_walk(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
+                                                           const Signal signal, unsigned* __restrict__ counters, unsigned* __restrict__ status)
+{
+    extern __shared__ __align__(128) float tiles[];
+    __shared__ __align__(8) unsigned long long sFull[OW_STAGES], sEmpty[OW_STAGES];
+    __shared__ unsigned sBroken;
+    __shared__ float sA[2][2][OW_C]; // [item parity][level][column]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0)
+    {
+        for (int i = 0; i < OW_STAGES; ++i)
+        {
+            mbar_init(&sFull[i], 1u);
+            mbar_init(&sEmpty[i], 2u); // both walking warps hand a slot back
+        }
+        sBroken = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    unsigned pos = 0; // ring position of the current item's tile 0 (all warps keep the same count)
+    unsigned itemNo = 0;
+    for (int it = blockIdx.x; it < nItems; it += gridDim.x, ++itemNo)
+    {
+        const QItem item = items[it];
+        const QTensor* __restrict__ Tp = tensors + item.tensor;
+        const int M = (int) Tp->M;
+        const int col0 = item.col0, nc = item.ncols;
+        const void* const tmap = Tp->tm[0][1];
+        const int ntiles = tmap ? (M + OW_R - 1) / OW_R : 0;
+        if (warp == 0)
+        {
+            // ================================ producer ================================
+            for (int q = 0; q < ntiles; ++q)
+            {
+                const unsigned p = pos + (unsigned) q;
+                const unsigned slot = p % OW_STAGES;
+                if (p >= (unsigned) OW_STAGES)
+                    mbar_wait(&sEmpty[slot], ((p / OW_STAGES) - 1u) & 1u, &sBroken, status);
+                if (*reinterpret_cast<volatile unsigned*>(&sBroken))
+                    break;
+                if (lane == 0)
+                {
+                    // the whole box counts, whether or not part of it lies outside the matrix (that part is zero-filled)
+                    mbar_arrive_expect_tx(&sFull[slot], (unsigned) (OW_TILE_FLOATS * 4));
+                    tensor_load_2d(tiles + slot * OW_TILE_FLOATS, tmap, q * OW_R, col0, &sFull[slot]);
+                }
+            }
+        }
+        else
+        {
+            // ================================ walkers: warp 1 = lower level, warp 2 = upper level ================================
+            float acc = 0.0f;
+            if (tmap)
+            {
+                for (int q = 0; q < ntiles; ++q)
+                {
+                    const unsigned p = pos + (unsigned) q;
+                    const unsigned slot = p % OW_STAGES;
+                    mbar_wait(&sFull[slot], (p / OW_STAGES) & 1u, &sBroken, status);
+                    if (lane < nc && !*reinterpret_cast<volatile unsigned*>(&sBroken))
+                    {
+                        // rows past the end of the matrix are zero-filled; adding +0 changes nothing (the sums start at +0 and a
+                        // round-to-nearest sum is -0 only if both operands are), so full tiles are walked whole
+                        const int nrows = min(OW_R, (M - q * OW_R + 3) & ~3);
+                        const float* vcol = tiles + slot * OW_TILE_FLOATS + lane * OW_R;
+                        acc = (warp == 1) ? walk_chunk<WALK_MIN0>(vcol, nrows, acc) : walk_chunk<WALK_MAX0>(vcol, nrows, acc);
+                    }
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&sEmpty[slot]);
+                }
+            }
+            else if (lane < nc)
+            {
+                // no tensor map (rows not a multiple of 4): the lane walks its column in global memory
+                const float* __restrict__ vcol = Tp->res_out + (size_t) (col0 + lane) * (size_t) M;
+                for (int i = 0; i < M; ++i)
+                {
+                    const float v = __ldcg(vcol + i);
+                    acc = __fadd_rn(acc, (warp == 1) ? fminf(v, 0.0f) : fmaxf(v, 0.0f));
+                }
+            }
+            if (lane < nc)
+                sA[itemNo & 1][warp - 1][lane] = acc;
+            asm volatile("bar.sync 1, 64;" ::: "memory"); // the two walking warps
+            if (warp == 1 && lane < nc)
+            {
+                const size_t j = (size_t) (col0 + lane);
+                unsigned* __restrict__ stats = Tp->stats;
+                const unsigned ones = stats[2 * j], nanFlag = stats[2 * j + 1];
+                stats[2 * j] = 0u; // re-armed for the next step
+                stats[2 * j + 1] = 0u;
+                // rows below the threshold = rows whose bit is 0 (a NaN row has bit 0 too, but then the range is NaN whatever
+                // the count); min/max drop a NaN where the reference adds it to the upper sum: put it back
+                float lo, up, v0, v1;
+                finalize_range<MODE_ONEBIT_ZERO>(sA[itemNo & 1][0][lane], nanFlag ? __int_as_float(0x7fc00000) : sA[itemNo & 1][1][lane],
+                                                 (unsigned) M - ones, 0.0f, Tp->M, lo, up);
+                levels_1bit(lo, up, v0, v1);
+                Tp->lv[2 * j] = v0;
+                Tp->lv[2 * j + 1] = v1;
+                unsigned char* const dst = Tp->pk[0] + j * (size_t) Tp->colBytes;
+                store_header(dst, lo, up);
+                if (Tp->bcast)
+                {
+                    const size_t off = (size_t) (dst - Tp->pk[0]) + (size_t) Tp->bcastOff;
+                    for (int b = 0; b < signal.nbcast; ++b)
+                        store_header(signal.bcastBase[b] + off, lo, up);
+                }
+            }
+        }
+        pos += (unsigned) ntiles;
+    }
+    __syncthreads();
+    // The last CTA to leave releases the peers' flags: each CTA's stores (into peer memory too) are ordered before its
+    // arrival by barrier + system-scope fence; the form kernel's stores were complete before this kernel began.
+    if (tid == 0)
+    {
+        __threadfence_system();
+        const unsigned done = atomicAdd(&counters[1], 1u);
+        if (done == gridDim.x - 1)
+        {
+            counters[1] = 0;
+            __threadfence_system();
+            for (int i = 0; i < signal.n; ++i)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
+        }
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------------------------
+
+void owner_make_items(const std::vector<std::pair<long long, long long>>& shapes, std::vector<QItem>& out)
+{
+    struct Cand
+    {
+        long long rows;
+        QItem item;
+    };
+    std::vector<Cand> cand;
+    for (size_t e = 0; e < shapes.size(); ++e)
+    {
+        const long long M = shapes[e].first, n = shapes[e].second;
+        if (M <= 0 || n <= 0)
+            continue;
+        for (long long c0 = 0; c0 < n; c0 += OW_C)
+            cand.push_back(Cand{M, QItem{(int) e, (int) c0, (int) std::min<long long>(OW_C, n - c0)}});
+    }
+    // tallest columns first: a launch lasts as long as its longest walk
+    std::stable_sort(cand.begin(), cand.end(), [](const Cand& x, const Cand& y) { return x.rows > y.rows; });
+    out.clear();
+    for (const Cand& cd : cand)
+        out.push_back(cd.item);
+}
+
+bool owner_set_map(QTensor* t, unsigned char* hostMap, unsigned char* devMap)
+{
+    const bool ok = (reinterpret_cast<uintptr_t>(devMap) & 127) == 0 && encode_map_2d(hostMap, t->res_out, t->M, t->N, OW_R, OW_C);
+    t->tm[0][0] = nullptr;
+    t->tm[0][1] = ok ? devMap : nullptr;
+    t->tm[1][0] = t->tm[1][1] = nullptr;
+    return ok;
+}
+
+// grid of the form kernel: at most three CTAs per SM; among the sizes from two to three per SM, the one whose warps share
+// the units most evenly
+static int form_grid(long long totalUnits, int numSMs)
+{
+    const long long need = (totalUnits + NWARPS - 1) / NWARPS;
+    const long long most = (long long) numSMs * 3;
+    if (need <= most)
+        return (int) need;
+    long long best = most;
+    double bestWaste = 2.0;
+    for (long long g = most; g >= (long long) numSMs * 2; --g)
+    {
+        const long long warps = g * NWARPS;
+        const long long rounds = (totalUnits + warps - 1) / warps;
+        const double waste = 1.0 - (double) totalUnits / (double) (rounds * warps);
+        if (waste < bestWaste - 1e-9)
+        {
+            bestWaste = waste;
+            best = g;
+        }
+    }
+    return (int) best;
+}
+
+cudaError_t launch_owner(cudaStream_t st, const QTensor* tensors, int nTensors, long long formUnits, const QItem* items, int nItems,
+                         const LaunchCfg& cfg, unsigned* counters, const Signal* signalp, unsigned* status)
+{
+    static const Signal none = {};
+    const Signal& signal = signalp ? *signalp : none;
+    if (!counters)
+        return cudaErrorInvalidValue;
+    if (nItems <= 0 || formUnits <= 0)
+        return signal.n > 0 ? launch_signal_only(st, signal) : cudaSuccess;
+    k_owner_form<<<form_grid(formUnits, cfg.numSMs), NT, 0, st>>>(tensors, nTensors, formUnits, signal);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return e;
+    e = cudaFuncSetAttribute(k_owner_walk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) OW_SMEM_BYTES);
+    if (e != cudaSuccess)
+        return e;
+    int grid = cfg.numSMs * 3;
+    if (grid > nItems)
+        grid = nItems;
+    k_owner_walk<<<grid, OW_THREADS, OW_SMEM_BYTES, st>>>(tensors, items, nItems, signal, counters, status);
+    return cudaGetLastError();
+}
+
+} // namespace qagg

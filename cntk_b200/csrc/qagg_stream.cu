@@ -16,10 +16,7 @@
 //     tensor copy per input (cp.async.bulk.tensor through a tensor map of the matrix: box = R rows x nc columns; an
 //     mbarrier per ring slot counts the bytes), as far ahead as the input ring has free slots -- across item
 //     boundaries too, so the consumers never wait for a pipeline to refill;
-//   * six "element" warps form
-//       v = gradient + (prev - level(prev))                                   (quantize), or
-//       v = sum over the K packed stripes in source order + (prev - level(prev))   (owner's reduce-requantize),
-//     store v to global memory and to a padded tile for the walkers, and OR the bit (v >= 0) into the item's packed
+//   * six "element" warps form v = gradient + (prev - level(prev)), store v to global memory and to a padded tile for the walkers, and OR the bit (v >= 0) into the item's packed
 //     words, which live in shared memory until the item ends;
 //   * two "walker" warps (one per level, lane = column) add min(v, 0) resp. max(v, 0) of the previous chunk to their
 //     running sums, in row order;
@@ -27,7 +24,7 @@
 // Every wait on an mbarrier is bounded: if one runs out, the CTA stops waiting altogether, bit 1 of the status word
 // is set and the kernel ends normally (the results of that launch are then invalid).
 // Matrices whose columns are not 16-byte aligned have no tensor maps; their chunks are fetched with plain loads.
-#include "qagg_device.cuh"
+#include "qagg_async.cuh"
 
 #include <cuda.h>
 
@@ -42,22 +39,9 @@ constexpr int ST_U = 2;                                // 16-byte positions per 
 constexpr int ST_TILE_VALUES = 4 * ST_U * ST_ETHREADS; // 1536 values per chunk
 constexpr int ST_IN_FLOATS = ST_TILE_VALUES;           // input tile: dense box, column stride R
 constexpr int ST_V_FLOATS = ST_TILE_VALUES + 4 * QAGG_STREAM_CMAX; // walkers' tile: column stride R + 4
-// resident CTAs per SM: three for the quantize kernel; two for the owner kernel, whose element warps need more than the 72
-// registers that three CTAs of 288 threads leave (spilled registers are costly here: with this much shared memory in use
-// the L1 cache that backs them is almost gone)
-__host__ __device__ constexpr int stream_ctas_per_sm(bool stripes)
-{
-    return stripes ? 2 : 3;
-}
-// input ring slots: 1 being formed, the others in flight (the owner kernel has less shared memory to spare)
-__host__ __device__ constexpr int stream_in_stages(bool stripes)
-{
-    return stripes ? 3 : 4;
-}
-__host__ __device__ constexpr size_t stream_smem_bytes(bool stripes)
-{
-    return (size_t) (2 * stream_in_stages(stripes) * ST_IN_FLOATS + 2 * ST_V_FLOATS + (stripes ? QAGG_STREAM_PKWORDS_OWNER : QAGG_STREAM_PKWORDS)) * 4;
-}
+constexpr int ST_CTAS_PER_SM = 3;
+constexpr int ST_IN_STAGES = 4; // input ring slots: one being formed, the others in flight
+constexpr size_t ST_SMEM_BYTES = (size_t) (2 * ST_IN_STAGES * ST_IN_FLOATS + 2 * ST_V_FLOATS + QAGG_STREAM_PKWORDS) * 4;
 
 // rows per chunk for a tile geometry of `boxCols` columns: a multiple of 32 (so that the walkers' tile, whose column
 // stride is R + 4, spreads the 128-bit reads of neighbouring columns over distinct banks), at most 256 (tensor copy box)
@@ -69,111 +53,10 @@ __host__ __device__ __forceinline__ int stream_rows(int boxCols)
 
 constexpr int ST_DESC = 4; // work items whose descriptors may be fetched ahead of the consumers
 
-// ---- mbarriers and bulk asynchronous copies (addresses and sizes are multiples of 16 bytes) -----------------------------
-__device__ __forceinline__ unsigned smem_addr(const void* p)
-{
-    return (unsigned) __cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-// one non-blocking test: has the phase with this parity completed?
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity)
-{
-    unsigned ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok)
-                 : "r"(smem_addr(bar)), "r"(parity)
-                 : "memory");
-    return ok != 0;
-}
-// Bounded wait for the phase of `bar` with the given parity to complete.  After ST_WAIT_TRIES tries it gives up: the
-// CTA-wide flag *broken makes every later wait return at once, and bit 1 of *status tells the host.
-constexpr int ST_WAIT_TRIES = 1 << 22;
-__device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity, unsigned* broken, unsigned* status, int maxTries = ST_WAIT_TRIES)
-{
-    if (mbar_try_wait(bar, parity))
-        return;
-    if (*reinterpret_cast<volatile unsigned*>(broken))
-        return;
-    // not there yet: poll with the warp asleep in between, so that the waiting costs the other warps no issue slots
-    for (int tries = 0; tries < maxTries; ++tries)
-    {
-        __nanosleep(128);
-        if (mbar_try_wait(bar, parity))
-            return;
-    }
-    *reinterpret_cast<volatile unsigned*>(broken) = 1u;
-    if (status)
-        atomicOr(status, 2u);
-}
-// box (rows x0 .., columns x1 ..) of the matrix behind `tmap` -> dense tile [column][row]
-__device__ __forceinline__ void tensor_load_2d(float* dstShared, const void* tmap, int x0, int x1, unsigned long long* bar)
-{
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_addr(dstShared)),
-                 "l"(tmap), "r"(smem_addr(bar)), "r"(x0), "r"(x1)
-                 : "memory");
-}
 // barrier of the eight consumer warps (the producer warp does not take part)
 __device__ __forceinline__ void consumer_sync()
 {
     asm volatile("bar.sync 1, 256;" ::: "memory");
-}
-
-// Ordered walk over the rows of one chunk (a multiple of 4, usually of 32): thirty-two rows per loop trip in two
-// register sets of sixteen, each set reloaded while the other is being added, so the loop carries no register moves.
-template <int KIND>
-__device__ __forceinline__ float walk_chunk(const float* __restrict__ vcol, int nrows, float acc)
-{
-    const float4* __restrict__ p = reinterpret_cast<const float4*>(vcol);
-    const int n16 = nrows >> 4;
-    unsigned dummy = 0;
-    if (n16 > 0)
-    {
-        float4 a0 = p[0], a1 = p[1], a2 = p[2], a3 = p[3];
-        int t = 0;
-        for (; t + 2 <= n16; t += 2)
-        {
-            const float4 b0 = p[4 * t + 4], b1 = p[4 * t + 5], b2 = p[4 * t + 6], b3 = p[4 * t + 7];
-            walk_step4<KIND>(acc, dummy, a0, 0.0f, false);
-            walk_step4<KIND>(acc, dummy, a1, 0.0f, false);
-            walk_step4<KIND>(acc, dummy, a2, 0.0f, false);
-            walk_step4<KIND>(acc, dummy, a3, 0.0f, false);
-            const int nx = 4 * min(t + 2, n16 - 1); // the last trip reloads rows it will not use
-            a0 = p[nx];
-            a1 = p[nx + 1];
-            a2 = p[nx + 2];
-            a3 = p[nx + 3];
-            walk_step4<KIND>(acc, dummy, b0, 0.0f, false);
-            walk_step4<KIND>(acc, dummy, b1, 0.0f, false);
-            walk_step4<KIND>(acc, dummy, b2, 0.0f, false);
-            walk_step4<KIND>(acc, dummy, b3, 0.0f, false);
-        }
-        if (t < n16)
-        {
-            walk_step4<KIND>(acc, dummy, a0, 0.0f, false);
-            walk_step4<KIND>(acc, dummy, a1, 0.0f, false);
-            walk_step4<KIND>(acc, dummy, a2, 0.0f, false);
-            walk_step4<KIND>(acc, dummy, a3, 0.0f, false);
-        }
-    }
-    for (int i = n16 << 4; i < nrows; ++i)
-        walk_step<KIND>(acc, dummy, vcol[i], 0.0f, false);
-    return acc;
-}
-
-__device__ __forceinline__ float deferred_residual(float prev, float lv0, float lv1)
-{
-    return __fsub_rn(prev, (prev >= 0.0f) ? lv1 : lv0);
 }
 
 // which of a descriptor's two tile geometries an item of `ncols` columns uses (the same answer on both sides of the ring)
@@ -182,17 +65,15 @@ __device__ __forceinline__ int stream_geometry(const QTensor& T, int ncols)
     return (T.boxCols[1] > 0 && ncols <= T.boxCols[1]) ? 1 : 0;
 }
 
-template <bool STRIPES>
-__global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream1(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
+__global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
                                                                      unsigned* __restrict__ counters, const Signal signal, unsigned* __restrict__ status)
 {
-    constexpr int SIN = stream_in_stages(STRIPES);
+    constexpr int SIN = ST_IN_STAGES;
     extern __shared__ __align__(128) float dsm[];
-    float* const inG = dsm;                                  // input ring: gradient (or raw own stripe) boxes
+    float* const inG = dsm;                                  // input ring: gradient boxes
     float* const inP = dsm + SIN * ST_IN_FLOATS;             // input ring: previous-state boxes
     float* const vt = dsm + 2 * SIN * ST_IN_FLOATS;          // the formed values of two chunks: one being walked, one being written
-    // the item's packed words (nc x Q), then -- owner kernel -- its packed source columns, headers included
-    // ([source][column][2 + Q] words)
+    // the item's packed words (nc x Q)
     unsigned* const pkw = reinterpret_cast<unsigned*>(dsm + 2 * SIN * ST_IN_FLOATS + 2 * ST_V_FLOATS);
     // work items in flight: buffer (n % ST_DESC) holds the CTA's n-th item: its queue index (>= nItems: the queue is
     // empty), the item and its matrix descriptor
@@ -208,7 +89,6 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
     __shared__ float sLower[QAGG_STREAM_CMAX], sUpper[QAGG_STREAM_CMAX];
     __shared__ unsigned sN0[QAGG_STREAM_CMAX], sNan[QAGG_STREAM_CMAX];
     __shared__ unsigned char* sDst[QAGG_STREAM_CMAX];
-    __shared__ float sSrc0[STRIPES ? QAGG_MAXK : 1][QAGG_STREAM_CMAX], sSrc1[STRIPES ? QAGG_MAXK : 1][QAGG_STREAM_CMAX];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0)
@@ -259,10 +139,9 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
             const int M = (int) T.M, col0 = sItem[b].col0;
             const int geo = stream_geometry(T, sItem[b].ncols);
             const int boxCols = T.boxCols[geo];
-            const bool hasG = !STRIPES || T.selfRaw;
             const void* const tmG = T.tm[geo][0];
             const void* const tmP = T.tm[geo][1];
-            const bool vec = tmP != nullptr && (!hasG || tmG != nullptr);
+            const bool vec = tmP != nullptr && tmG != nullptr;
             const int R = vec ? stream_rows(boxCols) : 1;
             const int nchunks = vec ? (M + R - 1) / R : 0;
             int issued = 0;
@@ -279,9 +158,8 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
                     if (lane == 0)
                     {
                         // the whole box counts, whether or not part of it lies outside the matrix (that part is zero-filled)
-                        mbar_arrive_expect_tx(&sFull[slot], (unsigned) ((hasG ? 2 : 1) * boxCols * R * 4));
-                        if (hasG)
-                            tensor_load_2d(inG + slot * ST_IN_FLOATS, tmG, issued * R, col0, &sFull[slot]);
+                        mbar_arrive_expect_tx(&sFull[slot], (unsigned) (2 * boxCols * R * 4));
+                        tensor_load_2d(inG + slot * ST_IN_FLOATS, tmG, issued * R, col0, &sFull[slot]);
                         tensor_load_2d(inP + slot * ST_IN_FLOATS, tmP, issued * R, col0, &sFull[slot]);
                     }
                 }
@@ -330,7 +208,7 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
         // ---- the item being streamed: geometry (uniform) and this thread's positions ----------------------------------------
         const QTensor* Tp = &sT[0];
         int M = 1, Q = 1, nc = 1, col0 = 0, R = 32, nchunks = 0;
-        bool hasG = true, vec = false;
+        bool vec = false;
         const float* gbase = nullptr;
         const float* pbase = nullptr;
         float* obase = nullptr;
@@ -357,8 +235,7 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
             nc = sItem[b].ncols;
             col0 = sItem[b].col0;
             const int geo = stream_geometry(T, nc);
-            hasG = !STRIPES || T.selfRaw;
-            vec = T.tm[geo][1] != nullptr && (!hasG || T.tm[geo][0] != nullptr);
+            vec = T.tm[geo][1] != nullptr && T.tm[geo][0] != nullptr;
             R = stream_rows(vec ? T.boxCols[geo] : nc);
             nchunks = (M + R - 1) / R;
             gbase = T.grad;
@@ -396,11 +273,7 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
         while (more)
         {
             const QTensor& T = *Tp;
-            const int nsrc = STRIPES ? T.nsrc : 0;
-            const int firstPacked = hasG ? 1 : 0;      // owner kernel: sources firstPacked .. nsrc - 1 are packed
-            const int colWords = Q + 2;
             const int vstride = R + 4;
-            unsigned* const srcw = pkw + nc * Q;       // staged packed sources
 
             // ---- per-item state ----------------------------------------------------------------------------------------
             for (int i = tid; i < nc * Q; i += NT)
@@ -411,34 +284,6 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
                 sLv1[tid] = lvReg1;
                 sNan[tid] = 0u;
                 sDst[tid] = packed_col(T, col0 + tid);
-            }
-            // owner kernel: the item's columns of every packed source are staged in shared memory when they fit next to
-            // the item's own packed words (one contiguous block of nc * (2 + Q) words per source); else they are read in place
-            const bool staged = STRIPES && (nc * Q + (nsrc - firstPacked) * nc * colWords <= QAGG_STREAM_PKWORDS_OWNER);
-            if (STRIPES)
-            {
-                if (staged)
-                {
-                    const int blockWords = nc * colWords;
-                    for (int s = firstPacked; s < nsrc; ++s)
-                    {
-                        const unsigned* src = reinterpret_cast<const unsigned*>(T.src[s] + (size_t) col0 * T.colBytes);
-                        unsigned* dst = srcw + (s - firstPacked) * blockWords;
-                        for (int i = tid; i < blockWords; i += NT)
-                            dst[i] = __ldg(src + i);
-                    }
-                    consumer_sync();
-                }
-                for (int i = tid; i < (nsrc - firstPacked) * nc; i += NT)
-                {
-                    const int sp = i / nc, c = i - sp * nc;
-                    const unsigned* hdr = staged ? srcw + (sp * nc + c) * colWords
-                                                 : reinterpret_cast<const unsigned*>(T.src[sp + firstPacked] + (size_t) (col0 + c) * T.colBytes);
-                    float v0, v1;
-                    levels_1bit(__uint_as_float(hdr[0]), __uint_as_float(hdr[1]), v0, v1);
-                    sSrc0[STRIPES ? sp : 0][c] = v0;
-                    sSrc1[STRIPES ? sp : 0][c] = v1;
-                }
             }
             consumer_sync();
 
@@ -463,14 +308,11 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
                             prev[1] = p4.y;
                             prev[2] = p4.z;
                             prev[3] = p4.w;
-                            if (hasG)
-                            {
-                                const float4 g4 = *reinterpret_cast<const float4*>(inG + inOff + iofs[u]);
-                                agg[0] = g4.x;
-                                agg[1] = g4.y;
-                                agg[2] = g4.z;
-                                agg[3] = g4.w;
-                            }
+                            const float4 g4 = *reinterpret_cast<const float4*>(inG + inOff + iofs[u]);
+                            agg[0] = g4.x;
+                            agg[1] = g4.y;
+                            agg[2] = g4.z;
+                            agg[3] = g4.w;
                         }
                         else
                         {
@@ -479,46 +321,12 @@ __global__ void __launch_bounds__(NT + 32, stream_ctas_per_sm(STRIPES)) k_stream
                             for (int i = 0; i < 4; ++i)
                             {
                                 prev[i] = (i < nv) ? pbase[gofs[u] + (size_t) row0 + i] : 0.0f;
-                                if (hasG)
-                                    agg[i] = (i < nv) ? gbase[gofs[u] + (size_t) row0 + i] : 0.0f;
+                                agg[i] = (i < nv) ? gbase[gofs[u] + (size_t) row0 + i] : 0.0f;
                             }
                         }
                         const float lv0 = sLv0[c], lv1 = sLv1[c];
                         // the usual case: the four rows are the same bit of four adjacent words
                         const bool flat = (nv == 4) && (pw[u] + 3u < (unsigned) Q);
-                        if (STRIPES)
-                        {
-                            // (word, bit) of the four rows
-                            unsigned wi[4], ki[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                            {
-                                const unsigned w = pw[u] + i;
-                                const unsigned over = flat ? 0u : w / (unsigned) Q;
-                                ki[i] = pk[u] + over;
-                                wi[i] = w - over * (unsigned) Q;
-                            }
-                            // the K sources in index order (the own stripe first), the residual last
-                            // (AllReduceDistGradAggregator.h:366-375, 405-435)
-                            bool first = !hasG;
-                            for (int sp = 0; sp < nsrc - firstPacked; ++sp)
-                            {
-                                const float s0 = sSrc0[STRIPES ? sp : 0][c], s1 = sSrc1[STRIPES ? sp : 0][c];
-                                const unsigned* words = staged ? srcw + (sp * nc + c) * colWords + 2
-                                                               : reinterpret_cast<const unsigned*>(T.src[sp + firstPacked] + (size_t) (col0 + c) * T.colBytes) + 2;
-#pragma unroll
-                                for (int i = 0; i < 4; ++i)
-                                {
-                                    if (i < nv)
-                                    {
-                                        const unsigned word = staged ? words[wi[i]] : __ldg(words + wi[i]);
-                                        const float val = ((word >> ki[i]) & 1u) ? s1 : s0;
-                                        agg[i] = first ? val : __fadd_rn(val, agg[i]);
-                                    }
-                                }
-                                first = false;
-                            }
-                        }
                         float v[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
@@ -767,14 +575,14 @@ static int nice_cols(double want, int most)
     return best;
 }
 
-void stream_make_items(const std::vector<std::pair<long long, long long>>& shapes, int numSMs, int bits, int packedSources,
-                       std::vector<QItem>& out, std::vector<std::pair<int, int>>& boxCols)
+void stream_make_items(const std::vector<std::pair<long long, long long>>& shapes, int numSMs, int bits, std::vector<QItem>& out,
+                       std::vector<std::pair<int, int>>& boxCols)
 {
     boxCols.assign(shapes.size(), std::pair<int, int>(0, 0));
     long long total = 0;
     for (auto& sh : shapes)
         total += sh.first * sh.second;
-    const long long slots = (long long) numSMs * stream_ctas_per_sm(packedSources > 0);
+    const long long slots = (long long) numSMs * ST_CTAS_PER_SM;
     long long target = total / (2 * slots > 0 ? 2 * slots : 1);
     target = target < 4096 ? 4096 : (target > 49152 ? 49152 : target);
     struct Cand
@@ -790,10 +598,7 @@ void stream_make_items(const std::vector<std::pair<long long, long long>>& shape
         if (M <= 0 || N <= 0)
             continue;
         const long long Q = (M * bits + 31) / 32;
-        // the owner kernel stages its packed sources in shared memory if an item is narrow enough for that
-        int fit = stream_max_cols(Q, packedSources);
-        if (fit < 1)
-            fit = stream_max_cols(Q);
+        const int fit = stream_max_cols(Q);
         // at least eight columns where the matrix has them: with fewer, a chunk has so many rows that the walkers' add
         // chains, not the memory system, set the pace
         const int most = (int) std::min<long long>(fit, N);
@@ -857,7 +662,7 @@ static EncodeTiledFn tensor_map_encoder()
 }
 
 // map of a column-major M x N fp32 matrix with a box of boxRows rows x boxCols columns; false if it cannot be encoded
-static bool encode_map(void* out128, const float* base, long long M, long long N, int boxRows, int boxCols)
+bool encode_map_2d(void* out128, const float* base, long long M, long long N, int boxRows, int boxCols)
 {
     EncodeTiledFn enc = tensor_map_encoder();
     if (!enc || !base || M <= 0 || N <= 0 || (M & 3) || (reinterpret_cast<uintptr_t>(base) & 15) || boxRows < 1 || boxRows > 256 || boxCols < 1 ||
@@ -877,29 +682,27 @@ static bool encode_map(void* out128, const float* base, long long M, long long N
     return true;
 }
 
-void stream_set_maps(QTensor* t, bool stripes, unsigned char* hostMaps, unsigned char* devMaps)
+void stream_set_maps(QTensor* t, unsigned char* hostMaps, unsigned char* devMaps)
 {
-    const bool hasG = !stripes || t->selfRaw;
     bool ok = (reinterpret_cast<uintptr_t>(t->res_out) & 15) == 0 && (reinterpret_cast<uintptr_t>(devMaps) & 127) == 0;
     for (int g = 0; g < 2 && ok; ++g)
     {
         if (t->boxCols[g] <= 0)
             continue;
         const int R = stream_rows(t->boxCols[g]);
-        if (hasG)
-            ok = ok && encode_map(hostMaps + (2 * g) * 128, t->grad, t->M, t->N, R, t->boxCols[g]);
-        ok = ok && encode_map(hostMaps + (2 * g + 1) * 128, t->res_in, t->M, t->N, R, t->boxCols[g]);
+        ok = ok && encode_map_2d(hostMaps + (2 * g) * 128, t->grad, t->M, t->N, R, t->boxCols[g]);
+        ok = ok && encode_map_2d(hostMaps + (2 * g + 1) * 128, t->res_in, t->M, t->N, R, t->boxCols[g]);
     }
     for (int g = 0; g < 2; ++g)
     {
         const bool have = ok && t->boxCols[g] > 0;
-        t->tm[g][0] = (have && hasG) ? devMaps + (2 * g) * 128 : nullptr;
+        t->tm[g][0] = have ? devMaps + (2 * g) * 128 : nullptr;
         t->tm[g][1] = have ? devMaps + (2 * g + 1) * 128 : nullptr;
     }
 }
 
-cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors, const QItem* items, int nItems,
-                           const LaunchCfg& cfg, unsigned* counters, const Signal* signalp, unsigned* status)
+cudaError_t launch_stream1(cudaStream_t st, const QTensor* tensors, const QItem* items, int nItems, const LaunchCfg& cfg, unsigned* counters,
+                           const Signal* signalp, unsigned* status)
 {
     static const Signal none = {};
     const Signal& signal = signalp ? *signalp : none;
@@ -907,24 +710,13 @@ cudaError_t launch_stream1(cudaStream_t st, bool stripes, const QTensor* tensors
         return cudaErrorInvalidValue;
     if (nItems <= 0)
         return signal.n > 0 ? launch_signal_only(st, signal) : cudaSuccess;
-    int grid = cfg.numSMs * stream_ctas_per_sm(stripes);
+    int grid = cfg.numSMs * ST_CTAS_PER_SM;
     if (grid > nItems)
         grid = nItems;
-    cudaError_t e;
-    if (stripes)
-    {
-        e = cudaFuncSetAttribute(k_stream1<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) stream_smem_bytes(true));
-        if (e != cudaSuccess)
-            return e;
-        k_stream1<true><<<grid, NT + 32, stream_smem_bytes(true), st>>>(tensors, items, nItems, counters, signal, status);
-    }
-    else
-    {
-        e = cudaFuncSetAttribute(k_stream1<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) stream_smem_bytes(false));
-        if (e != cudaSuccess)
-            return e;
-        k_stream1<false><<<grid, NT + 32, stream_smem_bytes(false), st>>>(tensors, items, nItems, counters, signal, status);
-    }
+    cudaError_t e = cudaFuncSetAttribute(k_stream1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) ST_SMEM_BYTES);
+    if (e != cudaSuccess)
+        return e;
+    k_stream1<<<grid, NT + 32, ST_SMEM_BYTES, st>>>(tensors, items, nItems, counters, signal, status);
     return cudaGetLastError();
 }
 

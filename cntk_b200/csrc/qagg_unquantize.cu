@@ -2,28 +2,37 @@
 //
 // Pure expand-and-store: a packed column of Q words becomes M floats, 32/bits times as many bytes, so the kernel is bound
 // by the write bandwidth of HBM and everything is arranged around the stores.
-//   * Output-major mapping.  Row i of a column is field i / Q of word i % Q.  A lane produces FOUR CONSECUTIVE ROWS and
-//     stores them as one aligned 16-byte vector, whatever Q is (the word-major mapping of the reference kernel, thread <->
-//     word, yields vector stores only when Q is a multiple of 4; a 9304-row column has Q = 291).  The four fields come
-//     from (usually) four adjacent words, re-read from the L1 cache for every field position.
-//   * Work unit = 512 consecutive rows of one column = one warp, four vectors per lane, all of a unit's words fetched before
-//     the first store.  Warps take units u, u + (warps in the grid), ...: no shared memory, no barrier, no atomics.  A launch
-//     has thousands of units per SM-resident warp set, so the grid (4 CTAs per SM) ends evenly; a launch with one CTA per
-//     group of columns did not (its last partial wave of CTAs ran on a mostly idle GPU).
-//   * Units are numbered matrix after matrix, column after column: consecutive warps write consecutive memory.
-// Matrices whose rows are not a multiple of 4 (or whose output is not 16-byte aligned) take a scalar form of the same loop.
+//   * Word-major mapping, as the layout suggests: word w of a column holds rows w, w + Q, w + 2Q, ...  A lane fetches FOUR
+//     ADJACENT WORDS once and, per field position k, stores the four rows 4w' + kQ .. + 3 as one aligned 16-byte vector
+//     (possible when M and Q are multiples of 4 and the output is 16-byte aligned).  Otherwise a lane takes four words
+//     32 apart and the warp stores 32 consecutive rows per position with 4-byte stores.
+//   * Work unit = 128 consecutive words of a matrix (columns laid end to end) x 8 field positions = one warp; 4 KB of
+//     output in the 1-bit case.  Warps take units u, u + (warps in the grid), ...: no shared memory, no barrier, no
+//     atomics.  A launch has ten or so units per resident warp and the grid is sized so that they divide evenly, so all
+//     CTAs end together; a launch with one CTA per group of columns did not (its last partial wave of CTAs ran on a mostly
+//     idle GPU).
+//   * Units are numbered matrix after matrix, the field-position blocks of one word group next to each other:
+//     neighbouring warps write neighbouring memory.
 #include "qagg_device.cuh"
 
 namespace qagg {
 
-constexpr int UNQ_ROWS = 512; // rows per unit: 32 lanes x 4 vectors x 4 rows
-constexpr int UNQ_VEC = 4;    // vectors per lane and unit
+constexpr int UNQ_WORDS = 128; // packed words per unit
+constexpr int UNQ_KPU = 8;     // field positions per unit
 
-long long unq_units(long long M, long long N)
+// field-position blocks per word: 4 for 1 bit, 2 for 2 bits, else 1 (always a power of two)
+__host__ __device__ __forceinline__ int unq_ksplit(int bits)
+{
+    const int vpw = 32 / bits;
+    return (vpw + UNQ_KPU - 1) / UNQ_KPU;
+}
+
+long long unq_units(long long M, long long N, int bits)
 {
     if (M <= 0 || N <= 0)
         return 0;
-    return N * ((M + UNQ_ROWS - 1) / UNQ_ROWS);
+    const long long Q = (M * bits + 31) / 32;
+    return ((N * Q + UNQ_WORDS - 1) / UNQ_WORDS) * unq_ksplit(bits);
 }
 
 // the two constants unquantizing needs: 1 bit -> the two level values; else -> (ufactor, quantimin)
@@ -41,9 +50,10 @@ __device__ __forceinline__ void unq_consts(int bits, float lower, float upper, f
     }
 }
 
+template <bool ONEBIT>
 __device__ __forceinline__ float unq_field(int bits, unsigned word, unsigned k, unsigned mask, float ca, float cb)
 {
-    if (bits == 1)
+    if (ONEBIT)
         return ((word >> k) & 1u) ? cb : ca;
     if (bits == 32)
         return __uint_as_float(word);
@@ -51,13 +61,13 @@ __device__ __forceinline__ float unq_field(int bits, unsigned word, unsigned k, 
     return __fadd_rn(__fmul_rn(__fadd_rn((float) field, 0.5f), ca), cb);
 }
 
-template <bool ADD, bool TABLE>
+template <bool ADD, bool TABLE, bool ONEBIT>
 __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, const QTensor* __restrict__ tensors, int nTensors, long long totalUnits)
 {
-    const int lane = threadIdx.x & 31;
+    const unsigned lane = threadIdx.x & 31;
     const long long gwarp = (long long) blockIdx.x * NWARPS + (threadIdx.x >> 5);
     const long long nwarps = (long long) gridDim.x * NWARPS;
-    int cur = 0; // table entry of the previous unit: units of one warp mostly stay within one matrix
+    int cur = 0; // table entry of the previous unit: consecutive units of a warp mostly stay within one matrix
     for (long long u = gwarp; u < totalUnits; u += nwarps)
     {
         const QTensor* Tp = &single;
@@ -81,134 +91,171 @@ __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, cons
         }
         const unsigned M = (unsigned) Tp->M;
         const unsigned Q = (unsigned) Tp->Q;
-        const int bits = Tp->bits;
+        const int bits = ONEBIT ? 1 : Tp->bits;
+        const unsigned vpw = 32u / (unsigned) bits;
         const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
-        const unsigned blocksPerCol = (M + UNQ_ROWS - 1) / UNQ_ROWS;
+        const int ks = unq_ksplit(bits);
+        const int ksShift = (ks == 4) ? 2 : (ks == 2) ? 1 : 0;
         const unsigned long long local = (unsigned long long) (u - (TABLE ? Tp->unit0 : 0));
-        const unsigned col = (unsigned) (local / blocksPerCol);
-        const unsigned row0 = (unsigned) (local - (unsigned long long) col * blocksPerCol) * UNQ_ROWS;
-        const unsigned char* colp = TABLE ? packed_col(*Tp, (int) col) : single.pk[0] + (size_t) col * (size_t) single.colBytes;
-        const float lower = __ldg(reinterpret_cast<const float*>(colp));
-        const float upper = __ldg(reinterpret_cast<const float*>(colp) + 1);
-        const unsigned* __restrict__ words = reinterpret_cast<const unsigned*>(colp + 8);
-        float ca, cb;
-        unq_consts(bits, lower, upper, ca, cb);
-        float* __restrict__ out = Tp->out + (size_t) col * M;
-        const bool vec = ((M & 3u) == 0) && ((reinterpret_cast<uintptr_t>(Tp->out) & 15) == 0);
+        const unsigned k0 = (unsigned) (local & (unsigned long long) (ks - 1)) * UNQ_KPU;
+        const unsigned long long t0 = (local >> ksShift) * UNQ_WORDS; // first word of the unit, columns laid end to end
+        const unsigned long long totalWords = (unsigned long long) Tp->N * Q;
+        // column and word of the unit's first word: a 32-bit division when the matrix is small enough for that
+        unsigned col0, w0;
+        if (totalWords <= 0xffffffffull)
+        {
+            col0 = (unsigned) t0 / Q;
+            w0 = (unsigned) t0 - col0 * Q;
+        }
+        else
+        {
+            col0 = (unsigned) (t0 / Q);
+            w0 = (unsigned) (t0 - (unsigned long long) col0 * Q);
+        }
+        const unsigned left = (unsigned) ((totalWords - t0 < UNQ_WORDS) ? (totalWords - t0) : UNQ_WORDS); // words of this unit
+        float* __restrict__ outBase = Tp->out;
+        const bool vec = ((M & 3u) == 0) && ((Q & 3u) == 0) && ((reinterpret_cast<uintptr_t>(outBase) & 15) == 0);
         if (vec)
         {
-            // lane <-> rows row0 + 4 * lane + 128 * i .. + 3
-            const unsigned r0 = row0 + 4u * lane;
-            unsigned k = r0 / Q, w = r0 - k * Q;
-            const unsigned advK = 128u / Q, advW = 128u - advK * Q;
-            unsigned wd[UNQ_VEC][4], kk[UNQ_VEC][4];
-#pragma unroll
-            for (int i = 0; i < UNQ_VEC; ++i)
+            // lane <-> words 4 * lane .. + 3 of the unit: the same column (Q is a multiple of 4), rows 4-aligned
+            const unsigned off = 4u * lane;
+            if (off < left)
             {
-                const bool live = r0 + 128u * i < M;
+                const unsigned tl = w0 + off;
+                const unsigned dc = tl / Q;
+                const unsigned c = col0 + dc, w = tl - dc * Q;
+                const unsigned char* colp = TABLE ? packed_col(*Tp, (int) c) : single.pk[0] + (size_t) c * (size_t) single.colBytes;
+                const float lower = __ldg(reinterpret_cast<const float*>(colp));
+                const float upper = __ldg(reinterpret_cast<const float*>(colp) + 1);
+                const unsigned* __restrict__ words = reinterpret_cast<const unsigned*>(colp + 8) + w;
+                const unsigned wa = __ldg(words), wb = __ldg(words + 1), wc = __ldg(words + 2), wd = __ldg(words + 3);
+                float ca, cb;
+                unq_consts(bits, lower, upper, ca, cb);
+                float* __restrict__ op = outBase + (size_t) c * M + w;
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
+                for (unsigned kk = 0; kk < UNQ_KPU; ++kk)
                 {
-                    unsigned ww = w + e, ke = k;
-                    while (ww >= Q) // the four rows straddle the end of the word array (several times over when Q < 4)
+                    const unsigned k = k0 + kk;
+                    if (k < vpw && w + k * Q < M)
                     {
-                        ww -= Q;
-                        ++ke;
-                    }
-                    kk[i][e] = ke;
-                    wd[i][e] = live ? __ldg(words + ww) : 0u;
-                }
-                w += advW;
-                k += advK;
-                if (w >= Q)
-                {
-                    w -= Q;
-                    ++k;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < UNQ_VEC; ++i)
-            {
-                const unsigned r = r0 + 128u * i;
-                if (r < M)
-                {
-                    float4 v;
-                    v.x = unq_field(bits, wd[i][0], kk[i][0], mask, ca, cb);
-                    v.y = unq_field(bits, wd[i][1], kk[i][1], mask, ca, cb);
-                    v.z = unq_field(bits, wd[i][2], kk[i][2], mask, ca, cb);
-                    v.w = unq_field(bits, wd[i][3], kk[i][3], mask, ca, cb);
-                    float4* p = reinterpret_cast<float4*>(out + r);
-                    if (ADD)
-                    {
-                        const float4 o = *p;
-                        v.x = __fadd_rn(v.x, o.x);
-                        v.y = __fadd_rn(v.y, o.y);
-                        v.z = __fadd_rn(v.z, o.z);
-                        v.w = __fadd_rn(v.w, o.w);
-                        *p = v;
-                    }
-                    else
-                    {
-                        __stcs(p, v);
+                        float4 v;
+                        v.x = unq_field<ONEBIT>(bits, wa, k, mask, ca, cb);
+                        v.y = unq_field<ONEBIT>(bits, wb, k, mask, ca, cb);
+                        v.z = unq_field<ONEBIT>(bits, wc, k, mask, ca, cb);
+                        v.w = unq_field<ONEBIT>(bits, wd, k, mask, ca, cb);
+                        float4* p = reinterpret_cast<float4*>(op + (size_t) k * Q);
+                        if (ADD)
+                        {
+                            const float4 o = *p;
+                            v.x = __fadd_rn(v.x, o.x);
+                            v.y = __fadd_rn(v.y, o.y);
+                            v.z = __fadd_rn(v.z, o.z);
+                            v.w = __fadd_rn(v.w, o.w);
+                            *p = v;
+                        }
+                        else
+                        {
+                            __stcs(p, v);
+                        }
                     }
                 }
             }
         }
         else
         {
-            // lane <-> rows row0 + lane + 32 * i
-            const unsigned r0 = row0 + lane;
-            unsigned k = r0 / Q, w = r0 - k * Q;
-            const unsigned advK = 32u / Q, advW = 32u - advK * Q;
-            constexpr int NS = UNQ_ROWS / 32;
-#pragma unroll 4
-            for (int i = 0; i < NS; ++i)
+            // lane <-> words lane, lane + 32, lane + 64, lane + 96 of the unit: per position the warp stores 32 consecutive rows
+            unsigned wd[4], cc[4], ww[4];
+            float lo[4], up[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
             {
-                const unsigned r = r0 + 32u * i;
-                if (r < M)
+                const unsigned off = lane + 32u * e;
+                wd[e] = 0u;
+                cc[e] = ww[e] = 0u;
+                lo[e] = up[e] = 0.0f;
+                if (off < left)
                 {
-                    float val = unq_field(bits, __ldg(words + w), k, mask, ca, cb);
-                    if (ADD)
-                        val = __fadd_rn(val, out[r]);
-                    out[r] = val;
+                    const unsigned tl = w0 + off;
+                    const unsigned dc = tl / Q;
+                    cc[e] = col0 + dc;
+                    ww[e] = tl - dc * Q;
+                    const unsigned char* colp = TABLE ? packed_col(*Tp, (int) cc[e]) : single.pk[0] + (size_t) cc[e] * (size_t) single.colBytes;
+                    lo[e] = __ldg(reinterpret_cast<const float*>(colp));
+                    up[e] = __ldg(reinterpret_cast<const float*>(colp) + 1);
+                    wd[e] = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + ww[e]);
                 }
-                w += advW;
-                k += advK;
-                if (w >= Q)
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+            {
+                if (lane + 32u * e < left)
                 {
-                    w -= Q;
-                    ++k;
+                    float ca, cb;
+                    unq_consts(bits, lo[e], up[e], ca, cb);
+                    float* __restrict__ op = outBase + (size_t) cc[e] * M + ww[e];
+#pragma unroll
+                    for (unsigned kk = 0; kk < UNQ_KPU; ++kk)
+                    {
+                        const unsigned k = k0 + kk;
+                        if (k < vpw && ww[e] + k * Q < M)
+                        {
+                            float val = unq_field<ONEBIT>(bits, wd[e], k, mask, ca, cb);
+                            if (ADD)
+                                val = __fadd_rn(val, op[(size_t) k * Q]);
+                            op[(size_t) k * Q] = val;
+                        }
+                    }
                 }
             }
         }
     }
 }
 
-cudaError_t launch_unquantize(cudaStream_t st, bool add, const QTensor* single, const QTensor* tensors, int nTensors, long long totalUnits,
+// Grid: at most four CTAs per SM; among the sizes from three to four per SM, the one whose warps share the units most evenly.
+static int unq_grid(long long totalUnits, int numSMs)
+{
+    const long long need = (totalUnits + NWARPS - 1) / NWARPS;
+    const long long most = (long long) numSMs * 4;
+    if (need <= most)
+        return (int) need;
+    long long best = most;
+    double bestWaste = 2.0;
+    for (long long g = most; g >= (long long) numSMs * 3; --g)
+    {
+        const long long warps = g * NWARPS;
+        const long long rounds = (totalUnits + warps - 1) / warps;
+        const double waste = 1.0 - (double) totalUnits / (double) (rounds * warps);
+        if (waste < bestWaste - 1e-9)
+        {
+            bestWaste = waste;
+            best = g;
+        }
+    }
+    return (int) best;
+}
+
+cudaError_t launch_unquantize(cudaStream_t st, bool add, int bits, const QTensor* single, const QTensor* tensors, int nTensors, long long totalUnits,
                               const LaunchCfg& cfg)
 {
     if (totalUnits <= 0)
         return cudaSuccess;
-    long long grid = (long long) cfg.numSMs * 4;
-    const long long need = (totalUnits + NWARPS - 1) / NWARPS;
-    if (grid > need)
-        grid = need;
+    const int grid = unq_grid(totalUnits, cfg.numSMs);
     static const QTensor zero = {};
     const QTensor& s = single ? *single : zero;
-    if (single)
-    {
-        if (add)
-            k_unquantize<true, false><<<(int) grid, NT, 0, st>>>(s, nullptr, 1, totalUnits);
-        else
-            k_unquantize<false, false><<<(int) grid, NT, 0, st>>>(s, nullptr, 1, totalUnits);
-    }
-    else
-    {
-        if (add)
-            k_unquantize<true, true><<<(int) grid, NT, 0, st>>>(s, tensors, nTensors, totalUnits);
-        else
-            k_unquantize<false, true><<<(int) grid, NT, 0, st>>>(s, tensors, nTensors, totalUnits);
-    }
+    const bool table = (single == nullptr);
+    const bool onebit = (bits == 1);
+#define QAGG_UNQ_CASE(A, T, O)                  \
+    if (add == A && table == T && onebit == O) \
+        k_unquantize<A, T, O><<<grid, NT, 0, st>>>(s, tensors, nTensors, totalUnits);
+    QAGG_UNQ_CASE(false, false, false)
+    QAGG_UNQ_CASE(false, false, true)
+    QAGG_UNQ_CASE(false, true, false)
+    QAGG_UNQ_CASE(false, true, true)
+    QAGG_UNQ_CASE(true, false, false)
+    QAGG_UNQ_CASE(true, false, true)
+    QAGG_UNQ_CASE(true, true, false)
+    QAGG_UNQ_CASE(true, true, true)
+#undef QAGG_UNQ_CASE
     return cudaGetLastError();
 }
 

@@ -61,7 +61,7 @@ _lib.qagg_plan_gather_slot_bytes.argtypes = [c_vp]
 _lib.qagg_plan_destroy.argtypes = [c_vp]
 _lib.qagg_stream_wait_selftest.argtypes = [c_vp, c_int, c_vp, c_vp]
 _lib.qagg_plan_stream_items.restype = c_i64
-_lib.qagg_plan_stream_items.argtypes = [c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, c_int, c_int, ctypes.POINTER(ctypes.c_int32), c_i64]
+_lib.qagg_plan_stream_items.argtypes = [c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, c_int, ctypes.POINTER(ctypes.c_int32), c_i64]
 _lib.qagg_unique_id.argtypes = [c_vp]
 _lib.qagg_comm_create.argtypes = [c_vp, c_int, c_int, c_int, ctypes.POINTER(c_vp)]
 _lib.qagg_comm_create_local_group.argtypes = [c_int, c_int, ctypes.POINTER(c_vp)]
@@ -199,17 +199,17 @@ class Plan:
             self.h = None
 
 
-def stream_items(shapes, bits=1, num_sms=148, packed_sources=0):
+def stream_items(shapes, bits=1, num_sms=148):
     """Work items of the streaming quantize kernel for a tensor set: list of (tensor, first column, columns) in queue
     order (qagg_plan_stream_items; host arithmetic only)."""
     T = len(shapes)
     Ms = (c_i64 * T)(*[s[0] for s in shapes])
     Ns = (c_i64 * T)(*[s[1] for s in shapes])
-    n = int(_lib.qagg_plan_stream_items(T, Ms, Ns, bits, num_sms, packed_sources, None, 0))
+    n = int(_lib.qagg_plan_stream_items(T, Ms, Ns, bits, num_sms, None, 0))
     if n < 0:
         _ok(n)
     buf = (ctypes.c_int32 * (3 * max(n, 1)))()
-    n2 = int(_lib.qagg_plan_stream_items(T, Ms, Ns, bits, num_sms, packed_sources, buf, n))
+    n2 = int(_lib.qagg_plan_stream_items(T, Ms, Ns, bits, num_sms, buf, n))
     if n2 < 0:
         _ok(n2)
     return [(buf[3 * k], buf[3 * k + 1], buf[3 * k + 2]) for k in range(n)]

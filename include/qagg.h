@@ -131,10 +131,8 @@ int qagg_plan_destroy(qagg_plan* p);
  * for a device with `num_sms` SMs; host arithmetic only.  An item is `columns` adjacent columns of one tensor, starting at
  * `first column`; items are listed in queue order (most row chunks first, the last quarter cut into thirds).  Writes
  * min(count, capacity) triples (tensor, first column, columns) to `items` and returns count, or a negative QAGG_E* code.
- * `packed_sources` = 0 for the quantize kernel, K (or K - 1 with a raw own stripe) for the owner kernel.  No reference
- * counterpart: the reference launches one kernel per matrix (Source/Math/MatrixQuantizerGPU.cu:226-341). */
-int64_t qagg_plan_stream_items(int num_tensors, const int64_t* M, const int64_t* N, int bits, int num_sms, int packed_sources,
-                               int32_t* items, int64_t capacity);
+ * No reference counterpart: the reference launches one kernel per matrix (Source/Math/MatrixQuantizerGPU.cu:226-341). */
+int64_t qagg_plan_stream_items(int num_tensors, const int64_t* M, const int64_t* N, int bits, int num_sms, int32_t* items, int64_t capacity);
 
 /* ---- communicator ---------------------------------------------------------------------------------
  * Replaces the MPI point-to-point traffic of the reference (Source/1BitSGD/AllReduceDistGradAggregator.h:303-365,

@@ -126,3 +126,51 @@ def aggregate_step(backend, state, grads, bits, zero_thr=True, self_quant=True, 
 
     _each_rank(executor, unquantize_all, K)
     return [gathered for _ in range(K)]
+
+
+def owner_of(col, num_cols, K):
+    """Rank whose stripe (GetStripeForNode) holds column `col` of a matrix with `num_cols` columns."""
+    per, rem = divmod(num_cols, K)
+    big = (per + 1) * rem
+    if col < big:
+        return col // (per + 1)
+    return rem + (col - big) // per
+
+
+def aggregate_columns(backend, owner, g, res, sres, bits, zero_thr=True, self_quant=True):
+    """The exchange restricted to a set of columns that share one owner rank.
+
+    A column's aggregate depends on that column alone -- its K gradients, its K pre-aggregation residuals and its
+    owner's stripe residual -- and on who owns it only through the order of the owner's sum (own stripe first, then the
+    sources by ascending rank).  So the steps of ``aggregate_step`` can be replayed for any sample of columns of a
+    full-size tensor.
+
+    g[r], res[r]: (n, M) float32 per rank r (n sampled columns); res[r] is updated in place to the new residual.
+    sres: (n, M) float32, the owner's stripe residual of these columns, updated in place.
+    Returns (out, packed): the aggregate every rank ends with, (n, M) float32, and the n requantized packed columns.
+    With K == 1 this is V1's quantize -> unquantize round trip (no stripe requantization, :429 never fires).
+    """
+    K = len(g)
+    n, M = g[0].shape
+    C = backend.packed_col_bytes(M, bits)
+    packed = []
+    for r in range(K):
+        p = np.zeros(n * C, np.uint8)
+        backend.quantize(np.ascontiguousarray(g[r]), res[r], res[r], p, bits, zero_thr)
+        packed.append(p)
+    out = np.zeros((n, M), np.float32)
+    if K == 1:
+        backend.unquantize(packed[0], out, bits, add=False)
+        return out, packed[0]
+    if self_quant:
+        agg = np.zeros((n, M), np.float32)
+        backend.unquantize(packed[owner], agg, bits, add=False)
+    else:
+        agg = np.ascontiguousarray(g[owner]).copy()
+    for src in range(K):
+        if src != owner:
+            backend.unquantize(packed[src], agg, bits, add=True)
+    requant = np.zeros(n * C, np.uint8)
+    backend.quantize(agg, sres, sres, requant, bits, zero_thr)
+    backend.unquantize(requant, out, bits, add=False)
+    return out, requant

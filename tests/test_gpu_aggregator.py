@@ -243,12 +243,13 @@ def test_lstm_shaped_set_ragged(G, oracle_port, K):
     run_group(G, oracle_port, LSTM_SMALL, K, 1, True, True, 10, lstm_inputs, check_every=5)
 
 
-@pytest.mark.parametrize("stream_knob", ["0", "2"])
-def test_kernel_choice_knob_changes_no_result(G, oracle_port, stream_knob, monkeypatch):
-    """QAGG_STREAM is a tuning knob read when an aggregator is created: 0 = resident-column kernels only (plain residuals),
-    2 = streaming kernel also for the owner's reduce-requantize (deferred stripe residuals).  Either way aggregates,
-    both residual sets and the gathered packed words stay bit-identical to the oracle (the default, 1, is what every
-    other 1-bit zero-threshold test in this file runs)."""
-    monkeypatch.setenv("QAGG_STREAM", stream_knob)
+@pytest.mark.parametrize("knob", ["QAGG_STREAM", "QAGG_OWNER"])
+def test_kernel_choice_knob_changes_no_result(G, oracle_port, knob, monkeypatch):
+    """Tuning knobs read when an aggregator is created: QAGG_STREAM=0 = resident-column kernels only (plain residuals),
+    QAGG_OWNER=0 = resident-column kernel for the owner's reduce-requantize only (plain stripe residuals).  Either way
+    aggregates, both residual sets and the gathered packed words stay bit-identical to the oracle (the default -- streaming
+    quantize kernel, form + walk owner kernels, both residual sets deferred -- is what every other 1-bit zero-threshold
+    test in this file runs)."""
+    monkeypatch.setenv(knob, "0")
     run_group(G, oracle_port, SPEECH_SMALL, 3, 1, True, True, 6, speech_inputs, check_every=3)
     run_group(G, oracle_port, mg.EXCHANGE_SHAPES, 2, 1, True, False, 4, mg.exchange_inputs, peer=True)

@@ -4,6 +4,7 @@ reproduce any sampled column of a full-size tensor exactly.
 
   * conservation (Tests/UnitTests/MathTests/MatrixQuantizerTests.cpp:327-338): in + old residual == new residual + output
   * every rank of a group ends with byte-identical aggregates
+  * multi-rank runs: sampled columns of every tensor replayed through the whole exchange on the CPU checker, bit-exact
   * a 1-bit column's output takes at most two values, and padding bits of the packed words are zero
   * sampled columns: packed words, reconstruction values and residuals identical to the oracle's
 """
@@ -85,34 +86,78 @@ def test_speech_dnn_full_size_single_rank(env):
         comm.destroy()
 
 
-def run_group_fullsize(lib, shapes, K, bits, make_grad, steps):
-    dev = "cuda:0"
+def run_group_fullsize(lib, oracle, shapes, K, bits, make_grad, steps, check_at, verify_ranks=None, peer=True):
+    """K ranks on one device, full-size tensors, `steps` error-feedback steps.  At the steps in `check_at` a seeded sample
+    of columns of every tensor (stripe edges included) is replayed on the CPU checker from the ranks' captured inputs and
+    compared bit for bit: aggregates, residuals, stripe residuals, gathered packed columns (tests/parity_util.py).  Every
+    step: all ranks end with byte-identical aggregates."""
+    import parity_util as pu
     comms = lib.Comm.local_group(K, 0)
     aggs = [lib.Aggregator(c, shapes, bits) for c in comms]
+    if peer and K > 1:
+        hs = [a.peer_handle() for a in aggs]
+        for a in aggs:
+            a.enable_peer(hs)
+    verify_ranks = sorted(set(verify_ranks if verify_ranks is not None else [0, K // 2, K - 1]))
+    columns = 0
     try:
-        for step in range(steps):
+        for step in range(1, steps + 1):
             work = [[make_grad(r, step, i, M, N) for i, (M, N) in enumerate(shapes)] for r in range(K)]
-            sums = [sum(work[r][i].double() for r in range(K)) for i in range(len(shapes))]
+            caps = None
+            if step in check_at:
+                cols = pu.pick_columns(shapes, K, seed=1000 + step)
+                caps = [pu.RankCapture(lib, aggs[r], r, K, shapes, bits, cols) for r in range(K)]
+                for r in range(K):
+                    caps[r].before(work[r])
             lib.step_group(aggs, [[t.data_ptr() for t in work[r]] for r in range(K)])
             torch.cuda.synchronize()
-            for i, (M, N) in enumerate(shapes):
+            for i in range(len(shapes)):
                 for r in range(1, K):
-                    assert torch.equal(work[0][i].view(torch.int32), work[r][i].view(torch.int32)), f"ranks 0 and {r} disagree on tensor {i}"
-                # the aggregate tracks the true sum: correlation check (quantization noise is large but unbiased per column)
-                if M * N >= 1 << 16 and float(sums[i].abs().max()) > 0:
-                    a, b = work[0][i].double().flatten(), sums[i].flatten()
-                    corr = float((a * b).sum() / (a.norm() * b.norm() + 1e-300))
-                    assert corr > (0.3 if bits == 1 else 0.9), f"tensor {i}: aggregate does not follow the sum of the gradients (corr {corr})"
+                    assert torch.equal(work[0][i].view(torch.int32), work[r][i].view(torch.int32)), f"step {step}: ranks 0 and {r} disagree on tensor {i}"
+            if caps:
+                inputs = [c.inp for c in caps]
+                for r in verify_ranks:
+                    caps[r].after(work[r])
+                    columns += pu.verify(oracle, caps[r], inputs)
+        for a in aggs:
+            a.check()
     finally:
         for a in aggs:
             a.destroy()
         for c in comms:
             c.destroy()
+    assert columns > 0
+    return columns
+
+
+def test_speech_dnn_full_size_8_ranks_100_steps(env):
+    """Config 2 at full size (16 tensors, 45,122,648 values per rank, 1 bit, threshold 0), 8 ranks, 100 error-feedback
+    steps; sampled columns against the CPU checker at steps 1, 25, 50, 75 and 100.  This is where the owner kernels meet
+    full-height 9304-row and 2048-row stripes."""
+    lib, workloads, oracle = env
+    shapes = workloads.speech_dnn()
+
+    def make(r, step, i, M, N):
+        return device_normal((N, M), 1e-3, 1000 * r + step + 7919 * i)
+
+    run_group_fullsize(lib, oracle, shapes, 8, 1, make, 100, {1, 25, 50, 75, 100})
+
+
+@pytest.mark.parametrize("K", [2, 4])
+def test_speech_dnn_full_size_2_and_4_ranks(env, K):
+    """Config 2 at full size on 2 and 4 ranks, 10 steps, sampled columns at steps 1, 5 and 10."""
+    lib, workloads, oracle = env
+
+    def make(r, step, i, M, N):
+        return device_normal((N, M), 1e-3, 77000 + 1000 * r + step + 7919 * i)
+
+    run_group_fullsize(lib, oracle, workloads.speech_dnn(), K, 1, make, 10, {1, 5, 10}, verify_ranks=[0, K - 1])
 
 
 def test_resnet50_full_size_4bit_8_ranks(env):
-    """Config 3: 161 tensors, 25,557,032 values, 4 bits, Laplace(0, 1e-4), 8 ranks on one device."""
-    lib, workloads, _ = env
+    """Config 3: 161 tensors, 25,557,032 values, 4 bits, Laplace(0, 1e-4), 8 ranks on one device, 20 steps; sampled columns
+    against the CPU checker at steps 1, 10 and 20."""
+    lib, workloads, oracle = env
     shapes = workloads.resnet50()
     assert len(shapes) == 161 and workloads.total_values(shapes) == 25557032
 
@@ -122,12 +167,13 @@ def test_resnet50_full_size_4bit_8_ranks(env):
         u = (torch.rand((N, M), generator=g, device="cuda:0", dtype=torch.float32) - 0.5).clamp(-0.4999999, 0.4999999)
         return -1e-4 * torch.sign(u) * torch.log1p(-2 * u.abs())  # inverse-CDF Laplace(0, 1e-4)
 
-    run_group_fullsize(lib, shapes, 8, 4, make, 2)
+    run_group_fullsize(lib, oracle, shapes, 8, 4, make, 20, {1, 10, 20})
 
 
 def test_lstm_lm_full_size_ragged(env):
     """Config 4: 50000-row embedding with 90 % all-zero columns (columns taller than shared memory: streamed path),
-    512 x 50000 softmax, bias vectors; 2 ranks; plus oracle spot checks of the embedding through the single-matrix entry point."""
+    512 x 50000 softmax, bias vectors; 2 ranks (6 steps) and 8 ranks (3 steps) with sampled columns against the CPU checker;
+    plus spot checks of the embedding through the single-matrix entry point."""
     lib, workloads, oracle = env
     shapes = workloads.lstm_lm()
 
@@ -140,7 +186,8 @@ def test_lstm_lm_full_size_ragged(env):
             a[zero] = 0.0
         return a
 
-    run_group_fullsize(lib, shapes, 2, 1, make, 2)
+    run_group_fullsize(lib, oracle, shapes, 2, 1, make, 6, {1, 3, 6}, verify_ranks=[0, 1])
+    run_group_fullsize(lib, oracle, shapes, 8, 1, make, 3, {1, 3}, verify_ranks=[0, 5])
     M, N = shapes[0]
     rng = np.random.default_rng(4)
     g = make(0, 0, 0, M, N)

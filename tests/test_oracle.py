@@ -193,3 +193,39 @@ def test_port_equals_reference_build_directly(oracle_port, oracle_ref):
             oracle_port.unquantize(pa, oa, bits, add=bool(it % 2))
             oracle_ref.unquantize(pb, ob_, bits, add=bool(it % 2))
             np.testing.assert_array_equal(oa.view(np.uint32), ob_.view(np.uint32))
+
+
+@pytest.mark.parametrize("K", [1, 2, 3, 8])
+def test_column_subset_replay_equals_full_exchange(oracle_port, K):
+    """aggregate_columns (what the full-size and multi-GPU checks replay for sampled columns) reproduces aggregate_step
+    column for column: aggregates, residuals, stripe residuals and packed columns, over three error-feedback steps."""
+    rng = np.random.default_rng(11 + K)
+    shapes = [(70, 19), (33, 5), (128, 1), (5, 16)]
+    for bits, zero_thr, self_q in ((1, True, True), (1, False, True), (4, True, True), (1, True, False)):
+        st = ox.ExchangeState(shapes, K)
+        sub_res = [[np.zeros((N, M), np.float32) for (M, N) in shapes] for _ in range(K)]
+        sub_sres = [np.zeros((N, M), np.float32) for (M, N) in shapes]  # indexed by global column
+        for step in range(3):
+            grads = [[(rng.standard_normal((N, M)) * 1e-2).astype(np.float32) for (M, N) in shapes] for _ in range(K)]
+            keep = [[a.copy() for a in grads[r]] for r in range(K)]
+            packed = ox.aggregate_step(oracle_port, st, grads, bits, zero_thr, self_q)
+            for i, (M, N) in enumerate(shapes):
+                C = oracle_port.packed_col_bytes(M, bits)
+                for owner in range(K):
+                    cols = [c for c in range(N) if ox.owner_of(c, N, K) == owner]
+                    s, n = ox.stripe(N, owner, K)
+                    assert cols == list(range(s, s + n))
+                    if not cols:
+                        continue
+                    g = [keep[r][i][cols] for r in range(K)]
+                    res = [np.ascontiguousarray(sub_res[r][i][cols]) for r in range(K)]
+                    sres = np.ascontiguousarray(sub_sres[i][cols])
+                    out, pk = ox.aggregate_columns(oracle_port, owner, g, res, sres, bits, zero_thr, self_q)
+                    for r in range(K):
+                        sub_res[r][i][cols] = res[r]
+                        np.testing.assert_array_equal(res[r].view(np.uint32), st.res[r][i][cols].view(np.uint32))
+                        np.testing.assert_array_equal(out.view(np.uint32), grads[r][i][cols].view(np.uint32))
+                    sub_sres[i][cols] = sres
+                    if K > 1:
+                        np.testing.assert_array_equal(sres.view(np.uint32), st.sres[owner][i].view(np.uint32))
+                    np.testing.assert_array_equal(pk, packed[0][i][s * C:(s + n) * C])

@@ -5,7 +5,6 @@ import pytest
 from cntk_b200 import lib, workloads
 
 PKWORDS = 2560        # shared-memory words for an item's packed columns (quantize kernel)
-PKWORDS_OWNER = 4480  # owner kernel
 TILE_VALUES = 1536    # values per chunk
 
 
@@ -63,18 +62,6 @@ def test_speech_set_queue_order_and_widths():
     assert max(tail) <= 11
     # deterministic
     assert items == lib.stream_items(shapes, bits=1, num_sms=148)
-
-
-@pytest.mark.parametrize("K", [2, 8])
-def test_owner_items_respect_staging_budget(K):
-    shapes = [(M, N // K) for M, N in workloads.speech_dnn() if N // K > 0]
-    items = lib.stream_items(shapes, bits=1, num_sms=148, packed_sources=K)
-    check_cover(shapes, items)
-    for t, c0, n in items:
-        Q = (shapes[t][0] + 31) // 32
-        staged = n * Q + K * n * (Q + 2)
-        # either the K packed sources fit next to the item's own words, or the item is as narrow as the fallback allows
-        assert staged <= PKWORDS_OWNER or n * Q <= PKWORDS
 
 
 def test_bad_arguments():
