@@ -714,9 +714,7 @@ __global__ void __launch_bounds__(NT, QAGG_CTAS_PER_SM) k_colquant(const QTensor
         {
             counters[0] = 0;
             counters[1] = 0;
-            __threadfence_system();
-            for (int i = 0; i < signal.n; ++i)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
+            release_flags(signal);
         }
     }
 }
@@ -790,9 +788,7 @@ static cudaError_t launch_cq(cudaStream_t st, const QTensor* single, const QTens
 
 __global__ void k_signal_only(const Signal signal)
 {
-    __threadfence_system();
-    for (int i = 0; i < signal.n; ++i)
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
+    release_flags(signal);
 }
 
 cudaError_t launch_signal_only(cudaStream_t st, const Signal& signal)
@@ -819,9 +815,7 @@ __global__ void __launch_bounds__(256) k_push(const uint4* __restrict__ src, siz
         if (done == gridDim.x - 1)
         {
             counters[1] = 0;
-            __threadfence_system();
-            for (int i = 0; i < signal.n; ++i)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
+            release_flags(signal);
         }
     }
 }

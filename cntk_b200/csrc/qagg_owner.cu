@@ -13,8 +13,8 @@
 //                  every peer's.  No shared memory, no barrier; warps take 32-word units u, u + warps, ...
 //                  It also counts each column's rows with v >= 0 and flags NaNs (integers: no order needed).
 //   k_owner_walk   the serial part, nothing else.  One CTA = a producer warp and two walking warps (one per level); a work
-//                  item is 32 adjacent columns, lane <-> column.  The producer brings tiles of 132 rows x 32 columns of
-//                  the just-written state (mostly still in L2) into a 4-slot ring with one tensor copy each; both walkers
+//                  item is 32 adjacent columns, lane <-> column.  The producer brings tiles of 252 rows x 32 columns of
+//                  the just-written state (mostly still in L2) into a 6-slot ring with one tensor copy each; both walkers
 //                  add min(v, 0) resp. max(v, 0) down their lane's tile column.  All columns of all owned stripes walk
 //                  concurrently, every walking warp has up to 32 active lanes, and the launch lasts as long as the tallest
 //                  column's add chain (about 4.4 cycles per row).  At the end: range, header (to all gather slots), the
@@ -30,11 +30,11 @@
 namespace qagg {
 
 constexpr int OW_HALF = 16;   // rows (field positions) per thread
-constexpr int OW_SRC = 8;     // packed sources fetched per batch
-constexpr int OW_R = 132;     // tile rows: 4 x an odd number, so that the 128-bit reads of neighbouring tile columns fall
-                              // into distinct banks (the tile is dense: column stride = OW_R floats)
+constexpr int OW_SRC = 4;     // packed sources fetched per batch
+constexpr int OW_R = 252;     // tile rows: 4 x an odd number, so that the 128-bit reads of neighbouring tile columns fall
+                              // into distinct banks (the tile is dense: column stride = OW_R floats); at most 256 (copy box)
 constexpr int OW_C = 32;      // tile columns = lanes of a walking warp
-constexpr int OW_STAGES = 4;  // ring slots
+constexpr int OW_STAGES = 6;  // ring slots: a walking warp drains a tile in about 0.6 us, a tensor copy takes a few times that
 constexpr int OW_TILE_FLOATS = OW_R * OW_C;
 constexpr int OW_THREADS = 96;
 constexpr size_t OW_SMEM_BYTES = (size_t) OW_STAGES * OW_TILE_FLOATS * 4;
@@ -47,155 +47,289 @@ long long owner_form_units(long long M, long long n)
     return 2 * ((n * Q + 31) / 32);
 }
 
-__global__ void __launch_bounds__(NT, 3) k_owner_form(const QTensor* __restrict__ tensors, int nTensors, long long totalUnits, const Signal signal)
+// where a unit's lane works: table entry, column, word, first field position
+struct FormCtx
 {
-    const unsigned lane = threadIdx.x & 31;
-    const long long gwarp = (long long) blockIdx.x * NWARPS + (threadIdx.x >> 5);
-    const long long nwarps = (long long) gridDim.x * NWARPS;
-    int cur = 0;
-    for (long long u = gwarp; u < totalUnits; u += nwarps)
+    const QTensor* T;
+    unsigned c, w, kb, col0;
+    bool live, full; // full: all OW_HALF rows of this lane exist (no per-row checks needed)
+};
+
+__device__ __forceinline__ FormCtx form_locate(const QTensor* __restrict__ tensors, int nTensors, long long u, int& cur, unsigned lane)
+{
+    if (!(tensors[cur].unit0 <= u && (cur + 1 >= nTensors || u < tensors[cur + 1].unit0)))
     {
-        if (!(tensors[cur].unit0 <= u && (cur + 1 >= nTensors || u < tensors[cur + 1].unit0)))
+        int lo = 0, hi = nTensors;
+        while (hi - lo > 1)
         {
-            int lo = 0, hi = nTensors;
-            while (hi - lo > 1)
-            {
-                const int mid = (lo + hi) >> 1;
-                if (tensors[mid].unit0 <= u)
-                    lo = mid;
-                else
-                    hi = mid;
-            }
-            cur = lo;
+            const int mid = (lo + hi) >> 1;
+            if (tensors[mid].unit0 <= u)
+                lo = mid;
+            else
+                hi = mid;
         }
-        const QTensor* __restrict__ Tp = tensors + cur;
-        const unsigned M = (unsigned) Tp->M;
-        const unsigned Q = (unsigned) Tp->Q;
-        const unsigned long long local = (unsigned long long) (u - Tp->unit0);
-        const unsigned kb = (unsigned) (local & 1ull) * OW_HALF;  // this unit's rows are field positions kb .. kb + 15
-        const unsigned long long t0 = (local >> 1) * 32ull;       // first word of the unit, columns laid end to end
-        const unsigned long long totalWords = (unsigned long long) Tp->N * Q;
-        unsigned col0, w0;
-        if (totalWords <= 0xffffffffull)
+        cur = lo;
+    }
+    FormCtx x;
+    x.T = tensors + cur;
+    const unsigned M = (unsigned) x.T->M;
+    const unsigned Q = (unsigned) x.T->Q;
+    const unsigned long long local = (unsigned long long) (u - x.T->unit0);
+    x.kb = (unsigned) (local & 1ull) * OW_HALF;          // this unit's rows are field positions kb .. kb + 15
+    const unsigned long long t0 = (local >> 1) * 32ull;  // first word of the unit, columns laid end to end
+    const unsigned long long totalWords = (unsigned long long) x.T->N * Q;
+    unsigned w0;
+    if (totalWords <= 0xffffffffull)
+    {
+        x.col0 = (unsigned) t0 / Q;
+        w0 = (unsigned) t0 - x.col0 * Q;
+    }
+    else
+    {
+        x.col0 = (unsigned) (t0 / Q);
+        w0 = (unsigned) (t0 - (unsigned long long) x.col0 * Q);
+    }
+    x.live = t0 + lane < totalWords;
+    const unsigned tl = w0 + lane;
+    const unsigned dc = tl / Q;
+    x.c = x.live ? x.col0 + dc : x.col0;
+    x.w = x.live ? tl - dc * Q : 0u;
+    x.full = x.live && (x.w + (x.kb + OW_HALF - 1) * Q < M);
+    return x;
+}
+
+// The unit's previous-state values go into flight: 4-byte asynchronous copies into the warp's staging buffer, slot
+// [k][lane] for row k of this lane.  A lane reads back only what it copied itself, so waiting for its own copy groups is
+// all the synchronisation needed.
+__device__ __forceinline__ void form_stage_prev(const FormCtx& x, float* __restrict__ buf, unsigned lane)
+{
+    if (x.live)
+    {
+        const unsigned M = (unsigned) x.T->M, Q = (unsigned) x.T->Q;
+        const float* __restrict__ p = x.T->res_in + (size_t) x.c * M + x.w + (size_t) x.kb * Q;
+        const unsigned dst = smem_addr(buf + lane);
+#pragma unroll
+        for (int k = 0; k < OW_HALF; ++k)
+            if (x.full || x.w + (x.kb + k) * Q < M)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + (unsigned) k * 128u), "l"(p + (size_t) k * Q) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory"); // every lane commits, with or without copies: the group counts stay in step
+}
+
+__device__ __forceinline__ void form_unit(const FormCtx& x, const float* __restrict__ buf, const Signal& signal, unsigned lane)
+{
+    const QTensor* __restrict__ Tp = x.T;
+    const unsigned M = (unsigned) Tp->M, Q = (unsigned) Tp->Q;
+    const unsigned c = x.c, w = x.w, kb = x.kb;
+    unsigned bitsOut = 0u;
+    float nanSum = 0.0f;
+    if (x.live)
+    {
+        const size_t colOff = (size_t) c * M + w + (size_t) kb * Q;
+        float* __restrict__ outp = Tp->res_out + colOff;
+        const bool selfRaw = Tp->selfRaw != 0;
+        const int nsrc = Tp->nsrc;
+        const size_t colBytes = (size_t) Tp->colBytes;
+        const float lv0 = Tp->lv[2 * (size_t) c], lv1 = Tp->lv[2 * (size_t) c + 1];
+        float agg[OW_HALF];
+        // the K sources in index order (the own stripe first), the residual last (AllReduceDistGradAggregator.h:366-375, 405-435)
+        if (selfRaw)
         {
-            col0 = (unsigned) t0 / Q;
-            w0 = (unsigned) t0 - col0 * Q;
+            const float* __restrict__ rawp = Tp->grad + colOff;
+#pragma unroll
+            for (int k = 0; k < OW_HALF; ++k)
+                agg[k] = (x.full || w + (kb + k) * Q < M) ? __ldcs(rawp + (size_t) k * Q) : 0.0f;
         }
         else
         {
-            col0 = (unsigned) (t0 / Q);
-            w0 = (unsigned) (t0 - (unsigned long long) col0 * Q);
+            // the first packed source starts the sum (the reference unquantizes it with add = false)
+            const unsigned char* colp = Tp->src[0] + (size_t) c * colBytes;
+            float v0, v1;
+            levels_1bit(__ldg(reinterpret_cast<const float*>(colp)), __ldg(reinterpret_cast<const float*>(colp) + 1), v0, v1);
+            const unsigned word = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + w) >> kb;
+#pragma unroll
+            for (int k = 0; k < OW_HALF; ++k)
+                agg[k] = (word & (1u << k)) ? v1 : v0;
         }
-        const bool live = t0 + lane < totalWords;
-        const unsigned tl = w0 + lane;
-        const unsigned dc = tl / Q;
-        const unsigned c = live ? col0 + dc : col0;
-        const unsigned w = live ? tl - dc * Q : 0u;
-        unsigned bitsOut = 0u, nan = 0u;
-        if (live)
+        for (int s = 1; s < nsrc; s += OW_SRC)
         {
-            const size_t colOff = (size_t) c * M + w;
-            const float* __restrict__ prevp = Tp->res_in + colOff;
-            float* __restrict__ outp = Tp->res_out + colOff;
-            const bool selfRaw = Tp->selfRaw != 0;
-            const float* __restrict__ rawp = Tp->grad + colOff; // used only when selfRaw
-            const int nsrc = Tp->nsrc;
-            const size_t colBytes = (size_t) Tp->colBytes;
-            float prev[OW_HALF], agg[OW_HALF];
+            unsigned sw[OW_SRC];
+            float sv0[OW_SRC], sv1[OW_SRC];
+#pragma unroll
+            for (int j = 0; j < OW_SRC; ++j)
+            {
+                // a source index past the end re-reads the last source; its result is discarded below
+                const unsigned char* colp = Tp->src[min(s + j, nsrc - 1)] + (size_t) c * colBytes;
+                sv0[j] = __ldg(reinterpret_cast<const float*>(colp));
+                sv1[j] = __ldg(reinterpret_cast<const float*>(colp) + 1);
+                sw[j] = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + w) >> kb;
+            }
+#pragma unroll
+            for (int j = 0; j < OW_SRC; ++j)
+            {
+                if (s + j < nsrc) // uniform over the warp's live lanes of one table entry
+                {
+                    float v0, v1;
+                    levels_1bit(sv0[j], sv1[j], v0, v1);
+#pragma unroll
+                    for (int k = 0; k < OW_HALF; ++k)
+                        agg[k] = __fadd_rn((sw[j] & (1u << k)) ? v1 : v0, agg[k]);
+                }
+            }
+        }
+        if (x.full)
+        {
 #pragma unroll
             for (int k = 0; k < OW_HALF; ++k)
             {
-                const unsigned row = w + (kb + k) * Q;
-                prev[k] = (row < M) ? __ldcs(prevp + (size_t) (kb + k) * Q) : 0.0f;
-                agg[k] = (selfRaw && row < M) ? __ldcs(rawp + (size_t) (kb + k) * Q) : 0.0f;
+                const float v = __fadd_rn(agg[k], deferred_residual(buf[k * 32 + lane], lv0, lv1));
+                outp[(size_t) k * Q] = v; // read again by the walk kernel: a plain store, so that it stays in L2
+                bitsOut |= (v >= 0.0f) ? (1u << k) : 0u;
+                nanSum = __fadd_rn(nanSum, v);
             }
-            const float lv0 = Tp->lv[2 * (size_t) c], lv1 = Tp->lv[2 * (size_t) c + 1];
-            // the K sources in index order (the own stripe first), the residual last (AllReduceDistGradAggregator.h:366-375, 405-435)
-            int s = selfRaw ? 1 : 0;
-            if (!selfRaw)
-            {
-                // the first packed source starts the sum (the reference unquantizes it with add = false)
-                const unsigned char* colp = Tp->src[0] + (size_t) c * colBytes;
-                float v0, v1;
-                levels_1bit(__ldg(reinterpret_cast<const float*>(colp)), __ldg(reinterpret_cast<const float*>(colp) + 1), v0, v1);
-                const unsigned word = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + w) >> kb;
-#pragma unroll
-                for (int k = 0; k < OW_HALF; ++k)
-                    agg[k] = ((word >> k) & 1u) ? v1 : v0;
-                s = 1;
-            }
-            for (; s < nsrc; s += OW_SRC)
-            {
-                unsigned sw[OW_SRC];
-                float slo[OW_SRC], sup[OW_SRC];
-#pragma unroll
-                for (int j = 0; j < OW_SRC; ++j)
-                {
-                    sw[j] = 0u;
-                    slo[j] = sup[j] = 0.0f;
-                    if (s + j < nsrc)
-                    {
-                        const unsigned char* colp = Tp->src[s + j] + (size_t) c * colBytes;
-                        slo[j] = __ldg(reinterpret_cast<const float*>(colp));
-                        sup[j] = __ldg(reinterpret_cast<const float*>(colp) + 1);
-                        sw[j] = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + w) >> kb;
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < OW_SRC; ++j)
-                {
-                    if (s + j < nsrc)
-                    {
-                        float v0, v1;
-                        levels_1bit(slo[j], sup[j], v0, v1);
-#pragma unroll
-                        for (int k = 0; k < OW_HALF; ++k)
-                            agg[k] = __fadd_rn(((sw[j] >> k) & 1u) ? v1 : v0, agg[k]);
-                    }
-                }
-            }
+        }
+        else
+        {
 #pragma unroll
             for (int k = 0; k < OW_HALF; ++k)
             {
                 if (w + (kb + k) * Q < M)
                 {
-                    const float v = __fadd_rn(agg[k], deferred_residual(prev[k], lv0, lv1));
-                    outp[(size_t) (kb + k) * Q] = v; // read again by the walk kernel: a plain store, so that it stays in L2
+                    const float v = __fadd_rn(agg[k], deferred_residual(buf[k * 32 + lane], lv0, lv1));
+                    outp[(size_t) k * Q] = v;
                     bitsOut |= (v >= 0.0f) ? (1u << k) : 0u;
-                    nan |= (v != v) ? 1u : 0u;
+                    nanSum = __fadd_rn(nanSum, v);
                 }
             }
-            // this half of the packed word, to this rank's gather slot and to every peer's
-            unsigned char* const dst = Tp->pk[0] + (size_t) c * colBytes;
-            const size_t wordOff = 8 + 4 * (size_t) w + (kb ? 2 : 0);
-            *reinterpret_cast<unsigned short*>(dst + wordOff) = (unsigned short) bitsOut;
-            if (Tp->bcast)
-            {
-                const size_t off = (size_t) (dst - Tp->pk[0]) + (size_t) Tp->bcastOff + wordOff;
-                for (int b = 0; b < signal.nbcast; ++b)
-                    *reinterpret_cast<unsigned short*>(signal.bcastBase[b] + off) = (unsigned short) bitsOut;
-            }
         }
-        // per-column count of rows with v >= 0: one atomic per warp when the warp lies inside one column
-        const unsigned ones = __popc(bitsOut);
-        unsigned* __restrict__ stats = Tp->stats;
-        const bool oneColumn = __all_sync(0xffffffffu, !live || c == col0);
-        if (oneColumn)
+        // this half of the packed word, to this rank's gather slot and to every peer's
+        unsigned char* const dst = Tp->pk[0] + (size_t) c * colBytes;
+        const size_t wordOff = 8 + 4 * (size_t) w + (kb ? 2 : 0);
+        *reinterpret_cast<unsigned short*>(dst + wordOff) = (unsigned short) bitsOut;
+        if (Tp->bcast)
         {
-            const unsigned tot = __reduce_add_sync(0xffffffffu, ones);
-            if (lane == 0 && tot)
-                atomicAdd(&stats[2 * (size_t) col0], tot);
+            const size_t off = (size_t) (dst - Tp->pk[0]) + (size_t) Tp->bcastOff + wordOff;
+            for (int b = 0; b < signal.nbcast; ++b)
+                *reinterpret_cast<unsigned short*>(signal.bcastBase[b] + off) = (unsigned short) bitsOut;
         }
-        else if (live && ones)
-        {
-            atomicAdd(&stats[2 * (size_t) c], ones);
-        }
-        if (live && nan)
-            atomicOr(&stats[2 * (size_t) c + 1], 1u);
     }
+    // per-column count of rows with v >= 0: one atomic per warp when the warp lies inside one column
+    const unsigned ones = __popc(bitsOut);
+    unsigned* __restrict__ stats = Tp->stats;
+    const bool oneColumn = __all_sync(0xffffffffu, !x.live || c == x.col0);
+    if (oneColumn)
+    {
+        const unsigned tot = __reduce_add_sync(0xffffffffu, ones);
+        if (lane == 0 && tot)
+            atomicAdd(&stats[2 * (size_t) x.col0], tot);
+    }
+    else if (x.live && ones)
+    {
+        atomicAdd(&stats[2 * (size_t) c], ones);
+    }
+    // a NaN among the values shows in their running sum (so does a pair of opposite infinities, whose column range is NaN
+    // in the reference as well: its level means are then infinities of opposite sign)
+    if (x.live && nanSum != nanSum)
+        atomicOr(&stats[2 * (size_t) c + 1], 1u);
 }
 
-__global__ void __launch_bounds__(OW_THREADS, 3) k_owner_walk(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
+// Warps take units u, u + warps, ...  The previous-state values of a warp's next two units are already on their way into
+// its three staging buffers while it works on the current one, so the memory latency overlaps the arithmetic without
+// holding registers (the loop is unrolled by three so that every buffer and context has a fixed name).
+constexpr int FORM_BUF_FLOATS = OW_HALF * 32;
+__global__ void __launch_bounds__(NT, 3) k_owner_form(const QTensor* __restrict__ tensors, int nTensors, long long totalUnits, const Signal signal)
+{
+    __shared__ __align__(16) float sStage[NWARPS][3][FORM_BUF_FLOATS];
+    const unsigned lane = threadIdx.x & 31;
+    const unsigned warp = threadIdx.x >> 5;
+    const long long gwarp = (long long) blockIdx.x * NWARPS + warp;
+    const long long nwarps = (long long) gridDim.x * NWARPS;
+    if (gwarp >= totalUnits)
+        return;
+    int cur = 0;
+    float* const b0 = sStage[warp][0];
+    float* const b1 = sStage[warp][1];
+    float* const b2 = sStage[warp][2];
+    FormCtx x0, x1, x2;
+    // units of this warp: u0 = gwarp, then + nwarps each; `have` says whether the unit exists
+    long long u = gwarp;
+    x0 = form_locate(tensors, nTensors, u, cur, lane);
+    form_stage_prev(x0, b0, lane);
+    bool have1 = u + nwarps < totalUnits;
+    if (have1)
+        x1 = form_locate(tensors, nTensors, u + nwarps, cur, lane);
+    else
+        x1 = x0, x1.live = false;
+    form_stage_prev(x1, b1, lane);
+    for (;;)
+    {
+        // ---- current x0, next x1, staging x2 ----
+        bool have2 = u + 2 * nwarps < totalUnits;
+        if (have2)
+            x2 = form_locate(tensors, nTensors, u + 2 * nwarps, cur, lane);
+        else
+            x2 = x0, x2.live = false;
+        form_stage_prev(x2, b2, lane);
+        asm volatile("cp.async.wait_group 2;" ::: "memory");
+        form_unit(x0, b0, signal, lane);
+        if (!have1)
+            break;
+        u += nwarps;
+        // ---- current x1, next x2, staging x0 ----
+        bool have0 = u + 2 * nwarps < totalUnits;
+        if (have0)
+            x0 = form_locate(tensors, nTensors, u + 2 * nwarps, cur, lane);
+        else
+            x0 = x1, x0.live = false;
+        form_stage_prev(x0, b0, lane);
+        asm volatile("cp.async.wait_group 2;" ::: "memory");
+        form_unit(x1, b1, signal, lane);
+        if (!have2)
+            break;
+        u += nwarps;
+        // ---- current x2, next x0, staging x1 ----
+        have1 = u + 2 * nwarps < totalUnits;
+        if (have1)
+            x1 = form_locate(tensors, nTensors, u + 2 * nwarps, cur, lane);
+        else
+            x1 = x2, x1.live = false;
+        form_stage_prev(x1, b1, lane);
+        asm volatile("cp.async.wait_group 2;" ::: "memory");
+        form_unit(x2, b2, signal, lane);
+        if (!have0)
+            break;
+        u += nwarps;
+        // the roles are back where they started: x0 current, x1 next
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+// one walking warp's pass over the tiles of an item: full tiles with the unrolled walk, the last (partial) one generally
+template <int KIND>
+__device__ __forceinline__ float walk_item(const float* tiles, unsigned long long* sFull, unsigned long long* sEmpty, unsigned* sBroken, unsigned* status,
+                                           unsigned pos, int ntiles, int M, bool active, int lane)
+{
+    float acc = 0.0f;
+    for (int q = 0; q < ntiles; ++q)
+    {
+        const unsigned p = pos + (unsigned) q;
+        const unsigned slot = p % OW_STAGES;
+        mbar_wait(&sFull[slot], (p / OW_STAGES) & 1u, sBroken, status, ST_WAIT_TRIES, 20);
+        if (active && !*reinterpret_cast<volatile unsigned*>(sBroken))
+        {
+            // rows past the end of the matrix are zero-filled, but a partial tile is walked only as far as the matrix goes
+            const float* vcol = tiles + slot * OW_TILE_FLOATS + lane * OW_R;
+            const int nrows = M - q * OW_R;
+            acc = (nrows >= OW_R) ? walk_tile<KIND, OW_R>(vcol, acc) : walk_chunk<KIND>(vcol, nrows, acc);
+        }
+        __syncwarp();
+        if (lane == 0)
+            mbar_arrive(&sEmpty[slot]);
+    }
+    return acc;
+}
+
+__global__ void __launch_bounds__(OW_THREADS, 1) k_owner_walk(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
                                                            const Signal signal, unsigned* __restrict__ counters, unsigned* __restrict__ status)
 {
     extern __shared__ __align__(128) float tiles[];
@@ -249,23 +383,11 @@ __global__ void __launch_bounds__(OW_THREADS, 3) k_owner_walk(const QTensor* __r
             float acc = 0.0f;
             if (tmap)
             {
-                for (int q = 0; q < ntiles; ++q)
-                {
-                    const unsigned p = pos + (unsigned) q;
-                    const unsigned slot = p % OW_STAGES;
-                    mbar_wait(&sFull[slot], (p / OW_STAGES) & 1u, &sBroken, status);
-                    if (lane < nc && !*reinterpret_cast<volatile unsigned*>(&sBroken))
-                    {
-                        // rows past the end of the matrix are zero-filled; adding +0 changes nothing (the sums start at +0 and a
-                        // round-to-nearest sum is -0 only if both operands are), so full tiles are walked whole
-                        const int nrows = min(OW_R, (M - q * OW_R + 3) & ~3);
-                        const float* vcol = tiles + slot * OW_TILE_FLOATS + lane * OW_R;
-                        acc = (warp == 1) ? walk_chunk<WALK_MIN0>(vcol, nrows, acc) : walk_chunk<WALK_MAX0>(vcol, nrows, acc);
-                    }
-                    __syncwarp();
-                    if (lane == 0)
-                        mbar_arrive(&sEmpty[slot]);
-                }
+                // the two levels are two copies of the loop, so that each warp runs straight-line code for its own level
+                if (warp == 1)
+                    acc = walk_item<WALK_MIN0>(tiles, sFull, sEmpty, &sBroken, status, pos, ntiles, M, lane < nc, lane);
+                else
+                    acc = walk_item<WALK_MAX0>(tiles, sFull, sEmpty, &sBroken, status, pos, ntiles, M, lane < nc, lane);
             }
             else if (lane < nc)
             {
@@ -317,9 +439,7 @@ __global__ void __launch_bounds__(OW_THREADS, 3) k_owner_walk(const QTensor* __r
         if (done == gridDim.x - 1)
         {
             counters[1] = 0;
-            __threadfence_system();
-            for (int i = 0; i < signal.n; ++i)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
+            release_flags(signal);
         }
     }
 }
@@ -398,7 +518,7 @@ cudaError_t launch_owner(cudaStream_t st, const QTensor* tensors, int nTensors, 
     e = cudaFuncSetAttribute(k_owner_walk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) OW_SMEM_BYTES);
     if (e != cudaSuccess)
         return e;
-    int grid = cfg.numSMs * 3;
+    int grid = cfg.numSMs; // one CTA per SM: the ring takes most of an SM's shared memory
     if (grid > nItems)
         grid = nItems;
     k_owner_walk<<<grid, OW_THREADS, OW_SMEM_BYTES, st>>>(tensors, items, nItems, signal, counters, status);

@@ -501,9 +501,7 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
         {
             counters[0] = 0;
             counters[1] = 0;
-            __threadfence_system();
-            for (int i = 0; i < signal.n; ++i)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(signal.flag[i]), "r"(signal.value) : "memory");
+            release_flags(signal);
         }
     }
 }

@@ -61,149 +61,182 @@ __device__ __forceinline__ float unq_field(int bits, unsigned word, unsigned k, 
     return __fadd_rn(__fmul_rn(__fadd_rn((float) field, 0.5f), ca), cb);
 }
 
-template <bool ADD, bool TABLE, bool ONEBIT>
-__global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, const QTensor* __restrict__ tensors, int nTensors, long long totalUnits)
+// One unit as a lane sees it: where it writes, and the packed words and column headers it needs (fetched one unit ahead).
+struct UnqUnit
 {
-    const unsigned lane = threadIdx.x & 31;
-    const long long gwarp = (long long) blockIdx.x * NWARPS + (threadIdx.x >> 5);
-    const long long nwarps = (long long) gridDim.x * NWARPS;
-    int cur = 0; // table entry of the previous unit: consecutive units of a warp mostly stay within one matrix
-    for (long long u = gwarp; u < totalUnits; u += nwarps)
+    float* op[4];     // destination of position 0 of each of the lane's (up to four) words; vector form: op[0] only
+    unsigned wd[4];   // the words
+    float lo[4], up[4];
+    unsigned w[4];    // word index within its column (for the end-of-column check)
+    unsigned M, Q, k0;
+    int bits;
+    unsigned live;    // bit e set: word e exists
+    bool vec;
+};
+
+template <bool TABLE>
+__device__ __forceinline__ void unq_fetch(UnqUnit& x, const QTensor& single, const QTensor* __restrict__ tensors, int nTensors, long long u, int& cur,
+                                          unsigned lane, bool onebit)
+{
+    const QTensor* Tp = &single;
+    if (TABLE)
     {
-        const QTensor* Tp = &single;
-        if (TABLE)
+        // last table entry whose first unit is <= u (entries without units share their successor's first unit)
+        if (!(tensors[cur].unit0 <= u && (cur + 1 >= nTensors || u < tensors[cur + 1].unit0)))
         {
-            // last table entry whose first unit is <= u (entries without units share their successor's first unit)
-            if (!(tensors[cur].unit0 <= u && (cur + 1 >= nTensors || u < tensors[cur + 1].unit0)))
+            int lo = 0, hi = nTensors;
+            while (hi - lo > 1)
             {
-                int lo = 0, hi = nTensors;
-                while (hi - lo > 1)
-                {
-                    const int mid = (lo + hi) >> 1;
-                    if (tensors[mid].unit0 <= u)
-                        lo = mid;
-                    else
-                        hi = mid;
-                }
-                cur = lo;
+                const int mid = (lo + hi) >> 1;
+                if (tensors[mid].unit0 <= u)
+                    lo = mid;
+                else
+                    hi = mid;
             }
-            Tp = tensors + cur;
+            cur = lo;
         }
-        const unsigned M = (unsigned) Tp->M;
-        const unsigned Q = (unsigned) Tp->Q;
-        const int bits = ONEBIT ? 1 : Tp->bits;
-        const unsigned vpw = 32u / (unsigned) bits;
-        const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
-        const int ks = unq_ksplit(bits);
-        const int ksShift = (ks == 4) ? 2 : (ks == 2) ? 1 : 0;
-        const unsigned long long local = (unsigned long long) (u - (TABLE ? Tp->unit0 : 0));
-        const unsigned k0 = (unsigned) (local & (unsigned long long) (ks - 1)) * UNQ_KPU;
-        const unsigned long long t0 = (local >> ksShift) * UNQ_WORDS; // first word of the unit, columns laid end to end
-        const unsigned long long totalWords = (unsigned long long) Tp->N * Q;
-        // column and word of the unit's first word: a 32-bit division when the matrix is small enough for that
-        unsigned col0, w0;
-        if (totalWords <= 0xffffffffull)
+        Tp = tensors + cur;
+    }
+    const unsigned M = (unsigned) Tp->M;
+    const unsigned Q = (unsigned) Tp->Q;
+    x.M = M;
+    x.Q = Q;
+    x.bits = onebit ? 1 : Tp->bits;
+    const int ks = unq_ksplit(x.bits);
+    const int ksShift = (ks == 4) ? 2 : (ks == 2) ? 1 : 0;
+    const unsigned long long local = (unsigned long long) (u - (TABLE ? Tp->unit0 : 0));
+    x.k0 = (unsigned) (local & (unsigned long long) (ks - 1)) * UNQ_KPU;
+    const unsigned long long t0 = (local >> ksShift) * UNQ_WORDS; // first word of the unit, columns laid end to end
+    const unsigned long long totalWords = (unsigned long long) Tp->N * Q;
+    // column and word of the unit's first word: a 32-bit division when the matrix is small enough for that
+    unsigned col0, w0;
+    if (totalWords <= 0xffffffffull)
+    {
+        col0 = (unsigned) t0 / Q;
+        w0 = (unsigned) t0 - col0 * Q;
+    }
+    else
+    {
+        col0 = (unsigned) (t0 / Q);
+        w0 = (unsigned) (t0 - (unsigned long long) col0 * Q);
+    }
+    const unsigned left = (unsigned) ((totalWords - t0 < UNQ_WORDS) ? (totalWords - t0) : UNQ_WORDS); // words of this unit
+    float* __restrict__ outBase = Tp->out;
+    x.vec = ((M & 3u) == 0) && ((Q & 3u) == 0) && ((reinterpret_cast<uintptr_t>(outBase) & 15) == 0);
+    x.live = 0u;
+    if (x.vec)
+    {
+        // lane <-> words 4 * lane .. + 3 of the unit: the same column (Q is a multiple of 4), rows 4-aligned
+        const unsigned off = 4u * lane;
+        if (off < left)
         {
-            col0 = (unsigned) t0 / Q;
-            w0 = (unsigned) t0 - col0 * Q;
+            const unsigned tl = w0 + off;
+            const unsigned dc = tl / Q;
+            const unsigned c = col0 + dc, w = tl - dc * Q;
+            const unsigned char* colp = TABLE ? packed_col(*Tp, (int) c) : single.pk[0] + (size_t) c * (size_t) single.colBytes;
+            x.lo[0] = __ldg(reinterpret_cast<const float*>(colp));
+            x.up[0] = __ldg(reinterpret_cast<const float*>(colp) + 1);
+            const unsigned* __restrict__ words = reinterpret_cast<const unsigned*>(colp + 8) + w;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                x.wd[e] = __ldg(words + e);
+            x.w[0] = w;
+            x.op[0] = outBase + (size_t) c * M + w + (size_t) x.k0 * Q;
+            x.live = 1u;
         }
-        else
+    }
+    else
+    {
+        // lane <-> words lane, lane + 32, lane + 64, lane + 96 of the unit: per position the warp stores 32 consecutive rows
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
         {
-            col0 = (unsigned) (t0 / Q);
-            w0 = (unsigned) (t0 - (unsigned long long) col0 * Q);
-        }
-        const unsigned left = (unsigned) ((totalWords - t0 < UNQ_WORDS) ? (totalWords - t0) : UNQ_WORDS); // words of this unit
-        float* __restrict__ outBase = Tp->out;
-        const bool vec = ((M & 3u) == 0) && ((Q & 3u) == 0) && ((reinterpret_cast<uintptr_t>(outBase) & 15) == 0);
-        if (vec)
-        {
-            // lane <-> words 4 * lane .. + 3 of the unit: the same column (Q is a multiple of 4), rows 4-aligned
-            const unsigned off = 4u * lane;
+            const unsigned off = lane + 32u * e;
             if (off < left)
             {
                 const unsigned tl = w0 + off;
                 const unsigned dc = tl / Q;
                 const unsigned c = col0 + dc, w = tl - dc * Q;
                 const unsigned char* colp = TABLE ? packed_col(*Tp, (int) c) : single.pk[0] + (size_t) c * (size_t) single.colBytes;
-                const float lower = __ldg(reinterpret_cast<const float*>(colp));
-                const float upper = __ldg(reinterpret_cast<const float*>(colp) + 1);
-                const unsigned* __restrict__ words = reinterpret_cast<const unsigned*>(colp + 8) + w;
-                const unsigned wa = __ldg(words), wb = __ldg(words + 1), wc = __ldg(words + 2), wd = __ldg(words + 3);
+                x.lo[e] = __ldg(reinterpret_cast<const float*>(colp));
+                x.up[e] = __ldg(reinterpret_cast<const float*>(colp) + 1);
+                x.wd[e] = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + w);
+                x.w[e] = w;
+                x.op[e] = outBase + (size_t) c * M + w + (size_t) x.k0 * Q;
+                x.live |= 1u << e;
+            }
+        }
+    }
+}
+
+template <bool ADD, bool ONEBIT>
+__device__ __forceinline__ void unq_emit(const UnqUnit& x)
+{
+    const int bits = ONEBIT ? 1 : x.bits;
+    const unsigned vpw = 32u / (unsigned) bits;
+    const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
+    const unsigned Q = x.Q, k0 = x.k0;
+    // positions of this unit that exist at all; a word's rows may end earlier (last words of a column whose height is not
+    // a multiple of Q): `full` says that they do not
+    const unsigned nk = (vpw - k0 < UNQ_KPU) ? vpw - k0 : UNQ_KPU;
+    if (x.vec)
+    {
+        if (!x.live)
+            return;
+        float ca, cb;
+        unq_consts(bits, x.lo[0], x.up[0], ca, cb);
+        const bool full = (nk == UNQ_KPU) && (x.w[0] + (k0 + UNQ_KPU - 1) * Q < x.M);
+        float* __restrict__ op = x.op[0];
+#pragma unroll
+        for (unsigned kk = 0; kk < UNQ_KPU; ++kk)
+        {
+            const unsigned k = k0 + kk;
+            if (full || (kk < nk && x.w[0] + k * Q < x.M))
+            {
+                float4 v;
+                v.x = unq_field<ONEBIT>(bits, x.wd[0], k, mask, ca, cb);
+                v.y = unq_field<ONEBIT>(bits, x.wd[1], k, mask, ca, cb);
+                v.z = unq_field<ONEBIT>(bits, x.wd[2], k, mask, ca, cb);
+                v.w = unq_field<ONEBIT>(bits, x.wd[3], k, mask, ca, cb);
+                float4* p = reinterpret_cast<float4*>(op + (size_t) kk * Q);
+                if (ADD)
+                {
+                    const float4 o = *p;
+                    v.x = __fadd_rn(v.x, o.x);
+                    v.y = __fadd_rn(v.y, o.y);
+                    v.z = __fadd_rn(v.z, o.z);
+                    v.w = __fadd_rn(v.w, o.w);
+                    *p = v;
+                }
+                else
+                {
+                    __stcs(p, v);
+                }
+            }
+        }
+    }
+    else
+    {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+        {
+            if (x.live & (1u << e))
+            {
                 float ca, cb;
-                unq_consts(bits, lower, upper, ca, cb);
-                float* __restrict__ op = outBase + (size_t) c * M + w;
+                unq_consts(bits, x.lo[e], x.up[e], ca, cb);
+                const bool full = (nk == UNQ_KPU) && (x.w[e] + (k0 + UNQ_KPU - 1) * Q < x.M);
+                float* __restrict__ op = x.op[e];
+                const unsigned word = x.wd[e];
 #pragma unroll
                 for (unsigned kk = 0; kk < UNQ_KPU; ++kk)
                 {
                     const unsigned k = k0 + kk;
-                    if (k < vpw && w + k * Q < M)
+                    if (full || (kk < nk && x.w[e] + k * Q < x.M))
                     {
-                        float4 v;
-                        v.x = unq_field<ONEBIT>(bits, wa, k, mask, ca, cb);
-                        v.y = unq_field<ONEBIT>(bits, wb, k, mask, ca, cb);
-                        v.z = unq_field<ONEBIT>(bits, wc, k, mask, ca, cb);
-                        v.w = unq_field<ONEBIT>(bits, wd, k, mask, ca, cb);
-                        float4* p = reinterpret_cast<float4*>(op + (size_t) k * Q);
+                        float val = unq_field<ONEBIT>(bits, word, k, mask, ca, cb);
                         if (ADD)
-                        {
-                            const float4 o = *p;
-                            v.x = __fadd_rn(v.x, o.x);
-                            v.y = __fadd_rn(v.y, o.y);
-                            v.z = __fadd_rn(v.z, o.z);
-                            v.w = __fadd_rn(v.w, o.w);
-                            *p = v;
-                        }
-                        else
-                        {
-                            __stcs(p, v);
-                        }
-                    }
-                }
-            }
-        }
-        else
-        {
-            // lane <-> words lane, lane + 32, lane + 64, lane + 96 of the unit: per position the warp stores 32 consecutive rows
-            unsigned wd[4], cc[4], ww[4];
-            float lo[4], up[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-            {
-                const unsigned off = lane + 32u * e;
-                wd[e] = 0u;
-                cc[e] = ww[e] = 0u;
-                lo[e] = up[e] = 0.0f;
-                if (off < left)
-                {
-                    const unsigned tl = w0 + off;
-                    const unsigned dc = tl / Q;
-                    cc[e] = col0 + dc;
-                    ww[e] = tl - dc * Q;
-                    const unsigned char* colp = TABLE ? packed_col(*Tp, (int) cc[e]) : single.pk[0] + (size_t) cc[e] * (size_t) single.colBytes;
-                    lo[e] = __ldg(reinterpret_cast<const float*>(colp));
-                    up[e] = __ldg(reinterpret_cast<const float*>(colp) + 1);
-                    wd[e] = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + ww[e]);
-                }
-            }
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-            {
-                if (lane + 32u * e < left)
-                {
-                    float ca, cb;
-                    unq_consts(bits, lo[e], up[e], ca, cb);
-                    float* __restrict__ op = outBase + (size_t) cc[e] * M + ww[e];
-#pragma unroll
-                    for (unsigned kk = 0; kk < UNQ_KPU; ++kk)
-                    {
-                        const unsigned k = k0 + kk;
-                        if (k < vpw && ww[e] + k * Q < M)
-                        {
-                            float val = unq_field<ONEBIT>(bits, wd[e], k, mask, ca, cb);
-                            if (ADD)
-                                val = __fadd_rn(val, op[(size_t) k * Q]);
-                            op[(size_t) k * Q] = val;
-                        }
+                            val = __fadd_rn(val, op[(size_t) kk * Q]);
+                        op[(size_t) kk * Q] = val;
                     }
                 }
             }
@@ -211,16 +244,49 @@ __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, cons
     }
 }
 
-// Grid: at most four CTAs per SM; among the sizes from three to four per SM, the one whose warps share the units most evenly.
+// Warps take units u, u + warps, ...; the words and headers of a warp's next unit are fetched before it expands the
+// current one, so the (dependent) loads of one unit overlap the stores of the other.
+template <bool ADD, bool TABLE, bool ONEBIT>
+__global__ void __launch_bounds__(NT, 3) k_unquantize(const QTensor single, const QTensor* __restrict__ tensors, int nTensors, long long totalUnits)
+{
+    const unsigned lane = threadIdx.x & 31;
+    const long long gwarp = (long long) blockIdx.x * NWARPS + (threadIdx.x >> 5);
+    const long long nwarps = (long long) gridDim.x * NWARPS;
+    long long u = gwarp;
+    if (u >= totalUnits)
+        return;
+    int cur = 0; // table entry of the previous unit: consecutive units of a warp mostly stay within one matrix
+    UnqUnit xa, xb;
+    unq_fetch<TABLE>(xa, single, tensors, nTensors, u, cur, lane, ONEBIT);
+    for (;;)
+    {
+        const bool moreB = u + nwarps < totalUnits;
+        if (moreB)
+            unq_fetch<TABLE>(xb, single, tensors, nTensors, u + nwarps, cur, lane, ONEBIT);
+        unq_emit<ADD, ONEBIT>(xa);
+        if (!moreB)
+            break;
+        u += nwarps;
+        const bool moreA = u + nwarps < totalUnits;
+        if (moreA)
+            unq_fetch<TABLE>(xa, single, tensors, nTensors, u + nwarps, cur, lane, ONEBIT);
+        unq_emit<ADD, ONEBIT>(xb);
+        if (!moreA)
+            break;
+        u += nwarps;
+    }
+}
+
+// Grid: at most three CTAs per SM; among the sizes from two to three per SM, the one whose warps share the units most evenly.
 static int unq_grid(long long totalUnits, int numSMs)
 {
     const long long need = (totalUnits + NWARPS - 1) / NWARPS;
-    const long long most = (long long) numSMs * 4;
+    const long long most = (long long) numSMs * 3;
     if (need <= most)
         return (int) need;
     long long best = most;
     double bestWaste = 2.0;
-    for (long long g = most; g >= (long long) numSMs * 3; --g)
+    for (long long g = most; g >= (long long) numSMs * 2; --g)
     {
         const long long warps = g * NWARPS;
         const long long rounds = (totalUnits + warps - 1) / warps;
