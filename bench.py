@@ -1,16 +1,22 @@
 #!/usr/bin/env python
 """Benchmark of the quantized gradient aggregation step (CNTK 1-bit SGD path) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload speech_dnn|...]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload speech_dnn|resnet50|lstm_lm|sweep]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
 
-A "step" is one AggregateGradients call over the whole gradient set of one rank (default: the speech-DNN set,
-16 tensors, 45,122,648 fp32 values, 1 bit, zero threshold, residual carried from step to step).  Rank 0 prints ONE
-JSON line.  `value` is fp32-gradient GB/s summed over ranks (4 * values * ranks / step time, step time = max over
-ranks of the CUDA-event time of the step); `per_gpu_value` is the per-GPU figure the metric is named after.
+A "step" is one AggregateGradients call over the whole gradient set of one rank, DistGradHeader included (default: the
+speech-DNN set, 16 tensors, 45,122,648 fp32 values, 1 bit, zero threshold, residual carried from step to step).  Rank 0
+prints ONE JSON line.  `value` is fp32-gradient GB/s summed over ranks (4 * values * ranks / step time, step time = max
+over ranks of the mean CUDA-event time of a step); `per_gpu_value` is the per-GPU figure the metric is named after.
 
---impl reference times the reference's own CPU quantizer (its headers compiled in place, oracle/_ref) driving the
-restated exchange with one thread per simulated rank on this box's host cores, and prints the same line shape.
+After the timed loops, and outside them, every rank checks results against the CPU checker (oracle/): a seeded sample of
+columns of every tensor of one more full-size step is replayed through the whole exchange from all ranks' inputs, and with
+more than one rank the small multi-rank parity set of tests/multi_gpu_check.py runs as well.  A differing byte ends the
+process with a non-zero status; the line carries "parity": {"checked": true, ...}.
+
+--impl reference times the reference's own CPU quantizer (its headers compiled in place, oracle/_ref; else the C port)
+driving the restated exchange with one thread per simulated rank on this box's host cores, and prints the same line shape.
+--workload sweep runs BASELINE config 5 (1024 rows x 1 Mi .. 1 Gi values; 1, 2 and 32 bits) and reports a table in "sweep".
 """
 import argparse
 import json
@@ -22,9 +28,11 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 METRIC = "1-bit aggregated fp32-grad GB/s per GPU (max over ranks) at 1/2/4/8 B200"
 UNIT = "GB/s of fp32 gradient, summed over GPUs (per_gpu_value = per GPU)"
+REFERENCE_STEP_CAP = 5  # a full-size CPU step takes about a second per rank-thread: the reference arm times at most this many
 
 
 def load_peaks():
@@ -84,9 +92,10 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the quantize kernel, from the ncu capture
-# summarised in profiles/k_stream1_speech_dnn_1bit.md (same build, same workload); None where no capture exists
-NCU_TRAFFIC_BYTES = {"speech_dnn": 502.62e6}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the quantize kernel at ONE rank, from the ncu
+# capture summarised in profiles/k_stream1_speech_dnn_1bit.md (same workload).  Reported only for the configuration that
+# was captured; null elsewhere.
+NCU_TRAFFIC_BYTES = {("speech_dnn", 1): 502.62e6}
 
 
 def get_shapes(name):
@@ -100,20 +109,44 @@ def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
 
+def bind_near_gpu(local_rank):
+    """Runs this process on the CPUs next to its GPU, so that the pinned buffers it allocates afterwards land on that NUMA
+    node (first touch).  Reads the topology from sysfs; changes no GPU setting.  Returns a short description."""
+    try:
+        import torch
+        p = torch.cuda.get_device_properties(local_rank)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/local_cpulist") as f:
+            spec = f.read().strip()
+        cpus = set()
+        for part in spec.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                cpus.update(range(int(a), int(b) + 1))
+            elif part:
+                cpus.add(int(part))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            return f"host thread bound to {len(allowed)} CPUs local to GPU {bdf}"
+        return "GPU-local CPUs not in this process's affinity mask: not bound"
+    except Exception as e:  # no sysfs entry, container without the topology: run unbound
+        return f"not bound ({type(e).__name__})"
+
+
 # ------------------------------------------------------------------------------------------------ reference arm
-def cpu_reference_run(shapes, bits, K, steps, warmup, col_div):
+def cpu_reference_run(shapes, bits, K, steps, warmup):
     """Times the CPU checker (reference headers when built, else the C port) on the restated exchange with K simulated
-    ranks, one host thread each.  Columns are divided by col_div to bound the run."""
+    ranks, one host thread each, on the FULL tensor set."""
     import numpy as np
     from concurrent.futures import ThreadPoolExecutor
     from oracle import backend, exchange
     be = backend.best_backend()
-    sub = [(m, max(1, n // col_div)) for (m, n) in shapes]
-    cores = min(K, os.cpu_count() or 1)
-    st = exchange.ExchangeState(sub, K)
+    cores = min(K, len(os.sched_getaffinity(0)) or 1)
+    st = exchange.ExchangeState(shapes, K)
     rngs = [np.random.default_rng(1000 * r) for r in range(K)]
-    pool = [[(rngs[r].standard_normal((n, m), dtype=np.float32) * np.float32(1e-3)) for (m, n) in sub] for r in range(K)]
-    V = sum(m * n for m, n in sub)
+    pool = [[(rngs[r].standard_normal((n, m), dtype=np.float32) * np.float32(1e-3)) for (m, n) in shapes] for r in range(K)]
+    V = sum(m * n for m, n in shapes)
     times = []
     with ThreadPoolExecutor(max_workers=cores) as ex:
         for s in range(warmup + steps):
@@ -125,26 +158,27 @@ def cpu_reference_run(shapes, bits, K, steps, warmup, col_div):
                 times.append(dt)
     t = sum(times) / len(times)
     return {"gbs_total": 4.0 * V * K / t / 1e9, "ms_per_step": t * 1e3, "cores": cores, "kind": be.kind, "values_per_rank": V,
-            "sample": f"{'all' if col_div == 1 else '1/' + str(col_div)} of the columns of every tensor ({V} values per rank), "
-                      f"{steps} steps after {warmup} warm-up, {K} simulated rank(s) on {cores} host thread(s)"}
+            "sample": f"all columns of every tensor ({V} values per rank), {steps} step(s) after {warmup} warm-up, "
+                      f"{K} simulated rank(s) on {cores} host thread(s)"}
 
 
 def run_reference(args):
     rank, _, world = dist_env()
     if rank != 0:
         return
-    shapes, bits = get_shapes(args.workload)
+    shapes, bits = get_shapes(args.workload if args.workload != "sweep" else "speech_dnn")
     K = args.gpus
-    # bound the run to a few minutes: one rank-step of the full speech set costs ~0.8 s on one core
-    col_div = 1 if K == 1 else (2 if K == 2 else 4)
-    steps = min(args.steps, 10)
-    warm = min(args.warmup, 1)
-    r = cpu_reference_run(shapes, bits, K, steps, warm, col_div)
+    steps = max(1, min(args.steps, REFERENCE_STEP_CAP))
+    warm = max(0, min(args.warmup, 1))
+    r = cpu_reference_run(shapes, bits, K, steps, warm)
     line = {"impl": "reference", "metric": METRIC, "value": r["gbs_total"], "unit": UNIT, "per_gpu_value": r["gbs_total"] / K,
-            "n_gpus": K, "steps": steps, "warmup": warm, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "n_gpus": K, "steps": steps, "warmup": warm, "steps_requested": args.steps, "warmup_requested": args.warmup,
+            "steps_cap": f"a full-size CPU step takes about a second: at most {REFERENCE_STEP_CAP} timed steps and 1 warm-up",
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "bits": bits, "values_per_rank": r["values_per_rank"], "ranks": K,
-                       "note": "reference CPU quantizer (MatrixQuantizerCPU arithmetic) + restated striped exchange on host cores"},
+            "config": {"workload": args.workload, "tensors": len(shapes), "values_per_rank": r["values_per_rank"], "bits": bits,
+                       "zero_threshold": True, "self_stripe_quantized": True, "parallelism": f"dp{K} striped by columns",
+                       "exchange": "reference CPU quantizer (MatrixQuantizerCPU arithmetic) + restated striped exchange in host memory, one thread per rank"},
             "cpu_baseline": {"value": r["gbs_total"], "unit": UNIT, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]},
             "e2e": {"value": r["gbs_total"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -152,63 +186,155 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------------------------ our arm
+class Ranks:
+    """torch.distributed plumbing of one rank: NCCL for device data, a gloo group for waits that must not spin."""
+
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.rank, self.local, self.K = dist_env()
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        self.gloo = None
+        if self.K > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.gloo = dist.new_group(backend="gloo")
+
+    def barrier(self):
+        if self.K > 1:
+            self.dist.barrier()
+
+    def quiet_barrier(self):
+        """Blocks in a socket, not in a GPU spin: used while rank 0 times host code."""
+        if self.K > 1:
+            self.dist.barrier(group=self.gloo)
+
+    def max_over_ranks(self, values):
+        t = self.torch.tensor(values, device=self.dev, dtype=self.torch.float64)
+        if self.K > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(x) for x in t]
+
+    def all_gather_bytes(self, blob):
+        torch = self.torch
+        mine = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(self.dev)
+        out = [torch.zeros_like(mine) for _ in range(self.K)]
+        self.dist.all_gather(out, mine)
+        return [bytes(h.cpu().numpy().tobytes()) for h in out]
+
+    def unique_id(self, lib):
+        if self.K == 1:
+            return None
+        torch = self.torch
+        idt = torch.zeros(lib.UNIQUE_ID_BYTES, dtype=torch.uint8, device=self.dev)
+        if self.rank == 0:
+            idt.copy_(torch.frombuffer(bytearray(lib.unique_id()), dtype=torch.uint8))
+        self.dist.broadcast(idt, 0)
+        return bytes(idt.cpu().numpy().tobytes())
+
+    def close(self):
+        if self.K > 1:
+            self.dist.destroy_process_group()
+
+
+def enable_peer(R, agg, handle_fn, enable_fn):
+    """All ranks must agree on the transport: the outcome of every set-up stage is reduced over the ranks."""
+    torch, dist = R.torch, R.dist
+    ok = 1
+    try:
+        allh = R.all_gather_bytes(handle_fn())
+    except Exception:
+        ok = 0
+    okt = torch.tensor([ok], device=R.dev)
+    dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+    if not int(okt.item()):
+        return False
+    try:
+        enable_fn(allh)
+    except Exception as e:  # cannot map peer memory here
+        ok = 0
+        print(f"[rank {R.rank}] peer mapping failed: {e}", file=sys.stderr)
+    okt = torch.tensor([ok], device=R.dev)
+    dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+    if not int(okt.item()):
+        raise SystemExit("peer mapping succeeded on some ranks only; rerun with --exchange nccl")
+    return True
+
+
+def check_full_size_step(R, lib, agg, shapes, bits, grads, refresh, stream):
+    """One more step of the aggregator that was just timed, with a seeded sample of columns of every tensor captured before
+    and after and replayed on the CPU checker from ALL ranks' inputs (tests/parity_util.py)."""
+    import numpy as np
+    import parity_util as pu
+    from oracle import backend
+    torch, K = R.torch, R.K
+    be = backend.OracleBackend()
+    cols = pu.pick_columns(shapes, K, seed=4242)
+    cap = pu.RankCapture(lib, agg, R.rank, K, shapes, bits, cols)
+    refresh(10007)
+    torch.cuda.synchronize()
+    cap.before(grads)
+    agg.step_header([g.data_ptr() for g in grads], [1.0, 2.0, 3.0], stream)
+    torch.cuda.synchronize()
+    cap.after(grads)
+    flat = torch.from_numpy(cap.flat_inputs()).to(R.dev)
+    if K > 1:
+        out = [torch.zeros_like(flat) for _ in range(K)]
+        R.dist.all_gather(out, flat)
+        inputs = [cap.inputs_from_flat(t.cpu().numpy()) for t in out]
+    else:
+        inputs = [cap.inp]
+    n = pu.verify(be, cap, inputs)
+    hdr = agg.header_result(3, stream)
+    assert hdr == [1.0 * K, 2.0 * K, 3.0 * K], f"header sum {hdr}"
+    return n
+
+
+def time_steps(R, agg, ptrs, refresh, steps, warmup, stream, header):
+    torch = R.torch
+    for s in range(warmup):
+        refresh(s)
+        agg.step_header(ptrs, header, stream)
+    torch.cuda.synchronize()
+    agg.set_profiling(True)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    R.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for s in range(steps):
+        refresh(warmup + s)
+        ev[s][0].record()
+        agg.step_header(ptrs, header, stream)
+        ev[s][1].record()
+    torch.cuda.synchronize()
+    R.barrier()
+    wall = time.perf_counter() - t0
+    step_ms = [a.elapsed_time(b) for a, b in ev]
+    phases = agg.phase_ms()
+    agg.set_profiling(False)
+    vals = R.max_over_ranks([sum(step_ms) / len(step_ms)] + phases)
+    return vals[0], vals[1:], wall / steps * 1e3
+
+
 def run_ours(args):
     import torch
-    import torch.distributed as dist
     from cntk_b200 import lib, workloads
 
-    rank, local_rank, world = dist_env()
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
+    R = Ranks()
+    rank, K, dev = R.rank, R.K, R.dev
+    if K != args.gpus and not (K == 1 and args.gpus == 1):
+        raise SystemExit("launch with torch.distributed.run for --gpus > 1 (WORLD_SIZE must equal --gpus)")
+    affinity = bind_near_gpu(R.local)
     shapes, bits = get_shapes(args.workload)
     V = workloads.total_values(shapes)
-    K = world
-
-    if K > 1:
-        dist.init_process_group("nccl", device_id=dev)
-        idt = torch.zeros(lib.UNIQUE_ID_BYTES, dtype=torch.uint8, device=dev)
-        if rank == 0:
-            idt.copy_(torch.frombuffer(bytearray(lib.unique_id()), dtype=torch.uint8))
-        dist.broadcast(idt, 0)
-        uid = bytes(idt.cpu().numpy().tobytes())
-    else:
-        uid = None
-    comm = lib.Comm.create(uid, rank, K, local_rank)
+    comm = lib.Comm.create(R.unique_id(lib), rank, K, R.local)
     agg = lib.Aggregator(comm, shapes, bits)
     exchange = "none (1 rank)"
     if K > 1:
         exchange = "nccl send/recv + all-gather"
-        if args.exchange == "p2p":
-            # stores into the peers' windows over NVLink instead of collectives; all ranks must agree, so the outcome of
-            # the set-up is reduced over ranks before anyone uses it
-            ok = 1
-            try:
-                mine = torch.frombuffer(bytearray(agg.peer_handle()), dtype=torch.uint8).to(dev)
-                allh = [torch.zeros_like(mine) for _ in range(K)]
-                dist.all_gather(allh, mine)
-            except Exception:
-                ok = 0
-            okt = torch.tensor([ok], device=dev)
-            dist.all_reduce(okt, op=dist.ReduceOp.MIN)
-            if int(okt.item()):
-                try:
-                    agg.enable_peer([bytes(h.cpu().numpy().tobytes()) for h in allh])
-                except Exception as e:  # cannot map peer memory here: every rank must fall back together
-                    ok = 0
-                    print(f"[rank {rank}] peer mapping failed: {e}", file=sys.stderr)
-                okt = torch.tensor([ok], device=dev)
-                dist.all_reduce(okt, op=dist.ReduceOp.MIN)
-                if int(okt.item()):
-                    exchange = "peer-memory stores over NVLink + flag hand-shake (no collective)"
-                else:
-                    raise SystemExit("peer mapping succeeded on some ranks only; rerun with --exchange nccl")
-
-    def barrier():
-        if K > 1:
-            dist.barrier()
+        if args.exchange == "p2p" and enable_peer(R, agg, agg.peer_handle, agg.enable_peer):
+            exchange = "peer-memory stores over NVLink + flag hand-shake (no collective)"
 
     # gradients: persistent buffers (as a trainer's are) refreshed between steps from a pool of pre-generated sets
     POOL = 3
@@ -227,75 +353,92 @@ def run_ours(args):
 
     # clocks are sampled from the warm-up to the end of the host-buffer loop: the timed region alone lasts a few
     # milliseconds, shorter than one nvidia-smi polling period
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(R.local)
     sampler.start()
-    for s in range(args.warmup):
-        refresh(s)
-        agg.step(ptrs, stream)
-    torch.cuda.synchronize()
+    header = [0.25 * (rank + 1), 256.0, 256.0, 0.5, 128.0]  # criterion, numSamples, numSamplesWithLabel, one evaluation pair
+    t_step, phases, wall_ms = time_steps(R, agg, ptrs, refresh, args.steps, args.warmup, stream, header)
 
-    agg.set_profiling(True)
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for s in range(args.steps):
-        refresh(args.warmup + s)
-        ev[s][0].record()
-        agg.step(ptrs, stream)
-        ev[s][1].record()
-    torch.cuda.synchronize()
-    barrier()
-    wall = time.perf_counter() - t0
-    step_ms = [a.elapsed_time(b) for a, b in ev]
-    phases = agg.phase_ms()
-    agg.set_profiling(False)
-    t_step = sum(step_ms) / len(step_ms)
-    tt = torch.tensor([t_step] + phases, device=dev, dtype=torch.float64)
-    if K > 1:
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    t_step = float(tt[0])
-    phases = [float(x) for x in tt[1:]]
-
-    # end to end through the host-buffer entry point: pinned host gradients in, aggregated gradients back out, chunks of
-    # tensors pipelined over streams inside the library (upload / kernels / download of different chunks overlap)
+    # end to end through the host-buffer entry point: pinned host gradients in, aggregated gradients back out, column chunks
+    # pipelined over streams inside the library (upload / kernels / download of different chunks overlap)
     hagg = lib.HostAggregator(comm, shapes, bits, chunks=args.e2e_chunks)
     if K > 1 and exchange.startswith("peer"):
-        mine = torch.frombuffer(bytearray(hagg.peer_handles()), dtype=torch.uint8).to(dev)
-        allh = [torch.zeros_like(mine) for _ in range(K)]
-        dist.all_gather(allh, mine)
-        hagg.enable_peer([bytes(h.cpu().numpy().tobytes()) for h in allh])
+        hagg.enable_peer(R.all_gather_bytes(hagg.peer_handles()))
     hpool = [torch.empty((n, m), dtype=torch.float32).normal_(0, 1e-3).pin_memory() for (m, n) in shapes]
     hgrads = [torch.empty((n, m), dtype=torch.float32).pin_memory() for (m, n) in shapes]
     hptrs = [h.data_ptr() for h in hgrads]
     e2e_steps = max(3, min(args.steps, 10))
-    e2e_t = []
-    for s in range(2 + e2e_steps):
-        for h, p in zip(hgrads, hpool):
-            h.copy_(p)
-        barrier()
-        torch.cuda.synchronize()
-        t1 = time.perf_counter()
-        hagg.step(hptrs)  # returns after the results are back in host memory
-        dt = time.perf_counter() - t1
-        if s >= 2:
-            e2e_t.append(dt)
-    e2e_ms = sum(e2e_t) / len(e2e_t) * 1e3
+
+    def timed_host_loop(fn):
+        ts = []
+        for s in range(2 + e2e_steps):
+            for h, p in zip(hgrads, hpool):
+                h.copy_(p)
+            R.barrier()
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            fn()
+            dt = time.perf_counter() - t1
+            if s >= 2:
+                ts.append(dt)
+        return R.max_over_ranks([sum(ts) / len(ts) * 1e3])[0]
+
+    e2e_ms = timed_host_loop(lambda: hagg.step(hptrs))  # returns after the results are back in host memory
+    copy_floor_ms = timed_host_loop(lambda: hagg.copy_only(hptrs))  # the same uploads and downloads, no kernels
     clocks = sampler.stop()
-    te = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-    if K > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_ms = float(te[0])
     hagg.check()
     e2e_launches = e2e_steps * hagg.chunks * agg.launches_per_step
-    barrier()
+    R.barrier()
     hagg.destroy()
+
+    # ---- parity, outside every timed region ----
+    parity = {"checked": False}
+    if not args.no_parity:
+        cols = check_full_size_step(R, lib, agg, shapes, bits, grads, refresh, stream)
+        small = 0
+        if K > 1:
+            import multi_gpu_check
+            small = multi_gpu_check.run_checks(comm, rank, K, dev)
+        agg.check(stream)
+        counts = R.max_over_ranks([float(cols), float(small)])
+        parity = {"checked": True, "ranks": K, "columns": int(counts[0]),
+                  "what": "sampled columns of every tensor of one full-size step (aggregate, residual, stripe residual, gathered packed "
+                          "column, header sum) bit-identical to the CPU checker on every rank"
+                          + ("; plus the small multi-rank set (NCCL and peer paths, 1 bit zero/mean threshold, 4 bits, raw own stripe, "
+                             "host-buffer aggregator), 4 steps each" if K > 1 else ""),
+                  "small_set_steps": int(counts[1])}
+
+    # ---- CPU baseline in the same run (rank 0; the other ranks wait without spinning) ----
+    cpu = None
+    if not args.no_cpu_baseline:
+        R.quiet_barrier()
+        if rank == 0:
+            r = cpu_reference_run(shapes, bits, K, 2 if K > 1 else 3, 1)
+            cpu = {"value": r["gbs_total"], "unit": UNIT, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]}
+        R.quiet_barrier()
 
     if rank == 0:
         peak, peak_kind = load_peaks()
         alg = workloads.algorithmic_bytes(shapes, bits, K)
-        k1_gbs = alg["quantize"] / (phases[0] * 1e-3) / 1e9 if phases[0] > 0 else 0.0
+
+        def roof(name, kernel, ms, extra=None):
+            gbs = alg[name] / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+            d = {"kernel": kernel, "achieved": gbs, "frac": gbs / peak, "algorithmic_bytes_per_launch": alg[name], "ms": ms}
+            if extra:
+                d.update(extra)
+            return d
+
+        k1 = roof("quantize", "k_stream1 (quantize: level sums + pack + deferred residual)", phases[0])
         kern_ms = phases[0] + phases[2] + phases[4]
+        roofline = {"bound": "hbm", "kernel": k1["kernel"], "achieved": k1["achieved"], "peak": peak, "unit": "GB/s", "frac": k1["frac"],
+                    "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, K)),
+                    "algorithmic_bytes_per_launch": alg["quantize"],
+                    "unquantize": roof("unquantize", "k_unquantize", phases[4]),
+                    "all_kernels": {"algorithmic_bytes": alg["total"], "ms": kern_ms,
+                                    "frac": alg["total"] / (kern_ms * 1e-3) / 1e9 / peak if kern_ms > 0 else None}}
+        if K > 1:
+            roofline["reduce_requantize"] = roof("reduce_requantize", "k_owner_form + k_owner_walk (owner: sum of stripes, requantize)", phases[2],
+                                                 {"note": "two launches; the walk is an ordered fp32 add chain over the tallest owned column, "
+                                                          "a latency floor of about 4.6 cycles per row whatever the bytes"})
         line = {
             "metric": METRIC, "value": 4.0 * V * K / (t_step * 1e-3) / 1e9, "unit": UNIT,
             "per_gpu_value": 4.0 * V / (t_step * 1e-3) / 1e9,
@@ -303,34 +446,94 @@ def run_ours(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "tensors": len(shapes), "values_per_rank": V, "bits": bits,
                        "zero_threshold": True, "self_stripe_quantized": True, "parallelism": f"dp{K} striped by columns", "exchange": exchange,
+                       "header": "a 5-value DistGradHeader is summed over the ranks inside every timed step",
                        "l2": "inputs (361 MB gradient + residual per step) exceed the 126 MB L2; gradients are also re-copied "
                              "from a pre-generated pool between steps, outside the per-step events",
-                       "timing": "CUDA events around each step on the launch stream, mean over steps, max over ranks"},
+                       "timing": "CUDA events around each step on the launch stream, mean over steps, max over ranks",
+                       "host": affinity},
             "phases_ms": {"quantize": phases[0], "scatter": phases[1], "reduce_requantize": phases[2], "all_gather": phases[3],
                           "unquantize": phases[4]},
-            "roofline": {"bound": "hbm", "kernel": "k_stream1 (quantize: level sums + pack + deferred residual)", "achieved": k1_gbs, "peak": peak,
-                         "unit": "GB/s", "frac": k1_gbs / peak, "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                         "algorithmic_bytes_per_launch": alg["quantize"],
-                         "all_kernels": {"algorithmic_bytes": alg["total"], "ms": kern_ms,
-                                         "frac": alg["total"] / (kern_ms * 1e-3) / 1e9 / peak if kern_ms > 0 else None}},
+            "roofline": roofline,
             "wire": {"bytes_per_step_per_gpu_each_way": agg.wire_bytes,
                      "nvlink_frac_of_770GBs": (agg.wire_bytes / ((phases[1] + phases[3]) * 1e-3) / 770e9) if K > 1 and (phases[1] + phases[3]) > 0 else None},
             "e2e": {"value": 4.0 * V * K / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * V, "d2h_bytes_per_step": 4 * V, "steps": e2e_steps,
-                    "chunks": args.e2e_chunks, "api": "qagg_hagg_step (pinned host buffers, chunk-pipelined)"},
+                    "chunks": hagg.chunks, "copy_floor_ms": copy_floor_ms,
+                    "api": "qagg_hagg_step (pinned host buffers, column chunks pipelined over three streams)"},
             "gpu_launches": agg.launches_per_step * args.steps, "gpu_launches_e2e": e2e_launches,
-            "clocks": clocks, "wall_ms_per_step_including_refresh": wall / args.steps * 1e3,
+            "parity": parity, "clocks": clocks, "wall_ms_per_step_including_refresh": wall_ms,
         }
-        if K == 1 and not args.no_cpu_baseline:
-            r = cpu_reference_run(shapes, bits, 1, 3, 1, 1)
-            line["cpu_baseline"] = {"value": r["gbs_total"], "unit": UNIT, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]}
+        if cpu:
+            line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
     agg.check(stream)
-    barrier()
+    R.barrier()
     agg.destroy()
     comm.destroy()
-    if K > 1:
-        dist.destroy_process_group()
+    R.close()
+
+
+def run_sweep(args):
+    """BASELINE config 5: one 1024-row matrix of 1 Mi .. 1 Gi values; 1 bit, 2 bits and the unquantized 32-bit arm; at the
+    launched number of ranks.  One JSON line with the table under "sweep"."""
+    import torch
+    from cntk_b200 import lib, workloads
+
+    R = Ranks()
+    rank, K, dev = R.rank, R.K, R.dev
+    comm = lib.Comm.create(R.unique_id(lib), rank, K, R.local)
+    peak, peak_kind = load_peaks()
+    stream = torch.cuda.current_stream().cuda_stream
+    rows = []
+    for k in range(args.sweep_max_k + 1):
+        shapes = workloads.sweep(k)
+        V = workloads.total_values(shapes)
+        g = torch.empty((shapes[0][1], shapes[0][0]), device=dev, dtype=torch.float32)
+        src = torch.randn(g.shape, device=dev, dtype=torch.float32) * 1e-3
+        for bits in (1, 2, 32):
+            if bits == 32:
+                agg = lib.DenseAggregator(comm, shapes)
+                peer_ok = K > 1 and enable_peer(R, agg, agg.peer_handle, agg.enable_peer)
+                step = lambda: agg.step([g.data_ptr()], stream)
+                alg_bytes = workloads.dense_algorithmic_bytes(shapes, K)
+                wire = agg.wire_bytes
+            else:
+                agg = lib.Aggregator(comm, shapes, bits)
+                peer_ok = K > 1 and enable_peer(R, agg, agg.peer_handle, agg.enable_peer)
+                step = lambda: agg.step([g.data_ptr()], stream)
+                alg_bytes = workloads.algorithmic_bytes(shapes, bits, K)["total"]
+                wire = agg.wire_bytes
+            steps = max(3, min(args.steps, 10))
+            for s in range(3):
+                g.copy_(src)
+                step()
+            torch.cuda.synchronize()
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+            R.barrier()
+            for s in range(steps):
+                g.copy_(src)
+                ev[s][0].record()
+                step()
+                ev[s][1].record()
+            torch.cuda.synchronize()
+            ms = R.max_over_ranks([sum(a.elapsed_time(b) for a, b in ev) / steps])[0]
+            agg.check(stream)
+            R.barrier()
+            agg.destroy()
+            rows.append({"values": V, "bits": bits, "ms_per_step": ms, "gbs_per_gpu": 4.0 * V / (ms * 1e-3) / 1e9,
+                         "hbm_frac": alg_bytes / (ms * 1e-3) / 1e9 / peak,
+                         "wire_bytes_each_way": wire, "nvlink_frac_of_770GBs_if_only_wire": (wire / (ms * 1e-3) / 770e9) if K > 1 else None,
+                         "peer": bool(peer_ok)})
+        del g, src
+        torch.cuda.empty_cache()
+    if rank == 0:
+        best = max(r["gbs_per_gpu"] for r in rows if r["bits"] == 1)
+        print(json.dumps({"metric": METRIC, "value": best * K, "unit": UNIT, "per_gpu_value": best, "n_gpus": K, "steps": args.steps, "warmup": 3,
+                          "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                          "config": {"workload": "sweep", "rows": 1024, "note": "value = the best 1-bit row of the table"},
+                          "peak": peak, "peak_kind": peak_kind, "sweep": rows}), flush=True)
+    comm.destroy()
+    R.close()
 
 
 def main():
@@ -339,14 +542,18 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="speech_dnn", choices=["speech_dnn", "resnet50", "lstm_lm", "round_trip_2048"])
+    ap.add_argument("--workload", default="speech_dnn", choices=["speech_dnn", "resnet50", "lstm_lm", "round_trip_2048", "sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-chunks", type=int, default=6, help="tensor chunks pipelined by the host-buffer entry point")
+    ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=6, help="column chunks pipelined by the host-buffer entry point")
+    ap.add_argument("--sweep-max-k", type=int, default=5, help="largest matrix of the sweep: 1024 x 1024 * 4^k values")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="multi-GPU transport of the packed stripes")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "sweep":
+        run_sweep(args)
     else:
         run_ours(args)
 

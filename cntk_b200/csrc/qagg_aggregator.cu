@@ -10,9 +10,8 @@
 //   K3  one launch unpacks every tensor from the gather buffer into the gradient.
 // All buffers live for the lifetime of the aggregator; nothing is allocated per step.
 #include "../../include/qagg.h"
+#include "qagg_comm.h"
 #include "qagg_internal.h"
-
-#include <nccl.h>
 
 #include <algorithm>
 #include <cstdlib>
@@ -21,17 +20,6 @@
 #include <vector>
 
 using namespace qagg;
-
-struct qagg_comm
-{
-    int rank = 0;
-    int K = 1;
-    int device = 0;
-    ncclComm_t nccl = nullptr;
-    bool local = false; // member of an in-process group (device-to-device copies instead of NCCL)
-    double* scalars = nullptr; // small device buffer for the header all-reduce
-    static const int kMaxScalars = 512;
-};
 
 namespace {
 
@@ -80,11 +68,13 @@ struct qagg_plan
 {
     int rank = 0, K = 1, T = 0, bits = 1;
     std::vector<int64_t> M, N, colBytes;
-    std::vector<std::vector<int64_t>> sStart, sN, tOff; // [p][i]
+    std::vector<int64_t> parentN, col0; // tensor i is columns [col0, col0 + N) of a matrix of parentN columns (whole: 0, N)
+    std::vector<std::vector<int64_t>> sStart, sN, tOff; // [p][i]; sStart is relative to the tensor's first column
     std::vector<int64_t> regionBytes;
     int64_t gatherSlot = 0;
 
-    int build(int rank_, int K_, int T_, const int64_t* M_, const int64_t* N_, int bits_)
+    int build(int rank_, int K_, int T_, const int64_t* M_, const int64_t* N_, int bits_, const int64_t* parentN_ = nullptr,
+              const int64_t* col0_ = nullptr)
     {
         if (K_ < 1 || K_ > QAGG_MAXK || rank_ < 0 || rank_ >= K_ || T_ < 0 || (T_ > 0 && (!M_ || !N_)))
             return fail(QAGG_EINVAL, "plan: bad arguments");
@@ -96,10 +86,18 @@ struct qagg_plan
         bits = bits_;
         M.assign(M_, M_ + T);
         N.assign(N_, N_ + T);
+        parentN = N;
+        col0.assign(T, 0);
+        if (parentN_ && col0_)
+        {
+            parentN.assign(parentN_, parentN_ + T);
+            col0.assign(col0_, col0_ + T);
+        }
         colBytes.resize(T);
         for (int i = 0; i < T; ++i)
         {
-            if (M[i] < 0 || N[i] < 0 || M[i] > 0x3fffffffLL || N[i] > 0x7fffffffLL)
+            if (M[i] < 0 || N[i] < 0 || M[i] > 0x3fffffffLL || N[i] > 0x7fffffffLL || col0[i] < 0 || col0[i] + N[i] > parentN[i] ||
+                parentN[i] > 0x7fffffffLL)
                 return fail(QAGG_EINVAL, "plan: bad tensor shape");
             colBytes[i] = 8 + 4 * ((M[i] * bits + 31) / 32);
         }
@@ -113,7 +111,12 @@ struct qagg_plan
             int64_t off = 0;
             for (int i = 0; i < T; ++i)
             {
-                qagg_stripe(N[i], p, K, &sStart[p][i], &sN[p][i]);
+                // the owner's stripe of the whole matrix, cut to this tensor's columns
+                int64_t ps = 0, pn = 0;
+                qagg_stripe(parentN[i], p, K, &ps, &pn);
+                const int64_t lo = std::max(ps, col0[i]), hi = std::min(ps + pn, col0[i] + N[i]);
+                sStart[p][i] = (hi > lo ? lo : col0[i]) - col0[i];
+                sN[p][i] = hi > lo ? hi - lo : 0;
                 tOff[p][i] = off;
                 off += align_up(sN[p][i] * colBytes[i], 16);
             }
@@ -131,7 +134,7 @@ struct qagg_aggregator
     int bits = 1;
     int flags = 0;
     int mode = 0;
-    std::vector<int64_t> M, N, colBytes;
+    std::vector<int64_t> M, N, colBytes, parentN, col0;
     // stripe geometry: [p][i]
     std::vector<std::vector<int64_t>> sStart, sN, tOff;
     std::vector<int64_t> regionBytes; // packed bytes of rank p's stripes over all tensors (16-byte aligned blocks)
@@ -141,7 +144,13 @@ struct qagg_aggregator
     // "window": [flags][receive slots][gather slots] in ONE allocation, so that a single IPC handle exposes to the
     // peers everything they write into this rank's memory
     DevBuf sendbuf, window, resAll, sresAll, tables, hostStage;
-    static const int64_t kFlagBytes = 512; // scatter flags [0, K), gather flags [64, 64 + K), status word at [127]
+    // scatter flags [0, K), gather flags [64, 64 + K), status word at [127]; then one header slot (QAGG_HEADER_MAX doubles) per rank
+    static const int64_t kHeaderOff = 512;
+    static const int64_t kFlagBytes = kHeaderOff + (int64_t) QAGG_MAXK * QAGG_HEADER_MAX * 8;
+    // header exchange: pinned, device-mapped host buffer: [0, MAX) this rank's header of the step, [MAX, 2 MAX) the sum
+    double* hdrHost = nullptr;
+    double* hdrDev = nullptr; // NCCL path only: device staging
+    int hdrN = 0;             // doubles in the step's header (0: the step carries none)
     unsigned char* recvbuf = nullptr;
     unsigned char* gatherbuf = nullptr;
     // peer-memory exchange (off until qagg_agg_enable_peer): packed columns are stored straight into the peers' windows
@@ -199,6 +208,10 @@ struct qagg_aggregator
 
     ~qagg_aggregator()
     {
+        if (hdrHost)
+            cudaFreeHost(hdrHost);
+        if (hdrDev)
+            cudaFree(hdrDev);
         for (int p = 0; p < QAGG_MAXK; ++p)
             if (peerOpened[p])
                 cudaIpcCloseMemHandle(peerWin[p]);
@@ -226,6 +239,7 @@ struct qagg_aggregator
         return peerWin[p] + kFlagBytes + peer_slot_bytes(p) * comm->K + (int64_t) slot * gatherSlot;
     }
     unsigned* peer_flags(int p) const { return reinterpret_cast<unsigned*>(peerWin[p]); }
+    double* header_slot(unsigned char* win, int src) const { return reinterpret_cast<double*>(win + kHeaderOff) + (int64_t) src * QAGG_HEADER_MAX; }
 };
 
 namespace {
@@ -312,8 +326,9 @@ int build_tables(qagg_aggregator* a)
         q1.res_out = a->res[i];
         q1.lv = a->deferred ? a->lv[i] : nullptr;
         q1.K = K;
-        q1.per = N / K;
-        q1.rem = N % K;
+        q1.per = a->parentN[i] / K;
+        q1.rem = a->parentN[i] % K;
+        q1.col0 = a->col0[i];
         QTensor& q3 = a->hK3[i];
         const long long unit0 = q3.unit0;
         q3 = q1;
@@ -751,7 +766,13 @@ int qagg_comm_destroy(qagg_comm* c)
 
 int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, int bits, int flags, qagg_aggregator** out)
 {
-    if (!comm || !out || num_tensors < 0 || (num_tensors > 0 && (!M || !N)))
+    return qagg_agg_create_slices(comm, num_tensors, M, N, nullptr, nullptr, bits, flags, out);
+}
+
+int qagg_agg_create_slices(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, const int64_t* whole_N, const int64_t* first_col,
+                           int bits, int flags, qagg_aggregator** out)
+{
+    if (!comm || !out || num_tensors < 0 || (num_tensors > 0 && (!M || !N)) || ((whole_N == nullptr) != (first_col == nullptr)))
         return fail(QAGG_EINVAL, "qagg_agg_create: bad arguments");
     if (!bits_ok(bits))
         return fail(QAGG_EINVAL, "bits must be a power of two in 1..32");
@@ -790,10 +811,12 @@ int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const in
     if (rc)
         return rc;
     qagg_plan plan;
-    if ((rc = plan.build(r, K, num_tensors, M, N, bits)))
+    if ((rc = plan.build(r, K, num_tensors, M, N, bits, whole_N, first_col)))
         return rc;
     a->M = plan.M;
     a->N = plan.N;
+    a->parentN = plan.parentN;
+    a->col0 = plan.col0;
     a->colBytes = plan.colBytes;
     a->sStart = plan.sStart;
     a->sN = plan.sN;
@@ -903,14 +926,97 @@ static int exchange_gather(qagg_aggregator* a, cudaStream_t st)
     return check_nccl(ncclAllGather(a->gather_slot(r), a->gatherbuf, (size_t) a->gatherSlot, ncclChar, a->comm->nccl, st), "ncclAllGather");
 }
 
+namespace {
+
+// the step's header goes into the pinned buffer (and, with one rank, straight to the result)
+int stage_header(qagg_aggregator* a, const double* header, int n)
+{
+    if (n < 0 || n > QAGG_HEADER_MAX || (n > 0 && !header))
+        return fail(QAGG_EINVAL, "header: at most 64 doubles");
+    a->hdrN = n;
+    if (n == 0)
+        return QAGG_OK;
+    if (!a->hdrHost)
+    {
+        int rc = check_cuda(cudaHostAlloc(reinterpret_cast<void**>(&a->hdrHost), 2 * QAGG_HEADER_MAX * sizeof(double), cudaHostAllocMapped | cudaHostAllocPortable),
+                            "cudaHostAlloc");
+        if (rc)
+            return rc;
+        std::memset(a->hdrHost, 0, 2 * QAGG_HEADER_MAX * sizeof(double));
+    }
+    std::memcpy(a->hdrHost, header, (size_t) n * sizeof(double));
+    if (a->comm->K == 1)
+        std::memcpy(a->hdrHost + QAGG_HEADER_MAX, header, (size_t) n * sizeof(double));
+    return QAGG_OK;
+}
+
+// peer mode, before the quantize kernel: this rank's header into slot `rank` of every rank's window (its own included); the
+// quantize kernel's flag release, which follows on the stream, publishes it together with the packed stripes
+int push_header(qagg_aggregator* a, cudaStream_t st)
+{
+    if (a->hdrN == 0 || a->comm->K == 1 || !a->peer)
+        return QAGG_OK;
+    HeaderPtrs dst = {};
+    for (int p = 0; p < a->comm->K; ++p)
+        dst.p[dst.n++] = a->header_slot(a->peerWin[p], a->comm->rank);
+    return check_cuda(launch_header_push(st, a->hdrHost, a->hdrN, dst), "header push launch");
+}
+
+// after the scatter (flag wait or send/recv): the sum over ranks into the pinned result
+int sum_header(qagg_aggregator* a, cudaStream_t st)
+{
+    if (a->hdrN == 0 || a->comm->K == 1)
+        return QAGG_OK;
+    double* out = a->hdrHost + QAGG_HEADER_MAX;
+    if (a->peer)
+    {
+        HeaderPtrs src = {};
+        for (int p = 0; p < a->comm->K; ++p)
+            src.p[src.n++] = a->header_slot(static_cast<unsigned char*>(a->window.p), p);
+        return check_cuda(launch_header_sum(st, src, a->hdrN, out), "header sum launch");
+    }
+    int rc;
+    if (!a->hdrDev && (rc = check_cuda(cudaMalloc(reinterpret_cast<void**>(&a->hdrDev), QAGG_HEADER_MAX * sizeof(double)), "cudaMalloc")))
+        return rc;
+    if ((rc = check_cuda(cudaMemcpyAsync(a->hdrDev, a->hdrHost, (size_t) a->hdrN * sizeof(double), cudaMemcpyHostToDevice, st), "header upload")))
+        return rc;
+    if ((rc = check_nccl(ncclAllReduce(a->hdrDev, a->hdrDev, (size_t) a->hdrN, ncclDouble, ncclSum, a->comm->nccl, st), "ncclAllReduce")))
+        return rc;
+    return check_cuda(cudaMemcpyAsync(out, a->hdrDev, (size_t) a->hdrN * sizeof(double), cudaMemcpyDeviceToHost, st), "header download");
+}
+
+} // namespace
+
+extern "C" int qagg_agg_step_header(qagg_aggregator* a, float* const* grads, const double* header, int n, void* stream);
+
 int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream)
+{
+    return qagg_agg_step_header(a, grads, nullptr, 0, stream);
+}
+
+int qagg_agg_step_header(qagg_aggregator* a, float* const* grads, const double* header, int n, void* stream)
 {
     if (!a || (a->T > 0 && !grads))
         return fail(QAGG_EINVAL, "qagg_agg_step: bad arguments");
     if (a->comm->local && a->comm->K > 1)
         return fail(QAGG_ESTATE, "aggregators of a local group must be stepped with qagg_agg_step_group");
+    {
+        int hrc = stage_header(a, header, n);
+        if (hrc)
+            return hrc;
+    }
     if (a->identity || a->totalValues == 0)
+    {
+        // nothing to aggregate, but the header is still summed over the ranks
+        if (a->hdrN > 0 && a->comm->K > 1)
+        {
+            if (a->comm->local)
+                return fail(QAGG_ESTATE, "header exchange of a local group needs qagg_agg_step_group_header");
+            std::memcpy(a->hdrHost + QAGG_HEADER_MAX, a->hdrHost, (size_t) a->hdrN * sizeof(double));
+            return qagg_comm_allreduce_f64(a->comm, a->hdrHost + QAGG_HEADER_MAX, a->hdrN, stream);
+        }
         return QAGG_OK;
+    }
     cudaStream_t st = (cudaStream_t) stream;
     int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
     if (rc)
@@ -920,6 +1026,8 @@ int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream)
     a->stepNo++;
     if ((rc = a->mark(0, st)))
         return rc;
+    if ((rc = push_header(a, st)))
+        return rc;
     if ((rc = launch_k1(a, st)))
         return rc;
     if ((rc = a->mark(1, st)))
@@ -927,6 +1035,8 @@ int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream)
     if (a->comm->K > 1)
     {
         if ((rc = a->peer ? wait_peers(a, false, st) : exchange_scatter(a, st)))
+            return rc;
+        if ((rc = sum_header(a, st)))
             return rc;
         if ((rc = a->mark(2, st)))
             return rc;
@@ -950,6 +1060,22 @@ int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream)
         return rc;
     if (a->profiling)
         a->profSteps++;
+    return QAGG_OK;
+}
+
+int qagg_agg_header_result(qagg_aggregator* a, double* out, int n, void* stream)
+{
+    if (!a || n < 0 || n > QAGG_HEADER_MAX || (n > 0 && !out))
+        return fail(QAGG_EINVAL, "qagg_agg_header_result: bad arguments");
+    if (n != a->hdrN)
+        return fail(QAGG_ESTATE, "qagg_agg_header_result: the last step carried a header of a different length");
+    int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    if ((rc = check_cuda(cudaStreamSynchronize((cudaStream_t) stream), "cudaStreamSynchronize")))
+        return rc;
+    if (n > 0)
+        std::memcpy(out, a->hdrHost + QAGG_HEADER_MAX, (size_t) n * sizeof(double));
     return QAGG_OK;
 }
 
@@ -1002,7 +1128,13 @@ int qagg_agg_phase_ms(qagg_aggregator* a, float* out5)
 
 int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* const* const* grads, void* stream)
 {
-    if (!aggs || !grads || num_ranks < 1)
+    return qagg_agg_step_group_header(aggs, num_ranks, grads, nullptr, 0, stream);
+}
+
+int qagg_agg_step_group_header(qagg_aggregator* const* aggs, int num_ranks, float* const* const* grads, const double* const* headers, int n,
+                               void* stream)
+{
+    if (!aggs || !grads || num_ranks < 1 || (n > 0 && !headers))
         return fail(QAGG_EINVAL, "qagg_agg_step_group: bad arguments");
     cudaStream_t st = (cudaStream_t) stream;
     const int K = num_ranks;
@@ -1013,11 +1145,25 @@ int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* cons
         if (aggs[r]->T != aggs[0]->T || aggs[r]->bits != aggs[0]->bits || aggs[r]->M != aggs[0]->M || aggs[r]->N != aggs[0]->N)
             return fail(QAGG_ESTATE, "qagg_agg_step_group: aggregators disagree on tensor shapes or bits");
     }
-    if (aggs[0]->identity || aggs[0]->totalValues == 0)
-        return QAGG_OK;
     int rc = check_cuda(cudaSetDevice(aggs[0]->comm->device), "cudaSetDevice");
     if (rc)
         return rc;
+    // the header: every rank's values are in its pinned buffer; one small kernel per rank adds them in rank order (the ranks
+    // share this process, so no exchange is needed)
+    for (int r = 0; r < K; ++r)
+        if ((rc = stage_header(aggs[r], n > 0 ? headers[r] : nullptr, n)))
+            return rc;
+    if (n > 0 && K > 1)
+    {
+        HeaderPtrs src = {};
+        for (int r = 0; r < K; ++r)
+            src.p[src.n++] = aggs[r]->hdrHost;
+        for (int r = 0; r < K; ++r)
+            if ((rc = check_cuda(launch_header_sum(st, src, n, aggs[r]->hdrHost + QAGG_HEADER_MAX), "header sum launch")))
+                return rc;
+    }
+    if (aggs[0]->identity || aggs[0]->totalValues == 0)
+        return QAGG_OK;
     const bool peer = aggs[0]->peer;
     for (int r = 0; r < K; ++r)
         if (aggs[r]->peer != peer)
@@ -1243,21 +1389,36 @@ struct qagg_host_aggregator
 {
     qagg_comm* comm = nullptr;
     int T = 0;
+    std::vector<int64_t> rows; // rows per tensor
+    // A chunk is a list of column slices (tensor, first column, columns) with about the same number of values as every other
+    // chunk: small tensors are grouped, large ones cut by COLUMNS.  Columns are independent of each other, and every slice
+    // keeps the stripe ownership of its whole tensor (GetStripeForNode on the whole matrix), so the results are
+    // bit-identical to aggregating the whole set at once.
+    struct Slice
+    {
+        int tensor;
+        int64_t col0, ncols;
+    };
+    std::vector<std::vector<Slice>> chunks;
     std::vector<qagg_aggregator*> kids;
-    std::vector<int> first;   // first tensor of each chunk; first[chunks] == T
-    std::vector<int64_t> elems; // elements per tensor
-    std::vector<cudaStream_t> streams;
+    // a three-stage pipeline: all uploads on one stream, all kernels on a second, all downloads on a third, so that the
+    // upload engine never waits behind a download; chunk c's kernels wait for uploaded[c], its download for computed[c]
+    cudaStream_t sIn = nullptr, sCompute = nullptr, sOut = nullptr;
+    std::vector<cudaEvent_t> uploaded, computed;
     std::vector<DevBuf> dev;  // one device gradient buffer per chunk
     std::vector<std::vector<float*>> devPtr;
-    std::vector<int> order;   // chunks in the order they are issued: largest first, so that the longest upload is not
-                              // left without anything to overlap with
     bool peer = false;
     ~qagg_host_aggregator()
     {
         for (auto* k : kids)
             qagg_agg_destroy(k);
-        for (auto s : streams)
-            cudaStreamDestroy(s);
+        for (auto e : uploaded)
+            cudaEventDestroy(e);
+        for (auto e : computed)
+            cudaEventDestroy(e);
+        for (auto st : {sIn, sCompute, sOut})
+            if (st)
+                cudaStreamDestroy(st);
     }
 };
 
@@ -1277,59 +1438,71 @@ int qagg_hagg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const i
     {
         if (M[i] < 0 || N[i] < 0)
             return fail(QAGG_EINVAL, "qagg_hagg_create: bad tensor shape");
-        h->elems.push_back(M[i] * N[i]);
+        h->rows.push_back(M[i]);
         total += M[i] * N[i];
     }
-    if (num_chunks > num_tensors)
-        num_chunks = num_tensors;
-    // consecutive tensors, about equal bytes per chunk
-    h->first.push_back(0);
-    int64_t acc = 0;
+    // equal-value chunks of column slices, in tensor order
+    const int64_t target = std::max<int64_t>(1, (total + num_chunks - 1) / num_chunks);
+    h->chunks.emplace_back();
+    int64_t room = target;
     for (int i = 0; i < num_tensors; ++i)
     {
-        acc += h->elems[i];
-        const int done = (int) h->first.size();
-        if (done < num_chunks && acc * num_chunks >= total * done && i + 1 < num_tensors)
-            h->first.push_back(i + 1);
+        int64_t c0 = 0;
+        while (c0 < N[i] && M[i] > 0)
+        {
+            if (room <= 0 && (int) h->chunks.size() < num_chunks)
+            {
+                h->chunks.emplace_back();
+                room = target;
+            }
+            int64_t take = (int) h->chunks.size() < num_chunks ? std::max<int64_t>(1, room / M[i]) : N[i] - c0;
+            take = std::min(take, N[i] - c0);
+            h->chunks.back().push_back({i, c0, take});
+            room -= take * M[i];
+            c0 += take;
+        }
     }
-    h->first.push_back(num_tensors);
-    const int chunks = (int) h->first.size() - 1;
+    if (h->chunks.back().empty())
+        h->chunks.pop_back();
+    if (h->chunks.empty())
+        h->chunks.emplace_back();
+    const int chunks = (int) h->chunks.size();
     h->dev.resize(chunks);
     h->devPtr.resize(chunks);
     for (int c = 0; c < chunks; ++c)
     {
-        const int i0 = h->first[c], i1 = h->first[c + 1];
+        std::vector<int64_t> cm, cn, pn, pc;
+        int64_t floats = 0;
+        for (auto& sl : h->chunks[c])
+        {
+            cm.push_back(M[sl.tensor]);
+            cn.push_back(sl.ncols);
+            pn.push_back(N[sl.tensor]);
+            pc.push_back(sl.col0);
+            floats += align_up(M[sl.tensor] * sl.ncols, 4);
+        }
         qagg_aggregator* kid = nullptr;
-        if ((rc = qagg_agg_create(comm, i1 - i0, M + i0, N + i0, bits, flags, &kid)))
+        if ((rc = qagg_agg_create_slices(comm, (int) cm.size(), cm.data(), cn.data(), pn.data(), pc.data(), bits, flags, &kid)))
             return rc;
         h->kids.push_back(kid);
-        int64_t floats = 0;
-        for (int i = i0; i < i1; ++i)
-            floats += align_up(h->elems[i], 4);
         if ((rc = h->dev[c].alloc((size_t) floats * 4, false)))
             return rc;
         int64_t o = 0;
-        for (int i = i0; i < i1; ++i)
+        for (auto& sl : h->chunks[c])
         {
             h->devPtr[c].push_back(static_cast<float*>(h->dev[c].p) + o);
-            o += align_up(h->elems[i], 4);
+            o += align_up(M[sl.tensor] * sl.ncols, 4);
         }
     }
-    std::vector<int64_t> chunkElems(chunks, 0);
-    for (int c = 0; c < chunks; ++c)
-        for (int i = h->first[c]; i < h->first[c + 1]; ++i)
-            chunkElems[c] += h->elems[i];
-    for (int c = 0; c < chunks; ++c)
-        h->order.push_back(c);
-    std::stable_sort(h->order.begin(), h->order.end(), [&](int x, int y) { return chunkElems[x] > chunkElems[y]; });
-    const int nStreams = std::min(chunks, 3);
-    for (int s = 0; s < nStreams; ++s)
-    {
-        cudaStream_t st;
-        if ((rc = check_cuda(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking), "cudaStreamCreate")))
+    for (cudaStream_t* st : {&h->sIn, &h->sCompute, &h->sOut})
+        if ((rc = check_cuda(cudaStreamCreateWithFlags(st, cudaStreamNonBlocking), "cudaStreamCreate")))
             return rc;
-        h->streams.push_back(st);
-    }
+    h->uploaded.resize(chunks);
+    h->computed.resize(chunks);
+    for (int c = 0; c < chunks; ++c)
+        if ((rc = check_cuda(cudaEventCreateWithFlags(&h->uploaded[c], cudaEventDisableTiming), "cudaEventCreate")) ||
+            (rc = check_cuda(cudaEventCreateWithFlags(&h->computed[c], cudaEventDisableTiming), "cudaEventCreate")))
+            return rc;
     *out = h.release();
     return QAGG_OK;
 }
@@ -1372,35 +1545,56 @@ int qagg_hagg_enable_peer(qagg_host_aggregator* h, const void* handles)
     return QAGG_OK;
 }
 
-int qagg_hagg_step(qagg_host_aggregator* h, float* const* host_grads)
+static int hagg_run(qagg_host_aggregator* h, float* const* host_grads, bool aggregate)
 {
     if (!h || !host_grads)
         return fail(QAGG_EINVAL, "qagg_hagg_step: bad arguments");
     int rc = check_cuda(cudaSetDevice(h->comm->device), "cudaSetDevice");
     if (rc)
         return rc;
-    const bool overlap = (h->comm->K == 1) || h->peer;
+    // Every rank issues the chunks in the same order on its one compute stream, so a flag wait of chunk c only ever waits
+    // for kernels that its peers enqueued before their own waits of chunk c.
     const size_t chunks = h->kids.size();
-    for (size_t k = 0; k < chunks; ++k)
+    for (size_t c = 0; c < chunks; ++c)
     {
-        const int c = h->order[k];
-        cudaStream_t st = h->streams[overlap ? k % h->streams.size() : 0];
-        const int i0 = h->first[c], i1 = h->first[c + 1];
-        for (int i = i0; i < i1; ++i)
-            if (h->elems[i] && (rc = check_cuda(cudaMemcpyAsync(h->devPtr[c][i - i0], host_grads[i], (size_t) h->elems[i] * 4, cudaMemcpyHostToDevice, st),
-                                                "gradient upload")))
+        const auto& slices = h->chunks[c];
+        for (size_t k = 0; k < slices.size(); ++k)
+        {
+            const int64_t M = h->rows[slices[k].tensor], bytes = M * slices[k].ncols * 4;
+            if (bytes && (rc = check_cuda(cudaMemcpyAsync(h->devPtr[c][k], host_grads[slices[k].tensor] + slices[k].col0 * M, (size_t) bytes,
+                                                          cudaMemcpyHostToDevice, h->sIn), "gradient upload")))
                 return rc;
-        if ((rc = qagg_agg_step(h->kids[c], h->devPtr[c].data(), st)))
+        }
+        if ((rc = check_cuda(cudaEventRecord(h->uploaded[c], h->sIn), "cudaEventRecord")) ||
+            (rc = check_cuda(cudaStreamWaitEvent(h->sCompute, h->uploaded[c], 0), "cudaStreamWaitEvent")))
             return rc;
-        for (int i = i0; i < i1; ++i)
-            if (h->elems[i] && (rc = check_cuda(cudaMemcpyAsync(host_grads[i], h->devPtr[c][i - i0], (size_t) h->elems[i] * 4, cudaMemcpyDeviceToHost, st),
-                                                "gradient download")))
+        if (aggregate && (rc = qagg_agg_step(h->kids[c], h->devPtr[c].data(), h->sCompute)))
+            return rc;
+        if ((rc = check_cuda(cudaEventRecord(h->computed[c], h->sCompute), "cudaEventRecord")) ||
+            (rc = check_cuda(cudaStreamWaitEvent(h->sOut, h->computed[c], 0), "cudaStreamWaitEvent")))
+            return rc;
+        for (size_t k = 0; k < slices.size(); ++k)
+        {
+            const int64_t M = h->rows[slices[k].tensor], bytes = M * slices[k].ncols * 4;
+            if (bytes && (rc = check_cuda(cudaMemcpyAsync(host_grads[slices[k].tensor] + slices[k].col0 * M, h->devPtr[c][k], (size_t) bytes,
+                                                          cudaMemcpyDeviceToHost, h->sOut), "gradient download")))
                 return rc;
+        }
     }
-    for (auto st : h->streams)
+    for (auto st : {h->sIn, h->sCompute, h->sOut})
         if ((rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize")))
             return rc;
     return QAGG_OK;
+}
+
+int qagg_hagg_step(qagg_host_aggregator* h, float* const* host_grads)
+{
+    return hagg_run(h, host_grads, true);
+}
+
+int qagg_hagg_copy_only(qagg_host_aggregator* h, float* const* host_grads)
+{
+    return hagg_run(h, host_grads, false);
 }
 
 int qagg_hagg_check(qagg_host_aggregator* h)

@@ -79,23 +79,30 @@ __device__ __forceinline__ unsigned quantize_multibit(const ValQ& q, int bits, f
 __device__ __forceinline__ unsigned char* packed_col(const QTensor& T, int j)
 {
     int p = 0;
-    int start = 0;
+    long long first = 0; // first column of owner p's stripe that lies inside this descriptor, in whole-matrix numbering
+    const long long jj = (long long) j + T.col0;
     if (T.K > 1)
     {
-        const int per = (int) T.per, rem = (int) T.rem;
-        const int big = (per + 1) * rem; // columns held by the ranks that got one extra
-        if (j < big)
+        const long long per = T.per, rem = T.rem;
+        const long long big = (per + 1) * rem; // columns held by the ranks that got one extra
+        if (jj < big)
         {
-            p = j / (per + 1);
-            start = p * (per + 1);
+            p = (int) (jj / (per + 1));
+            first = (long long) p * (per + 1);
         }
         else
         {
-            p = rem + (j - big) / per;
-            start = big + (p - rem) * per;
+            p = (int) (rem + (jj - big) / per);
+            first = big + (p - rem) * per;
         }
+        if (first < T.col0)
+            first = T.col0;
     }
-    return T.pk[p] + (size_t) (j - start) * (size_t) T.colBytes;
+    else
+    {
+        first = T.col0;
+    }
+    return T.pk[p] + (size_t) (jj - first) * (size_t) T.colBytes;
 }
 
 // ---- element (row, column j) of the matrix being quantized; slow general form (streamed columns only) ----

@@ -28,7 +28,9 @@ struct QTensor
     int colBytes;        // 8 + 4 * Q
     int bits;
     int K;               // owners the packed columns are routed over (1 = one contiguous packed matrix)
-    long long per, rem;  // N / K and N % K: owner p holds columns [p*per + min(p, rem), ...) (GetStripeForNode)
+    long long per, rem;  // (columns of the whole matrix) / K and % K: owner p holds columns [p*per + min(p, rem), ...)
+                         // (GetStripeForNode)
+    long long col0;      // this descriptor covers columns [col0, col0 + N) of the whole matrix (0 unless it is a column slice)
     unsigned char* pk[QAGG_MAXK]; // packed base for owner p; its first column is that owner's stripe start
     int nsrc;                           // reduce: number of packed sources
     int selfRaw;                        // reduce: 1 = start from `grad` instead of src[0]
@@ -56,6 +58,14 @@ struct Signal
     unsigned value;
     unsigned char* bcastBase[QAGG_MAXK]; // broadcast copies (peer gather slots) for matrices with bcast == 1
     int nbcast;
+};
+
+// header exchange: up to QAGG_HEADER_MAX doubles per rank (DistGradHeader needs 3 + 2 per evaluation node)
+#define QAGG_HEADER_MAX 64
+struct HeaderPtrs
+{
+    double* p[QAGG_MAXK];
+    int n;
 };
 
 struct QItem
@@ -112,6 +122,9 @@ cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int
 cudaError_t launch_unquantize(cudaStream_t st, bool add, int bits, const QTensor* single, const QTensor* tensors, int nTensors,
                               long long totalUnits, const LaunchCfg& cfg);
 long long unq_units(long long M, long long N, int bits); // work units of an M x N matrix in the unquantize kernel
+// header exchange kernels (qagg_kernels.cu): in[0..n) -> dst.p[*][0..n);  out[i] = src.p[0][i] + src.p[1][i] + ... in that order
+cudaError_t launch_header_push(cudaStream_t st, const double* in, int n, const HeaderPtrs& dst);
+cudaError_t launch_header_sum(cudaStream_t st, const HeaderPtrs& src, int n, double* out);
 cudaError_t get_launch_cfg(int device, LaunchCfg* cfg);
 // releases the flags of `signal` from a one-thread kernel (a rank with nothing to compute still has to tell its peers)
 cudaError_t launch_signal_only(cudaStream_t st, const Signal& signal);

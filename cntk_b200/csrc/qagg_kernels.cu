@@ -832,6 +832,47 @@ cudaError_t launch_push(cudaStream_t st, const void* src, size_t bytes, const Si
     return cudaGetLastError();
 }
 
+// Header exchange (the DistGradHeader / loss scalars of a step): every rank stores its n doubles into slot `rank` of every
+// rank's header area, then -- after the step's first flag wait -- sums the K slots in rank order, the same order everywhere.
+__global__ void k_header_push(const double* __restrict__ in, int n, const HeaderPtrs dst)
+{
+    const int i = threadIdx.x;
+    if (i < n)
+    {
+        const double v = in[i];
+        for (int p = 0; p < dst.n; ++p)
+            dst.p[p][i] = v;
+    }
+}
+
+__global__ void k_header_sum(const HeaderPtrs src, int n, double* __restrict__ out)
+{
+    const int i = threadIdx.x;
+    if (i < n)
+    {
+        double s = *reinterpret_cast<const volatile double*>(src.p[0] + i);
+        for (int p = 1; p < src.n; ++p)
+            s += *reinterpret_cast<const volatile double*>(src.p[p] + i);
+        out[i] = s;
+    }
+}
+
+cudaError_t launch_header_push(cudaStream_t st, const double* in, int n, const HeaderPtrs& dst)
+{
+    if (n <= 0 || dst.n <= 0)
+        return cudaSuccess;
+    k_header_push<<<1, QAGG_HEADER_MAX, 0, st>>>(in, n, dst);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_header_sum(cudaStream_t st, const HeaderPtrs& src, int n, double* out)
+{
+    if (n <= 0 || src.n <= 0)
+        return cudaSuccess;
+    k_header_sum<<<1, QAGG_HEADER_MAX, 0, st>>>(src, n, out);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status)
 {
     if (n > 32)

@@ -25,6 +25,9 @@ EXPORTS = [
     "qagg_agg_launches_per_step", "qagg_agg_peer_handle", "qagg_agg_enable_peer", "qagg_agg_set_wait_limit", "qagg_agg_check", "qagg_wait_flags",
     "qagg_hagg_create", "qagg_hagg_chunks", "qagg_hagg_peer_handles", "qagg_hagg_enable_peer", "qagg_hagg_step", "qagg_hagg_check",
     "qagg_hagg_destroy", "qagg_agg_set_profiling", "qagg_agg_phase_ms", "qagg_agg_destroy",
+    "qagg_agg_step_header", "qagg_agg_step_group_header", "qagg_agg_header_result", "qagg_agg_create_slices", "qagg_hagg_copy_only",
+    "qagg_dense_create", "qagg_dense_step", "qagg_dense_step_group", "qagg_dense_peer_handle", "qagg_dense_enable_peer", "qagg_dense_check",
+    "qagg_dense_wire_bytes", "qagg_dense_destroy",
 ]
 
 
@@ -73,6 +76,9 @@ _lib.qagg_comm_destroy.argtypes = [c_vp]
 _lib.qagg_agg_create.argtypes = [c_vp, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, c_int, ctypes.POINTER(c_vp)]
 _lib.qagg_agg_step.argtypes = [c_vp, ctypes.POINTER(c_vp), c_vp]
 _lib.qagg_agg_step_group.argtypes = [ctypes.POINTER(c_vp), c_int, ctypes.POINTER(ctypes.POINTER(c_vp)), c_vp]
+_lib.qagg_agg_step_header.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(ctypes.c_double), c_int, c_vp]
+_lib.qagg_agg_step_group_header.argtypes = [ctypes.POINTER(c_vp), c_int, ctypes.POINTER(ctypes.POINTER(c_vp)), ctypes.POINTER(ctypes.POINTER(ctypes.c_double)), c_int, c_vp]
+_lib.qagg_agg_header_result.argtypes = [c_vp, ctypes.POINTER(ctypes.c_double), c_int, c_vp]
 _lib.qagg_agg_step_host.argtypes = [c_vp, ctypes.POINTER(c_vp), c_vp]
 _lib.qagg_agg_reset_residuals.argtypes = [c_vp, c_vp]
 _lib.qagg_agg_residuals.argtypes = [c_vp, c_int, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
@@ -91,7 +97,19 @@ _lib.qagg_hagg_chunks.argtypes = [c_vp]
 _lib.qagg_hagg_peer_handles.argtypes = [c_vp, c_vp]
 _lib.qagg_hagg_enable_peer.argtypes = [c_vp, c_vp]
 _lib.qagg_hagg_step.argtypes = [c_vp, ctypes.POINTER(c_vp)]
+_lib.qagg_hagg_copy_only.argtypes = [c_vp, ctypes.POINTER(c_vp)]
+_lib.qagg_agg_create_slices.argtypes = [c_vp, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, c_int,
+                                        ctypes.POINTER(c_vp)]
 _lib.qagg_hagg_check.argtypes = [c_vp]
+_lib.qagg_dense_create.argtypes = [c_vp, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), ctypes.POINTER(c_vp)]
+_lib.qagg_dense_step.argtypes = [c_vp, ctypes.POINTER(c_vp), c_vp]
+_lib.qagg_dense_step_group.argtypes = [ctypes.POINTER(c_vp), c_int, ctypes.POINTER(ctypes.POINTER(c_vp)), c_vp]
+_lib.qagg_dense_peer_handle.argtypes = [c_vp, c_vp]
+_lib.qagg_dense_enable_peer.argtypes = [c_vp, c_vp]
+_lib.qagg_dense_check.argtypes = [c_vp, c_vp]
+_lib.qagg_dense_wire_bytes.restype = c_i64
+_lib.qagg_dense_wire_bytes.argtypes = [c_vp]
+_lib.qagg_dense_destroy.argtypes = [c_vp]
 _lib.qagg_hagg_destroy.argtypes = [c_vp]
 _lib.qagg_agg_set_profiling.argtypes = [c_vp, c_int]
 _lib.qagg_agg_phase_ms.argtypes = [c_vp, ctypes.POINTER(ctypes.c_float)]
@@ -271,13 +289,17 @@ class Comm:
 class Aggregator:
     """qagg_aggregator handle.  ``shapes`` is a list of (M, N)."""
 
-    def __init__(self, comm, shapes, bits, flags=ZERO_THRESHOLD | SELF_QUANTIZED):
+    def __init__(self, comm, shapes, bits, flags=ZERO_THRESHOLD | SELF_QUANTIZED, whole_cols=None, first_cols=None):
+        """whole_cols / first_cols: tensor i is columns [first_cols[i], first_cols[i] + N) of a matrix of whole_cols[i] columns."""
         self.comm, self.shapes, self.bits, self.flags = comm, [tuple(s) for s in shapes], bits, flags
         T = len(shapes)
         Ms = (c_i64 * T)(*[s[0] for s in shapes])
         Ns = (c_i64 * T)(*[s[1] for s in shapes])
         h = c_vp()
-        _ok(_lib.qagg_agg_create(comm.h, T, Ms, Ns, bits, flags, ctypes.byref(h)))
+        if whole_cols is None:
+            _ok(_lib.qagg_agg_create(comm.h, T, Ms, Ns, bits, flags, ctypes.byref(h)))
+        else:
+            _ok(_lib.qagg_agg_create_slices(comm.h, T, Ms, Ns, (c_i64 * T)(*whole_cols), (c_i64 * T)(*first_cols), bits, flags, ctypes.byref(h)))
         self.h = h
 
     def _ptrs(self, ptrs):
@@ -285,6 +307,16 @@ class Aggregator:
 
     def step(self, grad_ptrs, stream=0):
         _ok(_lib.qagg_agg_step(self.h, self._ptrs(grad_ptrs), stream))
+
+    def step_header(self, grad_ptrs, header, stream=0):
+        """One step that also sums `header` (a list of floats) over the ranks; fetch the sum with header_result()."""
+        arr = (ctypes.c_double * len(header))(*header)
+        _ok(_lib.qagg_agg_step_header(self.h, self._ptrs(grad_ptrs), arr, len(header), stream))
+
+    def header_result(self, n, stream=0):
+        out = (ctypes.c_double * max(n, 1))()
+        _ok(_lib.qagg_agg_header_result(self.h, out, n, stream))
+        return [float(out[i]) for i in range(n)]
 
     def step_host(self, host_grad_ptrs, stream=0):
         _ok(_lib.qagg_agg_step_host(self.h, self._ptrs(host_grad_ptrs), stream))
@@ -343,6 +375,50 @@ class Aggregator:
             self.h = None
 
 
+class DenseAggregator:
+    """qagg_dense_aggregator: unquantized fp32 sum over the ranks (gradientBits = 32)."""
+
+    def __init__(self, comm, shapes):
+        T = len(shapes)
+        Ms = (c_i64 * T)(*[s[0] for s in shapes])
+        Ns = (c_i64 * T)(*[s[1] for s in shapes])
+        h = c_vp()
+        _ok(_lib.qagg_dense_create(comm.h, T, Ms, Ns, ctypes.byref(h)))
+        self.h = h
+
+    def step(self, grad_ptrs, stream=0):
+        _ok(_lib.qagg_dense_step(self.h, (c_vp * len(grad_ptrs))(*[c_vp(p) for p in grad_ptrs]), stream))
+
+    def peer_handle(self):
+        buf = ctypes.create_string_buffer(PEER_HANDLE_BYTES)
+        _ok(_lib.qagg_dense_peer_handle(self.h, buf))
+        return buf.raw
+
+    def enable_peer(self, handles):
+        blob = b"".join(handles)
+        _ok(_lib.qagg_dense_enable_peer(self.h, ctypes.create_string_buffer(blob, len(blob))))
+
+    def check(self, stream=0):
+        _ok(_lib.qagg_dense_check(self.h, stream))
+
+    @property
+    def wire_bytes(self):
+        return int(_lib.qagg_dense_wire_bytes(self.h))
+
+    def destroy(self):
+        if self.h:
+            _ok(_lib.qagg_dense_destroy(self.h))
+            self.h = None
+
+
+def dense_step_group(aggs, grad_ptrs, stream=0):
+    K = len(aggs)
+    ha = (c_vp * K)(*[a.h for a in aggs])
+    rows = [(c_vp * len(g))(*[c_vp(p) for p in g]) for g in grad_ptrs]
+    pp = (ctypes.POINTER(c_vp) * K)(*[ctypes.cast(r, ctypes.POINTER(c_vp)) for r in rows])
+    _ok(_lib.qagg_dense_step_group(ha, K, pp, stream))
+
+
 class HostAggregator:
     """qagg_host_aggregator: aggregation of gradients held in host memory, chunk-pipelined over PCIe."""
 
@@ -367,6 +443,9 @@ class HostAggregator:
     def step(self, host_grad_ptrs):
         _ok(_lib.qagg_hagg_step(self.h, (c_vp * len(host_grad_ptrs))(*[c_vp(p) for p in host_grad_ptrs])))
 
+    def copy_only(self, host_grad_ptrs):
+        _ok(_lib.qagg_hagg_copy_only(self.h, (c_vp * len(host_grad_ptrs))(*[c_vp(p) for p in host_grad_ptrs])))
+
     def check(self):
         _ok(_lib.qagg_hagg_check(self.h))
 
@@ -376,10 +455,16 @@ class HostAggregator:
             self.h = None
 
 
-def step_group(aggs, grad_ptrs, stream=0):
-    """grad_ptrs[r][i]: device pointers of rank r's gradients."""
+def step_group(aggs, grad_ptrs, stream=0, headers=None):
+    """grad_ptrs[r][i]: device pointers of rank r's gradients; headers[r]: rank r's header values (optional)."""
     K = len(aggs)
     ha = (c_vp * K)(*[a.h for a in aggs])
     rows = [(c_vp * len(g))(*[c_vp(p) for p in g]) for g in grad_ptrs]
     pp = (ctypes.POINTER(c_vp) * K)(*[ctypes.cast(r, ctypes.POINTER(c_vp)) for r in rows])
-    _ok(_lib.qagg_agg_step_group(ha, K, pp, stream))
+    if headers is None:
+        _ok(_lib.qagg_agg_step_group(ha, K, pp, stream))
+        return
+    n = len(headers[0])
+    hrows = [(ctypes.c_double * n)(*h) for h in headers]
+    hp = (ctypes.POINTER(ctypes.c_double) * K)(*[ctypes.cast(r, ctypes.POINTER(ctypes.c_double)) for r in hrows])
+    _ok(_lib.qagg_agg_step_group_header(ha, K, pp, hp, n, stream))

@@ -68,3 +68,10 @@ def algorithmic_bytes(shapes, bits, K):
     k3 = 4 * V + P
     k2 = 0 if K == 1 else 8 * V / K + P * (1 + 1 / K)
     return {"quantize": k1, "reduce_requantize": k2, "unquantize": k3, "total": k1 + k2 + k3}
+
+
+def dense_algorithmic_bytes(shapes, K):
+    """Unquantized fp32 arm: bytes one rank must move through its HBM per step when every buffer is touched once: read the
+    gradients (4V), land the K received slices (4V), read them for the sum (4V), land the gathered result (4V), read it and
+    write the gradients (8V): 24V.  (With one rank the arm does nothing.)"""
+    return 0 if K == 1 else 24 * total_values(shapes)

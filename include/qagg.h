@@ -49,6 +49,7 @@ typedef struct qagg_comm qagg_comm;
 typedef struct qagg_aggregator qagg_aggregator;
 typedef struct qagg_plan qagg_plan;
 typedef struct qagg_host_aggregator qagg_host_aggregator;
+typedef struct qagg_dense_aggregator qagg_dense_aggregator;
 
 /* Last error message of the calling thread ("" if none). */
 const char* qagg_last_error(void);
@@ -165,11 +166,29 @@ int qagg_comm_destroy(qagg_comm* c);
  * residuals for its lifetime; tensor shapes are fixed at creation. */
 int qagg_agg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, int bits, int flags,
                     qagg_aggregator** out);
+/* The same for tensors that are column slices: tensor i is columns [first_col[i], first_col[i] + N[i]) of a matrix with
+ * whole_N[i] columns, and its columns keep the owners GetStripeForNode gives them in the WHOLE matrix -- so aggregating
+ * the slices of a matrix separately gives bit-identical results to aggregating it whole (a column's aggregate depends on
+ * its owner through the order of the owner's sum).  Both arrays null: whole matrices.  No reference counterpart. */
+int qagg_agg_create_slices(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, const int64_t* whole_N, const int64_t* first_col,
+                           int bits, int flags, qagg_aggregator** out);
 /* One AggregateGradients call: grads[i] (device, M[i] x N[i]) is replaced in place by the aggregate over all ranks.
  * Enqueues on `stream`; returns without waiting.  `grads` is a host array. */
 int qagg_agg_step(qagg_aggregator* a, float* const* grads, void* stream);
 /* The same for all K aggregators of a local group, in lock step: grads[r][i]. */
 int qagg_agg_step_group(qagg_aggregator* const* aggs, int num_ranks, float* const* const* grads, void* stream);
+/* One AggregateGradients call INCLUDING its DistGradHeader: besides the gradients, `header` (n <= 64 doubles in host memory:
+ * criterion, sample counts, evaluation pairs -- what Source/SGDLib/DistGradHeader.h:5-95 carries, what the V2 path packs into
+ * a double vector, Source/1BitSGD/V2AllReduceDistGradAggregator.h:222-248) is summed over all ranks as part of the same
+ * enqueued step.  Where the reference gathers headers on rank 0 and sends the sum back with four more MPI messages per rank
+ * (AllReduceDistGradAggregator.h:324-333, 380-383, 440-457, 504-514), the peer-memory path stores the header into every
+ * peer's window ahead of the quantize kernel, whose flag release publishes it with the packed stripes; after the first flag
+ * wait a one-block kernel adds the K headers in rank order (the same order on every rank).  The NCCL path all-reduces it.
+ * The call copies `header` before it returns.  qagg_agg_header_result waits for `stream` and returns the sum. */
+int qagg_agg_step_header(qagg_aggregator* a, float* const* grads, const double* header, int n, void* stream);
+int qagg_agg_step_group_header(qagg_aggregator* const* aggs, int num_ranks, float* const* const* grads, const double* const* headers, int n,
+                               void* stream);
+int qagg_agg_header_result(qagg_aggregator* a, double* out, int n, void* stream);
 /* The same through HOST gradient buffers (pinned memory recommended): copies host_grads[i] to the device, aggregates,
  * copies the result back into host_grads[i], and waits for completion. */
 int qagg_agg_step_host(qagg_aggregator* a, float* const* host_grads, void* stream);
@@ -191,20 +210,43 @@ int qagg_agg_copy_packed(qagg_aggregator* a, int tensor, void* dst_dev, void* st
 /* ---- aggregation from host buffers, software-pipelined ---------------------------------------------------------------
  * For gradients that live in (pinned) host memory -- the situation of the reference's CPU-device runs and of its GPU runs'
  * packed buffers, which always cross PCIe (Source/Math/MatrixQuantizerGPU.cu:126-142, 313-324).  The gradient set is cut
- * into `num_chunks` runs of consecutive tensors with about equal bytes; each chunk is uploaded, aggregated and downloaded on
- * its own stream so that the upload of one chunk, the kernels of another and the download of a third overlap.
+ * into `num_chunks` chunks of about equal bytes -- small tensors grouped, large ones cut by columns, every column keeping
+ * the owner it has in its whole tensor (qagg_agg_create_slices) -- and the chunks go through a three-stage pipeline (an
+ * upload stream, a compute stream, a download stream, linked by events), so that the upload of one chunk, the kernels of
+ * another and the download of a third overlap and the upload engine never waits behind a download.
  * qagg_hagg_step returns when all results are back in host_grads.  Residuals live inside the object.
  * Peer mode: qagg_hagg_peer_handles writes chunks * QAGG_PEER_HANDLE_BYTES bytes; qagg_hagg_enable_peer takes the
- * handles of all ranks, rank-major (K * chunks * QAGG_PEER_HANDLE_BYTES bytes).  Without peer mode and with more than one
- * rank the chunks run one after the other (one NCCL communicator needs one order of collectives). */
+ * handles of all ranks, rank-major (K * chunks * QAGG_PEER_HANDLE_BYTES bytes).  Every rank runs the chunks' kernels in
+ * the same order on one stream (which is also what one NCCL communicator needs without peer mode). */
 int qagg_hagg_create(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, int bits, int flags, int num_chunks,
                      qagg_host_aggregator** out);
 int qagg_hagg_chunks(const qagg_host_aggregator* h);
 int qagg_hagg_peer_handles(qagg_host_aggregator* h, void* out);
 int qagg_hagg_enable_peer(qagg_host_aggregator* h, const void* handles);
 int qagg_hagg_step(qagg_host_aggregator* h, float* const* host_grads);
+/* The uploads and downloads of qagg_hagg_step without the kernels between them: the copy floor of this machine for the
+ * same chunking (measurement aid; host_grads come back unchanged). */
+int qagg_hagg_copy_only(qagg_host_aggregator* h, float* const* host_grads);
 int qagg_hagg_check(qagg_host_aggregator* h);
 int qagg_hagg_destroy(qagg_host_aggregator* h);
+
+/* ---- unquantized aggregation (gradientBits = 32) ---------------------------------------------------------------------
+ * SimpleDistGradAggregator (Source/SGDLib/SimpleDistGradAggregator.h:262-485) / MPICommunicatorImpl::AggregateImpl
+ * (Source/CNTKv2LibraryDll/DistributedCommunicator.cpp:311-492): grads[i] is replaced in place by the fp32 sum over all
+ * ranks.  Where the reference packs the tensors below its threshold into one buffer (:327-361) and all-reduces buffers and
+ * large tensors with MPI or NCCL, all tensors are laid end to end here, cut into K equal slices, and moved by three kernels
+ * over peer-mapped windows (scatter to the slice's owner, sum at the owner IN RANK ORDER, gather from the owner): the
+ * result is the same on every rank and every run.  qagg_dense_peer_handle / _enable_peer work like the quantized
+ * aggregator's; without them more than one rank falls back to one ncclAllReduce of the flat buffer (summation order:
+ * NCCL's).  The reference's optional fp16 wire format (useFP16AllReduce, :411-429) is not built.  One rank: no-op. */
+int qagg_dense_create(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, qagg_dense_aggregator** out);
+int qagg_dense_step(qagg_dense_aggregator* a, float* const* grads, void* stream);
+int qagg_dense_step_group(qagg_dense_aggregator* const* aggs, int num_ranks, float* const* const* grads, void* stream);
+int qagg_dense_peer_handle(qagg_dense_aggregator* a, void* out);
+int qagg_dense_enable_peer(qagg_dense_aggregator* a, const void* handles);
+int qagg_dense_check(qagg_dense_aggregator* a, void* stream);
+int64_t qagg_dense_wire_bytes(const qagg_dense_aggregator* a);
+int qagg_dense_destroy(qagg_dense_aggregator* a);
 
 /* ---- peer-memory exchange (optional; replaces the two NCCL collectives of a step) ------------------------------------
  * Where the reference moves every stripe GPU -> pinned host -> MPI -> pinned host -> GPU (Source/Math/MatrixQuantizerGPU.cu:126-142,

@@ -174,3 +174,16 @@ def aggregate_columns(backend, owner, g, res, sres, bits, zero_thr=True, self_qu
     backend.quantize(agg, sres, sres, requant, bits, zero_thr)
     backend.unquantize(requant, out, bits, add=False)
     return out, requant
+
+
+def dense_sum(grads):
+    """The unquantized arm (gradientBits = 32): the fp32 sum over the ranks, added in ascending rank order with one rounding
+    per addition.  The reference leaves the order to its MPI / NCCL all-reduce (SimpleDistGradAggregator.h:262-485), so it
+    has no bit-level contract; the fixed order is the pin.  grads[r][i]: rank r's tensor i; returns the list of sums."""
+    out = []
+    for i in range(len(grads[0])):
+        acc = grads[0][i].astype(np.float32, copy=True)
+        for r in range(1, len(grads)):
+            acc = (acc + grads[r][i]).astype(np.float32)
+        out.append(acc)
+    return out

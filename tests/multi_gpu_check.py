@@ -1,4 +1,4 @@
-"""One rank of the multi-GPU parity check; launched by tests/test_gpu_multi.py as
+"""One rank of the multi-GPU parity check; launched by tests/test_gpu_multi.py (and runnable by hand) as
     python -m torch.distributed.run --nnodes=1 --nproc-per-node K --master-addr 127.0.0.1 --master-port P tests/multi_gpu_check.py
 
 Every rank builds all K ranks' seeded gradients, runs the CPU restatement of the exchange for all K ranks, runs ITS
@@ -26,17 +26,16 @@ def inputs(K, step):
     return [[mg.normal_input(M, N, 1e-3, 1000 * r + step + 7919 * i) for i, (M, N) in enumerate(SHAPES)] for r in range(K)]
 
 
-def main():
-    rank, local, K = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
-    idt = torch.zeros(lib.UNIQUE_ID_BYTES, dtype=torch.uint8, device=dev)
-    if rank == 0:
-        idt.copy_(torch.frombuffer(bytearray(lib.unique_id()), dtype=torch.uint8))
-    dist.broadcast(idt, 0)
-    comm = lib.Comm.create(bytes(idt.cpu().numpy().tobytes()), rank, K, local)
+def run_checks(comm, rank, K, dev):
+    """All checks of this module on an existing communicator (torch.distributed must be initialised: it carries the
+    peer handles and the barriers).  Raises AssertionError on the first differing byte; returns the number of
+    (configuration, step) pairs compared."""
     be = backend.OracleBackend()
+    compared = 0
+    # the communicator's own collectives: sum of rank-dependent doubles (exact) and the barrier
+    vals = comm.allreduce_f64([float(rank + 1), 0.5 * rank, 2.0 ** rank, -1.0])
+    assert vals == [K * (K + 1) / 2.0, 0.5 * K * (K - 1) / 2.0, float(2 ** K - 1), -float(K)], f"rank {rank}: allreduce_f64 gave {vals}"
+    comm.barrier()
     for bits, zero_thr, self_q, peer in ((1, True, True, False), (1, False, True, False), (4, True, True, False), (1, True, False, False),
                                          (1, True, True, True), (4, True, True, True), (1, True, False, True)):
         flags = (lib.ZERO_THRESHOLD if zero_thr else 0) | (lib.SELF_QUANTIZED if self_q else 0)
@@ -54,7 +53,12 @@ def main():
             for t, a in zip(dg, grads[rank]):
                 t.copy_(torch.from_numpy(a))
             packed = exchange.aggregate_step(be, st, grads, bits, zero_thr, self_q)
-            agg.step([t.data_ptr() for t in dg], torch.cuda.current_stream().cuda_stream)
+            # the step carries a DistGradHeader: rank-dependent doubles, summed in rank order (exact in double)
+            hdr = lambda r: [1.5 * (r + 1) + step, float(100 * r + 7), float(r), 0.125 * (r + 3), float(3 * r + step)]
+            agg.step_header([t.data_ptr() for t in dg], hdr(rank), torch.cuda.current_stream().cuda_stream)
+            got = agg.header_result(5, torch.cuda.current_stream().cuda_stream)
+            want = [sum(hdr(r)[k] for r in range(K)) for k in range(5)]
+            assert got == want, f"header sum: bits {bits} peer {peer} step {step} rank {rank}: {got} != {want}"
             torch.cuda.synchronize()
             for i, (M, N) in enumerate(SHAPES):
                 what = f"bits {bits} zero {zero_thr} self {self_q} peer {peer} step {step} rank {rank} tensor {i}"
@@ -73,9 +77,36 @@ def main():
                 agg.copy_packed(i, pk.data_ptr())
                 torch.cuda.synchronize()
                 assert np.array_equal(pk.cpu().numpy(), packed[rank][i]), "packed words: " + what
+            compared += 1
         agg.check()
         dist.barrier()  # nobody unmaps a window that a peer may still be writing to
         agg.destroy()
+    # the unquantized fp32 arm: peer-window kernels (rank-ordered sum: bit-exact) and the ncclAllReduce baseline (close)
+    for peer in (True, False):
+        dagg = lib.DenseAggregator(comm, SHAPES)
+        if peer:
+            mine = torch.frombuffer(bytearray(dagg.peer_handle()), dtype=torch.uint8).to(dev)
+            allh = [torch.zeros_like(mine) for _ in range(K)]
+            dist.all_gather(allh, mine)
+            dagg.enable_peer([bytes(h.cpu().numpy().tobytes()) for h in allh])
+        dg = [torch.zeros((N, M), dtype=torch.float32, device=dev) for (M, N) in SHAPES]
+        for step in range(3):
+            grads = inputs(K, step)
+            for t, a in zip(dg, grads[rank]):
+                t.copy_(torch.from_numpy(a))
+            want = exchange.dense_sum(grads)
+            dagg.step([t.data_ptr() for t in dg], torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            for i in range(len(SHAPES)):
+                got = dg[i].cpu().numpy()
+                if peer:
+                    assert np.array_equal(got.view(np.uint32), want[i].view(np.uint32)), f"dense sum: step {step} rank {rank} tensor {i}"
+                else:
+                    assert np.allclose(got, want[i], rtol=1e-5, atol=1e-9), f"dense sum (nccl): step {step} rank {rank} tensor {i}"
+            compared += 1
+        dagg.check()
+        dist.barrier()
+        dagg.destroy()
     # host-buffer aggregator, chunks pipelined over streams, peer-memory exchange per chunk
     hagg = lib.HostAggregator(comm, SHAPES, 1, chunks=3)
     mine = torch.frombuffer(bytearray(hagg.peer_handles()), dtype=torch.uint8).to(dev)
@@ -92,10 +123,25 @@ def main():
         hagg.step([t.data_ptr() for t in host])
         for i in range(len(SHAPES)):
             assert np.array_equal(host[i].numpy().view(np.uint32), grads[rank][i].view(np.uint32)), f"host aggregator: step {step} rank {rank} tensor {i}"
+        compared += 1
     hagg.check()
     dist.barrier()
     hagg.destroy()
     dist.barrier()
+    return compared
+
+
+def main():
+    rank, local, K = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    idt = torch.zeros(lib.UNIQUE_ID_BYTES, dtype=torch.uint8, device=dev)
+    if rank == 0:
+        idt.copy_(torch.frombuffer(bytearray(lib.unique_id()), dtype=torch.uint8))
+    dist.broadcast(idt, 0)
+    comm = lib.Comm.create(bytes(idt.cpu().numpy().tobytes()), rank, K, local)
+    run_checks(comm, rank, K, dev)
     comm.destroy()
     dist.destroy_process_group()
     if rank == 0:

@@ -253,3 +253,45 @@ def test_kernel_choice_knob_changes_no_result(G, oracle_port, knob, monkeypatch)
     monkeypatch.setenv(knob, "0")
     run_group(G, oracle_port, SPEECH_SMALL, 3, 1, True, True, 6, speech_inputs, check_every=3)
     run_group(G, oracle_port, mg.EXCHANGE_SHAPES, 2, 1, True, False, 4, mg.exchange_inputs, peer=True)
+
+
+@pytest.mark.parametrize("K,peer", [(1, False), (2, False), (3, True), (8, True)])
+def test_step_with_header_sums_it_in_rank_order(G, K, peer):
+    """qagg_agg_step_group_header: the DistGradHeader values ride with the step and come back summed over the ranks in
+    ascending rank order (exactly, as doubles); the gradients are aggregated as without a header."""
+    from cntk_b200 import lib
+    shapes = [(64, 9), (33, 2)]
+    comms = lib.Comm.local_group(K, 0)
+    aggs = [lib.Aggregator(c, shapes, 1) for c in comms]
+    plain = [lib.Aggregator(c, shapes, 1) for c in comms]
+    if peer:
+        for group in (aggs, plain):
+            hs = [a.peer_handle() for a in group]
+            for a in group:
+                a.enable_peer(hs)
+    rng = np.random.default_rng(5)
+    try:
+        for step in range(3):
+            n = 3 + 2 * step  # criterion, two sample counts, then evaluation pairs
+            headers = [[float(rng.standard_normal() * 10.0 ** int(rng.integers(-3, 6))) for _ in range(n)] for _ in range(K)]
+            g = [[torch.from_numpy((rng.standard_normal((N, M)) * 1e-3).astype(np.float32)).to(G.DEV) for (M, N) in shapes] for _ in range(K)]
+            g2 = [[t.clone() for t in row] for row in g]
+            lib.step_group(aggs, [[t.data_ptr() for t in row] for row in g], headers=headers)
+            lib.step_group(plain, [[t.data_ptr() for t in row] for row in g2])
+            expect = []
+            for i in range(n):
+                s = headers[0][i]
+                for r in range(1, K):
+                    s = s + headers[r][i]
+                expect.append(s)
+            for r in range(K):
+                assert aggs[r].header_result(n) == expect, f"step {step} rank {r}"
+                for a, b in zip(g[r], g2[r]):
+                    assert torch.equal(a.view(torch.int32), b.view(torch.int32))
+        with pytest.raises(lib.QaggError):
+            lib.step_group(aggs, [[t.data_ptr() for t in row] for row in g], headers=[[0.0] * 65] * K)
+    finally:
+        for a in aggs + plain:
+            a.destroy()
+        for c in comms:
+            c.destroy()
