@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <cstddef>
+#include <functional>
 #include <memory>
 #include <utility>
 
@@ -68,7 +69,13 @@ public:
             LogicError("Matrix::SetValue: only 0 is needed on this path");
         if (GetNumElements() && cudaMemset(m_data, 0, GetNumElements() * sizeof(ElemType)) != cudaSuccess)
             RuntimeError("Matrix::SetValue: cudaMemset failed");
+        if (m_onWrite && *m_onWrite)
+            (*m_onWrite)();
     }
+
+    // A matrix that something else keeps derived state about (the communicator's residual views) tells it when its content
+    // is overwritten through this interface.
+    void NotifyOnWrite(std::function<void()> fn) { m_onWrite = std::make_shared<std::function<void()>>(std::move(fn)); }
 
     static void SetDevice(DEVICEID_TYPE deviceId)
     {
@@ -83,6 +90,7 @@ public:
         std::swap(a.m_deviceId, b.m_deviceId);
         std::swap(a.m_data, b.m_data);
         std::swap(a.m_owner, b.m_owner);
+        std::swap(a.m_onWrite, b.m_onWrite);
     }
 
 private:
@@ -90,6 +98,7 @@ private:
     DEVICEID_TYPE m_deviceId;
     ElemType* m_data = nullptr;
     std::shared_ptr<void> m_owner;
+    std::shared_ptr<std::function<void()>> m_onWrite;
 };
 
 }}}

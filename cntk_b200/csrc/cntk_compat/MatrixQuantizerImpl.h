@@ -1,4 +1,4 @@
-// MatrixQuantizerImpl.h -- MatrixQuantizerImpl<float> with the reference's interface
+// MatrixQuantizerImpl.h -- MatrixQuantizerImpl<float / double> with the reference's interface
 // (Source/Math/MatrixQuantizerImpl.h:18-49), implemented over the C ABI of libqagg.
 //   QuantizeAsync(in, inResidual, outQ, outResidual, zeroThresholdFor1Bit)   inResidual may alias outResidual
 //   WaitQuantizeAsyncDone()
@@ -14,6 +14,24 @@
 #include "QuantizedMatrix.h"
 
 namespace Microsoft { namespace MSR { namespace CNTK {
+
+// the C entry points of the two element types behind one name
+inline int QaggQuantize(void* st, const float* g, const float* ri, float* ro, void* p, int64_t M, int64_t N, int bits, int z)
+{
+    return qagg_quantize(st, g, ri, ro, p, M, N, bits, z);
+}
+inline int QaggQuantize(void* st, const double* g, const double* ri, double* ro, void* p, int64_t M, int64_t N, int bits, int z)
+{
+    return qagg_quantize_f64(st, g, ri, ro, p, M, N, bits, z);
+}
+inline int QaggUnquantize(void* st, const void* p, float* out, int64_t M, int64_t N, int bits, int add)
+{
+    return qagg_unquantize(st, p, out, M, N, bits, add);
+}
+inline int QaggUnquantize(void* st, const void* p, double* out, int64_t M, int64_t N, int bits, int add)
+{
+    return qagg_unquantize_f64(st, p, out, M, N, bits, add);
+}
 
 template <class ElemType>
 class MatrixQuantizerImpl
@@ -68,14 +86,14 @@ public:
         if (outQ.GetDeviceId() == CPUDEVICE)
         {
             // kernel, then copy to the host buffer on the same stream; completion is observed in WaitQuantizeAsyncDone
-            QaggCheck(qagg_quantize(m_stream, in.Data(), inResidual.Data(), outResidual.Data(), Scratch(outQ.GetSize()), (int64_t) M, (int64_t) N, bits,
+            QaggCheck(QaggQuantize(m_stream, in.Data(), inResidual.Data(), outResidual.Data(), Scratch(outQ.GetSize()), (int64_t) M, (int64_t) N, bits,
                                     zeroThresholdFor1Bit ? 1 : 0), "QuantizeAsync");
             if (outQ.GetSize() && cudaMemcpyAsync(outQ.Buffer(), m_scratch, outQ.GetSize(), cudaMemcpyDeviceToHost, m_stream) != cudaSuccess)
                 RuntimeError("QuantizeAsync: copy of the packed matrix to the host failed");
         }
         else
         {
-            QaggCheck(qagg_quantize(m_stream, in.Data(), inResidual.Data(), outResidual.Data(), outQ.Buffer(), (int64_t) M, (int64_t) N, bits,
+            QaggCheck(QaggQuantize(m_stream, in.Data(), inResidual.Data(), outResidual.Data(), outQ.Buffer(), (int64_t) M, (int64_t) N, bits,
                                     zeroThresholdFor1Bit ? 1 : 0), "QuantizeAsync");
         }
     }
@@ -94,7 +112,7 @@ public:
                 RuntimeError("UnquantizeAsync: copy of the packed matrix to the device failed");
             packed = m_scratch;
         }
-        QaggCheck(qagg_unquantize(m_stream, packed, out.Data(), (int64_t) M, (int64_t) N, bits, add ? 1 : 0), "UnquantizeAsync");
+        QaggCheck(QaggUnquantize(m_stream, packed, out.Data(), (int64_t) M, (int64_t) N, bits, add ? 1 : 0), "UnquantizeAsync");
     }
     void WaitUnquantizeAsyncDone() override { Sync("WaitUnquantizeAsyncDone"); }
 

@@ -9,9 +9,10 @@
 // Kept from the reference: aggregation starts only once distributeAfterSamples samples have been seen (:31); an empty
 // minibatch contributes zero gradients (:35-36); evalCriterion, trainingLoss and the sample count are summed over the
 // workers BEFORE the gradients (:40-50) and the local learner is updated with the aggregated count (:69); an empty
-// (aggregated) minibatch skips the local update and returns false (:66-67); CreateCheckpoint zeroes the quantization
-// residuals, because they are not part of the checkpoint (:73-91); useAsyncBufferedParameterUpdate = true is a
-// LogicError, as in the reference (:24-25).
+// (aggregated) minibatch skips the local update and returns false (:66-67); the learner OWNS the two residual sets
+// (m_residuals, m_stripeResiduals: created by the communicator on the first call and handed back through the vectors,
+// :56-60) and CreateCheckpoint zeroes them, because they are not part of the checkpoint (:73-91);
+// useAsyncBufferedParameterUpdate = true is a LogicError, as in the reference (:24-25).
 #pragma once
 
 #include <memory>
@@ -64,7 +65,7 @@ public:
             info.evalCriterionValue = header[0];
             info.trainingLossValue = header[1];
             info.numberOfSamples = (size_t) header[2];
-            m_communicator->QuantizedAggregateInPlace(gradientValues, m_communicator->Workers());
+            m_communicator->QuantizedAggregateInPlace(gradientValues, m_residuals, m_stripeResiduals, m_communicator->Workers());
         }
         m_sampleCount += info.numberOfSamples;
         if (info.IsEmpty())
@@ -76,12 +77,20 @@ public:
     // Returns the one piece of state the base class checkpoints here, the total sample count.
     size_t CreateCheckpoint()
     {
-        m_communicator->ResetResiduals();
+        for (auto& r : m_residuals)
+            if (r)
+                r->SetValue(0.0f);
+        for (auto& r : m_stripeResiduals)
+            if (r)
+                r->SetValue(0.0f);
         return m_sampleCount;
     }
     void RestoreFromCheckpoint(size_t totalNumberOfSamplesSeen) { m_sampleCount = totalNumberOfSamplesSeen; }
 
     size_t TotalNumberOfSamplesSeen() const { return m_sampleCount; }
+    // the residual views the learner holds (for inspection; call MaterializeResiduals() on the communicator before reading)
+    const std::vector<NDArrayViewPtr>& Residuals() const { return m_residuals; }
+    const std::vector<NDArrayViewPtr>& StripeResiduals() const { return m_stripeResiduals; }
     QuantizedDistributedCommunicatorPtr GetCommunicator() const { return m_communicator; }
 
 private:
@@ -89,6 +98,9 @@ private:
     LearnerPtr m_learner;
     size_t m_distributeAfterSamples;
     size_t m_sampleCount = 0;
+    // residuals of quantized gradients and of the aggregated stripes this worker owns
+    std::vector<NDArrayViewPtr> m_residuals;
+    std::vector<NDArrayViewPtr> m_stripeResiduals;
 };
 typedef std::shared_ptr<QuantizedDataParallelDistributedLearner> DistributedLearnerPtr;
 

@@ -1,4 +1,4 @@
-// QuantizedMatrix.h -- QuantizedMatrix<float> with the reference's interface and byte layout
+// QuantizedMatrix.h -- QuantizedMatrix<float / double> with the reference's interface and byte layout
 // (Source/Math/QuantizedMatrix.h:53-124, QuantizedMatrix.cpp:8-107): N packed columns of
 // QuantizedColumnSize(bits, rows) bytes each; ColumnSlice(start, n) is the byte range [start*C, (start+n)*C).
 // deviceId == CPUDEVICE puts the buffer in pinned host memory (what the reference aggregator uses as MPI buffers,
@@ -20,15 +20,15 @@ class QuantizedMatrixBase
 template <class ElemType>
 class QuantizedMatrix : public QuantizedMatrixBase
 {
-    static_assert(sizeof(ElemType) == 4, "this build implements the float path (QWord = uint32)");
+    static_assert(sizeof(ElemType) == 4 || sizeof(ElemType) == 8, "ElemType is float (QWord = uint32) or double (QWord = uint64)");
 
 public:
     QuantizedMatrix(size_t numRows, size_t numCols, size_t nbits, DEVICEID_TYPE deviceId, void* /*allocator*/ = nullptr)
         : m_numRows(numRows), m_numCols(numCols), m_numBits(nbits), m_deviceId(deviceId)
     {
-        const int64_t c = qagg_packed_col_bytes((int64_t) numRows, (int) nbits);
+        const int64_t c = sizeof(ElemType) == 8 ? qagg_packed_col_bytes_f64((int64_t) numRows, (int) nbits) : qagg_packed_col_bytes((int64_t) numRows, (int) nbits);
         if (c < 0)
-            LogicError("QuantizedMatrix: nbits=%zu must be a power of two dividing the 32-bit word", nbits); // QuantizedMatrix.cpp:12-15
+            LogicError("QuantizedMatrix: nbits=%zu must be a power of two dividing the %zu-bit word", nbits, 8 * sizeof(ElemType)); // QuantizedMatrix.cpp:12-15
         m_qColSize = (size_t) c;
         const size_t bytes = m_qColSize * numCols != 0 ? m_qColSize * numCols : 1;
         void* p = nullptr;

@@ -163,6 +163,7 @@ struct qagg_aggregator
     // region to the peers; false = the requantize kernel itself stores every packed word K times
     bool pushGather = false;
     std::vector<float*> res, sres;
+    bool externalRes = false; // the residual buffers belong to the caller (qagg_agg_bind_residuals)
     // 1 bit with threshold 0: the quantize kernel (and optionally the owner's reduce-requantize kernel) is the streaming
     // kernel, which keeps its residual set in deferred form: the buffer above holds the quantized values v, and lv (slv)
     // each column's two reconstruction values (see qagg_internal.h)
@@ -178,6 +179,7 @@ struct qagg_aggregator
     std::vector<QTensor> hK1, hK2, hK3;
     std::vector<QItem> iK1, iK2;
     long long k3Units = 0; // work units of the unquantize launch
+    int k3SmemWords = 0;   // shared-memory words per warp the unquantize launch needs
     QTensor *dK1 = nullptr, *dK2 = nullptr, *dK3 = nullptr;
     QItem *dI1 = nullptr, *dI2 = nullptr;
     DevBuf queue; // three pairs of work-queue counters (one pair per kernel), zero when no kernel is running
@@ -294,11 +296,14 @@ int build_tables(qagg_aggregator* a)
     a->hK1.assign(T, QTensor{});
     a->hK3.assign(T, QTensor{});
     a->k3Units = 0;
+    a->k3SmemWords = 0;
     for (int i = 0; i < T; ++i)
     {
         // every entry, empty matrices included, carries the running unit count (the kernel searches this column)
         a->hK3[i].unit0 = a->k3Units;
         a->k3Units += unq_units(a->M[i], a->N[i], a->bits);
+        if (a->N[i] > 0)
+            a->k3SmemWords = std::max(a->k3SmemWords, unq_smem_words(a->M[i], a->bits));
     }
     a->hK2.clear();
     a->k2Tensor.clear();
@@ -580,7 +585,7 @@ int wait_peers(qagg_aggregator* a, bool gatherPhase, cudaStream_t st)
 }
 int launch_k3(qagg_aggregator* a, cudaStream_t st)
 {
-    return check_cuda(launch_unquantize(st, false, a->bits, nullptr, a->dK3, (int) a->hK3.size(), a->k3Units, a->cfg), "unquantize launch");
+    return check_cuda(launch_unquantize(st, false, a->bits, nullptr, a->dK3, (int) a->hK3.size(), a->k3Units, a->k3SmemWords, a->cfg), "unquantize launch");
 }
 
 } // namespace
@@ -1616,11 +1621,108 @@ int qagg_hagg_destroy(qagg_host_aggregator* h)
     return QAGG_OK;
 }
 
+int qagg_agg_bind_residuals(qagg_aggregator* a, float* const* value_residuals, float* const* stripe_residuals, int keep_plain)
+{
+    if (!a || (a->T > 0 && (!value_residuals || !stripe_residuals)))
+        return fail(QAGG_EINVAL, "qagg_agg_bind_residuals: bad arguments");
+    const int r = a->comm->rank, K = a->comm->K;
+    for (int i = 0; i < a->T; ++i)
+    {
+        if (a->M[i] * a->N[i] > 0 && !value_residuals[i])
+            return fail(QAGG_EINVAL, "qagg_agg_bind_residuals: null residual buffer");
+        if (K > 1 && a->M[i] * a->sN[r][i] > 0 && !stripe_residuals[i])
+            return fail(QAGG_EINVAL, "qagg_agg_bind_residuals: null stripe residual buffer for a tensor whose stripe this rank owns");
+        if ((reinterpret_cast<uintptr_t>(value_residuals[i]) & 3) || (reinterpret_cast<uintptr_t>(stripe_residuals[i]) & 3))
+            return fail(QAGG_EINVAL, "qagg_agg_bind_residuals: buffers must be 4-byte aligned");
+    }
+    int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    // no step may still be using the old buffers or tables
+    if ((rc = check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize")))
+        return rc;
+    for (int i = 0; i < a->T; ++i)
+    {
+        a->res[i] = value_residuals[i];
+        a->sres[i] = (K > 1 && a->sN[r][i] > 0) ? stripe_residuals[i] : nullptr;
+    }
+    a->externalRes = true;
+    if (keep_plain)
+    {
+        a->deferred = false;
+        a->deferredOwner = false;
+    }
+    // the buffers hold plain residuals now: with zero reconstruction values the deferred form means exactly that
+    if (a->lvAll.p && (rc = check_cuda(cudaMemset(a->lvAll.p, 0, a->lvAll.bytes), "cudaMemset")))
+        return rc;
+    if (a->slvAll.p && (rc = check_cuda(cudaMemset(a->slvAll.p, 0, a->slvAll.bytes), "cudaMemset")))
+        return rc;
+    if ((rc = build_tables(a)))
+        return rc;
+    a->tableBytes = std::max(a->tableBytes, (size_t) align_up((int64_t) table_bytes(a), 256));
+    if (a->tables.bytes < 2 * a->tableBytes)
+    {
+        cudaFree(a->tables.p);
+        a->tables.p = nullptr;
+        if ((rc = a->tables.alloc(2 * a->tableBytes, true)))
+            return rc;
+    }
+    for (auto& b : a->bindings)
+        b = qagg_aggregator::Binding();
+    a->curBinding = 0;
+    return QAGG_OK;
+}
+
+int qagg_agg_materialize_residuals(qagg_aggregator* a, void* stream)
+{
+    if (!a)
+        return fail(QAGG_EINVAL, "null aggregator");
+    cudaStream_t st = (cudaStream_t) stream;
+    const int r = a->comm->rank;
+    int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    for (int i = 0; i < a->T; ++i)
+    {
+        if (a->deferred && a->M[i] * a->N[i] > 0)
+        {
+            if ((rc = check_cuda(launch_materialize(st, a->res[i], a->lv[i], a->res[i], a->M[i], a->N[i], a->cfg.numSMs), "residual export")) ||
+                (rc = check_cuda(cudaMemsetAsync(a->lv[i], 0, (size_t) a->N[i] * 8, st), "cudaMemsetAsync")))
+                return rc;
+        }
+        if (a->deferredOwner && a->sres[i] && a->M[i] * a->sN[r][i] > 0)
+        {
+            if ((rc = check_cuda(launch_materialize(st, a->sres[i], a->slv[i], a->sres[i], a->M[i], a->sN[r][i], a->cfg.numSMs), "residual export")) ||
+                (rc = check_cuda(cudaMemsetAsync(a->slv[i], 0, (size_t) a->sN[r][i] * 8, st), "cudaMemsetAsync")))
+                return rc;
+        }
+    }
+    return QAGG_OK;
+}
+
 int qagg_agg_reset_residuals(qagg_aggregator* a, void* stream)
 {
     if (!a)
         return fail(QAGG_EINVAL, "null aggregator");
     cudaStream_t st = (cudaStream_t) stream;
+    if (a->externalRes)
+    {
+        // the caller's buffers, one by one
+        const int rr = a->comm->rank;
+        int rc = QAGG_OK;
+        for (int i = 0; i < a->T && !rc; ++i)
+        {
+            if (a->M[i] * a->N[i] > 0)
+                rc = check_cuda(cudaMemsetAsync(a->res[i], 0, (size_t) (a->M[i] * a->N[i]) * 4, st), "cudaMemsetAsync");
+            if (!rc && a->sres[i] && a->M[i] * a->sN[rr][i] > 0)
+                rc = check_cuda(cudaMemsetAsync(a->sres[i], 0, (size_t) (a->M[i] * a->sN[rr][i]) * 4, st), "cudaMemsetAsync");
+        }
+        if (!rc && a->lvAll.p)
+            rc = check_cuda(cudaMemsetAsync(a->lvAll.p, 0, a->lvAll.bytes, st), "cudaMemsetAsync");
+        if (!rc && a->slvAll.p)
+            rc = check_cuda(cudaMemsetAsync(a->slvAll.p, 0, a->slvAll.bytes, st), "cudaMemsetAsync");
+        return rc;
+    }
     int64_t resFloats = 0, sresFloats = 0;
     const int r = a->comm->rank;
     for (int i = 0; i < a->T; ++i)

@@ -167,7 +167,7 @@ int qagg_unquantize(void* stream, const void* packed, float* out, int64_t M, int
     fill_layout(&t, M, N, bits);
     t.out = out;
     t.pk[0] = static_cast<unsigned char*>(const_cast<void*>(packed));
-    return check_cuda(launch_unquantize((cudaStream_t) stream, add != 0, bits, &t, nullptr, 1, unq_units(M, N, bits), cfg), "unquantize kernel launch");
+    return check_cuda(launch_unquantize((cudaStream_t) stream, add != 0, bits, &t, nullptr, 1, unq_units(M, N, bits), unq_smem_words(M, bits), cfg), "unquantize kernel launch");
 }
 
 int qagg_reduce_requantize(void* stream, const void* const* stripes, int K, const float* self_raw,

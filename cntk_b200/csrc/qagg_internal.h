@@ -119,9 +119,11 @@ cudaError_t launch_push(cudaStream_t st, const void* src, size_t bytes, const Si
 cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status);
 // unquantize (qagg_unquantize.cu): `single` != nullptr: one matrix described by value; otherwise `tensors` is a device table
 // of nTensors entries (all of `bits` bits) whose unit0 fields are the running sums of unq_units() (entry order = unit order)
+// smemWordsPerWarp: the largest unq_smem_words() over the matrices of the launch (0: none of them takes the row-major form)
 cudaError_t launch_unquantize(cudaStream_t st, bool add, int bits, const QTensor* single, const QTensor* tensors, int nTensors,
-                              long long totalUnits, const LaunchCfg& cfg);
+                              long long totalUnits, int smemWordsPerWarp, const LaunchCfg& cfg);
 long long unq_units(long long M, long long N, int bits); // work units of an M x N matrix in the unquantize kernel
+int unq_smem_words(long long M, int bits);               // shared-memory words per warp an M-row matrix needs there
 // header exchange kernels (qagg_kernels.cu): in[0..n) -> dst.p[*][0..n);  out[i] = src.p[0][i] + src.p[1][i] + ... in that order
 cudaError_t launch_header_push(cudaStream_t st, const double* in, int n, const HeaderPtrs& dst);
 cudaError_t launch_header_sum(cudaStream_t st, const HeaderPtrs& src, int n, double* out);

@@ -6,19 +6,25 @@
 //     ADJACENT WORDS once and, per field position k, stores the four rows 4w' + kQ .. + 3 as one aligned 16-byte vector
 //     (possible when M and Q are multiples of 4 and the output is 16-byte aligned).  Otherwise a lane takes four words
 //     32 apart and the warp stores 32 consecutive rows per position with 4-byte stores.
-//   * Work unit = 128 consecutive words of a matrix (columns laid end to end) x 8 field positions = one warp; 4 KB of
-//     output in the 1-bit case.  Warps take units u, u + (warps in the grid), ...: no shared memory, no barrier, no
-//     atomics.  A launch has ten or so units per resident warp and the grid is sized so that they divide evenly, so all
-//     CTAs end together; a launch with one CTA per group of columns did not (its last partial wave of CTAs ran on a mostly
-//     idle GPU).
+//   * Work unit = 128 consecutive words of a matrix (columns laid end to end), all field positions = one warp; 16 KB of
+//     output in the 1-bit case, every store independent of every other.  One unit per warp, eight warps per CTA: no shared
+//     memory (in this form), no barrier, no atomics; the hardware scheduler keeps the SMs full.
 //   * Units are numbered matrix after matrix, the field-position blocks of one word group next to each other:
 //     neighbouring warps write neighbouring memory.
+//   * Columns whose word count Q is not a multiple of 4 (a 9304-row column has Q = 291) cannot take the vector form above:
+//     rows w + kQ are then not 16-byte aligned for every k.  They are expanded ROW-MAJOR instead: a warp copies the column's
+//     Q packed words into its slice of shared memory (a padded layout, so that lanes reading words four apart hit distinct
+//     banks), and every lane produces four CONSECUTIVE rows -- row i is field i / Q of word i % Q -- as one aligned 16-byte
+//     store.  Work unit there = 2048 consecutive rows of one column.  With 4-byte stores this shape ran at 2.7 TB/s.
 #include "qagg_device.cuh"
+
+#include <algorithm>
+#include <cstdlib>
 
 namespace qagg {
 
 constexpr int UNQ_WORDS = 128; // packed words per unit
-constexpr int UNQ_KPU = 8;     // field positions per unit
+constexpr int UNQ_KPU = 32;    // field positions per unit: all of them (the unit table still allows a split by position blocks)
 
 // field-position blocks per word: 4 for 1 bit, 2 for 2 bits, else 1 (always a power of two)
 __host__ __device__ __forceinline__ int unq_ksplit(int bits)
@@ -27,12 +33,34 @@ __host__ __device__ __forceinline__ int unq_ksplit(int bits)
     return (vpw + UNQ_KPU - 1) / UNQ_KPU;
 }
 
+constexpr int UNQ_RM_ROWS = 2048; // row-major form: rows per unit (32 lanes x 16 vectors x 4 rows)
+constexpr int UNQ_RM_QMAX = 2048;  // row-major form: most packed words of a column (64 K rows at 1 bit)
+
+// which shapes take the row-major form (decided by the shape alone, so that host and device agree on the unit count)
+__host__ __device__ __forceinline__ bool unq_row_major(long long M, long long Q)
+{
+    return (M & 3) == 0 && (Q & 3) != 0 && Q <= UNQ_RM_QMAX;
+}
+// shared-memory words a warp needs to hold Q packed words in the padded layout
+__host__ __device__ __forceinline__ int unq_rm_words(long long Q)
+{
+    return (int) (Q + (Q >> 5) + 1);
+}
+
 long long unq_units(long long M, long long N, int bits)
 {
     if (M <= 0 || N <= 0)
         return 0;
     const long long Q = (M * bits + 31) / 32;
+    if (unq_row_major(M, Q))
+        return N * ((M + UNQ_RM_ROWS - 1) / UNQ_RM_ROWS);
     return ((N * Q + UNQ_WORDS - 1) / UNQ_WORDS) * unq_ksplit(bits);
+}
+
+int unq_smem_words(long long M, int bits)
+{
+    const long long Q = (M * bits + 31) / 32;
+    return (M > 0 && unq_row_major(M, Q)) ? unq_rm_words(Q) : 0;
 }
 
 // the two constants unquantizing needs: 1 bit -> the two level values; else -> (ufactor, quantimin)
@@ -61,182 +89,224 @@ __device__ __forceinline__ float unq_field(int bits, unsigned word, unsigned k, 
     return __fadd_rn(__fmul_rn(__fadd_rn((float) field, 0.5f), ca), cb);
 }
 
-// One unit as a lane sees it: where it writes, and the packed words and column headers it needs (fetched one unit ahead).
-struct UnqUnit
+template <bool ADD, bool TABLE, bool ONEBIT>
+__global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, const QTensor* __restrict__ tensors, int nTensors, long long totalUnits,
+                                                   int smemWords)
 {
-    float* op[4];     // destination of position 0 of each of the lane's (up to four) words; vector form: op[0] only
-    unsigned wd[4];   // the words
-    float lo[4], up[4];
-    unsigned w[4];    // word index within its column (for the end-of-column check)
-    unsigned M, Q, k0;
-    int bits;
-    unsigned live;    // bit e set: word e exists
-    bool vec;
-};
-
-template <bool TABLE>
-__device__ __forceinline__ void unq_fetch(UnqUnit& x, const QTensor& single, const QTensor* __restrict__ tensors, int nTensors, long long u, int& cur,
-                                          unsigned lane, bool onebit)
-{
-    const QTensor* Tp = &single;
-    if (TABLE)
+    extern __shared__ unsigned sWords[]; // row-major form: smemWords words per warp
+    const unsigned lane = threadIdx.x & 31;
+    unsigned* const sw = sWords + (size_t) (threadIdx.x >> 5) * (size_t) smemWords;
+    const long long gwarp = (long long) blockIdx.x * NWARPS + (threadIdx.x >> 5);
+    const long long nwarps = (long long) gridDim.x * NWARPS;
+    int cur = 0; // table entry of the previous unit: consecutive units of a warp mostly stay within one matrix
+    for (long long u = gwarp; u < totalUnits; u += nwarps)
     {
-        // last table entry whose first unit is <= u (entries without units share their successor's first unit)
-        if (!(tensors[cur].unit0 <= u && (cur + 1 >= nTensors || u < tensors[cur + 1].unit0)))
+        const QTensor* Tp = &single;
+        if (TABLE)
         {
-            int lo = 0, hi = nTensors;
-            while (hi - lo > 1)
+            // last table entry whose first unit is <= u (entries without units share their successor's first unit)
+            if (!(tensors[cur].unit0 <= u && (cur + 1 >= nTensors || u < tensors[cur + 1].unit0)))
             {
-                const int mid = (lo + hi) >> 1;
-                if (tensors[mid].unit0 <= u)
-                    lo = mid;
-                else
-                    hi = mid;
+                int lo = 0, hi = nTensors;
+                while (hi - lo > 1)
+                {
+                    const int mid = (lo + hi) >> 1;
+                    if (tensors[mid].unit0 <= u)
+                        lo = mid;
+                    else
+                        hi = mid;
+                }
+                cur = lo;
             }
-            cur = lo;
+            Tp = tensors + cur;
         }
-        Tp = tensors + cur;
-    }
-    const unsigned M = (unsigned) Tp->M;
-    const unsigned Q = (unsigned) Tp->Q;
-    x.M = M;
-    x.Q = Q;
-    x.bits = onebit ? 1 : Tp->bits;
-    const int ks = unq_ksplit(x.bits);
-    const int ksShift = (ks == 4) ? 2 : (ks == 2) ? 1 : 0;
-    const unsigned long long local = (unsigned long long) (u - (TABLE ? Tp->unit0 : 0));
-    x.k0 = (unsigned) (local & (unsigned long long) (ks - 1)) * UNQ_KPU;
-    const unsigned long long t0 = (local >> ksShift) * UNQ_WORDS; // first word of the unit, columns laid end to end
-    const unsigned long long totalWords = (unsigned long long) Tp->N * Q;
-    // column and word of the unit's first word: a 32-bit division when the matrix is small enough for that
-    unsigned col0, w0;
-    if (totalWords <= 0xffffffffull)
-    {
-        col0 = (unsigned) t0 / Q;
-        w0 = (unsigned) t0 - col0 * Q;
-    }
-    else
-    {
-        col0 = (unsigned) (t0 / Q);
-        w0 = (unsigned) (t0 - (unsigned long long) col0 * Q);
-    }
-    const unsigned left = (unsigned) ((totalWords - t0 < UNQ_WORDS) ? (totalWords - t0) : UNQ_WORDS); // words of this unit
-    float* __restrict__ outBase = Tp->out;
-    x.vec = ((M & 3u) == 0) && ((Q & 3u) == 0) && ((reinterpret_cast<uintptr_t>(outBase) & 15) == 0);
-    x.live = 0u;
-    if (x.vec)
-    {
-        // lane <-> words 4 * lane .. + 3 of the unit: the same column (Q is a multiple of 4), rows 4-aligned
-        const unsigned off = 4u * lane;
-        if (off < left)
+        const unsigned M = (unsigned) Tp->M;
+        const unsigned Q = (unsigned) Tp->Q;
+        const int bits = ONEBIT ? 1 : Tp->bits;
+        const unsigned vpw = 32u / (unsigned) bits;
+        const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
+        if (unq_row_major(M, Q))
         {
-            const unsigned tl = w0 + off;
-            const unsigned dc = tl / Q;
-            const unsigned c = col0 + dc, w = tl - dc * Q;
+            // ---- row-major form: unit = rows [r0, r0 + 1024) of one column ----
+            const unsigned blocksPerCol = (M + UNQ_RM_ROWS - 1) / UNQ_RM_ROWS;
+            const unsigned long long localU = (unsigned long long) (u - (TABLE ? Tp->unit0 : 0));
+            const unsigned c = (unsigned) (localU / blocksPerCol);
+            const unsigned r0 = (unsigned) (localU - (unsigned long long) c * blocksPerCol) * UNQ_RM_ROWS;
             const unsigned char* colp = TABLE ? packed_col(*Tp, (int) c) : single.pk[0] + (size_t) c * (size_t) single.colBytes;
-            x.lo[0] = __ldg(reinterpret_cast<const float*>(colp));
-            x.up[0] = __ldg(reinterpret_cast<const float*>(colp) + 1);
-            const unsigned* __restrict__ words = reinterpret_cast<const unsigned*>(colp + 8) + w;
+            const unsigned* __restrict__ words = reinterpret_cast<const unsigned*>(colp + 8);
+            __syncwarp(); // the previous unit's reads of the staging slice are done
+            for (unsigned w = lane; w < Q; w += 32)
+                sw[w + (w >> 5)] = __ldg(words + w);
+            float ca, cb;
+            unq_consts(bits, __ldg(reinterpret_cast<const float*>(colp)), __ldg(reinterpret_cast<const float*>(colp) + 1), ca, cb);
+            __syncwarp();
+            float* __restrict__ out = Tp->out + (size_t) c * M;
+            const bool aligned = (reinterpret_cast<uintptr_t>(Tp->out) & 15) == 0;
+            unsigned r = r0 + 4u * lane;
+            unsigned k = r / Q, w = r - k * Q;
+            const unsigned advK = 128u / Q, advW = 128u - advK * Q;
+#pragma unroll 4
+            for (int t = 0; t < UNQ_RM_ROWS / 128; ++t)
+            {
+                if (r < M)
+                {
+                    float v[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                x.wd[e] = __ldg(words + e);
-            x.w[0] = w;
-            x.op[0] = outBase + (size_t) c * M + w + (size_t) x.k0 * Q;
-            x.live = 1u;
+                    for (unsigned e = 0; e < 4; ++e)
+                    {
+                        unsigned ww = w + e, kk = k;
+                        while (ww >= Q) // the four rows straddle the end of the word array (more than once when Q < 4)
+                        {
+                            ww -= Q;
+                            ++kk;
+                        }
+                        v[e] = unq_field<ONEBIT>(bits, sw[ww + (ww >> 5)], kk, mask, ca, cb);
+                    }
+                    float* p = out + r;
+                    if (ADD)
+                    {
+                        v[0] = __fadd_rn(v[0], p[0]);
+                        v[1] = __fadd_rn(v[1], p[1]);
+                        v[2] = __fadd_rn(v[2], p[2]);
+                        v[3] = __fadd_rn(v[3], p[3]);
+                    }
+                    if (aligned)
+                    {
+                        const float4 v4 = make_float4(v[0], v[1], v[2], v[3]);
+                        if (ADD)
+                            *reinterpret_cast<float4*>(p) = v4;
+                        else
+                            __stcs(reinterpret_cast<float4*>(p), v4);
+                    }
+                    else
+                    {
+                        p[0] = v[0];
+                        p[1] = v[1];
+                        p[2] = v[2];
+                        p[3] = v[3];
+                    }
+                }
+                r += 128u;
+                w += advW;
+                k += advK;
+                if (w >= Q)
+                {
+                    w -= Q;
+                    ++k;
+                }
+            }
+            continue;
         }
-    }
-    else
-    {
-        // lane <-> words lane, lane + 32, lane + 64, lane + 96 of the unit: per position the warp stores 32 consecutive rows
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
+        const int ks = unq_ksplit(bits);
+        const int ksShift = (ks == 4) ? 2 : (ks == 2) ? 1 : 0;
+        const unsigned long long local = (unsigned long long) (u - (TABLE ? Tp->unit0 : 0));
+        const unsigned k0 = (unsigned) (local & (unsigned long long) (ks - 1)) * UNQ_KPU;
+        const unsigned long long t0 = (local >> ksShift) * UNQ_WORDS; // first word of the unit, columns laid end to end
+        const unsigned long long totalWords = (unsigned long long) Tp->N * Q;
+        // column and word of the unit's first word: a 32-bit division when the matrix is small enough for that
+        unsigned col0, w0;
+        if (totalWords <= 0xffffffffull)
         {
-            const unsigned off = lane + 32u * e;
+            col0 = (unsigned) t0 / Q;
+            w0 = (unsigned) t0 - col0 * Q;
+        }
+        else
+        {
+            col0 = (unsigned) (t0 / Q);
+            w0 = (unsigned) (t0 - (unsigned long long) col0 * Q);
+        }
+        const unsigned left = (unsigned) ((totalWords - t0 < UNQ_WORDS) ? (totalWords - t0) : UNQ_WORDS); // words of this unit
+        float* __restrict__ outBase = Tp->out;
+        const bool vec = ((M & 3u) == 0) && ((Q & 3u) == 0) && ((reinterpret_cast<uintptr_t>(outBase) & 15) == 0);
+        if (vec)
+        {
+            // lane <-> words 4 * lane .. + 3 of the unit: the same column (Q is a multiple of 4), rows 4-aligned
+            const unsigned off = 4u * lane;
             if (off < left)
             {
                 const unsigned tl = w0 + off;
                 const unsigned dc = tl / Q;
                 const unsigned c = col0 + dc, w = tl - dc * Q;
                 const unsigned char* colp = TABLE ? packed_col(*Tp, (int) c) : single.pk[0] + (size_t) c * (size_t) single.colBytes;
-                x.lo[e] = __ldg(reinterpret_cast<const float*>(colp));
-                x.up[e] = __ldg(reinterpret_cast<const float*>(colp) + 1);
-                x.wd[e] = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + w);
-                x.w[e] = w;
-                x.op[e] = outBase + (size_t) c * M + w + (size_t) x.k0 * Q;
-                x.live |= 1u << e;
-            }
-        }
-    }
-}
-
-template <bool ADD, bool ONEBIT>
-__device__ __forceinline__ void unq_emit(const UnqUnit& x)
-{
-    const int bits = ONEBIT ? 1 : x.bits;
-    const unsigned vpw = 32u / (unsigned) bits;
-    const unsigned mask = (bits >= 32) ? 0xffffffffu : ((1u << bits) - 1u);
-    const unsigned Q = x.Q, k0 = x.k0;
-    // positions of this unit that exist at all; a word's rows may end earlier (last words of a column whose height is not
-    // a multiple of Q): `full` says that they do not
-    const unsigned nk = (vpw - k0 < UNQ_KPU) ? vpw - k0 : UNQ_KPU;
-    if (x.vec)
-    {
-        if (!x.live)
-            return;
-        float ca, cb;
-        unq_consts(bits, x.lo[0], x.up[0], ca, cb);
-        const bool full = (nk == UNQ_KPU) && (x.w[0] + (k0 + UNQ_KPU - 1) * Q < x.M);
-        float* __restrict__ op = x.op[0];
-#pragma unroll
-        for (unsigned kk = 0; kk < UNQ_KPU; ++kk)
-        {
-            const unsigned k = k0 + kk;
-            if (full || (kk < nk && x.w[0] + k * Q < x.M))
-            {
-                float4 v;
-                v.x = unq_field<ONEBIT>(bits, x.wd[0], k, mask, ca, cb);
-                v.y = unq_field<ONEBIT>(bits, x.wd[1], k, mask, ca, cb);
-                v.z = unq_field<ONEBIT>(bits, x.wd[2], k, mask, ca, cb);
-                v.w = unq_field<ONEBIT>(bits, x.wd[3], k, mask, ca, cb);
-                float4* p = reinterpret_cast<float4*>(op + (size_t) kk * Q);
-                if (ADD)
-                {
-                    const float4 o = *p;
-                    v.x = __fadd_rn(v.x, o.x);
-                    v.y = __fadd_rn(v.y, o.y);
-                    v.z = __fadd_rn(v.z, o.z);
-                    v.w = __fadd_rn(v.w, o.w);
-                    *p = v;
-                }
-                else
-                {
-                    __stcs(p, v);
-                }
-            }
-        }
-    }
-    else
-    {
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-        {
-            if (x.live & (1u << e))
-            {
+                const float lower = __ldg(reinterpret_cast<const float*>(colp));
+                const float upper = __ldg(reinterpret_cast<const float*>(colp) + 1);
+                const unsigned* __restrict__ words = reinterpret_cast<const unsigned*>(colp + 8) + w;
+                const unsigned wa = __ldg(words), wb = __ldg(words + 1), wc = __ldg(words + 2), wd = __ldg(words + 3);
                 float ca, cb;
-                unq_consts(bits, x.lo[e], x.up[e], ca, cb);
-                const bool full = (nk == UNQ_KPU) && (x.w[e] + (k0 + UNQ_KPU - 1) * Q < x.M);
-                float* __restrict__ op = x.op[e];
-                const unsigned word = x.wd[e];
+                unq_consts(bits, lower, upper, ca, cb);
+                float* __restrict__ op = outBase + (size_t) c * M + w;
 #pragma unroll
                 for (unsigned kk = 0; kk < UNQ_KPU; ++kk)
                 {
                     const unsigned k = k0 + kk;
-                    if (full || (kk < nk && x.w[e] + k * Q < x.M))
+                    if (k < vpw && w + k * Q < M)
                     {
-                        float val = unq_field<ONEBIT>(bits, word, k, mask, ca, cb);
+                        float4 v;
+                        v.x = unq_field<ONEBIT>(bits, wa, k, mask, ca, cb);
+                        v.y = unq_field<ONEBIT>(bits, wb, k, mask, ca, cb);
+                        v.z = unq_field<ONEBIT>(bits, wc, k, mask, ca, cb);
+                        v.w = unq_field<ONEBIT>(bits, wd, k, mask, ca, cb);
+                        float4* p = reinterpret_cast<float4*>(op + (size_t) k * Q);
                         if (ADD)
-                            val = __fadd_rn(val, op[(size_t) kk * Q]);
-                        op[(size_t) kk * Q] = val;
+                        {
+                            const float4 o = *p;
+                            v.x = __fadd_rn(v.x, o.x);
+                            v.y = __fadd_rn(v.y, o.y);
+                            v.z = __fadd_rn(v.z, o.z);
+                            v.w = __fadd_rn(v.w, o.w);
+                            *p = v;
+                        }
+                        else
+                        {
+                            __stcs(p, v);
+                        }
+                    }
+                }
+            }
+        }
+        else
+        {
+            // lane <-> words lane, lane + 32, lane + 64, lane + 96 of the unit: per position the warp stores 32 consecutive rows
+            unsigned wd[4], cc[4], ww[4];
+            float lo[4], up[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+            {
+                const unsigned off = lane + 32u * e;
+                wd[e] = 0u;
+                cc[e] = ww[e] = 0u;
+                lo[e] = up[e] = 0.0f;
+                if (off < left)
+                {
+                    const unsigned tl = w0 + off;
+                    const unsigned dc = tl / Q;
+                    cc[e] = col0 + dc;
+                    ww[e] = tl - dc * Q;
+                    const unsigned char* colp = TABLE ? packed_col(*Tp, (int) cc[e]) : single.pk[0] + (size_t) cc[e] * (size_t) single.colBytes;
+                    lo[e] = __ldg(reinterpret_cast<const float*>(colp));
+                    up[e] = __ldg(reinterpret_cast<const float*>(colp) + 1);
+                    wd[e] = __ldg(reinterpret_cast<const unsigned*>(colp + 8) + ww[e]);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+            {
+                if (lane + 32u * e < left)
+                {
+                    float ca, cb;
+                    unq_consts(bits, lo[e], up[e], ca, cb);
+                    float* __restrict__ op = outBase + (size_t) cc[e] * M + ww[e];
+#pragma unroll
+                    for (unsigned kk = 0; kk < UNQ_KPU; ++kk)
+                    {
+                        const unsigned k = k0 + kk;
+                        if (k < vpw && ww[e] + k * Q < M)
+                        {
+                            float val = unq_field<ONEBIT>(bits, wd[e], k, mask, ca, cb);
+                            if (ADD)
+                                val = __fadd_rn(val, op[(size_t) k * Q]);
+                            op[(size_t) k * Q] = val;
+                        }
                     }
                 }
             }
@@ -244,75 +314,37 @@ __device__ __forceinline__ void unq_emit(const UnqUnit& x)
     }
 }
 
-// Warps take units u, u + warps, ...; the words and headers of a warp's next unit are fetched before it expands the
-// current one, so the (dependent) loads of one unit overlap the stores of the other.
-template <bool ADD, bool TABLE, bool ONEBIT>
-__global__ void __launch_bounds__(NT, 3) k_unquantize(const QTensor single, const QTensor* __restrict__ tensors, int nTensors, long long totalUnits)
-{
-    const unsigned lane = threadIdx.x & 31;
-    const long long gwarp = (long long) blockIdx.x * NWARPS + (threadIdx.x >> 5);
-    const long long nwarps = (long long) gridDim.x * NWARPS;
-    long long u = gwarp;
-    if (u >= totalUnits)
-        return;
-    int cur = 0; // table entry of the previous unit: consecutive units of a warp mostly stay within one matrix
-    UnqUnit xa, xb;
-    unq_fetch<TABLE>(xa, single, tensors, nTensors, u, cur, lane, ONEBIT);
-    for (;;)
-    {
-        const bool moreB = u + nwarps < totalUnits;
-        if (moreB)
-            unq_fetch<TABLE>(xb, single, tensors, nTensors, u + nwarps, cur, lane, ONEBIT);
-        unq_emit<ADD, ONEBIT>(xa);
-        if (!moreB)
-            break;
-        u += nwarps;
-        const bool moreA = u + nwarps < totalUnits;
-        if (moreA)
-            unq_fetch<TABLE>(xa, single, tensors, nTensors, u + nwarps, cur, lane, ONEBIT);
-        unq_emit<ADD, ONEBIT>(xb);
-        if (!moreA)
-            break;
-        u += nwarps;
-    }
-}
-
-// Grid: at most three CTAs per SM; among the sizes from two to three per SM, the one whose warps share the units most evenly.
-static int unq_grid(long long totalUnits, int numSMs)
+// Grid: one unit per warp, eight per CTA.  The hardware's CTA scheduler backfills the SMs as CTAs finish; a persistent grid
+// whose warps loop over units measured 10 to 15 % slower here (each warp's unit starts with a chain of dependent loads --
+// table entry, column header, words -- that a fresh CTA's eight warps issue all at once).
+static int unq_grid(long long totalUnits, int /*numSMs*/)
 {
     const long long need = (totalUnits + NWARPS - 1) / NWARPS;
-    const long long most = (long long) numSMs * 3;
-    if (need <= most)
-        return (int) need;
-    long long best = most;
-    double bestWaste = 2.0;
-    for (long long g = most; g >= (long long) numSMs * 2; --g)
-    {
-        const long long warps = g * NWARPS;
-        const long long rounds = (totalUnits + warps - 1) / warps;
-        const double waste = 1.0 - (double) totalUnits / (double) (rounds * warps);
-        if (waste < bestWaste - 1e-9)
-        {
-            bestWaste = waste;
-            best = g;
-        }
-    }
-    return (int) best;
+    return (int) std::min<long long>(need, 0x7fffffff);
 }
 
 cudaError_t launch_unquantize(cudaStream_t st, bool add, int bits, const QTensor* single, const QTensor* tensors, int nTensors, long long totalUnits,
-                              const LaunchCfg& cfg)
+                              int smemWordsPerWarp, const LaunchCfg& cfg)
 {
     if (totalUnits <= 0)
         return cudaSuccess;
+    const size_t smemBytes = (size_t) smemWordsPerWarp * NWARPS * sizeof(unsigned); // at most 8 x 2113 words = 66 KB
     const int grid = unq_grid(totalUnits, cfg.numSMs);
     static const QTensor zero = {};
     const QTensor& s = single ? *single : zero;
     const bool table = (single == nullptr);
     const bool onebit = (bits == 1);
-#define QAGG_UNQ_CASE(A, T, O)                  \
-    if (add == A && table == T && onebit == O) \
-        k_unquantize<A, T, O><<<grid, NT, 0, st>>>(s, tensors, nTensors, totalUnits);
+#define QAGG_UNQ_CASE(A, T, O)                                                                                                         \
+    if (add == A && table == T && onebit == O)                                                                                         \
+    {                                                                                                                                  \
+        if (smemBytes > 48 * 1024)                                                                                                     \
+        {                                                                                                                              \
+            const cudaError_t e = cudaFuncSetAttribute(k_unquantize<A, T, O>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smemBytes); \
+            if (e != cudaSuccess)                                                                                                      \
+                return e;                                                                                                              \
+        }                                                                                                                              \
+        k_unquantize<A, T, O><<<grid, NT, smemBytes, st>>>(s, tensors, nTensors, totalUnits, smemWordsPerWarp);                         \
+    }
     QAGG_UNQ_CASE(false, false, false)
     QAGG_UNQ_CASE(false, false, true)
     QAGG_UNQ_CASE(false, true, false)

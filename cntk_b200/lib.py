@@ -27,7 +27,8 @@ EXPORTS = [
     "qagg_hagg_destroy", "qagg_agg_set_profiling", "qagg_agg_phase_ms", "qagg_agg_destroy",
     "qagg_agg_step_header", "qagg_agg_step_group_header", "qagg_agg_header_result", "qagg_agg_create_slices", "qagg_hagg_copy_only",
     "qagg_dense_create", "qagg_dense_step", "qagg_dense_step_group", "qagg_dense_peer_handle", "qagg_dense_enable_peer", "qagg_dense_check",
-    "qagg_dense_wire_bytes", "qagg_dense_destroy",
+    "qagg_dense_wire_bytes", "qagg_dense_destroy", "qagg_agg_bind_residuals", "qagg_agg_materialize_residuals",
+    "qagg_packed_col_bytes_f64", "qagg_packed_bytes_f64", "qagg_quantize_f64", "qagg_unquantize_f64",
 ]
 
 
@@ -49,6 +50,12 @@ _lib.qagg_packed_bytes.argtypes = [c_i64, c_i64, c_int]
 _lib.qagg_stripe.argtypes = [c_i64, c_int, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64)]
 _lib.qagg_quantize.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
 _lib.qagg_unquantize.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
+_lib.qagg_packed_col_bytes_f64.restype = c_i64
+_lib.qagg_packed_col_bytes_f64.argtypes = [c_i64, c_int]
+_lib.qagg_packed_bytes_f64.restype = c_i64
+_lib.qagg_packed_bytes_f64.argtypes = [c_i64, c_i64, c_int]
+_lib.qagg_quantize_f64.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
+_lib.qagg_unquantize_f64.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
 _lib.qagg_reduce_requantize.argtypes = [c_vp, ctypes.POINTER(c_vp), c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int]
 _lib.qagg_quantize_batch_noalloc.argtypes = [c_vp, c_int, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), ctypes.POINTER(c_vp),
                                              ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, c_int]
@@ -81,6 +88,8 @@ _lib.qagg_agg_step_group_header.argtypes = [ctypes.POINTER(c_vp), c_int, ctypes.
 _lib.qagg_agg_header_result.argtypes = [c_vp, ctypes.POINTER(ctypes.c_double), c_int, c_vp]
 _lib.qagg_agg_step_host.argtypes = [c_vp, ctypes.POINTER(c_vp), c_vp]
 _lib.qagg_agg_reset_residuals.argtypes = [c_vp, c_vp]
+_lib.qagg_agg_bind_residuals.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), c_int]
+_lib.qagg_agg_materialize_residuals.argtypes = [c_vp, c_vp]
 _lib.qagg_agg_residuals.argtypes = [c_vp, c_int, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
 _lib.qagg_agg_copy_residual.argtypes = [c_vp, c_int, c_int, c_vp, c_vp]
 _lib.qagg_agg_copy_packed.argtypes = [c_vp, c_int, c_vp, c_vp]
@@ -156,6 +165,21 @@ def quantize(grad_ptr, res_in_ptr, res_out_ptr, packed_ptr, M, N, bits, zero_thr
 
 def unquantize(packed_ptr, out_ptr, M, N, bits, add=False, stream=0):
     _ok(_lib.qagg_unquantize(stream, packed_ptr, out_ptr, M, N, bits, int(bool(add))))
+
+
+def packed_bytes_f64(M, N, bits):
+    v = _lib.qagg_packed_bytes_f64(M, N, bits)
+    if v < 0:
+        _ok(int(v))
+    return int(v)
+
+
+def quantize_f64(grad_ptr, res_in_ptr, res_out_ptr, packed_ptr, M, N, bits, zero_thr=True, stream=0):
+    _ok(_lib.qagg_quantize_f64(stream, grad_ptr, res_in_ptr, res_out_ptr, packed_ptr, M, N, bits, int(bool(zero_thr))))
+
+
+def unquantize_f64(packed_ptr, out_ptr, M, N, bits, add=False, stream=0):
+    _ok(_lib.qagg_unquantize_f64(stream, packed_ptr, out_ptr, M, N, bits, int(bool(add))))
 
 
 def reduce_requantize(stripe_ptrs, self_raw_ptr, sres_in_ptr, sres_out_ptr, packed_out_ptr, M, n, bits, zero_thr=True, stream=0):
@@ -320,6 +344,14 @@ class Aggregator:
 
     def step_host(self, host_grad_ptrs, stream=0):
         _ok(_lib.qagg_agg_step_host(self.h, self._ptrs(host_grad_ptrs), stream))
+
+    def bind_residuals(self, value_ptrs, stripe_ptrs, keep_plain=False):
+        """Caller-owned residual buffers (device pointers; stripe pointer 0 where this rank owns no column)."""
+        _ok(_lib.qagg_agg_bind_residuals(self.h, self._ptrs(value_ptrs), (c_vp * len(stripe_ptrs))(*[c_vp(p) if p else c_vp(None) for p in stripe_ptrs]),
+                                         int(bool(keep_plain))))
+
+    def materialize_residuals(self, stream=0):
+        _ok(_lib.qagg_agg_materialize_residuals(self.h, stream))
 
     def reset_residuals(self, stream=0):
         _ok(_lib.qagg_agg_reset_residuals(self.h, stream))

@@ -88,6 +88,17 @@ int qagg_reduce_requantize(void* stream, const void* const* stripes, int K, cons
                            const float* sres_in, float* sres_out, void* packed_out,
                            int64_t M, int64_t n, int bits, int zero_threshold);
 
+/* The same three for ElemType = double (MatrixQuantizerImpl<double>; QWord = unsigned long long, Source/Math/ValueQuantizer.h:48-55):
+ * a packed column is `double lower; double upper; uint64 words[Q]`, Q = ceil(M*bits/64), 64 one-bit values per word, bits a
+ * power of two in 1..64 (64 = bit-cast pass-through).  Bit-identical to the reference CPU quantizer instantiated for double
+ * (what its own 1-bit end-to-end tests run, precision=double).  Buffers must be 8-byte aligned.  The striped aggregator is
+ * float only. */
+int64_t qagg_packed_col_bytes_f64(int64_t M, int bits);
+int64_t qagg_packed_bytes_f64(int64_t M, int64_t N, int bits);
+int qagg_quantize_f64(void* stream, const double* grad, const double* res_in, double* res_out, void* packed,
+                      int64_t M, int64_t N, int bits, int zero_threshold);
+int qagg_unquantize_f64(void* stream, const void* packed, double* out, int64_t M, int64_t N, int bits, int add);
+
 /* Batched qagg_quantize that allocates nothing.  It has no counterpart in the reference.
  * For callers that must not allocate device memory at call time -- a plugin whose host framework owns the rest of the
  * card, a step that cannot afford the device-wide stall of cudaMalloc, a component with a memory budget fixed at start-up.
@@ -195,6 +206,22 @@ int qagg_agg_step_host(qagg_aggregator* a, float* const* host_grads, void* strea
 /* ResetResidue on both quantizer sets (AllReduceDistGradAggregator.h:121-136; also what V2's CreateCheckpoint does,
  * Source/1BitSGD/QuantizedDataParallelDistributedLearner.h:73-91). */
 int qagg_agg_reset_residuals(qagg_aggregator* a, void* stream);
+/* Caller-owned residuals, as the V2 interface has them (valueQuantizationResidues / stripeQuantizationResidues of
+ * QuantizedDistributedCommunicator::QuantizedAggregate, Source/CNTKv2LibraryDll/API/CNTKLibrary.h:6246-6259; the reference
+ * creates them on first use, Source/1BitSGD/QuantizedDistributedCommunicator.h:246-261, and the learner owns and zeroes them,
+ * Source/1BitSGD/QuantizedDataParallelDistributedLearner.h:56-60, 73-91).  value_residuals[i] is an M[i] x N[i] device
+ * buffer, stripe_residuals[i] an M[i] x n buffer for the n columns of tensor i that this rank owns (ignored, may be NULL,
+ * where n == 0 or with one rank).  From this call on the aggregator keeps its error-feedback state in these buffers
+ * instead of its own; their CONTENT AT THE TIME OF THE CALL is taken as plain residuals.
+ *   keep_plain != 0: the buffers hold plain residuals after every step (resident-column kernels; slower).
+ *   keep_plain == 0: for 1 bit with threshold 0 the buffers hold the DEFERRED form between steps (the value that was
+ *     quantized; the column's two reconstruction values stay inside the aggregator, see qagg_agg_residuals).  Before reading
+ *     them call qagg_agg_materialize_residuals (turns them into plain residuals in place, on `stream`); after writing them
+ *     from outside (e.g. zeroing them for a checkpoint) call qagg_agg_bind_residuals again, or use
+ *     qagg_agg_reset_residuals, which zeroes bound buffers too.
+ * Synchronises the device.  No reference counterpart as a function: the reference passes the buffers on every call. */
+int qagg_agg_bind_residuals(qagg_aggregator* a, float* const* value_residuals, float* const* stripe_residuals, int keep_plain);
+int qagg_agg_materialize_residuals(qagg_aggregator* a, void* stream);
 /* Device pointers to internal state, for inspection: the M x N residual and the M x n stripe residual of tensor i
  * (stripe pointer NULL when this rank owns no column of it).  For 1 bit with threshold 0 the aggregator keeps the
  * residual in a deferred form (the quantized value plus the column's two reconstruction values; the subtraction is done

@@ -45,15 +45,17 @@ def _ptr(a):
     return a.ctypes.data_as(ctypes.c_void_p)
 
 
-def _check_f32(a, name):
-    if a.dtype != np.float32 or not a.flags["C_CONTIGUOUS"]:
-        raise ValueError(f"{name} must be C-contiguous float32")
+def _check(a, name, dtype):
+    if a.dtype != dtype or not a.flags["C_CONTIGUOUS"]:
+        raise ValueError(f"{name} must be C-contiguous {np.dtype(dtype).name}")
 
 
 class _Backend:
     prefix = None
     path = None
     kind = None
+    suffix = ""          # "_f64": the double instantiation (ElemType = double, QWord = uint64)
+    dtype = np.float32
 
     def __init__(self):
         if not os.path.exists(self.path):
@@ -62,13 +64,13 @@ class _Backend:
             raise FileNotFoundError(self.path)
         self.lib = ctypes.CDLL(self.path)
         p = self.prefix
-        self._q = getattr(self.lib, p + "quantize")
+        self._q = getattr(self.lib, p + "quantize" + self.suffix)
         self._q.restype = ctypes.c_int
         self._q.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int]
-        self._u = getattr(self.lib, p + "unquantize")
+        self._u = getattr(self.lib, p + "unquantize" + self.suffix)
         self._u.restype = ctypes.c_int
         self._u.argtypes = [ctypes.c_void_p] * 2 + [ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int]
-        self._c = getattr(self.lib, p + "packed_col_bytes")
+        self._c = getattr(self.lib, p + "packed_col_bytes" + self.suffix)
         self._c.restype = ctypes.c_int64
         self._c.argtypes = [ctypes.c_int64, ctypes.c_int]
 
@@ -79,7 +81,7 @@ class _Backend:
         """grad/res_in/res_out: (N, M) float32 (column-major M x N); packed: uint8[N*C]. In place allowed."""
         N, M = grad.shape
         for a, n in ((grad, "grad"), (res_in, "res_in"), (res_out, "res_out")):
-            _check_f32(a, n)
+            _check(a, n, self.dtype)
             assert a.shape == (N, M)
         assert packed.dtype == np.uint8 and packed.size == N * self.packed_col_bytes(M, bits)
         rc = self._q(_ptr(grad), _ptr(res_in), _ptr(res_out), _ptr(packed), M, N, bits, int(bool(zero_thr)))
@@ -88,7 +90,7 @@ class _Backend:
 
     def unquantize(self, packed, out, bits, add=False):
         N, M = out.shape
-        _check_f32(out, "out")
+        _check(out, "out", self.dtype)
         assert packed.dtype == np.uint8 and packed.size == N * self.packed_col_bytes(M, bits)
         rc = self._u(_ptr(packed), _ptr(out), M, N, bits, int(bool(add)))
         if rc != 0:
@@ -112,6 +114,16 @@ class RefBackend(_Backend):
     prefix = "ref_"
     path = os.path.join(_HERE, "_ref", "libqagg_ref.so")
     kind = "reference"
+
+
+class OracleBackendF64(OracleBackend):
+    suffix = "_f64"
+    dtype = np.float64
+
+
+class RefBackendF64(RefBackend):
+    suffix = "_f64"
+    dtype = np.float64
 
 
 def have_ref():

@@ -2,15 +2,22 @@
 // the results for tests/test_gpu_compat.py to compare with the CPU oracle.
 //   mode "quantizer": the loop of TestRunQuantization (Tests/UnitTests/MathTests/MatrixQuantizerTests.cpp:268-316):
 //       MatrixQuantizerImpl::Create, QuantizeAsync(in, residue, CPU QuantizedMatrix, residue), UnquantizeAsync(add = it > 0)
+//   mode "quantizer_f64": the same loop with MatrixQuantizerImpl<double> (64-bit packed words)
 //   mode "aggregator": AllReduceDistGradAggregator::AggregateGradients on one rank (SGD.cpp:1376), two calls
 //   mode "aggregator_async": the same with useAsyncAggregation = true (one-step-stale results, AllReduceDistGradAggregator.h:156-229)
-// usage: compat_check <mode> <in.bin> <out.bin> M N bits zeroThr iters
+//   mode "multi": one of K processes (one per GPU), tied together by a unique id passed through a file: the V1 aggregator,
+//       the V2 aggregator (synchronous and buffered asynchronous), the V2 learner and the unquantized aggregator run a
+//       real K-rank exchange, DistGradHeader included
+// usage: compat_check <mode> <in.bin> <out.bin> M N bits zeroThr iters [rank K idfile]
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <fstream>
+#include <thread>
 #include <vector>
 
 #include "../../cntk_b200/csrc/cntk_compat/AllReduceDistGradAggregator.h"
+#include "../../cntk_b200/csrc/cntk_compat/SimpleDistGradAggregator.h"
 #include "../../cntk_b200/csrc/cntk_compat/QuantizedDataParallelDistributedLearner.h"
 #include "../../cntk_b200/csrc/cntk_compat/V2AllReduceDistGradAggregator.h"
 #include "../../cntk_b200/csrc/cntk_compat/MatrixQuantizer.h"
@@ -66,6 +73,29 @@ int main(int argc, char** argv)
             try { QuantizedMatrix<float> bad(8, 8, 3, CPUDEVICE); } catch (const std::logic_error&) { threw = true; }
             if (!threw) return 6;
         }
+        else if (mode == "quantizer_f64")
+        {
+            // the same loop for ElemType = double (CPUMatrix1BitQuantizeDouble / GPUMatrix1BitQuantizeDouble); the input file holds doubles
+            std::unique_ptr<MatrixQuantizerImpl<double>> q(MatrixQuantizerImpl<double>::Create(0, false));
+            Matrix<double> inM(M, N, 0), residue(M, N, 0), out(M, N, 0);
+            std::vector<double> ind(M * N), hr(M * N), ho(M * N);
+            for (int it = 0; it < iters; ++it)
+            {
+                if (fread(ind.data(), 8, ind.size(), fi) != ind.size())
+                    return 4;
+                cudaMemcpy(inM.Data(), ind.data(), ind.size() * 8, cudaMemcpyHostToDevice);
+                QuantizedMatrix<double> packed(M, N, bits, CPUDEVICE);
+                q->QuantizeAsync(inM, residue, packed, residue, zeroThr != 0);
+                q->WaitQuantizeAsyncDone();
+                q->UnquantizeAsync(packed, out, it > 0);
+                q->WaitUnquantizeAsyncDone();
+                fwrite(packed.Buffer(), 1, packed.GetSize(), fo);
+                cudaMemcpy(hr.data(), residue.Data(), hr.size() * 8, cudaMemcpyDeviceToHost);
+                cudaMemcpy(ho.data(), out.Data(), ho.size() * 8, cudaMemcpyDeviceToHost);
+                fwrite(hr.data(), 8, hr.size(), fo);
+                fwrite(ho.data(), 8, ho.size(), fo);
+            }
+        }
         else if (mode == "aggregator")
         {
             auto mpi = std::make_shared<MPIWrapper>(std::string(), 0, 1, 0);
@@ -99,7 +129,10 @@ int main(int argc, char** argv)
             auto view = std::make_shared<Matrix<float>>(M, N, 0);
             cudaMemcpy(view->Data(), in.data(), in.size() * 4, cudaMemcpyHostToDevice);
             std::vector<::CNTK::NDArrayViewPtr> vals{view};
-            comm->QuantizedAggregateInPlace(vals, comm->Workers());
+            std::vector<::CNTK::NDArrayViewPtr> noResidues, noStripeResidues;
+            comm->QuantizedAggregateInPlace(vals, noResidues, noStripeResidues, comm->Workers());
+            if (!noResidues.empty() || !noStripeResidues.empty()) // one worker: the residual vectors come back as they went in
+                return 24;
             auto v = download(*view);
             if (memcmp(v.data(), in.data(), in.size() * 4) != 0)
                 return 9;
@@ -125,10 +158,6 @@ int main(int argc, char** argv)
                     if (x != 0.0f)
                         return 15;
                 DistGradHeader::Destroy(h2);
-                bool threwAsync = false;
-                try { V2AllReduceDistGradAggregator<float> bad(comm, true, 0, 0); } catch (const std::logic_error&) { threwAsync = true; }
-                if (!threwAsync)
-                    return 16;
             }
             // QuantizedDataParallelDistributedLearner: warm-start threshold, aggregated sample count, empty minibatch, checkpoint
             {
@@ -211,6 +240,190 @@ int main(int argc, char** argv)
             try { agg.AggregateGradients(grads, hdr, true); } catch (const std::logic_error&) { threw = true; }
             if (!threw)
                 return 11;
+            DistGradHeader::Destroy(hdr);
+        }
+        else if (mode == "multi")
+        {
+            if (argc < 12)
+                return 2;
+            const int rank = atoi(argv[9]), K = atoi(argv[10]);
+            const std::string idfile = argv[11];
+            std::string id;
+            if (rank == 0)
+            {
+                id = MPIWrapper::NewUniqueId();
+                std::ofstream(idfile + ".tmp", std::ios::binary).write(id.data(), (std::streamsize) id.size());
+                if (rename((idfile + ".tmp").c_str(), idfile.c_str()) != 0)
+                    return 30;
+            }
+            else
+            {
+                for (int tries = 0; tries < 600 && id.empty(); ++tries)
+                {
+                    std::ifstream f(idfile, std::ios::binary);
+                    if (f)
+                        id.assign((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+                    else
+                        std::this_thread::sleep_for(std::chrono::milliseconds(100));
+                }
+                if (id.size() != QAGG_UNIQUE_ID_BYTES)
+                    return 31;
+            }
+            int ndev = 0;
+            cudaGetDeviceCount(&ndev);
+            const int dev = rank % (ndev > 0 ? ndev : 1);
+            auto mpi = std::make_shared<MPIWrapper>(id, rank, K, dev);
+            // inputs: per iteration, per rank: g0 (M x N) then g1 (M x 1); every process reads the whole file
+            std::vector<std::vector<float>> mine0(iters), mine1(iters);
+            for (int it = 0; it < iters; ++it)
+                for (int r = 0; r < K; ++r)
+                {
+                    std::vector<float> a(M * N), b(M);
+                    if (fread(a.data(), 4, a.size(), fi) != a.size() || fread(b.data(), 4, b.size(), fi) != b.size())
+                        return 4;
+                    if (r == rank)
+                    {
+                        mine0[it] = a;
+                        mine1[it] = b;
+                    }
+                }
+            Matrix<float> g0(M, N, dev), g1(M, 1, dev);
+            std::vector<Matrix<float>*> grads{&g0, &g1};
+            auto load = [&](int it) {
+                cudaMemcpy(g0.Data(), mine0[it].data(), M * N * 4, cudaMemcpyHostToDevice);
+                cudaMemcpy(g1.Data(), mine1[it].data(), M * 4, cudaMemcpyHostToDevice);
+            };
+            auto dump = [&]() {
+                auto a = download(g0), b = download(g1);
+                fwrite(a.data(), 4, a.size(), fo);
+                fwrite(b.data(), 4, b.size(), fo);
+            };
+            DistGradHeader* hdr = DistGradHeader::Create(1);
+            auto fillHeader = [&](DistGradHeader* h) {
+                h->Clear();
+                h->numSamples = 7 + rank;
+                h->numSamplesWithLabel = 5 + rank;
+                h->criterion = 1.5 * (rank + 1);
+                h->evalErrors[0] = {0.25 * rank, (size_t) (3 + rank)};
+            };
+            auto headerIsSum = [&](const DistGradHeader* h) {
+                size_t ns = 0, nl = 0, ne = 0;
+                double cr = 0, ee = 0;
+                for (int r = 0; r < K; ++r)
+                {
+                    ns += 7 + r;
+                    nl += 5 + r;
+                    cr += 1.5 * (r + 1);
+                    ee += 0.25 * r;
+                    ne += 3 + r;
+                }
+                return h->numSamples == ns && h->numSamplesWithLabel == nl && h->criterion == cr && h->evalErrors[0].first == ee &&
+                       h->evalErrors[0].second == ne;
+            };
+            // A. V1 aggregator, synchronous
+            {
+                AllReduceDistGradAggregator<float> agg(mpi, bits, zeroThr != 0, true, false, 0, 0);
+                for (int it = 0; it < iters; ++it)
+                {
+                    load(it);
+                    fillHeader(hdr);
+                    if (!agg.AggregateGradients(grads, hdr, it == 0) || !headerIsSum(hdr))
+                        return 32;
+                    dump();
+                }
+                agg.WaitAll();
+            }
+            // B. V2 aggregator over the V2 communicator, synchronous; its residual views, made readable, are dumped at the end
+            auto comm = ::CNTK::QuantizedMPICommunicator(mpi, zeroThr != 0, true, (size_t) bits);
+            {
+                V2AllReduceDistGradAggregator<float> agg(comm, false, 0, 0);
+                for (int it = 0; it < iters; ++it)
+                {
+                    load(it);
+                    fillHeader(hdr);
+                    if (!agg.AggregateGradients(grads, hdr, it == 0) || !headerIsSum(hdr))
+                        return 33;
+                    dump();
+                }
+                if (agg.Residuals().size() != 2 || !agg.Residuals()[0] || agg.StripeResiduals().size() != 2)
+                    return 34;
+                static_cast<::CNTK::QuantizedMPICommunicatorImpl*>(comm.get())->MaterializeResiduals();
+                auto r0 = download(*agg.Residuals()[0]);
+                fwrite(r0.data(), 4, r0.size(), fo);
+                // resetState zeroes the residuals: the next step equals a first step
+                load(0);
+                fillHeader(hdr);
+                if (!agg.AggregateGradients(grads, hdr, true))
+                    return 35;
+                dump();
+            }
+            // C. the same, buffered asynchronous: results are one call stale, zeros after the reset
+            {
+                auto comm2 = ::CNTK::QuantizedMPICommunicator(mpi, zeroThr != 0, true, (size_t) bits);
+                V2AllReduceDistGradAggregator<float> agg(comm2, true, 0, 0);
+                for (int it = 0; it <= iters; ++it)
+                {
+                    hdr->Clear();
+                    if (it < iters)
+                    {
+                        load(it);
+                        fillHeader(hdr);
+                    }
+                    else
+                    {
+                        g0.SetValue(0);
+                        g1.SetValue(0);
+                        hdr->numSamples = 1; // keeps the pipeline going for the drain call
+                    }
+                    if (!agg.AggregateGradients(grads, hdr, it == 0))
+                        return 36;
+                    if (it == 0 ? (hdr->numSamples != 0) : !headerIsSum(hdr))
+                        return 37;
+                    dump();
+                }
+            }
+            // D. the V2 learner: aggregation from the first sample on, checkpoint zeroes the residuals
+            {
+                struct NullLearner : ::CNTK::Learner
+                {
+                    bool Update(std::vector<::CNTK::NDArrayViewPtr>&, size_t, bool) override { return true; }
+                };
+                auto comm3 = ::CNTK::QuantizedMPICommunicator(mpi, zeroThr != 0, true, (size_t) bits);
+                auto dl = ::CNTK::CreateQuantizedDataParallelDistributedLearner(comm3, std::make_shared<NullLearner>(), 0);
+                std::vector<::CNTK::NDArrayViewPtr> vals{std::make_shared<Matrix<float>>(M, N, g0.Data(), dev), std::make_shared<Matrix<float>>(M, 1, g1.Data(), dev)};
+                for (int it = 0; it < iters; ++it)
+                {
+                    load(it);
+                    ::CNTK::MinibatchInfo info;
+                    info.numberOfSamples = 4 + rank;
+                    info.trainingLossValue = 2.0 + rank;
+                    info.evalCriterionValue = 0.5;
+                    if (!dl->Update(vals, info))
+                        return 38;
+                    size_t ns = 0;
+                    double tl = 0;
+                    for (int r = 0; r < K; ++r)
+                    {
+                        ns += 4 + r;
+                        tl += 2.0 + r;
+                    }
+                    if (info.numberOfSamples != ns || info.trainingLossValue != tl || info.evalCriterionValue != 0.5 * K)
+                        return 39;
+                    dump();
+                    if (it == 0)
+                        dl->CreateCheckpoint(); // residuals zeroed: the next step starts from scratch again
+                }
+            }
+            // E. the unquantized aggregator (gradientBits = 32), all-reduce path
+            {
+                SimpleDistGradAggregator<float> agg(mpi, false, dev, 0);
+                load(0);
+                fillHeader(hdr);
+                if (!agg.AggregateGradients(grads, hdr, false) || !headerIsSum(hdr))
+                    return 40;
+                dump();
+            }
+            mpi->WaitAll();
             DistGradHeader::Destroy(hdr);
         }
         else

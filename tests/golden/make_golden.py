@@ -10,6 +10,8 @@ and writes
                         for the 2048x2048 ten-step round trip, and for small striped exchanges.
   golden_small.npz      full arrays (inputs and outputs) of the smallest cases, so a mismatch can
                         be localised without the reference.
+  golden_digests_f64.json  the unit-test grid in double precision (ElemType = double, 64-bit packed words, bits up to
+                        64): `python tests/golden/make_golden.py f64` writes this file alone.
 Inputs come from numpy's PCG64 streams keyed by the seeds below; their digests are recorded too,
 so a drift in the generator is reported as such and not as a parity failure.
 """
@@ -101,6 +103,46 @@ def run_exchange(be, K, bits, zero_thr, self_quant, keep=None):
     return digests
 
 
+# ---- ElemType = double (the reference's CPUMatrix1BitQuantizeDouble / GPUMatrix1BitQuantizeDouble grid,
+# MatrixQuantizerTests.cpp:404-472: the same ten cases, bits up to 64) --------------------------------------
+BITS_F64 = [1, 2, 4, 8, 16, 32, 64]
+
+
+def uniform_input_f64(rows, cols, low, high, seed):
+    rng = np.random.default_rng(seed)
+    return rng.uniform(low, high, size=(cols, rows))
+
+
+def run_unit_case_f64(be, rows, cols, low, high, seed, bits, zero_thr):
+    res = np.zeros((cols, rows), np.float64)
+    out = np.zeros((cols, rows), np.float64)
+    packed = np.zeros(cols * be.packed_col_bytes(rows, bits), np.uint8)
+    digests = []
+    for it in range(ITERS):
+        g = uniform_input_f64(rows, cols, low, high, seed + it)
+        be.quantize(g, res, res, packed, bits, zero_thr)
+        be.unquantize(packed, out, bits, add=(it > 0))
+        digests.append(sha(packed, res, out))
+    return digests
+
+
+def unit_digests_f64(be):
+    dig = {}
+    for (rows, cols, low, high, seed) in UNIT_CASES:
+        for bits in BITS_F64:
+            for zero_thr in ((False, True) if bits == 1 else (False,)):
+                dig[f"{rows}x{cols}_seed{seed}_b{bits}_z{int(zero_thr)}"] = run_unit_case_f64(be, rows, cols, low, high, seed, bits, zero_thr)
+    return dig
+
+
+def main_f64():
+    """golden_digests_f64.json: the unit grid in double precision, from the reference's headers."""
+    dig = unit_digests_f64(ob.RefBackendF64())
+    with open(os.path.join(HERE, "golden_digests_f64.json"), "w") as f:
+        json.dump({"unit": dig}, f, indent=1, sort_keys=True)
+    print("wrote", len(dig), "double-precision unit digests")
+
+
 def main():
     be = ob.RefBackend()
     dig = {"unit": {}, "config1": {}, "exchange": {}, "inputs": {}}
@@ -154,4 +196,8 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "f64":
+        main_f64()  # the float fixtures are left as they are
+    else:
+        main()
+        main_f64()

@@ -295,3 +295,65 @@ def test_step_with_header_sums_it_in_rank_order(G, K, peer):
             a.destroy()
         for c in comms:
             c.destroy()
+
+
+@pytest.mark.parametrize("keep_plain", [False, True])
+def test_caller_owned_residual_buffers(G, oracle_port, keep_plain):
+    """qagg_agg_bind_residuals: the error-feedback state lives in buffers the caller owns (the V2 interface's
+    valueQuantizationResidues / stripeQuantizationResidues).  Their content at bind time is taken as plain residuals; with
+    keep_plain they hold plain residuals after every step, otherwise after qagg_agg_materialize_residuals; zeroing them from
+    outside and binding again starts over."""
+    from cntk_b200 import lib
+    K, bits = 3, 1
+    shapes = [(256, 40), (100, 7), (256, 1)]
+    comms = lib.Comm.local_group(K, 0)
+    aggs = [lib.Aggregator(c, shapes, bits) for c in comms]
+    rng = np.random.default_rng(8)
+    st = ox.ExchangeState(shapes, K)
+    # start from non-zero residuals, to show that bound content is used
+    for r in range(K):
+        for i, (M, N) in enumerate(shapes):
+            st.res[r][i][...] = (rng.standard_normal((N, M)) * 1e-4).astype(np.float32)
+            st.sres[r][i][...] = (rng.standard_normal(st.sres[r][i].shape) * 1e-4).astype(np.float32)
+    vres = [[torch.from_numpy(st.res[r][i].copy()).to(G.DEV) for i in range(len(shapes))] for r in range(K)]
+    sres = [[torch.from_numpy(st.sres[r][i].copy()).to(G.DEV) if st.sres[r][i].size else None for i in range(len(shapes))] for r in range(K)]
+
+    def bind():
+        for r in range(K):
+            aggs[r].bind_residuals([t.data_ptr() for t in vres[r]], [t.data_ptr() if t is not None else 0 for t in sres[r]], keep_plain)
+
+    def compare(what):
+        for r in range(K):
+            if not keep_plain:
+                aggs[r].materialize_residuals()
+            torch.cuda.synchronize()
+            for i in range(len(shapes)):
+                G.assert_same_bits(G.host(vres[r][i]), st.res[r][i], f"{what}: rank {r} tensor {i} residual buffer")
+                if sres[r][i] is not None:
+                    G.assert_same_bits(G.host(sres[r][i]), st.sres[r][i], f"{what}: rank {r} tensor {i} stripe residual buffer")
+
+    try:
+        bind()
+        for step in range(4):
+            grads = [[(rng.standard_normal((N, M)) * 1e-3).astype(np.float32) for (M, N) in shapes] for _ in range(K)]
+            dg = [[torch.from_numpy(a).to(G.DEV) for a in grads[r]] for r in range(K)]
+            ox.aggregate_step(oracle_port, st, grads, bits)
+            lib.step_group(aggs, [[t.data_ptr() for t in dg[r]] for r in range(K)])
+            torch.cuda.synchronize()
+            for r in range(K):
+                for i in range(len(shapes)):
+                    G.assert_same_bits(G.host(dg[r][i]), grads[r][i], f"step {step} rank {r} tensor {i} aggregate")
+            if step in (1, 3):
+                compare(f"step {step}")
+            if step == 1:
+                # the caller zeroes its buffers (a checkpoint) and tells the aggregator by binding them again
+                for r in range(K):
+                    for t in vres[r] + [x for x in sres[r] if x is not None]:
+                        t.zero_()
+                st.reset()
+                bind()
+    finally:
+        for a in aggs:
+            a.destroy()
+        for c in comms:
+            c.destroy()

@@ -26,7 +26,7 @@ def exe(tmp_path_factory):
     libdir = os.path.join(ROOT, "cntk_b200")
     cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     cmd = ["g++", "-std=c++17", "-O1", f"-I{cuda}/include", os.path.join(ROOT, "tests", "cpp", "compat_check.cpp"), "-o", out,
-           "-L", libdir, "-l:libqagg.so", f"-L{cuda}/lib64", "-lcudart", f"-Wl,-rpath,{libdir}", f"-Wl,-rpath,{cuda}/lib64"]
+           "-L", libdir, "-l:libqagg.so", f"-L{cuda}/lib64", "-lcudart", "-lpthread", f"-Wl,-rpath,{libdir}", f"-Wl,-rpath,{cuda}/lib64"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     assert res.returncode == 0, res.stderr
     return out

@@ -229,3 +229,69 @@ def test_column_subset_replay_equals_full_exchange(oracle_port, K):
                     if K > 1:
                         np.testing.assert_array_equal(sres.view(np.uint32), st.sres[owner][i].view(np.uint32))
                     np.testing.assert_array_equal(pk, packed[0][i][s * C:(s + n) * C])
+
+
+# ---- ElemType = double --------------------------------------------------------------------------------------------
+
+@pytest.fixture(scope="module")
+def oracle_port_f64():
+    from oracle import backend
+    backend.build()
+    return backend.OracleBackendF64()
+
+
+def test_double_port_reproduces_reference_unit_grid(oracle_port_f64):
+    """The C port's double instantiation against digests made by the reference's own headers with ElemType = double
+    (tests/golden/golden_digests_f64.json): ten shape/range cases x bits {1..64} x both 1-bit modes x 5 iterations."""
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_digests_f64.json")) as f:
+        want = json.load(f)["unit"]
+    got = mg.unit_digests_f64(oracle_port_f64)
+    assert got.keys() == want.keys()
+    for k in want:
+        assert got[k] == want[k], k
+
+
+def test_double_layout(oracle_port_f64):
+    # QuantizedColumn<double>::QuantizedColumnSize: two doubles + 64-bit words (Source/Math/QuantizedMatrix.h:42-47)
+    assert oracle_port_f64.packed_col_bytes(70, 1) == 16 + 8 * 2
+    assert oracle_port_f64.packed_col_bytes(2048, 1) == 16 + 8 * 32
+    assert oracle_port_f64.packed_col_bytes(64, 4) == 16 + 8 * 4
+    assert oracle_port_f64.packed_col_bytes(10, 64) == 16 + 8 * 10
+    # an all-zero column: range collapses, every real row's bit is 1, padding bits stay 0; word w holds rows w, w + Q, ...
+    g = np.zeros((1, 70), np.float64)
+    r = np.zeros((1, 70), np.float64)
+    p = np.zeros(oracle_port_f64.packed_col_bytes(70, 1), np.uint8)
+    oracle_port_f64.quantize(g, r, r, p, 1, True)
+    lo, hi = struct.unpack("<dd", p[:16].tobytes())
+    assert lo == 0.0 and hi == 0.0
+    assert list(np.frombuffer(p[16:].tobytes(), dtype="<u8")) == [(1 << 35) - 1, (1 << 35) - 1]
+    assert not r.any()
+
+
+def test_double_port_equals_reference_build_directly(oracle_port_f64):
+    from oracle import backend
+    if not backend.have_ref():
+        pytest.skip("oracle/_ref/libqagg_ref.so not present")
+    ref = backend.RefBackendF64()
+    rng = np.random.default_rng(9)
+    for trial in range(30):
+        M = int(rng.integers(1, 300))
+        N = int(rng.integers(1, 12))
+        bits = int(rng.choice([1, 2, 4, 8, 16, 32, 64]))
+        zero_thr = bool(rng.integers(0, 2))
+        scale = float(10.0 ** rng.integers(-6, 2))
+        ra = np.zeros((N, M), np.float64)
+        rb = np.zeros((N, M), np.float64)
+        for it in range(3):
+            g = rng.standard_normal((N, M)) * scale
+            pa = np.zeros(N * oracle_port_f64.packed_col_bytes(M, bits), np.uint8)
+            pb = np.zeros_like(pa)
+            oracle_port_f64.quantize(g, ra, ra, pa, bits, zero_thr)
+            ref.quantize(g, rb, rb, pb, bits, zero_thr)
+            np.testing.assert_array_equal(pa, pb)
+            np.testing.assert_array_equal(ra.view(np.uint64), rb.view(np.uint64))
+            oa = np.full((N, M), 0.25)
+            ob_ = np.full((N, M), 0.25)
+            oracle_port_f64.unquantize(pa, oa, bits, add=bool(it % 2))
+            ref.unquantize(pb, ob_, bits, add=bool(it % 2))
+            np.testing.assert_array_equal(oa.view(np.uint64), ob_.view(np.uint64))
