@@ -16,6 +16,10 @@ process with a non-zero status; the line carries "parity": {"checked": true, ...
 
 --impl reference times the reference's own CPU quantizer (its headers compiled in place, oracle/_ref; else the C port)
 driving the restated exchange with one thread per simulated rank on this box's host cores, and prints the same line shape.
+--local-ranks K (one GPU) steps K simulated ranks as an in-process group and prints each rank's kernel times per phase: the way
+to look at the owner's reduce-requantize kernels, which a single rank never runs, on one device and under a profiler.  Its
+line is a kernel-time table, not a bench value.  --fused-update adds the learner step (momentum SGD) fused into the last
+kernel beside the unfused sequence.
 --workload sweep runs BASELINE config 5 (1024 rows x 1 Mi .. 1 Gi values; 1, 2 and 32 bits) and reports a table in "sweep".
 """
 import argparse
@@ -536,6 +540,106 @@ def run_sweep(args):
     R.close()
 
 
+def run_local_group(args):
+    """K simulated ranks on ONE GPU (qagg_comm_create_local_group): every rank's quantize / reduce-requantize / unquantize
+    kernel time from the aggregator's phase events, mean over the timed steps.  The ranks run one after the other on one
+    device, so the step time of the group is meaningless; the per-rank kernel times are what a rank would spend."""
+    import torch
+    from cntk_b200 import lib, workloads
+    K = args.local_ranks
+    shapes, bits = get_shapes(args.workload)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    comms = lib.Comm.local_group(K, 0)
+    aggs = [lib.Aggregator(c, shapes, bits) for c in comms]
+    if K > 1 and args.exchange == "p2p":
+        hs = [a.peer_handle() for a in aggs]
+        for a in aggs:
+            a.enable_peer(hs)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234)
+    pool = [torch.randn((n, m), generator=gen, device=dev, dtype=torch.float32) * 1e-3 for (m, n) in shapes]  # shared by the ranks
+    grads = [[torch.empty_like(t) for t in pool] for _ in range(K)]
+    ptrs = [[t.data_ptr() for t in grads[r]] for r in range(K)]
+
+    def refresh():
+        for r in range(K):
+            for g, p_ in zip(grads[r], pool):
+                g.copy_(p_)
+
+    def timed(steps):
+        for a in aggs:
+            a.set_profiling(True)
+        for _ in range(steps):
+            refresh()
+            lib.step_group(aggs, ptrs)
+        torch.cuda.synchronize()
+        ph = [a.phase_ms() for a in aggs]
+        for a in aggs:
+            a.set_profiling(False)
+        return ph
+
+    for _ in range(args.warmup):
+        refresh()
+        lib.step_group(aggs, ptrs)
+    torch.cuda.synchronize()
+    ph = timed(args.steps)
+    V = workloads.total_values(shapes)
+    P = workloads.packed_bytes(shapes, bits)
+    peak, peak_kind = load_peaks()
+    us = lambda k: [round(p_[k] * 1e3, 1) for p_ in ph]
+    k1, k2, k3 = us(0), us(2), us(4)
+    out = {"mode": "local_group", "note": "kernel times of K simulated ranks on one GPU; not a bench value", "simulated_ranks": K,
+           "workload": args.workload, "bits": bits, "steps": args.steps, "warmup": args.warmup,
+           "quantize_us": k1, "reduce_requantize_us": k2, "unquantize_us": k3,
+           "roofline_frac_of_" + peak_kind: {
+               "quantize": round((12 * V + P) / (max(k1) * 1e-6) / (peak * 1e9), 3),
+               "reduce_requantize": round((8 * V / K + P * (1 + 1.0 / K)) / (max(k2) * 1e-6) / (peak * 1e9), 3) if K > 1 else None,
+               "unquantize": round((4 * V + P) / (max(k3) * 1e-6) / (peak * 1e9), 3)}}
+    if args.fused_update:
+        w = [[torch.randn_like(t) for t in pool] for _ in range(K)]
+        sm = [[torch.zeros_like(t) for t in pool] for _ in range(K)]
+        for r in range(K):
+            aggs[r].bind_update([t.data_ptr() for t in w[r]], [t.data_ptr() for t in sm[r]])
+        lr, mom, ug = 0.05, 0.9, 0.1
+
+        def rank_update_ms(fused):
+            # one rank's unquantize kernel (+ its separate update launches when not fused), from events around them
+            for a in aggs:
+                a.set_update(fused, lr, mom, ug)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            tot = 0.0
+            for it in range(args.warmup + args.steps):
+                refresh()
+                lib.step_group(aggs, ptrs)
+                e0.record()
+                if not fused:
+                    for i, (m, n) in enumerate(shapes):
+                        lib.sgd_update(w[0][i].data_ptr(), grads[0][i].data_ptr(), sm[0][i].data_ptr(), m * n, lr, mom, ug)
+                e1.record()
+                torch.cuda.synchronize()
+                if it >= args.warmup:
+                    tot += e0.elapsed_time(e1)
+            return tot / args.steps
+
+        unf = rank_update_ms(False)
+        k3_plain = max(k3) * 1e-3
+        rank_update_ms(True)  # switches the fused step on (and warms it up)
+        ph_f = timed(args.steps)
+        k3_fused = max(p_[4] for p_ in ph_f)
+        out["consumer_fusion"] = {"rule": "momentum SGD (Matrix::MomentumSGDUpdate)", "unfused_ms": round(k3_plain + unf, 4),
+                                  "unfused_parts_ms": {"unquantize": round(k3_plain, 4), "update_kernels": round(unf, 4)},
+                                  "fused_ms": round(k3_fused, 4),
+                                  "bytes_unfused": 24 * V + P, "bytes_fused": 16 * V + P,
+                                  "fused_frac_of_" + peak_kind: round((16 * V + P) / (k3_fused * 1e-3) / (peak * 1e9), 3)}
+    for a in aggs:
+        a.check()
+        a.destroy()
+    for c in comms:
+        c.destroy()
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -548,10 +652,14 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=6, help="column chunks pipelined by the host-buffer entry point")
     ap.add_argument("--sweep-max-k", type=int, default=5, help="largest matrix of the sweep: 1024 x 1024 * 4^k values")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"], help="multi-GPU transport of the packed stripes")
+    ap.add_argument("--local-ranks", type=int, default=0, help="one GPU: kernel times of this many simulated ranks (not a bench value)")
+    ap.add_argument("--fused-update", action="store_true", help="with --local-ranks: time the learner step fused into the last kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.local_ranks > 0:
+        run_local_group(args)
     elif args.workload == "sweep":
         run_sweep(args)
     else:

@@ -41,6 +41,19 @@ public:
 };
 typedef std::shared_ptr<Learner> LearnerPtr;
 
+// A learner whose update the quantized exchange can apply itself (no reference counterpart: the reference always writes the
+// aggregated gradients and then calls Update).  The rule must be a function of the aggregated sample count alone, which the
+// distributed learner knows before the gradients are exchanged (the header is summed first, :40-50 of the reference file).
+class FusableLearner
+{
+public:
+    virtual ~FusableLearner() {}
+    virtual void UpdateRuleFor(size_t trainingSampleCount, float& learningRate, float& momentum, float& unitGainFactor) const = 0;
+    virtual const std::vector<NDArrayViewPtr>& Parameters() const = 0;
+    virtual const std::vector<NDArrayViewPtr>& SmoothedGradients() const = 0;
+    virtual void NoteUpdate(size_t trainingSampleCount) = 0; // the bookkeeping Update would have done
+};
+
 class QuantizedDataParallelDistributedLearner
 {
 public:
@@ -65,6 +78,20 @@ public:
             info.evalCriterionValue = header[0];
             info.trainingLossValue = header[1];
             info.numberOfSamples = (size_t) header[2];
+            // consumer fusion: with the aggregated sample count known, the exchange's last kernel can take the learner's step
+            // itself; the gradient views then keep the local gradients
+            auto* fusable = m_fuseUpdate ? dynamic_cast<FusableLearner*>(m_learner.get()) : nullptr;
+            auto* impl = dynamic_cast<QuantizedMPICommunicatorImpl*>(m_communicator.get());
+            if (fusable && impl && !info.IsEmpty() && m_communicator->Workers().size() > 1)
+            {
+                float lr, momentum, unitGainFactor;
+                fusable->UpdateRuleFor(info.numberOfSamples, lr, momentum, unitGainFactor);
+                impl->FuseUpdateIntoNextAggregate(fusable->Parameters(), fusable->SmoothedGradients(), lr, momentum, unitGainFactor);
+                m_communicator->QuantizedAggregateInPlace(gradientValues, m_residuals, m_stripeResiduals, m_communicator->Workers());
+                fusable->NoteUpdate(info.numberOfSamples);
+                m_sampleCount += info.numberOfSamples;
+                return true;
+            }
             m_communicator->QuantizedAggregateInPlace(gradientValues, m_residuals, m_stripeResiduals, m_communicator->Workers());
         }
         m_sampleCount += info.numberOfSamples;
@@ -87,6 +114,10 @@ public:
     }
     void RestoreFromCheckpoint(size_t totalNumberOfSamplesSeen) { m_sampleCount = totalNumberOfSamplesSeen; }
 
+    // Lets the exchange apply the local learner's step when that learner is a FusableLearner (off by default: the
+    // reference's behaviour -- aggregated gradients written, then Update -- is the default).
+    void SetConsumerFusion(bool on) { m_fuseUpdate = on; }
+
     size_t TotalNumberOfSamplesSeen() const { return m_sampleCount; }
     // the residual views the learner holds (for inspection; call MaterializeResiduals() on the communicator before reading)
     const std::vector<NDArrayViewPtr>& Residuals() const { return m_residuals; }
@@ -98,6 +129,7 @@ private:
     LearnerPtr m_learner;
     size_t m_distributeAfterSamples;
     size_t m_sampleCount = 0;
+    bool m_fuseUpdate = false;
     // residuals of quantized gradients and of the aggregated stripes this worker owns
     std::vector<NDArrayViewPtr> m_residuals;
     std::vector<NDArrayViewPtr> m_stripeResiduals;

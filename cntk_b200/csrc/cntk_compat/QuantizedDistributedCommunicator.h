@@ -231,6 +231,34 @@ public:
         }
         for (size_t i = 0; i < n; ++i)
             m_ptrs[i] = aggregatedOutputs[i]->Data();
+        // a fused learner step, armed for this call only
+        if (m_fuse.armed)
+        {
+            m_fuse.armed = false;
+            if (m_fuse.params.size() != n || m_fuse.smoothed.size() != n)
+                LogicError("QuantizedAggregate: one parameter and one smoothed-gradient view per value is expected");
+            std::vector<float*> pp(n), ss(n);
+            for (size_t i = 0; i < n; ++i)
+            {
+                if (m_fuse.params[i]->GetNumRows() != inValues[i]->GetNumRows() || m_fuse.params[i]->GetNumCols() != inValues[i]->GetNumCols() ||
+                    m_fuse.smoothed[i]->GetNumElements() != inValues[i]->GetNumElements())
+                    LogicError("QuantizedAggregate: a parameter view has a different shape than its gradient");
+                pp[i] = m_fuse.params[i]->Data();
+                ss[i] = m_fuse.smoothed[i]->Data();
+            }
+            if (pp != m_boundParams || ss != m_boundSmoothed)
+            {
+                QaggCheck(qagg_agg_bind_update(m_agg, pp.data(), ss.data()), "qagg_agg_bind_update");
+                m_boundParams = pp;
+                m_boundSmoothed = ss;
+            }
+            // the parameters were last written on the calling thread's stream: inputsReady already orders this step after that
+            QaggCheck(qagg_agg_set_update(m_agg, 1, m_fuse.lr, m_fuse.momentum, m_fuse.unitGain), "qagg_agg_set_update");
+        }
+        else if (!m_boundParams.empty())
+        {
+            QaggCheck(qagg_agg_set_update(m_agg, 0, 0.0f, 0.0f, 1.0f), "qagg_agg_set_update");
+        }
         QaggCheck(qagg_agg_step(m_agg, m_ptrs.data(), m_stream), "QuantizedAggregate");
         if (cudaStreamSynchronize(m_stream) != cudaSuccess)
             RuntimeError("QuantizedAggregate: the aggregation step failed on the device");
@@ -247,6 +275,20 @@ public:
     {
         CheckWorkers(sendToWorkers);
         Microsoft::MSR::CNTK::QaggCheck(qagg_comm_allreduce_f64(m_mpi->Handle(), hostValues.data(), (int) hostValues.size(), nullptr), "AggregateInPlace");
+    }
+
+    // Arms the NEXT QuantizedAggregate / QuantizedAggregateInPlace call (more than one worker) to end in the momentum-SGD
+    // update of `parameters` and `smoothedGradients` (one view per value, same shapes) instead of writing the aggregated
+    // gradients: see qagg_agg_set_update.  No reference counterpart.
+    void FuseUpdateIntoNextAggregate(const std::vector<NDArrayViewPtr>& parameters, const std::vector<NDArrayViewPtr>& smoothedGradients,
+                                     float learningRate, float momentum, float unitGainFactor)
+    {
+        m_fuse.params = parameters;
+        m_fuse.smoothed = smoothedGradients;
+        m_fuse.lr = learningRate;
+        m_fuse.momentum = momentum;
+        m_fuse.unitGain = unitGainFactor;
+        m_fuse.armed = true;
     }
 
     // turns every bound residual view into plain residuals (what a caller must do before reading them)
@@ -299,6 +341,13 @@ private:
     std::unordered_set<DistributedWorkerDescriptor> m_workers;
     DistributedWorkerDescriptor m_me;
     qagg_aggregator* m_agg = nullptr;
+    struct
+    {
+        bool armed = false;
+        std::vector<NDArrayViewPtr> params, smoothed;
+        float lr = 0.0f, momentum = 0.0f, unitGain = 1.0f;
+    } m_fuse;
+    std::vector<float*> m_boundParams, m_boundSmoothed;
     std::vector<int64_t> m_rows, m_cols;
     std::vector<float*> m_ptrs, m_boundValue, m_boundStripe;
     bool m_boundPlain = false;

@@ -182,6 +182,11 @@ struct qagg_aggregator
     int k3SmemWords = 0;   // shared-memory words per warp the unquantize launch needs
     QTensor *dK1 = nullptr, *dK2 = nullptr, *dK3 = nullptr;
     QItem *dI1 = nullptr, *dI2 = nullptr;
+    // consumer fusion: a copy of the unquantize table whose destinations are the caller's parameter and smoothed-gradient
+    // matrices, and the rule the unquantize launch applies when `updating`
+    DevBuf updTable;
+    bool updBound = false, updating = false;
+    UpdateRule updRule = {};
     DevBuf queue; // three pairs of work-queue counters (one pair per kernel), zero when no kernel is running
     std::vector<int> k2Tensor; // tensor index of each K2 table entry
     // The device tables (and tensor maps) hold the gradient pointers.  Two sets are kept, each bound to one array of
@@ -585,7 +590,55 @@ int wait_peers(qagg_aggregator* a, bool gatherPhase, cudaStream_t st)
 }
 int launch_k3(qagg_aggregator* a, cudaStream_t st)
 {
-    return check_cuda(launch_unquantize(st, false, a->bits, nullptr, a->dK3, (int) a->hK3.size(), a->k3Units, a->k3SmemWords, a->cfg), "unquantize launch");
+    if (a->updating)
+        return check_cuda(launch_unquantize(st, UNQ_UPDATE, a->bits, nullptr, static_cast<const QTensor*>(a->updTable.p), (int) a->hK3.size(), a->k3Units,
+                                            a->k3SmemWords, a->cfg, &a->updRule), "unquantize-update launch");
+    return check_cuda(launch_unquantize(st, UNQ_STORE, a->bits, nullptr, a->dK3, (int) a->hK3.size(), a->k3Units, a->k3SmemWords, a->cfg), "unquantize launch");
+}
+
+// Creation-time handshake (process groups only): every rank must describe the same exchange -- tensor count, shapes, column
+// slices, bit width, flags -- or the stripes one rank sends would not be what its peers expect, which no later check would
+// catch.  Each rank hashes its description (FNV-1a), cuts the hash into four 16-bit pieces p and all-reduces (p, p * p):
+// the pieces agree on all K ranks exactly when K * sum(p^2) == (sum p)^2, every quantity exact in a double.  All ranks see
+// the same sums, so all of them fail together.  The reference has no such check (a mismatch there shows as an MPI
+// truncation error or a hang); its nearest relative is the dimension check of ResetState
+// (Source/1BitSGD/AllReduceDistGradAggregator.h:69-71).
+int handshake(qagg_comm* comm, int T, const int64_t* M, const int64_t* N, const int64_t* wholeN, const int64_t* firstCol, int bits, int flags)
+{
+    if (comm->K == 1 || comm->local)
+        return QAGG_OK;
+    unsigned long long h = 1469598103934665603ull;
+    auto mix = [&h](long long v) {
+        for (int b = 0; b < 8; ++b)
+        {
+            h ^= (unsigned long long) ((v >> (8 * b)) & 0xff);
+            h *= 1099511628211ull;
+        }
+    };
+    mix(T);
+    mix(bits);
+    mix(flags);
+    mix(comm->K);
+    for (int i = 0; i < T; ++i)
+    {
+        mix(M[i]);
+        mix(N[i]);
+        mix(wholeN ? wholeN[i] : N[i]);
+        mix(firstCol ? firstCol[i] : 0);
+    }
+    double v[8];
+    for (int j = 0; j < 4; ++j)
+    {
+        v[j] = (double) ((h >> (16 * j)) & 0xffffull);
+        v[4 + j] = v[j] * v[j];
+    }
+    int rc = qagg_comm_allreduce_f64(comm, v, 8, nullptr);
+    if (rc)
+        return rc;
+    for (int j = 0; j < 4; ++j)
+        if ((double) comm->K * v[4 + j] != v[j] * v[j])
+            return fail(QAGG_ESTATE, "qagg_agg_create: the ranks do not describe the same exchange (tensor count, shapes, slices, bits or flags differ)");
+    return QAGG_OK;
 }
 
 } // namespace
@@ -786,6 +839,8 @@ int qagg_agg_create_slices(qagg_comm* comm, int num_tensors, const int64_t* M, c
             return fail(QAGG_EINVAL, "qagg_agg_create: bad tensor shape");
     int rc = check_cuda(cudaSetDevice(comm->device), "cudaSetDevice");
     if (rc)
+        return rc;
+    if ((rc = handshake(comm, num_tensors, M, N, whole_N, first_col, bits, flags)))
         return rc;
     std::unique_ptr<qagg_aggregator> a(new qagg_aggregator);
     a->comm = comm;
@@ -1325,6 +1380,15 @@ int qagg_agg_check(qagg_aggregator* a, void* stream)
         return fail(QAGG_ETIMEOUT, "a device-side wait for a peer's flag ran out: a peer did not reach the step (results of that step are invalid)");
     if (st & 2u)
         return fail(QAGG_ETIMEOUT, "a device-side wait for a copy into shared memory ran out (results of that step are invalid)");
+    // an asynchronous NCCL error (a peer process died, a link went down) does not show in a launch's return value
+    if (a->comm->nccl)
+    {
+        ncclResult_t asyncErr = ncclSuccess;
+        if ((rc = check_nccl(ncclCommGetAsyncError(a->comm->nccl, &asyncErr), "ncclCommGetAsyncError")))
+            return rc;
+        if (asyncErr != ncclSuccess && asyncErr != ncclInProgress)
+            return check_nccl(asyncErr, "asynchronous NCCL error");
+    }
     return QAGG_OK;
 }
 
@@ -1618,6 +1682,61 @@ int qagg_hagg_check(qagg_host_aggregator* h)
 int qagg_hagg_destroy(qagg_host_aggregator* h)
 {
     delete h;
+    return QAGG_OK;
+}
+
+int qagg_agg_bind_update(qagg_aggregator* a, float* const* params, float* const* smoothed)
+{
+    if (!a)
+        return fail(QAGG_EINVAL, "qagg_agg_bind_update: null aggregator");
+    int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    if (!params && !smoothed)
+    {
+        a->updBound = a->updating = false;
+        return QAGG_OK;
+    }
+    if (!params || !smoothed)
+        return fail(QAGG_EINVAL, "qagg_agg_bind_update: parameters and smoothed gradients come together");
+    if (a->identity)
+        return fail(QAGG_ESTATE, "qagg_agg_bind_update: this aggregator leaves the gradients as they are (one worker, identity semantics)");
+    std::vector<QTensor> tab(a->hK3);
+    for (int i = 0; i < a->T; ++i)
+    {
+        if (a->M[i] * a->N[i] > 0 && (!params[i] || !smoothed[i]))
+            return fail(QAGG_EINVAL, "qagg_agg_bind_update: null matrix pointer");
+        if (((uintptr_t) params[i] | (uintptr_t) smoothed[i]) & 3)
+            return fail(QAGG_EINVAL, "qagg_agg_bind_update: matrices must be 4-byte aligned");
+        tab[i].out = params[i];
+        tab[i].res_out = smoothed[i];
+    }
+    // an earlier step may still be reading the table
+    if ((rc = check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize")))
+        return rc;
+    if (!a->updTable.p && (rc = a->updTable.alloc(tab.size() * sizeof(QTensor), false)))
+        return rc;
+    if (!tab.empty() && (rc = check_cuda(cudaMemcpy(a->updTable.p, tab.data(), tab.size() * sizeof(QTensor), cudaMemcpyHostToDevice), "table upload")))
+        return rc;
+    a->updBound = true;
+    return QAGG_OK;
+}
+
+int qagg_agg_set_update(qagg_aggregator* a, int enabled, float learn_rate_per_sample, float momentum, float unit_gain_factor)
+{
+    if (!a)
+        return fail(QAGG_EINVAL, "qagg_agg_set_update: null aggregator");
+    if (!enabled)
+    {
+        a->updating = false;
+        return QAGG_OK;
+    }
+    if (!a->updBound)
+        return fail(QAGG_ESTATE, "qagg_agg_set_update: no parameter matrices bound (qagg_agg_bind_update)");
+    if (!(momentum >= 0.0f && momentum <= 1.0f))
+        return fail(QAGG_EINVAL, "qagg_agg_set_update: momentum must lie in [0, 1]");
+    a->updRule = make_update_rule(learn_rate_per_sample, momentum, unit_gain_factor);
+    a->updating = true;
     return QAGG_OK;
 }
 

@@ -47,7 +47,7 @@ void fill_layout(QTensor* t, long long M, long long N, int bits)
 }
 
 // per-device launch configuration, looked up once
-static int launch_cfg_for_current_device(LaunchCfg* cfg)
+int launch_cfg_for_current_device(LaunchCfg* cfg)
 {
     static std::mutex mu;
     static LaunchCfg cache[64];
@@ -70,7 +70,7 @@ static int launch_cfg_for_current_device(LaunchCfg* cfg)
     return QAGG_OK;
 }
 
-static int check_dims(int64_t M, int64_t N, int bits)
+int check_dims(long long M, long long N, int bits)
 {
     if (!bits_ok(bits))
         return fail(QAGG_EINVAL, "bits must be a power of two in 1..32");
@@ -167,7 +167,7 @@ int qagg_unquantize(void* stream, const void* packed, float* out, int64_t M, int
     fill_layout(&t, M, N, bits);
     t.out = out;
     t.pk[0] = static_cast<unsigned char*>(const_cast<void*>(packed));
-    return check_cuda(launch_unquantize((cudaStream_t) stream, add != 0, bits, &t, nullptr, 1, unq_units(M, N, bits), unq_smem_words(M, bits), cfg), "unquantize kernel launch");
+    return check_cuda(launch_unquantize((cudaStream_t) stream, add != 0 ? UNQ_ADD : UNQ_STORE, bits, &t, nullptr, 1, unq_units(M, N, bits), unq_smem_words(M, bits), cfg), "unquantize kernel launch");
 }
 
 int qagg_reduce_requantize(void* stream, const void* const* stripes, int K, const float* self_raw,

@@ -64,6 +64,20 @@ __device__ __forceinline__ void levels_1bit(float lower, float upper, float& val
     val1 = __fadd_rn(__fmul_rn(1.5f, ufactor), lower);
 }
 
+// one element of the momentum-SGD update (see UpdateRule): returns the new parameter, rewrites the smoothed gradient
+__device__ __forceinline__ float sgd_apply(const UpdateRule& r, float g, float& smoothed, float param)
+{
+    float s;
+    if (r.kind == 0)
+        s = __fmaf_rn(r.a, g, smoothed);
+    else if (r.kind == 1)
+        s = __fmul_rn(r.a, g);
+    else
+        s = __fmul_rn(r.beta, __fmaf_rn(r.a, g, smoothed));
+    smoothed = s;
+    return __fsub_rn(param, s);
+}
+
 __device__ __forceinline__ unsigned quantize_multibit(const ValQ& q, int bits, float v)
 {
     if (bits == 32)

@@ -49,6 +49,30 @@ struct QTensor
     unsigned* stats; // owner kernels only: two words per column (rows with a set bit, NaN seen), zero between steps
 };
 
+// What the unquantize kernel does with a value it has expanded.
+constexpr int UNQ_STORE = 0;  // out = value
+constexpr int UNQ_ADD = 1;    // out += value
+constexpr int UNQ_UPDATE = 2; // momentum-SGD step on (parameter, smoothed gradient) with the value as the gradient
+
+// The momentum-SGD update of Matrix<ElemType>::MomentumSGDUpdate (Source/Math/Matrix.cpp:1681-1698): the smoothed gradient
+// becomes ScaleAndAdd(alpha, gradient, momentum, smoothed) with alpha = unitGainFactor * learnRatePerSample, then the
+// parameter loses the smoothed gradient.  ScaleAndAdd with a weight on the destination (Matrix.cpp:5415-5429) has three
+// forms, chosen on the host:
+//   kind 0 (momentum == 1): smoothed += alpha * g                       a = alpha
+//   kind 1 (momentum == 0): smoothed  = alpha * g                       a = alpha
+//   kind 2 (otherwise)    : smoothed  = (smoothed + (alpha / momentum) * g) * momentum     a = alpha / momentum
+// The reference hands the multiply-add to a BLAS axpy; it is taken as ONE fused multiply-add here (what cuBLAS and the
+// vector units of current CPUs do), and the scaling as one multiplication.
+struct UpdateRule
+{
+    float a;
+    float beta;
+    int kind;
+};
+UpdateRule make_update_rule(float learnRatePerSample, float momentum, float unitGainFactor);
+// plain update kernel over n values (qagg_update.cu): the same arithmetic from a gradient held in memory
+cudaError_t launch_sgd_update(cudaStream_t st, float* params, const float* grads, float* smoothed, long long n, const UpdateRule& rule, int numSMs);
+
 // Flags that the last CTA of a kernel writes (release, system scope) after all of the kernel's stores: one word in each
 // peer's memory, set to `value`.  n == 0: no signalling.
 struct Signal
@@ -120,8 +144,10 @@ cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int
 // unquantize (qagg_unquantize.cu): `single` != nullptr: one matrix described by value; otherwise `tensors` is a device table
 // of nTensors entries (all of `bits` bits) whose unit0 fields are the running sums of unq_units() (entry order = unit order)
 // smemWordsPerWarp: the largest unq_smem_words() over the matrices of the launch (0: none of them takes the row-major form)
-cudaError_t launch_unquantize(cudaStream_t st, bool add, int bits, const QTensor* single, const QTensor* tensors, int nTensors,
-                              long long totalUnits, int smemWordsPerWarp, const LaunchCfg& cfg);
+// mode: UNQ_STORE, UNQ_ADD, or UNQ_UPDATE (needs `rule`; each entry's `out` is then the parameter matrix and `res_out` the
+// smoothed gradient, both M x N)
+cudaError_t launch_unquantize(cudaStream_t st, int mode, int bits, const QTensor* single, const QTensor* tensors, int nTensors,
+                              long long totalUnits, int smemWordsPerWarp, const LaunchCfg& cfg, const UpdateRule* rule = nullptr);
 long long unq_units(long long M, long long N, int bits); // work units of an M x N matrix in the unquantize kernel
 int unq_smem_words(long long M, int bits);               // shared-memory words per warp an M-row matrix needs there
 // header exchange kernels (qagg_kernels.cu): in[0..n) -> dst.p[*][0..n);  out[i] = src.p[0][i] + src.p[1][i] + ... in that order
@@ -191,5 +217,7 @@ int check_cuda(cudaError_t e, const char* what);
 bool bits_ok(int bits);
 int mode_of(int bits, int zeroThr);
 void fill_layout(QTensor* t, long long M, long long N, int bits);
+int launch_cfg_for_current_device(LaunchCfg* cfg); // per-device launch configuration, looked up once
+int check_dims(long long M, long long N, int bits); // shape and bit-width limits of the single-matrix entry points
 
 } // namespace qagg

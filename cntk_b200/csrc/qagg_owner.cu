@@ -26,7 +26,6 @@
 #include "qagg_async.cuh"
 
 #include <algorithm>
-#include <cstdlib>
 
 namespace qagg {
 
@@ -487,11 +486,7 @@ static int form_grid(long long totalUnits, int numSMs)
     const long long most = (long long) numSMs * 3;
     if (need <= most)
         return (int) need;
-    if (const char* e = getenv("QAGG_FORM_GRID")) // experiment: units per warp
-    {
-        const long long per = atoi(e) > 0 ? atoi(e) : 1;
-        return (int) std::min<long long>((need + per - 1) / per, 0x7fffffff);
-    }
+
     long long best = most;
     double bestWaste = 2.0;
     for (long long g = most; g >= (long long) numSMs * 2; --g)

@@ -16,10 +16,13 @@
 //     Q packed words into its slice of shared memory (a padded layout, so that lanes reading words four apart hit distinct
 //     banks), and every lane produces four CONSECUTIVE rows -- row i is field i / Q of word i % Q -- as one aligned 16-byte
 //     store.  Work unit there = 2048 consecutive rows of one column.  With 4-byte stores this shape ran at 2.7 TB/s.
+//   * What happens to an expanded value is the kernel's MODE: stored (UNQ_STORE), added to what the destination holds
+//     (UNQ_ADD), or consumed on the spot by the momentum-SGD update that follows aggregation in the training loop
+//     (UNQ_UPDATE: the smoothed gradient and the parameter are read, updated and written; the aggregated gradient itself
+//     never goes to memory, which saves its write here and its read in a separate update kernel).
 #include "qagg_device.cuh"
 
 #include <algorithm>
-#include <cstdlib>
 
 namespace qagg {
 
@@ -89,9 +92,58 @@ __device__ __forceinline__ float unq_field(int bits, unsigned word, unsigned k, 
     return __fadd_rn(__fmul_rn(__fadd_rn((float) field, 0.5f), ca), cb);
 }
 
-template <bool ADD, bool TABLE, bool ONEBIT>
+// ---- what a lane does with expanded values ----------------------------------------------------------------------------
+// four consecutive rows at p (16-byte aligned); sp = the same rows of the smoothed gradient (UNQ_UPDATE only)
+template <int MODE>
+__device__ __forceinline__ void unq_emit4(float4* p, float4* sp, float4 v, const UpdateRule& rule)
+{
+    if (MODE == UNQ_STORE)
+    {
+        __stcs(p, v);
+    }
+    else if (MODE == UNQ_ADD)
+    {
+        const float4 o = *p;
+        v.x = __fadd_rn(v.x, o.x);
+        v.y = __fadd_rn(v.y, o.y);
+        v.z = __fadd_rn(v.z, o.z);
+        v.w = __fadd_rn(v.w, o.w);
+        *p = v;
+    }
+    else
+    {
+        float4 s = __ldcs(sp);
+        float4 w = __ldcs(p);
+        w.x = sgd_apply(rule, v.x, s.x, w.x);
+        w.y = sgd_apply(rule, v.y, s.y, w.y);
+        w.z = sgd_apply(rule, v.z, s.z, w.z);
+        w.w = sgd_apply(rule, v.w, s.w, w.w);
+        __stcs(sp, s);
+        __stcs(p, w);
+    }
+}
+template <int MODE>
+__device__ __forceinline__ void unq_emit1(float* p, float* sp, float v, const UpdateRule& rule)
+{
+    if (MODE == UNQ_STORE)
+    {
+        *p = v;
+    }
+    else if (MODE == UNQ_ADD)
+    {
+        *p = __fadd_rn(v, *p);
+    }
+    else
+    {
+        float s = *sp;
+        *p = sgd_apply(rule, v, s, *p);
+        *sp = s;
+    }
+}
+
+template <int MODE, bool TABLE, bool ONEBIT>
 __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, const QTensor* __restrict__ tensors, int nTensors, long long totalUnits,
-                                                   int smemWords)
+                                                   int smemWords, const UpdateRule rule)
 {
     extern __shared__ unsigned sWords[]; // row-major form: smemWords words per warp
     const unsigned lane = threadIdx.x & 31;
@@ -141,7 +193,8 @@ __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, cons
             unq_consts(bits, __ldg(reinterpret_cast<const float*>(colp)), __ldg(reinterpret_cast<const float*>(colp) + 1), ca, cb);
             __syncwarp();
             float* __restrict__ out = Tp->out + (size_t) c * M;
-            const bool aligned = (reinterpret_cast<uintptr_t>(Tp->out) & 15) == 0;
+            const bool aligned = (reinterpret_cast<uintptr_t>(Tp->out) & 15) == 0 &&
+                                 (MODE != UNQ_UPDATE || (reinterpret_cast<uintptr_t>(Tp->res_out) & 15) == 0);
             unsigned r = r0 + 4u * lane;
             unsigned k = r / Q, w = r - k * Q;
             const unsigned advK = 128u / Q, advW = 128u - advK * Q;
@@ -163,27 +216,16 @@ __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, cons
                         v[e] = unq_field<ONEBIT>(bits, sw[ww + (ww >> 5)], kk, mask, ca, cb);
                     }
                     float* p = out + r;
-                    if (ADD)
-                    {
-                        v[0] = __fadd_rn(v[0], p[0]);
-                        v[1] = __fadd_rn(v[1], p[1]);
-                        v[2] = __fadd_rn(v[2], p[2]);
-                        v[3] = __fadd_rn(v[3], p[3]);
-                    }
+                    float* sp = (MODE == UNQ_UPDATE) ? Tp->res_out + (size_t) c * M + r : nullptr;
                     if (aligned)
                     {
-                        const float4 v4 = make_float4(v[0], v[1], v[2], v[3]);
-                        if (ADD)
-                            *reinterpret_cast<float4*>(p) = v4;
-                        else
-                            __stcs(reinterpret_cast<float4*>(p), v4);
+                        unq_emit4<MODE>(reinterpret_cast<float4*>(p), reinterpret_cast<float4*>(sp), make_float4(v[0], v[1], v[2], v[3]), rule);
                     }
                     else
                     {
-                        p[0] = v[0];
-                        p[1] = v[1];
-                        p[2] = v[2];
-                        p[3] = v[3];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            unq_emit1<MODE>(p + e, sp + e, v[e], rule);
                     }
                 }
                 r += 128u;
@@ -217,7 +259,8 @@ __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, cons
         }
         const unsigned left = (unsigned) ((totalWords - t0 < UNQ_WORDS) ? (totalWords - t0) : UNQ_WORDS); // words of this unit
         float* __restrict__ outBase = Tp->out;
-        const bool vec = ((M & 3u) == 0) && ((Q & 3u) == 0) && ((reinterpret_cast<uintptr_t>(outBase) & 15) == 0);
+        const bool vec = ((M & 3u) == 0) && ((Q & 3u) == 0) && ((reinterpret_cast<uintptr_t>(outBase) & 15) == 0) &&
+                         (MODE != UNQ_UPDATE || (reinterpret_cast<uintptr_t>(Tp->res_out) & 15) == 0);
         if (vec)
         {
             // lane <-> words 4 * lane .. + 3 of the unit: the same column (Q is a multiple of 4), rows 4-aligned
@@ -235,6 +278,7 @@ __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, cons
                 float ca, cb;
                 unq_consts(bits, lower, upper, ca, cb);
                 float* __restrict__ op = outBase + (size_t) c * M + w;
+                float* __restrict__ sp = (MODE == UNQ_UPDATE) ? Tp->res_out + (size_t) c * M + w : nullptr;
 #pragma unroll
                 for (unsigned kk = 0; kk < UNQ_KPU; ++kk)
                 {
@@ -246,20 +290,7 @@ __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, cons
                         v.y = unq_field<ONEBIT>(bits, wb, k, mask, ca, cb);
                         v.z = unq_field<ONEBIT>(bits, wc, k, mask, ca, cb);
                         v.w = unq_field<ONEBIT>(bits, wd, k, mask, ca, cb);
-                        float4* p = reinterpret_cast<float4*>(op + (size_t) k * Q);
-                        if (ADD)
-                        {
-                            const float4 o = *p;
-                            v.x = __fadd_rn(v.x, o.x);
-                            v.y = __fadd_rn(v.y, o.y);
-                            v.z = __fadd_rn(v.z, o.z);
-                            v.w = __fadd_rn(v.w, o.w);
-                            *p = v;
-                        }
-                        else
-                        {
-                            __stcs(p, v);
-                        }
+                        unq_emit4<MODE>(reinterpret_cast<float4*>(op + (size_t) k * Q), reinterpret_cast<float4*>(sp + (size_t) k * Q), v, rule);
                     }
                 }
             }
@@ -296,17 +327,13 @@ __global__ void __launch_bounds__(NT, 4) k_unquantize(const QTensor single, cons
                     float ca, cb;
                     unq_consts(bits, lo[e], up[e], ca, cb);
                     float* __restrict__ op = outBase + (size_t) cc[e] * M + ww[e];
+                    float* __restrict__ sp = (MODE == UNQ_UPDATE) ? Tp->res_out + (size_t) cc[e] * M + ww[e] : nullptr;
 #pragma unroll
                     for (unsigned kk = 0; kk < UNQ_KPU; ++kk)
                     {
                         const unsigned k = k0 + kk;
                         if (k < vpw && ww[e] + k * Q < M)
-                        {
-                            float val = unq_field<ONEBIT>(bits, wd[e], k, mask, ca, cb);
-                            if (ADD)
-                                val = __fadd_rn(val, op[(size_t) k * Q]);
-                            op[(size_t) k * Q] = val;
-                        }
+                            unq_emit1<MODE>(op + (size_t) k * Q, sp + (size_t) k * Q, unq_field<ONEBIT>(bits, wd[e], k, mask, ca, cb), rule);
                     }
                 }
             }
@@ -323,19 +350,22 @@ static int unq_grid(long long totalUnits, int /*numSMs*/)
     return (int) std::min<long long>(need, 0x7fffffff);
 }
 
-cudaError_t launch_unquantize(cudaStream_t st, bool add, int bits, const QTensor* single, const QTensor* tensors, int nTensors, long long totalUnits,
-                              int smemWordsPerWarp, const LaunchCfg& cfg)
+cudaError_t launch_unquantize(cudaStream_t st, int mode, int bits, const QTensor* single, const QTensor* tensors, int nTensors, long long totalUnits,
+                              int smemWordsPerWarp, const LaunchCfg& cfg, const UpdateRule* rule)
 {
     if (totalUnits <= 0)
         return cudaSuccess;
+    if (mode == UNQ_UPDATE && !rule)
+        return cudaErrorInvalidValue;
     const size_t smemBytes = (size_t) smemWordsPerWarp * NWARPS * sizeof(unsigned); // at most 8 x 2113 words = 66 KB
     const int grid = unq_grid(totalUnits, cfg.numSMs);
     static const QTensor zero = {};
     const QTensor& s = single ? *single : zero;
     const bool table = (single == nullptr);
     const bool onebit = (bits == 1);
+    const UpdateRule r = rule ? *rule : UpdateRule{};
 #define QAGG_UNQ_CASE(A, T, O)                                                                                                         \
-    if (add == A && table == T && onebit == O)                                                                                         \
+    if (mode == A && table == T && onebit == O)                                                                                        \
     {                                                                                                                                  \
         if (smemBytes > 48 * 1024)                                                                                                     \
         {                                                                                                                              \
@@ -343,16 +373,20 @@ cudaError_t launch_unquantize(cudaStream_t st, bool add, int bits, const QTensor
             if (e != cudaSuccess)                                                                                                      \
                 return e;                                                                                                              \
         }                                                                                                                              \
-        k_unquantize<A, T, O><<<grid, NT, smemBytes, st>>>(s, tensors, nTensors, totalUnits, smemWordsPerWarp);                         \
+        k_unquantize<A, T, O><<<grid, NT, smemBytes, st>>>(s, tensors, nTensors, totalUnits, smemWordsPerWarp, r);                      \
     }
-    QAGG_UNQ_CASE(false, false, false)
-    QAGG_UNQ_CASE(false, false, true)
-    QAGG_UNQ_CASE(false, true, false)
-    QAGG_UNQ_CASE(false, true, true)
-    QAGG_UNQ_CASE(true, false, false)
-    QAGG_UNQ_CASE(true, false, true)
-    QAGG_UNQ_CASE(true, true, false)
-    QAGG_UNQ_CASE(true, true, true)
+    QAGG_UNQ_CASE(UNQ_STORE, false, false)
+    QAGG_UNQ_CASE(UNQ_STORE, false, true)
+    QAGG_UNQ_CASE(UNQ_STORE, true, false)
+    QAGG_UNQ_CASE(UNQ_STORE, true, true)
+    QAGG_UNQ_CASE(UNQ_ADD, false, false)
+    QAGG_UNQ_CASE(UNQ_ADD, false, true)
+    QAGG_UNQ_CASE(UNQ_ADD, true, false)
+    QAGG_UNQ_CASE(UNQ_ADD, true, true)
+    QAGG_UNQ_CASE(UNQ_UPDATE, false, false)
+    QAGG_UNQ_CASE(UNQ_UPDATE, false, true)
+    QAGG_UNQ_CASE(UNQ_UPDATE, true, false)
+    QAGG_UNQ_CASE(UNQ_UPDATE, true, true)
 #undef QAGG_UNQ_CASE
     return cudaGetLastError();
 }

@@ -29,6 +29,7 @@ EXPORTS = [
     "qagg_dense_create", "qagg_dense_step", "qagg_dense_step_group", "qagg_dense_peer_handle", "qagg_dense_enable_peer", "qagg_dense_check",
     "qagg_dense_wire_bytes", "qagg_dense_destroy", "qagg_agg_bind_residuals", "qagg_agg_materialize_residuals",
     "qagg_packed_col_bytes_f64", "qagg_packed_bytes_f64", "qagg_quantize_f64", "qagg_unquantize_f64",
+    "qagg_sgd_update", "qagg_unquantize_sgd", "qagg_agg_bind_update", "qagg_agg_set_update",
 ]
 
 
@@ -88,6 +89,10 @@ _lib.qagg_agg_step_group_header.argtypes = [ctypes.POINTER(c_vp), c_int, ctypes.
 _lib.qagg_agg_header_result.argtypes = [c_vp, ctypes.POINTER(ctypes.c_double), c_int, c_vp]
 _lib.qagg_agg_step_host.argtypes = [c_vp, ctypes.POINTER(c_vp), c_vp]
 _lib.qagg_agg_reset_residuals.argtypes = [c_vp, c_vp]
+_lib.qagg_sgd_update.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i64, ctypes.c_float, ctypes.c_float, ctypes.c_float]
+_lib.qagg_unquantize_sgd.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float]
+_lib.qagg_agg_bind_update.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
+_lib.qagg_agg_set_update.argtypes = [c_vp, c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float]
 _lib.qagg_agg_bind_residuals.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), c_int]
 _lib.qagg_agg_materialize_residuals.argtypes = [c_vp, c_vp]
 _lib.qagg_agg_residuals.argtypes = [c_vp, c_int, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
@@ -180,6 +185,16 @@ def quantize_f64(grad_ptr, res_in_ptr, res_out_ptr, packed_ptr, M, N, bits, zero
 
 def unquantize_f64(packed_ptr, out_ptr, M, N, bits, add=False, stream=0):
     _ok(_lib.qagg_unquantize_f64(stream, packed_ptr, out_ptr, M, N, bits, int(bool(add))))
+
+
+def sgd_update(params_ptr, grads_ptr, smoothed_ptr, n, learn_rate, momentum, unit_gain, stream=0):
+    """Momentum-SGD step over n values (Matrix::MomentumSGDUpdate, Source/Math/Matrix.cpp:1681-1698)."""
+    _ok(_lib.qagg_sgd_update(stream, params_ptr, grads_ptr, smoothed_ptr, n, learn_rate, momentum, unit_gain))
+
+
+def unquantize_sgd(packed_ptr, params_ptr, smoothed_ptr, M, N, bits, learn_rate, momentum, unit_gain, stream=0):
+    """The same step with the gradient taken from a packed matrix as it is expanded."""
+    _ok(_lib.qagg_unquantize_sgd(stream, packed_ptr, params_ptr, smoothed_ptr, M, N, bits, learn_rate, momentum, unit_gain))
 
 
 def reduce_requantize(stripe_ptrs, self_raw_ptr, sres_in_ptr, sres_out_ptr, packed_out_ptr, M, n, bits, zero_thr=True, stream=0):
@@ -349,6 +364,17 @@ class Aggregator:
         """Caller-owned residual buffers (device pointers; stripe pointer 0 where this rank owns no column)."""
         _ok(_lib.qagg_agg_bind_residuals(self.h, self._ptrs(value_ptrs), (c_vp * len(stripe_ptrs))(*[c_vp(p) if p else c_vp(None) for p in stripe_ptrs]),
                                          int(bool(keep_plain))))
+
+    def bind_update(self, param_ptrs, smoothed_ptrs):
+        """Parameter and smoothed-gradient matrices for the fused learner step (None, None unbinds)."""
+        if param_ptrs is None and smoothed_ptrs is None:
+            _ok(_lib.qagg_agg_bind_update(self.h, None, None))
+        else:
+            _ok(_lib.qagg_agg_bind_update(self.h, self._ptrs(param_ptrs), self._ptrs(smoothed_ptrs)))
+
+    def set_update(self, enabled, learn_rate=0.0, momentum=0.0, unit_gain=1.0):
+        """While enabled, every step ends in the momentum-SGD update of the bound matrices instead of writing gradients."""
+        _ok(_lib.qagg_agg_set_update(self.h, int(bool(enabled)), learn_rate, momentum, unit_gain))
 
     def materialize_residuals(self, stream=0):
         _ok(_lib.qagg_agg_materialize_residuals(self.h, stream))

@@ -222,6 +222,32 @@ int qagg_agg_reset_residuals(qagg_aggregator* a, void* stream);
  * Synchronises the device.  No reference counterpart as a function: the reference passes the buffers on every call. */
 int qagg_agg_bind_residuals(qagg_aggregator* a, float* const* value_residuals, float* const* stripe_residuals, int keep_plain);
 int qagg_agg_materialize_residuals(qagg_aggregator* a, void* stream);
+/* ---- consumer fusion: the learner's momentum-SGD step taken straight from the packed aggregate ---------------------------
+ * The training loops update the parameters right after aggregation (V1: SGD<ElemType>::UpdateWeights,
+ * Source/SGDLib/SGD.cpp:1405-1457, 2509-2527; V2: m_learner->Update in
+ * Source/1BitSGD/QuantizedDataParallelDistributedLearner.h:69 -> LearnerMomentumSGD::Update,
+ * Source/CNTKv2LibraryDll/Learner.cpp:610-645).  Both end in Matrix<ElemType>::MomentumSGDUpdate
+ * (Source/Math/Matrix.cpp:1681-1698):
+ *     smoothed = ScaleAndAdd(unit_gain_factor * learn_rate_per_sample, gradient, momentum, smoothed);  param -= smoothed
+ * with ScaleAndAdd's three forms for momentum == 1, == 0 and otherwise (Matrix.cpp:5415-5429; the last one is
+ * (smoothed + (alpha / momentum) * gradient) * momentum).  The multiply-add, a BLAS axpy in the reference, is ONE fused
+ * multiply-add here.  Not covered: clipping, L1/L2 regularisation, update noise, Nesterov, AdaGrad and its relatives.
+ *
+ * qagg_sgd_update: that step over n values of a gradient held in device memory.
+ * qagg_unquantize_sgd: the same with the gradient taken from a packed matrix as it is expanded (never written).
+ * qagg_agg_bind_update + qagg_agg_set_update: make the aggregator's last kernel do it.  params[i] and smoothed[i] are
+ *   M[i] x N[i] device matrices.  While enabled, every qagg_agg_step* variant ends by updating them with the aggregated
+ *   gradient INSTEAD of writing it: the gradient buffers keep what the caller put there.  The three scalars are those of the
+ *   step that follows; a caller whose momentum depends on the aggregated sample count of the very same step (the header sum)
+ *   must know that count beforehand (fixed minibatch size) or use the unfused calls for that step.  bind_update
+ *   synchronises the device; passing two NULLs unbinds.  Refused (QAGG_ESTATE) for an aggregator created with
+ *   QAGG_V2_IDENTITY_K1 on one rank, which leaves gradients untouched. */
+int qagg_sgd_update(void* stream, float* params, const float* grads, float* smoothed, int64_t n, float learn_rate_per_sample, float momentum,
+                    float unit_gain_factor);
+int qagg_unquantize_sgd(void* stream, const void* packed, float* params, float* smoothed, int64_t M, int64_t N, int bits, float learn_rate_per_sample,
+                        float momentum, float unit_gain_factor);
+int qagg_agg_bind_update(qagg_aggregator* a, float* const* params, float* const* smoothed);
+int qagg_agg_set_update(qagg_aggregator* a, int enabled, float learn_rate_per_sample, float momentum, float unit_gain_factor);
 /* Device pointers to internal state, for inspection: the M x N residual and the M x n stripe residual of tensor i
  * (stripe pointer NULL when this rank owns no column of it).  For 1 bit with threshold 0 the aggregator keeps the
  * residual in a deferred form (the quantized value plus the column's two reconstruction values; the subtraction is done

@@ -110,6 +110,17 @@ class OracleBackend(_Backend):
         return int(s.value), int(n.value)
 
 
+    def sgd_update(self, param, grad, smoothed, learn_rate, momentum, unit_gain):
+        """Momentum-SGD step in place on float32 arrays of one size (Matrix::MomentumSGDUpdate, Source/Math/Matrix.cpp:1681-1698)."""
+        for a, n in ((param, "param"), (grad, "grad"), (smoothed, "smoothed")):
+            _check(a, n, np.float32)
+            assert a.size == param.size
+        f = self.lib.oracle_sgd_update
+        f.restype = None
+        f.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int64] + [ctypes.c_float] * 3
+        f(_ptr(param), _ptr(grad), _ptr(smoothed), param.size, learn_rate, momentum, unit_gain)
+
+
 class RefBackend(_Backend):
     prefix = "ref_"
     path = os.path.join(_HERE, "_ref", "libqagg_ref.so")

@@ -69,3 +69,30 @@ ORACLE_API void oracle_stripe(int64_t numCols, int64_t nodeRank, int64_t numNode
     *start = per * nodeRank + (residue < nodeRank ? residue : nodeRank);
     *n = per + ((nodeRank < residue) ? 1 : 0);
 }
+
+/* The learner step that consumes the aggregate: Matrix<ElemType>::MomentumSGDUpdate (Source/Math/Matrix.cpp:1681-1698) =
+ *   ScaleAndAdd(unitGainFactor * learnRatePerSample, gradients, momentum, smoothedGradients);  *this -= smoothedGradients;
+ * with ScaleAndAdd(alpha, a, beta, c) of Matrix.cpp:5415-5429:
+ *   beta == 1: c += alpha * a;   beta == 0: c = alpha * a;   else: c += (alpha / beta) * a, then c *= beta.
+ * PARITY UNPINNED for this function: the reference delegates `c += alpha * a` to a BLAS axpy (cblas_saxpy,
+ * Source/Math/CPUMatrixImpl.h:5481-5507; cuBLAS on the GPU), a library that is not part of the reference checkout, and
+ * whether that rounds once (fused multiply-add) or twice is the library's choice.  It is restated here as ONE fused
+ * multiply-add (fmaf), which is what vectorised BLAS builds and cuBLAS do on current hardware; the scaling and the final
+ * subtraction are single operations either way. */
+ORACLE_API void oracle_sgd_update(float* param, const float* grad, float* smoothed, int64_t n, float learnRatePerSample, float momentum,
+                                  float unitGainFactor)
+{
+    const float alpha = unitGainFactor * learnRatePerSample;
+    for (int64_t i = 0; i < n; ++i)
+    {
+        float s;
+        if (momentum == 1.0f)
+            s = fmaf(alpha, grad[i], smoothed[i]);
+        else if (momentum == 0.0f)
+            s = alpha * grad[i];
+        else
+            s = momentum * fmaf(alpha / momentum, grad[i], smoothed[i]);
+        smoothed[i] = s;
+        param[i] = param[i] - s;
+    }
+}

@@ -5,9 +5,12 @@
 //   mode "quantizer_f64": the same loop with MatrixQuantizerImpl<double> (64-bit packed words)
 //   mode "aggregator": AllReduceDistGradAggregator::AggregateGradients on one rank (SGD.cpp:1376), two calls
 //   mode "aggregator_async": the same with useAsyncAggregation = true (one-step-stale results, AllReduceDistGradAggregator.h:156-229)
+//   mode "schedule": SGD's per-epoch bookkeeping (gradientBits as a per-epoch array re-creating the aggregator, warm start by
+//       parallelizationStartEpoch: SGD.cpp:427-432, 553-559, 2336-2359) on one rank
 //   mode "multi": one of K processes (one per GPU), tied together by a unique id passed through a file: the V1 aggregator,
 //       the V2 aggregator (synchronous and buffered asynchronous), the V2 learner and the unquantized aggregator run a
-//       real K-rank exchange, DistGradHeader included
+//       real K-rank exchange, DistGradHeader included; the V2 learner also runs over a momentum-SGD learner with and without
+//       the update fused into the exchange
 // usage: compat_check <mode> <in.bin> <out.bin> M N bits zeroThr iters [rank K idfile]
 #include <cstdio>
 #include <cstdlib>
@@ -17,8 +20,10 @@
 #include <vector>
 
 #include "../../cntk_b200/csrc/cntk_compat/AllReduceDistGradAggregator.h"
+#include "../../cntk_b200/csrc/cntk_compat/DataParallelSGD.h"
 #include "../../cntk_b200/csrc/cntk_compat/SimpleDistGradAggregator.h"
 #include "../../cntk_b200/csrc/cntk_compat/QuantizedDataParallelDistributedLearner.h"
+#include "../../cntk_b200/csrc/cntk_compat/MomentumSGDLearner.h"
 #include "../../cntk_b200/csrc/cntk_compat/V2AllReduceDistGradAggregator.h"
 #include "../../cntk_b200/csrc/cntk_compat/MatrixQuantizer.h"
 #include "../../cntk_b200/csrc/cntk_compat/QuantizedDistributedCommunicator.h"
@@ -242,6 +247,75 @@ int main(int argc, char** argv)
                 return 11;
             DistGradHeader::Destroy(hdr);
         }
+        else if (mode == "schedule")
+        {
+            // SGD's per-epoch aggregator bookkeeping on one rank: gradientBits = 1:1:4:32 (the last value repeats),
+            // parallelizationStartEpoch = 2; five epochs of two minibatches.  Epoch 0 must leave the gradients alone, epochs 1
+            // and 2 are quantize -> unquantize round trips at 1 and 4 bits from zero residuals, epochs 3 and 4 the
+            // unquantized sum over one rank.
+            auto mpi = std::make_shared<MPIWrapper>(std::string(), 0, 1, 0);
+            DataParallelSGDConfig cfg;
+            cfg.gradientBits = {1, 1, 4, 32};
+            cfg.parallelizationStartEpoch = 2;
+            cfg.useZeroThresholdFor1BitQuantization = zeroThr != 0;
+            DataParallelSGD<float> sgd(mpi, cfg, 1, 0);
+            Matrix<float> g0(M, N, 0), g1(M, 1, 0);
+            std::vector<Matrix<float>*> grads{&g0, &g1};
+            sgd.BeginTraining(0);
+            for (int epoch = 0; epoch < 5; ++epoch)
+            {
+                sgd.BeginEpoch((size_t) epoch);
+                if (sgd.CurrentNumGradientBits() != (epoch < 2 ? 1 : epoch == 2 ? 4 : 32))
+                    return 50;
+                for (int mb = 0; mb < 2; ++mb)
+                {
+                    if (fread(in.data(), 4, in.size(), fi) != in.size())
+                        return 4;
+                    cudaMemcpy(g0.Data(), in.data(), in.size() * 4, cudaMemcpyHostToDevice);
+                    cudaMemcpy(g1.Data(), in.data(), M * 4, cudaMemcpyHostToDevice);
+                    sgd.Header().Clear();
+                    sgd.Header().numSamples = 9;
+                    sgd.Header().criterion = 0.75;
+                    if (!sgd.AggregateMinibatch(grads, mb == 0) || sgd.Header().numSamples != 9 || sgd.Header().criterion != 0.75)
+                        return 51;
+                    auto a = download(g0), b = download(g1);
+                    fwrite(a.data(), 4, a.size(), fo);
+                    fwrite(b.data(), 4, b.size(), fo);
+                }
+            }
+            if (sgd.TimesInitialized() != 3) // 1 bit at the start, 4 bits before epoch 2, 32 bits before epoch 3
+                return 52;
+            // the checks of the configuration (SGD.cpp:3318-3319, 3338-3342)
+            int refused = 0;
+            for (int bad = 0; bad < 3; ++bad)
+            {
+                DataParallelSGDConfig c;
+                if (bad == 0)
+                    c.gradientBits = {0};
+                else if (bad == 1)
+                    c.gradientBits = {1, 33};
+                else
+                    c.parallelizationStartEpoch = 0;
+                try { DataParallelSGD<float> x(mpi, c, 1, 0); } catch (const std::invalid_argument&) { ++refused; }
+            }
+            if (refused != 3)
+                return 53;
+            // useV2Aggregator on one worker: the V2 communicator returns at once, gradients stay as they are
+            DataParallelSGDConfig v2 = cfg;
+            v2.useV2Aggregator = true;
+            v2.parallelizationStartEpoch = 1;
+            DataParallelSGD<float> sgd2(mpi, v2, 1, 0);
+            sgd2.BeginTraining(0);
+            sgd2.BeginEpoch(0);
+            cudaMemcpy(g0.Data(), in.data(), in.size() * 4, cudaMemcpyHostToDevice);
+            sgd2.Header().Clear();
+            sgd2.Header().numSamples = 3;
+            if (!sgd2.AggregateMinibatch(grads, true))
+                return 54;
+            auto v = download(g0);
+            if (memcmp(v.data(), in.data(), in.size() * 4) != 0)
+                return 55;
+        }
         else if (mode == "multi")
         {
             if (argc < 12)
@@ -422,6 +496,53 @@ int main(int argc, char** argv)
                 if (!agg.AggregateGradients(grads, hdr, false) || !headerIsSum(hdr))
                     return 40;
                 dump();
+            }
+            // F. the V2 learner over a momentum-SGD learner, twice: the reference's order (aggregate, then Update) and with the
+            //    update fused into the exchange's last kernel.  Same parameters and smoothed gradients bit for bit; the fused
+            //    run leaves the gradient views alone.  Parameters start as 1 + 1000 * (this rank's first gradients).
+            {
+                const float lr = 0.05f, momentum = 0.9f;
+                std::vector<float> p0(M * N), p1(M);
+                for (size_t i = 0; i < p0.size(); ++i)
+                    p0[i] = 1.0f + 1000.0f * mine0[0][i];
+                for (size_t i = 0; i < p1.size(); ++i)
+                    p1[i] = 1.0f + 1000.0f * mine1[0][i];
+                std::vector<::CNTK::NDArrayViewPtr> params[2];
+                std::shared_ptr<::CNTK::MomentumSGDLearner> sgd[2];
+                ::CNTK::DistributedLearnerPtr dl[2];
+                for (int f = 0; f < 2; ++f)
+                {
+                    params[f] = {std::make_shared<Matrix<float>>(M, N, dev), std::make_shared<Matrix<float>>(M, 1, dev)};
+                    cudaMemcpy(params[f][0]->Data(), p0.data(), p0.size() * 4, cudaMemcpyHostToDevice);
+                    cudaMemcpy(params[f][1]->Data(), p1.data(), p1.size() * 4, cudaMemcpyHostToDevice);
+                    sgd[f] = std::make_shared<::CNTK::MomentumSGDLearner>(params[f], lr, momentum, true);
+                    dl[f] = ::CNTK::CreateQuantizedDataParallelDistributedLearner(::CNTK::QuantizedMPICommunicator(mpi, zeroThr != 0, true, (size_t) bits),
+                                                                                  sgd[f], 0);
+                    dl[f]->SetConsumerFusion(f == 1);
+                }
+                std::vector<::CNTK::NDArrayViewPtr> vals{std::make_shared<Matrix<float>>(M, N, g0.Data(), dev), std::make_shared<Matrix<float>>(M, 1, g1.Data(), dev)};
+                for (int it = 0; it < iters; ++it)
+                    for (int f = 0; f < 2; ++f)
+                    {
+                        load(it);
+                        ::CNTK::MinibatchInfo info;
+                        info.numberOfSamples = 4 + rank;
+                        if (!dl[f]->Update(vals, info))
+                            return 41;
+                        if (f == 1 && (download(g0) != mine0[it] || download(g1) != mine1[it]))
+                            return 42; // the fused step must not touch the gradient views
+                    }
+                for (int t = 0; t < 2; ++t)
+                {
+                    const auto a = download(*params[0][t]), b = download(*params[1][t]);
+                    const auto sa = download(*sgd[0]->SmoothedGradients()[t]), sb = download(*sgd[1]->SmoothedGradients()[t]);
+                    if (memcmp(a.data(), b.data(), a.size() * 4) != 0 || memcmp(sa.data(), sb.data(), sa.size() * 4) != 0)
+                        return 43;
+                    fwrite(b.data(), 4, b.size(), fo);
+                    fwrite(sb.data(), 4, sb.size(), fo);
+                }
+                if (sgd[1]->TotalNumberOfMinibatchesSeen() != (size_t) iters || sgd[0]->TotalNumberOfSamplesSeen() != sgd[1]->TotalNumberOfSamplesSeen())
+                    return 44;
             }
             mpi->WaitAll();
             DistGradHeader::Destroy(hdr);

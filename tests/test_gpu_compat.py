@@ -103,3 +103,30 @@ def test_aggregator_buffered_async_hands_back_the_previous_aggregate(exe, tmp_pa
             assert np.array_equal(dump[off:off + ref.size], ref), f"call {it + 1}: aggregate of step {it} differs"
             off += ref.size
     assert off == dump.size
+
+
+def test_per_epoch_bit_schedule_and_warm_start(exe, tmp_path, oracle_port):
+    """DataParallelSGD (the bookkeeping of Source/SGDLib/SGD.cpp:427-432, 553-559, 2336-2359): gradientBits = 1:1:4:32 with
+    parallelizationStartEpoch = 2 over five epochs of two minibatches.  Epoch 0 leaves the gradients alone; a change of bit
+    width creates a new aggregator with zero residuals; every epoch's first minibatch resets the residuals; 32 bits is the
+    unquantized sum (the identity on one rank)."""
+    M, N = 256, 40
+    inputs = [mg.normal_input(M, N, 1e-3, 900 + i) for i in range(10)]
+    dump = run(exe, tmp_path, "schedule", inputs, M, N, 1, True)
+    off = 0
+    for epoch in range(5):
+        bits = [None, 1, 4, 32, 32][epoch]
+        for mb in range(2):
+            if mb == 0:
+                res = {}  # residuals per tensor shape: zero at every epoch's first minibatch
+            x = inputs[2 * epoch + mb]
+            for g in (x.copy(), x[:1].copy()):
+                if bits not in (None, 32):
+                    r = res.setdefault(g.shape, np.zeros(g.shape, np.float32))
+                    packed = np.zeros(g.shape[0] * oracle_port.packed_col_bytes(M, bits), np.uint8)
+                    oracle_port.quantize(g, r, r, packed, bits, True)
+                    oracle_port.unquantize(packed, g, bits, add=False)
+                ref = g.view(np.uint8).reshape(-1)
+                assert np.array_equal(dump[off:off + ref.size], ref), f"epoch {epoch} minibatch {mb}: aggregate differs"
+                off += ref.size
+    assert off == dump.size

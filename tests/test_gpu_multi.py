@@ -36,7 +36,8 @@ def test_cpp_mirror_classes_run_a_real_exchange(K, tmp_path, oracle_port):
     """tests/cpp/compat_check.cpp in mode "multi": K processes, one per GPU, tied together by a unique id passed through a
     file, drive the C++ mirror classes the way SGDLib and the V2 trainer drive the reference's: AllReduceDistGradAggregator,
     V2AllReduceDistGradAggregator (synchronous and buffered asynchronous) over QuantizedMPICommunicator with caller-owned
-    residuals, QuantizedDataParallelDistributedLearner (checkpoint zeroes the residuals) and SimpleDistGradAggregator.
+    residuals, QuantizedDataParallelDistributedLearner (checkpoint zeroes the residuals; over a momentum-SGD learner with and
+    without the update fused into the exchange) and SimpleDistGradAggregator.
     Every rank's dumps are compared with the CPU checker bit for bit (the unquantized arm, whose all-reduce order is
     NCCL's, within 1e-5); the DistGradHeader sums are checked inside the program."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < K:
@@ -117,4 +118,14 @@ def test_cpp_mirror_classes_run_a_real_exchange(K, tmp_path, oracle_port):
             same(take((1, M)), seqD[it][r][1], f"learner step {it} tensor 1")
         assert np.allclose(take((N, M)), dense[0], rtol=1e-5, atol=1e-9), f"rank {r}: unquantized aggregator tensor 0"
         assert np.allclose(take((1, M)), dense[1], rtol=1e-5, atol=1e-9), f"rank {r}: unquantized aggregator tensor 1"
+        # F: momentum-SGD learner (learning rate 0.05, momentum 0.9, unit gain), fused == unfused inside the program; here
+        # against the CPU checker's update applied to the CPU checker's aggregates
+        w = [(1.0 + 1000.0 * inputs[0][r][t]).astype(np.float32) for t in range(2)]
+        sm = [np.zeros_like(a) for a in w]
+        for it in range(iters):
+            for t in range(2):
+                oracle_port.sgd_update(w[t].reshape(-1), np.ascontiguousarray(seq[it][r][t]).reshape(-1), sm[t].reshape(-1), 0.05, 0.9, np.float32(1.0) - np.float32(0.9))
+        for t, shape in enumerate([(N, M), (1, M)]):
+            same(take(shape), w[t], f"fused learner: parameters of tensor {t}")
+            same(take(shape), sm[t], f"fused learner: smoothed gradients of tensor {t}")
         assert off == dump.size
