@@ -173,6 +173,9 @@ struct qagg_aggregator
     std::vector<unsigned char> hostMaps; // their host mirror
     DevBuf ownMaps, ownStats;            // owner kernels: one tensor map per owned stripe; two counters per owned column
     long long k2Units = 0;               // work units of the owner's form kernel
+    // owner kernels, tall matrices apart: their table entries, form units and walk items come first (see launch_owner)
+    OwnerSplit k2Split = {};
+    bool k2SplitOn = false;
     DevBuf lvAll, slvAll;
     std::vector<float*> lv, slv;
     // device tables and their host mirrors
@@ -226,6 +229,12 @@ struct qagg_aggregator
             for (auto& e : slot)
                 if (e)
                     cudaEventDestroy(e);
+        if (k2Split.fork)
+            cudaEventDestroy(k2Split.fork);
+        if (k2Split.join)
+            cudaEventDestroy(k2Split.join);
+        if (k2Split.side)
+            cudaStreamDestroy(k2Split.side);
     }
     int mark(int i, cudaStream_t st)
     {
@@ -364,6 +373,36 @@ int build_tables(qagg_aggregator* a)
             for (auto& it : tmp)
                 cost1.push_back({M * it.ncols, it});
         }
+    }
+    // The owner's table.  With the two-kernel owner, matrices much taller than the rest come first: their walk is the longest
+    // dependent chain and gets a launch of its own (launch_owner).  "Tall": more than half the rows of the tallest owned matrix.
+    std::vector<int> k2Order;
+    {
+        int64_t tallest = 0;
+        for (int i = 0; i < T; ++i)
+            if (K > 1 && a->M[i] > 0 && a->N[i] > 0 && a->sN[r][i] > 0)
+                tallest = std::max(tallest, a->M[i]);
+        for (int pass = 0; pass < 2; ++pass)
+            for (int i = 0; i < T; ++i)
+            {
+                if (!(K > 1 && a->M[i] > 0 && a->N[i] > 0 && a->sN[r][i] > 0))
+                    continue;
+                const bool tall = a->deferredOwner && 2 * a->M[i] > tallest;
+                if (tall == (pass == 0))
+                    k2Order.push_back(i);
+            }
+        a->k2Split.tallUnits = 0;
+        a->k2Split.tallItems = 0;
+        for (int i : k2Order)
+            if (a->deferredOwner && 2 * a->M[i] > tallest)
+            {
+                a->k2Split.tallUnits += owner_form_units(a->M[i], a->sN[r][i]);
+                a->k2Split.tallItems += (int) ((a->sN[r][i] + 31) / 32);
+            }
+    }
+    for (int i : k2Order)
+    {
+        const int64_t M = a->M[i];
         if (K > 1 && a->sN[r][i] > 0)
         {
             QTensor q2 = {};
@@ -432,6 +471,20 @@ int build_tables(qagg_aggregator* a)
         int rc = check_cuda(cudaMemcpy(a->ownMaps.p, maps.data(), maps.size(), cudaMemcpyHostToDevice), "tensor map upload");
         if (rc)
             return rc;
+        // the tall matrices' walk on a stream of its own (tuning knob, results never change: QAGG_OWNER_SPLIT=0 keeps one
+        // form and one walk launch)
+        bool wantSplit = a->k2Split.tallItems > 0 && a->k2Split.tallItems < (int) a->iK2.size();
+        if (const char* e = std::getenv("QAGG_OWNER_SPLIT"))
+            if (e[0] == '0')
+                wantSplit = false;
+        if (wantSplit && !a->k2Split.side)
+        {
+            if ((rc = check_cuda(cudaStreamCreateWithFlags(&a->k2Split.side, cudaStreamNonBlocking), "cudaStreamCreate")) ||
+                (rc = check_cuda(cudaEventCreateWithFlags(&a->k2Split.fork, cudaEventDisableTiming), "cudaEventCreate")) ||
+                (rc = check_cuda(cudaEventCreateWithFlags(&a->k2Split.join, cudaEventDisableTiming), "cudaEventCreate")))
+                return rc;
+        }
+        a->k2SplitOn = wantSplit;
     }
     return QAGG_OK;
 }
@@ -534,6 +587,13 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
     return QAGG_OK;
 }
 
+// peer mode, process group, streaming quantize kernel: the header values are pushed by that kernel's first CTA and summed by
+// the flag wait that follows, instead of by two small kernels of their own
+bool header_rides_with_k1(const qagg_aggregator* a)
+{
+    return a->hdrN > 0 && a->comm->K > 1 && a->peer && !a->comm->local && a->deferred && !a->iK1.empty();
+}
+
 // peer mode: which flag words (one per peer, indexed by this rank) the kernel releases when it is done
 Signal make_signal(const qagg_aggregator* a, bool gatherPhase)
 {
@@ -550,6 +610,13 @@ Signal make_signal(const qagg_aggregator* a, bool gatherPhase)
             sg.bcastBase[sg.nbcast++] = a->peer_gather_slot(p, r);
     }
     sg.value = a->stepNo;
+    if (!gatherPhase && header_rides_with_k1(a))
+    {
+        sg.hdrIn = a->hdrHost;
+        sg.hdrN = a->hdrN;
+        for (int p = 0; p < K; ++p)
+            sg.hdrDst[sg.hdrDstN++] = a->header_slot(a->peerWin[p], r);
+    }
     return sg;
 }
 int launch_k1(qagg_aggregator* a, cudaStream_t st)
@@ -568,7 +635,7 @@ int launch_k2(qagg_aggregator* a, cudaStream_t st)
     if (a->peer && a->pushGather)
     {
         int rc = check_cuda(a->deferredOwner ? launch_owner(st, a->dK2, (int) a->hK2.size(), a->k2Units, a->dI2, (int) a->iK2.size(), a->cfg, q2, nullptr,
-                                                            a->status_word())
+                                                            a->status_word(), a->k2SplitOn ? &a->k2Split : nullptr)
                                              : launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg, q2, nullptr),
                             "reduce-requantize launch");
         if (rc)
@@ -578,13 +645,23 @@ int launch_k2(qagg_aggregator* a, cudaStream_t st)
                                       a->cfg.numSMs), "gather push launch");
     }
     if (a->deferredOwner)
-        return check_cuda(launch_owner(st, a->dK2, (int) a->hK2.size(), a->k2Units, a->dI2, (int) a->iK2.size(), a->cfg, q2, &sg, a->status_word()),
+        return check_cuda(launch_owner(st, a->dK2, (int) a->hK2.size(), a->k2Units, a->dI2, (int) a->iK2.size(), a->cfg, q2, &sg, a->status_word(),
+                                       a->k2SplitOn ? &a->k2Split : nullptr),
                           "reduce-requantize launch");
     return check_cuda(launch_colquant(st, true, a->mode, nullptr, a->dK2, a->dI2, (int) a->iK2.size(), 0, a->cfg, q2, &sg),
                       "reduce-requantize launch");
 }
 int wait_peers(qagg_aggregator* a, bool gatherPhase, cudaStream_t st)
 {
+    if (!gatherPhase && a->hdrN > 0 && a->comm->K > 1 && !a->comm->local)
+    {
+        // the scatter wait also sums the header values that the ranks stored before releasing their flags
+        HeaderPtrs src = {};
+        for (int p = 0; p < a->comm->K; ++p)
+            src.p[src.n++] = a->header_slot(static_cast<unsigned char*>(a->window.p), p);
+        return check_cuda(launch_wait_flags(st, a->flag_words(), a->comm->K, a->comm->rank, a->stepNo, a->waitPolls, a->status_word(), &src, a->hdrN,
+                                            a->hdrHost + QAGG_HEADER_MAX), "flag wait launch");
+    }
     return check_cuda(launch_wait_flags(st, a->flag_words() + (gatherPhase ? 64 : 0), a->comm->K, a->comm->rank, a->stepNo, a->waitPolls,
                                         a->status_word()), "flag wait launch");
 }
@@ -1014,7 +1091,7 @@ int stage_header(qagg_aggregator* a, const double* header, int n)
 // quantize kernel's flag release, which follows on the stream, publishes it together with the packed stripes
 int push_header(qagg_aggregator* a, cudaStream_t st)
 {
-    if (a->hdrN == 0 || a->comm->K == 1 || !a->peer)
+    if (a->hdrN == 0 || a->comm->K == 1 || !a->peer || header_rides_with_k1(a))
         return QAGG_OK;
     HeaderPtrs dst = {};
     for (int p = 0; p < a->comm->K; ++p)
@@ -1028,6 +1105,8 @@ int sum_header(qagg_aggregator* a, cudaStream_t st)
     if (a->hdrN == 0 || a->comm->K == 1)
         return QAGG_OK;
     double* out = a->hdrHost + QAGG_HEADER_MAX;
+    if (a->peer && !a->comm->local)
+        return QAGG_OK; // summed by the scatter wait (wait_peers)
     if (a->peer)
     {
         HeaderPtrs src = {};
@@ -1949,8 +2028,11 @@ int qagg_agg_launches_per_step(const qagg_aggregator* a)
         return 0;
     if (a->comm->K == 1)
         return 2;
-    // quantize, owner (one kernel, or form + walk), unquantize; + two flag waits (+ the gather push) in peer mode
-    return 3 + (a->deferredOwner ? 1 : 0) + (a->peer ? 2 + (a->pushGather ? 1 : 0) : 0);
+    // quantize, owner (one kernel, or form + walk, or both twice when the tall matrices go apart), unquantize; + two flag waits
+    // (+ the gather push) (+ a header push when the last step carried a header that the quantize kernel did not take along)
+    // in peer mode
+    return 3 + (a->deferredOwner ? (a->k2SplitOn ? 3 : 1) : 0) +
+           (a->peer ? 2 + (a->pushGather ? 1 : 0) + ((a->hdrN > 0 && !header_rides_with_k1(a)) ? 1 : 0) : 0);
 }
 
 int qagg_agg_destroy(qagg_aggregator* a)

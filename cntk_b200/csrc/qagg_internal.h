@@ -82,6 +82,11 @@ struct Signal
     unsigned value;
     unsigned char* bcastBase[QAGG_MAXK]; // broadcast copies (peer gather slots) for matrices with bcast == 1
     int nbcast;
+    // header values that ride with the kernel (streaming quantize kernel only): its first CTA copies hdrN doubles from hdrIn
+    // (pinned host memory) into every hdrDst[p] (this rank's header slot in each rank's window) before the flags are released
+    const double* hdrIn;
+    double* hdrDst[QAGG_MAXK];
+    int hdrN, hdrDstN;
 };
 
 // header exchange: up to QAGG_HEADER_MAX doubles per rank (DistGradHeader needs 3 + 2 per evaluation node)
@@ -140,7 +145,9 @@ cudaError_t launch_colquant(cudaStream_t st, bool stripes, int mode, const QTens
 cudaError_t launch_push(cudaStream_t st, const void* src, size_t bytes, const Signal& signal, unsigned* counters, int numSMs);
 // one warp polls flags[i] (i < n, i != skip) until each is >= value (wrap-safe) or maxPolls polls have passed; on
 // give-up it ORs 1 into *status and returns: the context stays usable and the host reads the status later
-cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status);
+// hdrSrc (optional): once the flags are in, the hdrN doubles behind each hdrSrc->p[] are added in index order into hdrOut
+cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status,
+                              const HeaderPtrs* hdrSrc = nullptr, int hdrN = 0, double* hdrOut = nullptr);
 // unquantize (qagg_unquantize.cu): `single` != nullptr: one matrix described by value; otherwise `tensors` is a device table
 // of nTensors entries (all of `bits` bits) whose unit0 fields are the running sums of unq_units() (entry order = unit order)
 // smemWordsPerWarp: the largest unq_smem_words() over the matrices of the launch (0: none of them takes the row-major form)
@@ -204,8 +211,19 @@ void owner_make_items(const std::vector<std::pair<long long, long long>>& shapes
 bool owner_set_map(QTensor* t, unsigned char* hostMap, unsigned char* devMap);
 // form kernel, then walk kernel; the walk kernel's last CTA releases signal.flag[] (`counters` as for launch_colquant; only
 // [1] is used).  Its waits for tiles in flight are bounded like the streaming kernel's (bit 1 of *status).
+// `split` (optional): the table's first entries are "tall" matrices -- tallUnits form units, tallItems walk items -- whose
+// walk runs on the stream `side` (ordered by the events `fork` and `join`) while the other matrices are formed and walked on
+// `st`; on return `st` is ordered after everything.  counters[1..3] are used.
+struct OwnerSplit
+{
+    long long tallUnits;
+    int tallItems;
+    cudaStream_t side;
+    cudaEvent_t fork, join;
+};
 cudaError_t launch_owner(cudaStream_t st, const QTensor* tensors, int nTensors, long long formUnits, const QItem* items, int nItems,
-                         const LaunchCfg& cfg, unsigned* counters, const Signal* signal = nullptr, unsigned* status = nullptr);
+                         const LaunchCfg& cfg, unsigned* counters, const Signal* signal = nullptr, unsigned* status = nullptr,
+                         const OwnerSplit* split = nullptr);
 // runs the streaming kernel's bounded mbarrier wait on a barrier that nothing completes (see qagg_stream_wait_selftest)
 cudaError_t launch_stream_wait_selftest(cudaStream_t st, int maxTries, unsigned* status, long long* cycles);
 // dst[i, j] = buf[i, j] - (buf[i, j] >= 0 ? lv[2j + 1] : lv[2j]): the residual proper of a deferred state (dst may be buf)

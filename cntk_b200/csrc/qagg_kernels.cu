@@ -721,7 +721,8 @@ __global__ void __launch_bounds__(NT, QAGG_CTAS_PER_SM) k_colquant(const QTensor
 
 // One warp waits for the peers' flags.  Every wait is bounded: after maxPolls polls the lane gives up, records it in
 // *status and the kernel ends normally.
-__global__ void k_wait_flags(const unsigned* __restrict__ flags, int n, int skip, unsigned value, long long maxPolls, unsigned* __restrict__ status)
+__global__ void k_wait_flags(const unsigned* __restrict__ flags, int n, int skip, unsigned value, long long maxPolls, unsigned* __restrict__ status,
+                             const HeaderPtrs hdrSrc, int hdrN, double* __restrict__ hdrOut)
 {
     const int i = threadIdx.x;
     if (i < n && i != skip)
@@ -742,6 +743,16 @@ __global__ void k_wait_flags(const unsigned* __restrict__ flags, int n, int skip
         }
     }
     __threadfence_system();
+    __syncwarp();
+    // the header values every rank stored before it released its flag: summed in rank order (a wait that gave up sums
+    // whatever is there; the status word says so)
+    for (int j = i; j < hdrN; j += 32)
+    {
+        double s = *reinterpret_cast<const volatile double*>(hdrSrc.p[0] + j);
+        for (int p = 1; p < hdrSrc.n; ++p)
+            s += *reinterpret_cast<const volatile double*>(hdrSrc.p[p] + j);
+        hdrOut[j] = s;
+    }
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------
@@ -873,11 +884,14 @@ cudaError_t launch_header_sum(cudaStream_t st, const HeaderPtrs& src, int n, dou
     return cudaGetLastError();
 }
 
-cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status)
+cudaError_t launch_wait_flags(cudaStream_t st, const unsigned* flags, int n, int skip, unsigned value, long long maxPolls, unsigned* status,
+                              const HeaderPtrs* hdrSrc, int hdrN, double* hdrOut)
 {
     if (n > 32)
         return cudaErrorInvalidValue;
-    k_wait_flags<<<1, 32, 0, st>>>(flags, n, skip, value, maxPolls, status);
+    static const HeaderPtrs none = {};
+    const bool sum = hdrSrc && hdrN > 0 && hdrOut;
+    k_wait_flags<<<1, 32, 0, st>>>(flags, n, skip, value, maxPolls, status, sum ? *hdrSrc : none, sum ? hdrN : 0, hdrOut);
     return cudaGetLastError();
 }
 

@@ -237,12 +237,14 @@ __device__ __forceinline__ void form_unit(const FormCtx& x, const float* __restr
 // its three staging buffers while it works on the current one, so the memory latency overlaps the arithmetic without
 // holding registers (the loop is unrolled by three so that every buffer and context has a fixed name).
 constexpr int FORM_BUF_FLOATS = OW_HALF * 32;
-__global__ void __launch_bounds__(NT, 3) k_owner_form(const QTensor* __restrict__ tensors, int nTensors, long long totalUnits, const Signal signal)
+__global__ void __launch_bounds__(NT, 3) k_owner_form(const QTensor* __restrict__ tensors, int nTensors, long long unitBegin, long long totalUnits,
+                                                     const Signal signal)
 {
+    // this launch covers units [unitBegin, totalUnits) of the table
     __shared__ __align__(16) float sStage[NWARPS][3][FORM_BUF_FLOATS];
     const unsigned lane = threadIdx.x & 31;
     const unsigned warp = threadIdx.x >> 5;
-    const long long gwarp = (long long) blockIdx.x * NWARPS + warp;
+    const long long gwarp = unitBegin + (long long) blockIdx.x * NWARPS + warp;
     const long long nwarps = (long long) gridDim.x * NWARPS;
     if (gwarp >= totalUnits)
         return;
@@ -330,7 +332,8 @@ __device__ __forceinline__ float walk_item(const float* tiles, unsigned long lon
 }
 
 __global__ void __launch_bounds__(OW_THREADS, 1) k_owner_walk(const QTensor* __restrict__ tensors, const QItem* __restrict__ items, int nItems,
-                                                           const Signal signal, unsigned* __restrict__ counters, unsigned* __restrict__ status)
+                                                           const Signal signal, unsigned* __restrict__ counters, unsigned* __restrict__ status,
+                                                           int doneSlot, unsigned nLaunches)
 {
     extern __shared__ __align__(128) float tiles[];
     __shared__ __align__(8) unsigned long long sFull[OW_STAGES], sEmpty[OW_STAGES];
@@ -350,8 +353,13 @@ __global__ void __launch_bounds__(OW_THREADS, 1) k_owner_walk(const QTensor* __r
     __syncthreads();
     unsigned pos = 0; // ring position of the current item's tile 0 (all warps keep the same count)
     unsigned itemNo = 0;
-    for (int it = blockIdx.x; it < nItems; it += gridDim.x, ++itemNo)
+    // Items are sorted tallest first and dealt out in rounds, every other round in reverse CTA order: the CTAs that drew
+    // the tallest items of one round get the shortest of the next (or none).
+    for (;; ++itemNo)
     {
+        const int it = (int) (itemNo * gridDim.x + ((itemNo & 1u) ? gridDim.x - 1u - blockIdx.x : blockIdx.x));
+        if (it >= nItems)
+            break;
         const QItem item = items[it];
         const QTensor* __restrict__ Tp = tensors + item.tensor;
         const int M = (int) Tp->M;
@@ -431,15 +439,26 @@ __global__ void __launch_bounds__(OW_THREADS, 1) k_owner_walk(const QTensor* __r
     }
     __syncthreads();
     // The last CTA to leave releases the peers' flags: each CTA's stores (into peer memory too) are ordered before its
-    // arrival by barrier + system-scope fence; the form kernel's stores were complete before this kernel began.
+    // arrival by barrier + system-scope fence; the form kernel's stores were complete before this kernel began.  When the
+    // owner's work is split over nLaunches concurrent walk launches, the last CTA of each arrives at a second counter and
+    // the last of those releases.
     if (tid == 0)
     {
         __threadfence_system();
-        const unsigned done = atomicAdd(&counters[1], 1u);
+        const unsigned done = atomicAdd(&counters[doneSlot], 1u);
         if (done == gridDim.x - 1)
         {
-            counters[1] = 0;
-            release_flags(signal);
+            counters[doneSlot] = 0;
+            bool last = true;
+            if (nLaunches > 1u)
+            {
+                __threadfence();
+                last = (atomicAdd(&counters[3], 1u) == nLaunches - 1u);
+                if (last)
+                    counters[3] = 0;
+            }
+            if (last)
+                release_flags(signal);
         }
     }
 }
@@ -504,7 +523,7 @@ static int form_grid(long long totalUnits, int numSMs)
 }
 
 cudaError_t launch_owner(cudaStream_t st, const QTensor* tensors, int nTensors, long long formUnits, const QItem* items, int nItems,
-                         const LaunchCfg& cfg, unsigned* counters, const Signal* signalp, unsigned* status)
+                         const LaunchCfg& cfg, unsigned* counters, const Signal* signalp, unsigned* status, const OwnerSplit* split)
 {
     static const Signal none = {};
     const Signal& signal = signalp ? *signalp : none;
@@ -512,17 +531,43 @@ cudaError_t launch_owner(cudaStream_t st, const QTensor* tensors, int nTensors, 
         return cudaErrorInvalidValue;
     if (nItems <= 0 || formUnits <= 0)
         return signal.n > 0 ? launch_signal_only(st, signal) : cudaSuccess;
-    k_owner_form<<<form_grid(formUnits, cfg.numSMs), NT, 0, st>>>(tensors, nTensors, formUnits, signal);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = cudaFuncSetAttribute(k_owner_walk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) OW_SMEM_BYTES);
     if (e != cudaSuccess)
         return e;
-    e = cudaFuncSetAttribute(k_owner_walk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) OW_SMEM_BYTES);
-    if (e != cudaSuccess)
+    const int tallGrid = split ? std::min(split->tallItems, cfg.numSMs) : 0;
+    if (split && split->tallItems > 0 && split->tallItems < nItems && split->tallUnits > 0 && split->tallUnits < formUnits && 8 * tallGrid <= cfg.numSMs)
+    {
+        // (Taken only when the tall walk needs few SMs: with many tall items -- 2 ranks on the speech set -- the form work
+        // dominates and one launch of each kind measured faster.)
+        // Tall matrices first: their walk is the longest dependent chain of the step, so it starts as early as possible, and
+        // the other matrices are formed and walked beside it, on a second stream, on the SMs it leaves free (one walk CTA
+        // fills an SM's shared memory, so the launches that run beside it are sized for the remaining SMs).  The tall walk
+        // stays on `st`, right behind the form launch it depends on: a same-stream successor starts before work that waits
+        // for an event, and the launches beside it must not take its SMs first.
+        const int restSMs = cfg.numSMs - tallGrid;
+        k_owner_form<<<form_grid(split->tallUnits, cfg.numSMs), NT, 0, st>>>(tensors, nTensors, 0, split->tallUnits, signal);
+        if ((e = cudaGetLastError()) != cudaSuccess || (e = cudaEventRecord(split->fork, st)) != cudaSuccess)
+            return e;
+        k_owner_walk<<<tallGrid, OW_THREADS, OW_SMEM_BYTES, st>>>(tensors, items, split->tallItems, signal, counters, status, 1, 2u);
+        if ((e = cudaGetLastError()) != cudaSuccess || (e = cudaStreamWaitEvent(split->side, split->fork, 0)) != cudaSuccess)
+            return e;
+        k_owner_form<<<form_grid(formUnits - split->tallUnits, restSMs), NT, 0, split->side>>>(tensors, nTensors, split->tallUnits, formUnits, signal);
+        if ((e = cudaGetLastError()) != cudaSuccess)
+            return e;
+        const int restItems = nItems - split->tallItems;
+        k_owner_walk<<<std::min(restItems, restSMs), OW_THREADS, OW_SMEM_BYTES, split->side>>>(tensors, items + split->tallItems, restItems, signal, counters,
+                                                                                               status, 2, 2u);
+        if ((e = cudaGetLastError()) != cudaSuccess || (e = cudaEventRecord(split->join, split->side)) != cudaSuccess)
+            return e;
+        return cudaStreamWaitEvent(st, split->join, 0);
+    }
+    k_owner_form<<<form_grid(formUnits, cfg.numSMs), NT, 0, st>>>(tensors, nTensors, 0, formUnits, signal);
+    if ((e = cudaGetLastError()) != cudaSuccess)
         return e;
     int grid = cfg.numSMs; // one CTA per SM: the ring takes most of an SM's shared memory
     if (grid > nItems)
         grid = nItems;
-    k_owner_walk<<<grid, OW_THREADS, OW_SMEM_BYTES, st>>>(tensors, items, nItems, signal, counters, status);
+    k_owner_walk<<<grid, OW_THREADS, OW_SMEM_BYTES, st>>>(tensors, items, nItems, signal, counters, status, 1, 1u);
     return cudaGetLastError();
 }
 

@@ -91,6 +91,14 @@ __global__ void __launch_bounds__(NT + 32, ST_CTAS_PER_SM) k_stream1(const QTens
     __shared__ unsigned char* sDst[QAGG_STREAM_CMAX];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (blockIdx.x == 0 && tid < signal.hdrN)
+    {
+        // the step's header values ride along: into this rank's slot of every rank's window (ordered before the flag release
+        // like every other store of this CTA)
+        const double v = signal.hdrIn[tid];
+        for (int p = 0; p < signal.hdrDstN; ++p)
+            signal.hdrDst[p][tid] = v;
+    }
     if (tid == 0)
     {
         // the walkers of the CTAs that share an SM sit on different warp pairs (a per-SM ticket that only ever grows)

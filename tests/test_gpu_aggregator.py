@@ -243,10 +243,11 @@ def test_lstm_shaped_set_ragged(G, oracle_port, K):
     run_group(G, oracle_port, LSTM_SMALL, K, 1, True, True, 10, lstm_inputs, check_every=5)
 
 
-@pytest.mark.parametrize("knob", ["QAGG_STREAM", "QAGG_OWNER"])
+@pytest.mark.parametrize("knob", ["QAGG_STREAM", "QAGG_OWNER", "QAGG_OWNER_SPLIT"])
 def test_kernel_choice_knob_changes_no_result(G, oracle_port, knob, monkeypatch):
     """Tuning knobs read when an aggregator is created: QAGG_STREAM=0 = resident-column kernels only (plain residuals),
-    QAGG_OWNER=0 = resident-column kernel for the owner's reduce-requantize only (plain stripe residuals).  Either way
+    QAGG_OWNER=0 = resident-column kernel for the owner's reduce-requantize only (plain stripe residuals),
+    QAGG_OWNER_SPLIT=0 = one form and one walk launch instead of the tall matrices' walk on a stream of its own.  Either way
     aggregates, both residual sets and the gathered packed words stay bit-identical to the oracle (the default -- streaming
     quantize kernel, form + walk owner kernels, both residual sets deferred -- is what every other 1-bit zero-threshold
     test in this file runs)."""
