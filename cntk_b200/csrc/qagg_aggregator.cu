@@ -473,7 +473,8 @@ int build_tables(qagg_aggregator* a)
             return rc;
         // the tall matrices' walk on a stream of its own (tuning knob, results never change: QAGG_OWNER_SPLIT=0 keeps one
         // form and one walk launch)
-        bool wantSplit = a->k2Split.tallItems > 0 && a->k2Split.tallItems < (int) a->iK2.size();
+        bool wantSplit = a->k2Split.tallItems > 0 && a->k2Split.tallItems < (int) a->iK2.size() &&
+                         8 * std::min(a->k2Split.tallItems, a->cfg.numSMs) <= a->cfg.numSMs; // launch_owner's own condition
         if (const char* e = std::getenv("QAGG_OWNER_SPLIT"))
             if (e[0] == '0')
                 wantSplit = false;
