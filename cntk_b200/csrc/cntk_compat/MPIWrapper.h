@@ -39,6 +39,19 @@ public:
 
     qagg_comm* Handle() const { return m_comm; }
 
+    // The process-wide instance, as MPIWrapper::GetInstance (Source/Common/MPIWrapper.cpp:375-430) keeps one: the reference
+    // creates it from MPI_COMM_WORLD on first use; here the launcher creates it (it knows rank, size and the unique id) and
+    // registers it, and the factories that take no MPIWrapper argument (QuantizedMPICommunicator's reference signature) find
+    // it.  GetInstance() returns null when none was registered.
+    static std::shared_ptr<MPIWrapper>& InstanceSlot()
+    {
+        static std::shared_ptr<MPIWrapper> s_instance;
+        return s_instance;
+    }
+    static void SetInstance(const std::shared_ptr<MPIWrapper>& mpi) { InstanceSlot() = mpi; }
+    static std::shared_ptr<MPIWrapper> GetInstance() { return InstanceSlot(); }
+    static void DeleteInstance() { InstanceSlot().reset(); }
+
 private:
     qagg_comm* m_comm = nullptr;
 };

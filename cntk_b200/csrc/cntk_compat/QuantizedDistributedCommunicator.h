@@ -362,4 +362,13 @@ inline QuantizedDistributedCommunicatorPtr QuantizedMPICommunicator(const Micros
     return std::make_shared<QuantizedMPICommunicatorImpl>(mpi, zeroThresholdFor1Bit, useQuantizationForSelfStripe, numQuantizationBits);
 }
 
+// the reference's own signature (Source/CNTKv2LibraryDll/API/CNTKLibrary.h:6273): over the process-wide MPIWrapper instance
+inline QuantizedDistributedCommunicatorPtr QuantizedMPICommunicator(bool zeroThresholdFor1Bit, bool useQuantizationForSelfStripe, size_t numQuantizationBits)
+{
+    auto mpi = Microsoft::MSR::CNTK::MPIWrapper::GetInstance();
+    if (!mpi)
+        Microsoft::MSR::CNTK::RuntimeError("QuantizedMPICommunicator: no MPIWrapper instance has been registered (MPIWrapper::SetInstance)");
+    return QuantizedMPICommunicator(mpi, zeroThresholdFor1Bit, useQuantizationForSelfStripe, numQuantizationBits);
+}
+
 } // namespace CNTK

@@ -462,7 +462,14 @@ int main(int argc, char** argv)
                 {
                     bool Update(std::vector<::CNTK::NDArrayViewPtr>&, size_t, bool) override { return true; }
                 };
-                auto comm3 = ::CNTK::QuantizedMPICommunicator(mpi, zeroThr != 0, true, (size_t) bits);
+                // the factory with the reference's own signature finds the registered process-wide MPIWrapper
+                bool threwNoInstance = false;
+                try { ::CNTK::QuantizedMPICommunicator(zeroThr != 0, true, (size_t) bits); } catch (const std::runtime_error&) { threwNoInstance = true; }
+                if (!threwNoInstance)
+                    return 45;
+                MPIWrapper::SetInstance(mpi);
+                auto comm3 = ::CNTK::QuantizedMPICommunicator(zeroThr != 0, true, (size_t) bits);
+                MPIWrapper::DeleteInstance();
                 auto dl = ::CNTK::CreateQuantizedDataParallelDistributedLearner(comm3, std::make_shared<NullLearner>(), 0);
                 std::vector<::CNTK::NDArrayViewPtr> vals{std::make_shared<Matrix<float>>(M, N, g0.Data(), dev), std::make_shared<Matrix<float>>(M, 1, g1.Data(), dev)};
                 for (int it = 0; it < iters; ++it)
