@@ -36,6 +36,22 @@ def run_checks(comm, rank, K, dev):
     vals = comm.allreduce_f64([float(rank + 1), 0.5 * rank, 2.0 ** rank, -1.0])
     assert vals == [K * (K + 1) / 2.0, 0.5 * K * (K - 1) / 2.0, float(2 ** K - 1), -float(K)], f"rank {rank}: allreduce_f64 gave {vals}"
     comm.barrier()
+    # creation handshake: one rank asks for a different first tensor -> EVERY rank's creation fails, with a state error
+    if K > 1:
+        odd = [(SHAPES[0][0] + 1, SHAPES[0][1])] + list(SHAPES[1:]) if rank == K - 1 else SHAPES
+        try:
+            lib.Aggregator(comm, odd, 1)
+            raised = False
+        except lib.QaggError as e:
+            raised = "do not describe the same exchange" in str(e)
+        assert raised, f"rank {rank}: mismatched shapes were not refused at creation"
+        try:
+            lib.Aggregator(comm, SHAPES, 1 if rank else 2)
+            raised = False
+        except lib.QaggError:
+            raised = True
+        assert raised, f"rank {rank}: mismatched bit widths were not refused at creation"
+        comm.barrier()
     for bits, zero_thr, self_q, peer in ((1, True, True, False), (1, False, True, False), (4, True, True, False), (1, True, False, False),
                                          (1, True, True, True), (4, True, True, True), (1, True, False, True)):
         flags = (lib.ZERO_THRESHOLD if zero_thr else 0) | (lib.SELF_QUANTIZED if self_q else 0)
