@@ -176,6 +176,10 @@ struct qagg_aggregator
     // owner kernels, tall matrices apart: their table entries, form units and walk items come first (see launch_owner)
     OwnerSplit k2Split = {};
     bool k2SplitOn = false;
+    // the stream the last step was enqueued on: calls that rewrite what that step reads (tables, tensor maps, residual
+    // state) from another stream wait for it first
+    cudaStream_t lastStream = nullptr;
+    bool stepped = false;
     DevBuf lvAll, slvAll;
     std::vector<float*> lv, slv;
     // device tables and their host mirrors
@@ -560,9 +564,11 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
         const int i = a->k2Tensor[e];
         a->hK2[e].grad = grads[i] + a->sStart[r][i] * a->M[i];
     }
-    // an earlier step may still be reading the tables of that set
+    // an earlier step may still be reading the tables of that set -- on this stream or on the one it was enqueued on
     int rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
     if (rc)
+        return rc;
+    if (a->stepped && a->lastStream != st && (rc = check_cuda(cudaStreamSynchronize(a->lastStream), "cudaStreamSynchronize")))
         return rc;
     if (a->deferred)
     {
@@ -1163,6 +1169,8 @@ int qagg_agg_step_header(qagg_aggregator* a, float* const* grads, const double* 
         return rc;
     if ((rc = bind_grads(a, grads, st)))
         return rc;
+    a->lastStream = st;
+    a->stepped = true;
     a->stepNo++;
     if ((rc = a->mark(0, st)))
         return rc;
@@ -1315,6 +1323,8 @@ int qagg_agg_step_group_header(qagg_aggregator* const* aggs, int num_ranks, floa
     {
         if ((rc = bind_grads(aggs[r], grads[r], st)))
             return rc;
+        aggs[r]->lastStream = st;
+        aggs[r]->stepped = true;
         aggs[r]->stepNo++;
         if ((rc = aggs[r]->mark(0, st)) || (rc = launch_k1(aggs[r], st)) || (rc = aggs[r]->mark(1, st)))
             return rc;
@@ -1470,6 +1480,18 @@ int qagg_agg_check(qagg_aggregator* a, void* stream)
             return check_nccl(asyncErr, "asynchronous NCCL error");
     }
     return QAGG_OK;
+}
+
+int qagg_agg_clear_status(qagg_aggregator* a, void* stream)
+{
+    if (!a)
+        return fail(QAGG_EINVAL, "null aggregator");
+    int rc = check_cuda(cudaSetDevice(a->comm->device), "cudaSetDevice");
+    if (rc)
+        return rc;
+    if ((rc = check_cuda(cudaMemsetAsync(a->status_word(), 0, sizeof(unsigned), (cudaStream_t) stream), "status clear")))
+        return rc;
+    return check_cuda(cudaStreamSynchronize((cudaStream_t) stream), "cudaStreamSynchronize");
 }
 
 int qagg_stream_wait_selftest(void* stream, int max_tries, unsigned* status_dev, long long* cycles_dev)
@@ -1950,8 +1972,15 @@ int qagg_agg_residuals(qagg_aggregator* a, int tensor, float** residual, float**
     if (a->deferred)
     {
         // turn this tensor's deferred state into plain residuals in place (with zero reconstruction values the state means
-        // the same), so that the caller sees residuals; runs on the default stream and waits
+        // the same), so that the caller sees residuals; runs on the default stream and waits (first for the last step, which
+        // may have been enqueued on a stream that the default stream does not order itself after)
         const int r = a->comm->rank;
+        if (a->stepped && a->lastStream != nullptr)
+        {
+            const int src = check_cuda(cudaStreamSynchronize(a->lastStream), "cudaStreamSynchronize");
+            if (src)
+                return src;
+        }
         int rc = check_cuda(launch_materialize(nullptr, a->res[tensor], a->lv[tensor], a->res[tensor], a->M[tensor], a->N[tensor], a->cfg.numSMs),
                             "residual export");
         if (!rc && a->N[tensor] > 0)

@@ -29,7 +29,7 @@ EXPORTS = [
     "qagg_dense_create", "qagg_dense_step", "qagg_dense_step_group", "qagg_dense_peer_handle", "qagg_dense_enable_peer", "qagg_dense_check",
     "qagg_dense_wire_bytes", "qagg_dense_destroy", "qagg_agg_bind_residuals", "qagg_agg_materialize_residuals",
     "qagg_packed_col_bytes_f64", "qagg_packed_bytes_f64", "qagg_quantize_f64", "qagg_unquantize_f64",
-    "qagg_sgd_update", "qagg_unquantize_sgd", "qagg_agg_bind_update", "qagg_agg_set_update",
+    "qagg_sgd_update", "qagg_unquantize_sgd", "qagg_agg_bind_update", "qagg_agg_set_update", "qagg_agg_clear_status",
 ]
 
 
@@ -91,6 +91,7 @@ _lib.qagg_agg_step_host.argtypes = [c_vp, ctypes.POINTER(c_vp), c_vp]
 _lib.qagg_agg_reset_residuals.argtypes = [c_vp, c_vp]
 _lib.qagg_sgd_update.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i64, ctypes.c_float, ctypes.c_float, ctypes.c_float]
 _lib.qagg_unquantize_sgd.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float]
+_lib.qagg_agg_clear_status.argtypes = [c_vp, c_vp]
 _lib.qagg_agg_bind_update.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
 _lib.qagg_agg_set_update.argtypes = [c_vp, c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float]
 _lib.qagg_agg_bind_residuals.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), c_int]
@@ -364,6 +365,9 @@ class Aggregator:
         """Caller-owned residual buffers (device pointers; stripe pointer 0 where this rank owns no column)."""
         _ok(_lib.qagg_agg_bind_residuals(self.h, self._ptrs(value_ptrs), (c_vp * len(stripe_ptrs))(*[c_vp(p) if p else c_vp(None) for p in stripe_ptrs]),
                                          int(bool(keep_plain))))
+
+    def clear_status(self, stream=0):
+        _ok(_lib.qagg_agg_clear_status(self.h, stream))
 
     def bind_update(self, param_ptrs, smoothed_ptrs):
         """Parameter and smoothed-gradient matrices for the fused learner step (None, None unbinds)."""

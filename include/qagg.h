@@ -317,6 +317,12 @@ int qagg_agg_peer_handle(qagg_aggregator* a, void* out);
 int qagg_agg_enable_peer(qagg_aggregator* a, const void* handles);
 int qagg_agg_set_wait_limit(qagg_aggregator* a, long long max_polls);
 int qagg_agg_check(qagg_aggregator* a, void* stream);
+/* The time-out report is sticky: once set, every later qagg_agg_check repeats it.  After the cause has been dealt with
+ * (the missing peer is back and every rank agrees to go on) this call clears it; waits for `stream`.  The results of the
+ * step that timed out stay invalid, and so does the residual state it wrote: reset the residuals as well.
+ * Streams: an aggregator's steps may be enqueued on any stream, one step at a time; calls that rewrite what an enqueued
+ * step reads (a step with new gradient pointers, qagg_agg_residuals) wait for the stream of the last step themselves. */
+int qagg_agg_clear_status(qagg_aggregator* a, void* stream);
 /* Failure detection of the streaming quantize kernel, exercised without a fault: one warp runs the kernel's own bounded
  * wait on an mbarrier phase that nothing will ever complete.  After `max_tries` polls the wait gives up, ORs 2 into
  * *status_dev and the kernel ends normally; a second wait in the same kernel returns at once.  cycles_dev (2 x int64,

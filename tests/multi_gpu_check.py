@@ -52,6 +52,30 @@ def run_checks(comm, rank, K, dev):
             raised = True
         assert raised, f"rank {rank}: mismatched bit widths were not refused at creation"
         comm.barrier()
+        # a rank that skips a step (between steps, nothing of its own in flight): the others' bounded flag waits give up
+        # after the set number of polls, their kernels end normally, qagg_agg_check reports the time-out on the host and
+        # keeps reporting it until it is cleared; the aggregator is then dropped (the ranks' step counts differ)
+        agg = lib.Aggregator(comm, SHAPES, 1)
+        mine = torch.frombuffer(bytearray(agg.peer_handle()), dtype=torch.uint8).to(dev)
+        allh = [torch.zeros_like(mine) for _ in range(K)]
+        dist.all_gather(allh, mine)
+        agg.enable_peer([bytes(h.cpu().numpy().tobytes()) for h in allh])
+        agg.set_wait_limit(20000)
+        dg = [torch.zeros((N, M), dtype=torch.float32, device=dev) for (M, N) in SHAPES]
+        if rank != K - 1:
+            agg.step([t.data_ptr() for t in dg], torch.cuda.current_stream().cuda_stream)
+            for attempt in range(2):
+                try:
+                    agg.check(torch.cuda.current_stream().cuda_stream)
+                    reported = False
+                except lib.QaggError as e:
+                    reported = "wait" in str(e)
+                assert reported, f"rank {rank}: a peer that skipped the step was not reported (attempt {attempt})"
+            agg.clear_status(torch.cuda.current_stream().cuda_stream)
+            agg.check(torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        comm.barrier()
+        agg.destroy()
     for bits, zero_thr, self_q, peer in ((1, True, True, False), (1, False, True, False), (4, True, True, False), (1, True, False, False),
                                          (1, True, True, True), (4, True, True, True), (1, True, False, True)):
         flags = (lib.ZERO_THRESHOLD if zero_thr else 0) | (lib.SELF_QUANTIZED if self_q else 0)
