@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libqagg.so")
-SOURCES = ["qagg_kernels.cu", "qagg_stream.cu", "qagg_unquantize.cu", "qagg_owner.cu", "qagg_capi.cu", "qagg_aggregator.cu", "qagg_dense.cu", "qagg_f64.cu", "qagg_update.cu", "qagg_noalloc.cu"]
+SOURCES = ["qagg_kernels.cu", "qagg_stream.cu", "qagg_unquantize.cu", "qagg_owner.cu", "qagg_capi.cu", "qagg_aggregator.cu", "qagg_dense.cu", "qagg_f64.cu", "qagg_agg_f64.cu", "qagg_update.cu", "qagg_noalloc.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -26,9 +26,33 @@
 
 namespace Microsoft { namespace MSR { namespace CNTK {
 
+// which entry points of the library an element type goes through: float -> the tuned aggregator, double -> the aggregator
+// composed from the double-precision matrix kernels (ElemType = double is what the reference's 1-bit end-to-end tests run)
+template <class ElemType>
+struct QaggAggregatorApi;
+template <>
+struct QaggAggregatorApi<float>
+{
+    typedef qagg_aggregator* Handle;
+    static int Create(qagg_comm* c, int n, const int64_t* M, const int64_t* N, int bits, int flags, Handle* out) { return qagg_agg_create(c, n, M, N, bits, flags, out); }
+    static int Step(Handle h, float* const* g, void* st) { return qagg_agg_step(h, g, st); }
+    static int Reset(Handle h) { return qagg_agg_reset_residuals(h, nullptr); }
+    static void Destroy(Handle h) { qagg_agg_destroy(h); }
+};
+template <>
+struct QaggAggregatorApi<double>
+{
+    typedef qagg_aggregator_f64* Handle;
+    static int Create(qagg_comm* c, int n, const int64_t* M, const int64_t* N, int bits, int flags, Handle* out) { return qagg_agg_f64_create(c, n, M, N, bits, flags, out); }
+    static int Step(Handle h, double* const* g, void* st) { return qagg_agg_f64_step(h, g, st); }
+    static int Reset(Handle h) { return qagg_agg_f64_reset_residuals(h, nullptr); }
+    static void Destroy(Handle h) { qagg_agg_f64_destroy(h); }
+};
+
 template <class ElemType>
 class AllReduceDistGradAggregator : public IDistGradAggregator<ElemType>
 {
+    typedef QaggAggregatorApi<ElemType> Api;
     using IDistGradAggregator<ElemType>::m_mpi;
 
 public:
@@ -43,7 +67,7 @@ public:
         if (m_pending)
             cudaStreamSynchronize(m_aggStream);
         if (m_agg)
-            qagg_agg_destroy(m_agg);
+            Api::Destroy(m_agg);
         if (m_bufferedHeader)
             DistGradHeader::Destroy(m_bufferedHeader);
         if (m_mainDone)
@@ -64,7 +88,7 @@ public:
         {
             if (m_useAsync && m_pending)
                 LogicError("Unexpected pending async gradient aggregation found when resetting aggregator state!");
-            QaggCheck(qagg_agg_reset_residuals(m_agg, nullptr), "ResetResidue");
+            QaggCheck(Api::Reset(m_agg), "ResetResidue");
             if (m_useAsync)
             {
                 for (auto& b : m_buffered)
@@ -140,7 +164,7 @@ private:
                     RuntimeError("AggregateGradients: clearing the gradients of a rank without samples failed");
         for (size_t i = 0; i < gradients.size(); ++i)
             m_ptrs[i] = gradients[i]->Data();
-        QaggCheck(qagg_agg_step(m_agg, m_ptrs.data(), stream), "AggregateGradients");
+        QaggCheck(Api::Step(m_agg, m_ptrs.data(), stream), "AggregateGradients");
     }
     // header: numSamples, numSamplesWithLabel, criterion and the eval pairs, summed over ranks; then wait for the step
     void Finish(DistGradHeader* header, cudaStream_t stream)
@@ -180,7 +204,7 @@ private:
             m_cols.push_back(g->GetNumCols());
         }
         const int flags = (m_zeroThr ? QAGG_ZERO_THRESHOLD : 0) | (m_selfQuant ? QAGG_SELF_QUANTIZED : 0);
-        QaggCheck(qagg_agg_create(m_mpi->Handle(), (int) gradients.size(), M.data(), N.data(), m_nBits, flags, &m_agg), "qagg_agg_create");
+        QaggCheck(Api::Create(m_mpi->Handle(), (int) gradients.size(), M.data(), N.data(), m_nBits, flags, &m_agg), "qagg_agg_create");
         m_ptrs.resize(gradients.size());
         if (m_useAsync)
         {
@@ -199,8 +223,8 @@ private:
     bool m_zeroThr, m_selfQuant, m_useAsync;
     int m_traceLevel, m_syncStatsTrace;
     size_t m_iterationCount = 0;
-    qagg_aggregator* m_agg = nullptr;
-    std::vector<float*> m_ptrs;
+    typename Api::Handle m_agg = nullptr;
+    std::vector<ElemType*> m_ptrs;
     std::vector<size_t> m_rows, m_cols;
     // buffered asynchronous aggregation
     std::vector<std::unique_ptr<Matrix<ElemType>>> m_buffered;

@@ -30,6 +30,8 @@ EXPORTS = [
     "qagg_dense_wire_bytes", "qagg_dense_destroy", "qagg_agg_bind_residuals", "qagg_agg_materialize_residuals",
     "qagg_packed_col_bytes_f64", "qagg_packed_bytes_f64", "qagg_quantize_f64", "qagg_unquantize_f64",
     "qagg_sgd_update", "qagg_unquantize_sgd", "qagg_agg_bind_update", "qagg_agg_set_update", "qagg_agg_clear_status",
+    "qagg_agg_f64_create", "qagg_agg_f64_step", "qagg_agg_f64_step_group", "qagg_agg_f64_reset_residuals", "qagg_agg_f64_residuals",
+    "qagg_agg_f64_destroy", "qagg_agg_f64_copy_residual",
 ]
 
 
@@ -92,6 +94,13 @@ _lib.qagg_agg_reset_residuals.argtypes = [c_vp, c_vp]
 _lib.qagg_sgd_update.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i64, ctypes.c_float, ctypes.c_float, ctypes.c_float]
 _lib.qagg_unquantize_sgd.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float]
 _lib.qagg_agg_clear_status.argtypes = [c_vp, c_vp]
+_lib.qagg_agg_f64_create.argtypes = [c_vp, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), c_int, c_int, ctypes.POINTER(c_vp)]
+_lib.qagg_agg_f64_step.argtypes = [c_vp, ctypes.POINTER(c_vp), c_vp]
+_lib.qagg_agg_f64_step_group.argtypes = [ctypes.POINTER(c_vp), c_int, ctypes.POINTER(ctypes.POINTER(c_vp)), c_vp]
+_lib.qagg_agg_f64_reset_residuals.argtypes = [c_vp, c_vp]
+_lib.qagg_agg_f64_residuals.argtypes = [c_vp, c_int, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
+_lib.qagg_agg_f64_destroy.argtypes = [c_vp]
+_lib.qagg_agg_f64_copy_residual.argtypes = [c_vp, c_int, c_int, c_vp, c_vp]
 _lib.qagg_agg_bind_update.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
 _lib.qagg_agg_set_update.argtypes = [c_vp, c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float]
 _lib.qagg_agg_bind_residuals.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), c_int]
@@ -530,3 +539,47 @@ def step_group(aggs, grad_ptrs, stream=0, headers=None):
     hrows = [(ctypes.c_double * n)(*h) for h in headers]
     hp = (ctypes.POINTER(ctypes.c_double) * K)(*[ctypes.cast(r, ctypes.POINTER(ctypes.c_double)) for r in hrows])
     _ok(_lib.qagg_agg_step_group_header(ha, K, pp, hp, n, stream))
+
+
+class AggregatorF64:
+    """AllReduceDistGradAggregator<double>: the striped aggregation for double gradients (qagg_agg_f64_*)."""
+
+    def __init__(self, comm, shapes, bits, flags=ZERO_THRESHOLD | SELF_QUANTIZED):
+        T = len(shapes)
+        M = (c_i64 * max(T, 1))(*[s[0] for s in shapes])
+        N = (c_i64 * max(T, 1))(*[s[1] for s in shapes])
+        h = c_vp()
+        _ok(_lib.qagg_agg_f64_create(comm.h, T, M, N, bits, flags, ctypes.byref(h)))
+        self.h, self.T = h, T
+
+    def _ptrs(self, ptrs):
+        assert len(ptrs) == self.T
+        return (c_vp * max(self.T, 1))(*[c_vp(p) if p else c_vp(None) for p in ptrs])
+
+    def step(self, grad_ptrs, stream=0):
+        _ok(_lib.qagg_agg_f64_step(self.h, self._ptrs(grad_ptrs), stream))
+
+    def reset_residuals(self, stream=0):
+        _ok(_lib.qagg_agg_f64_reset_residuals(self.h, stream))
+
+    def residual_ptrs(self, tensor):
+        r, s = c_vp(), c_vp()
+        _ok(_lib.qagg_agg_f64_residuals(self.h, tensor, ctypes.byref(r), ctypes.byref(s)))
+        return r.value, s.value
+
+    def copy_residual(self, tensor, which, dst_ptr, stream=0):
+        _ok(_lib.qagg_agg_f64_copy_residual(self.h, tensor, which, dst_ptr, stream))
+
+    def destroy(self):
+        if self.h:
+            _ok(_lib.qagg_agg_f64_destroy(self.h))
+            self.h = None
+
+
+def step_group_f64(aggs, grad_ptrs, stream=0):
+    """One step of every rank of an in-process group of double aggregators."""
+    K = len(aggs)
+    handles = (c_vp * K)(*[a.h for a in aggs])
+    rows = [a._ptrs(p) for a, p in zip(aggs, grad_ptrs)]
+    table = (ctypes.POINTER(c_vp) * K)(*[ctypes.cast(r, ctypes.POINTER(c_vp)) for r in rows])
+    _ok(_lib.qagg_agg_f64_step_group(handles, K, table, stream))

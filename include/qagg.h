@@ -99,6 +99,23 @@ int qagg_quantize_f64(void* stream, const double* grad, const double* res_in, do
                       int64_t M, int64_t N, int bits, int zero_threshold);
 int qagg_unquantize_f64(void* stream, const void* packed, double* out, int64_t M, int64_t N, int bits, int add);
 
+/* The striped aggregation for double gradients: AllReduceDistGradAggregator<double> (Source/1BitSGD/AllReduceDistGradAggregator.h:237-566;
+ * the reference's 1-bit end-to-end tests run precision=double), composed from qagg_quantize_f64 / qagg_unquantize_f64 one
+ * matrix at a time exactly as the reference composes it from its quantizer; stripes travel by NCCL send/recv (process
+ * groups) or device copies (in-process groups, qagg_agg_f64_step_group).  Flags as for qagg_agg_create.  Bit-identical to
+ * the CPU checker; one launch per matrix and phase, so it is the functional double path, not a tuned one.  Residuals are
+ * plain (never deferred); qagg_agg_f64_residuals hands out the device pointers (stripe pointer for the columns this rank
+ * owns, NULL with one rank). */
+typedef struct qagg_aggregator_f64 qagg_aggregator_f64;
+int qagg_agg_f64_create(qagg_comm* comm, int num_tensors, const int64_t* M, const int64_t* N, int bits, int flags, qagg_aggregator_f64** out);
+int qagg_agg_f64_step(qagg_aggregator_f64* a, double* const* grads, void* stream);
+int qagg_agg_f64_step_group(qagg_aggregator_f64* const* aggs, int num_ranks, double* const* const* grads, void* stream);
+int qagg_agg_f64_reset_residuals(qagg_aggregator_f64* a, void* stream);
+int qagg_agg_f64_residuals(qagg_aggregator_f64* a, int tensor, double** residual, double** stripe_residual);
+/* which: 0 = residual (M x N), 1 = stripe residual (M x owned columns) -> dst (device) */
+int qagg_agg_f64_copy_residual(qagg_aggregator_f64* a, int tensor, int which, double* dst, void* stream);
+int qagg_agg_f64_destroy(qagg_aggregator_f64* a);
+
 /* Batched qagg_quantize that allocates nothing.  It has no counterpart in the reference.
  * For callers that must not allocate device memory at call time -- a plugin whose host framework owns the rest of the
  * card, a step that cannot afford the device-wide stall of cudaMalloc, a component with a memory budget fixed at start-up.

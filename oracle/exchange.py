@@ -30,11 +30,12 @@ class ExchangeState:
     (M x n_rank) of every tensor, zero-initialised (1BitSGD/MatrixQuantizer.h:27-30;
     AllReduceDistGradAggregator.h:87, :97)."""
 
-    def __init__(self, shapes, K):
+    def __init__(self, shapes, K, dtype=np.float32):
         self.shapes = [tuple(s) for s in shapes]  # (M, N) per tensor
         self.K = K
-        self.res = [[np.zeros((N, M), np.float32) for (M, N) in self.shapes] for _ in range(K)]
-        self.sres = [[np.zeros((stripe(N, r, K)[1], M), np.float32) for (M, N) in self.shapes] for r in range(K)]
+        self.dtype = dtype  # np.float64 with the double checkers (ElemType = double)
+        self.res = [[np.zeros((N, M), dtype) for (M, N) in self.shapes] for _ in range(K)]
+        self.sres = [[np.zeros((stripe(N, r, K)[1], M), dtype) for (M, N) in self.shapes] for r in range(K)]
 
     def reset(self):
         """ResetResidue on every quantizer (AllReduceDistGradAggregator.h:121-136)."""

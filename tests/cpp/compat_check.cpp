@@ -551,6 +551,25 @@ int main(int argc, char** argv)
                 if (sgd[1]->TotalNumberOfMinibatchesSeen() != (size_t) iters || sgd[0]->TotalNumberOfSamplesSeen() != sgd[1]->TotalNumberOfSamplesSeen())
                     return 44;
             }
+            // G. the V1 aggregator for double gradients (the float inputs widened), synchronous
+            {
+                AllReduceDistGradAggregator<double> agg(mpi, bits, zeroThr != 0, true, false, 0, 0);
+                Matrix<double> d0(M, N, dev), d1(M, 1, dev);
+                std::vector<Matrix<double>*> dgrads{&d0, &d1};
+                for (int it = 0; it < iters; ++it)
+                {
+                    std::vector<double> w0(mine0[it].begin(), mine0[it].end()), w1(mine1[it].begin(), mine1[it].end());
+                    cudaMemcpy(d0.Data(), w0.data(), w0.size() * 8, cudaMemcpyHostToDevice);
+                    cudaMemcpy(d1.Data(), w1.data(), w1.size() * 8, cudaMemcpyHostToDevice);
+                    fillHeader(hdr);
+                    if (!agg.AggregateGradients(dgrads, hdr, it == 0) || !headerIsSum(hdr))
+                        return 46;
+                    cudaMemcpy(w0.data(), d0.Data(), w0.size() * 8, cudaMemcpyDeviceToHost);
+                    cudaMemcpy(w1.data(), d1.Data(), w1.size() * 8, cudaMemcpyDeviceToHost);
+                    fwrite(w0.data(), 8, w0.size(), fo);
+                    fwrite(w1.data(), 8, w1.size(), fo);
+                }
+            }
             mpi->WaitAll();
             DistGradHeader::Destroy(hdr);
         }

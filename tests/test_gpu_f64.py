@@ -128,3 +128,51 @@ def test_matrix_quantizer_impl_double_like_the_reference_unit_test(env, tmp_path
             assert np.array_equal(dump[off:off + ref.size], ref), f"iteration {it}: {name} differs"
             off += ref.size
     assert off == dump.size
+
+
+@pytest.mark.parametrize("K", [1, 2, 3, 8])
+@pytest.mark.parametrize("bits,zero_thr,self_quant", [(1, True, True), (1, False, True), (1, True, False), (4, True, True), (64, True, True)])
+def test_double_aggregator_bit_exact(env, K, bits, zero_thr, self_quant):
+    """qagg_agg_f64_*: AllReduceDistGradAggregator<double> on an in-process group, four steps with the residuals carried:
+    every rank's aggregate, residual and stripe residual byte-identical to the CPU restatement of the exchange run with
+    the double checker (includes tensors with fewer columns than ranks, single columns, a column taller than one chunk)."""
+    lib, oracle = env
+    from oracle import exchange as ox
+    shapes = [(70, 9), (256, 33), (1500, 2), (64, 1), (5, 16)]
+    flags = (lib.ZERO_THRESHOLD if zero_thr else 0) | (lib.SELF_QUANTIZED if self_quant else 0)
+    comms = lib.Comm.local_group(K, 0)
+    aggs = [lib.AggregatorF64(c, shapes, bits, flags) for c in comms]
+    st = ox.ExchangeState(shapes, K, dtype=np.float64)
+    rng = np.random.default_rng(1000 * K + bits)
+    dev = "cuda:0"
+    try:
+        for step in range(4):
+            grads = [[(rng.standard_normal((N, M)) * 1e-3) for (M, N) in shapes] for _ in range(K)]
+            dg = [[torch.from_numpy(a).to(dev) for a in grads[r]] for r in range(K)]
+            ox.aggregate_step(oracle, st, grads, bits, zero_thr, self_quant)
+            lib.step_group_f64(aggs, [[t.data_ptr() for t in dg[r]] for r in range(K)])
+            torch.cuda.synchronize()
+            for r in range(K):
+                for i, (M, N) in enumerate(shapes):
+                    what = f"K {K} bits {bits} step {step} rank {r} tensor {i}"
+                    assert np.array_equal(dg[r][i].cpu().numpy().view(np.uint64), grads[r][i].view(np.uint64)), "aggregate: " + what
+                    res = torch.zeros((N, M), dtype=torch.float64, device=dev)
+                    aggs[r].copy_residual(i, 0, res.data_ptr())
+                    torch.cuda.synchronize()
+                    assert np.array_equal(res.cpu().numpy().view(np.uint64), st.res[r][i].view(np.uint64)), "residual: " + what
+                    n = ox.stripe(N, r, K)[1]
+                    if K > 1 and n:
+                        sres = torch.zeros((n, M), dtype=torch.float64, device=dev)
+                        aggs[r].copy_residual(i, 1, sres.data_ptr())
+                        torch.cuda.synchronize()
+                        assert np.array_equal(sres.cpu().numpy().view(np.uint64), st.sres[r][i].view(np.uint64)), "stripe residual: " + what
+            if step == 1:
+                for a in aggs:
+                    a.reset_residuals()
+                st.reset()
+    finally:
+        for a in aggs:
+            a.destroy()
+        for c in comms:
+            c.destroy()
+

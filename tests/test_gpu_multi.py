@@ -37,7 +37,7 @@ def test_cpp_mirror_classes_run_a_real_exchange(K, tmp_path, oracle_port):
     file, drive the C++ mirror classes the way SGDLib and the V2 trainer drive the reference's: AllReduceDistGradAggregator,
     V2AllReduceDistGradAggregator (synchronous and buffered asynchronous) over QuantizedMPICommunicator with caller-owned
     residuals, QuantizedDataParallelDistributedLearner (checkpoint zeroes the residuals; over a momentum-SGD learner with and
-    without the update fused into the exchange) and SimpleDistGradAggregator.
+    without the update fused into the exchange), SimpleDistGradAggregator and AllReduceDistGradAggregator<double>.
     Every rank's dumps are compared with the CPU checker bit for bit (the unquantized arm, whose all-reduce order is
     NCCL's, within 1e-5); the DistGradHeader sums are checked inside the program."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < K:
@@ -83,6 +83,12 @@ def test_cpp_mirror_classes_run_a_real_exchange(K, tmp_path, oracle_port):
     stD.reset()                                             # the learner's checkpoint after its first step
     seqD += run_steps(stD, range(1, iters))
     dense = ox.dense_sum([[a for a in inputs[0][r]] for r in range(K)])
+    from oracle import backend as ob
+    st64, seq64, o64 = ox.ExchangeState(shapes, K, dtype=np.float64), [], ob.OracleBackendF64()
+    for it in range(iters):
+        g64 = [[a.astype(np.float64) for a in inputs[it][r]] for r in range(K)]
+        ox.aggregate_step(o64, st64, g64, bits)
+        seq64.append(g64)
     for r in range(K):
         dump = np.fromfile(str(tmp_path / f"out{r}.bin"), dtype=np.float32)
         off = 0
@@ -128,4 +134,8 @@ def test_cpp_mirror_classes_run_a_real_exchange(K, tmp_path, oracle_port):
         for t, shape in enumerate([(N, M), (1, M)]):
             same(take(shape), w[t], f"fused learner: parameters of tensor {t}")
             same(take(shape), sm[t], f"fused learner: smoothed gradients of tensor {t}")
+        for it in range(iters):                             # G: double gradients
+            for t, shape in enumerate([(N, M), (1, M)]):
+                got = take((shape[0], 2 * shape[1])).view(np.float64)
+                assert np.array_equal(got.view(np.uint64), seq64[it][r][t].view(np.uint64)), f"rank {r}: double aggregator step {it} tensor {t}"
         assert off == dump.size
