@@ -6,8 +6,9 @@
 // Kept from the reference: gradients are summed IN PLACE; a rank with numSamples == 0 contributes zero gradients
 // (:283-299); the header is summed over the ranks and the return value is "any samples processed" (:146); sparse gradients
 // are refused; syncStatsTrace > 0 prints "Actual gradient aggregation time" every that many calls.  The pack threshold is
-// accepted and ignored: every tensor is packed.  useAsyncAggregation (double buffering) is not built for this arm: asking
-// for it throws, as an unsupported mode should.
+// accepted and ignored: every tensor is packed.  useFP16AllReduce casts to half, sums as halves and casts back
+// (Source/CNTKv2LibraryDll/DistributedCommunicator.cpp:411-429).  useAsyncAggregation (double buffering) is not built for this
+// arm: asking for it throws, as an unsupported mode should.
 #pragma once
 
 #include <chrono>
@@ -31,8 +32,7 @@ public:
         (void) packThresholdSizeInBytes;
         if (useAsyncAggregation)
             LogicError("SimpleDistGradAggregator: buffered asynchronous aggregation is not implemented for the unquantized arm in this build");
-        if (useFP16AllReduce)
-            LogicError("SimpleDistGradAggregator: the fp16 all-reduce is not implemented in this build");
+        m_fp16 = useFP16AllReduce;
     }
     ~SimpleDistGradAggregator() override
     {
@@ -63,6 +63,7 @@ public:
             N.push_back((int64_t) g->GetNumCols());
         }
         QaggCheck(qagg_dense_create(m_mpi->Handle(), (int) gradients.size(), M.data(), N.data(), &m_agg), "qagg_dense_create");
+        QaggCheck(qagg_dense_set_fp16(m_agg, m_fp16 ? 1 : 0), "qagg_dense_set_fp16");
         m_ptrs.resize(gradients.size());
     }
 
@@ -113,6 +114,7 @@ public:
 
 private:
     int m_deviceId, m_syncStatsTrace;
+    bool m_fp16 = false; // useFP16AllReduce: values travel and are summed as halves
     size_t m_iterationCount = 0;
     qagg_dense_aggregator* m_agg = nullptr;
     std::vector<float*> m_ptrs;

@@ -18,6 +18,8 @@
 #include "qagg_comm.h"
 #include "qagg_device.cuh"
 
+#include <cuda_fp16.h>
+
 #include <algorithm>
 #include <cstring>
 #include <memory>
@@ -89,6 +91,30 @@ __device__ __forceinline__ void dense_store_unit(const DenseTensor& tt, long lon
     if (off + 3 < tt.count) p[3] = v.w;
 }
 
+// ---- fp16 transport (useFP16AllReduce, Source/CNTKv2LibraryDll/DistributedCommunicator.cpp:411-429): the gradients are cast
+// to half (round to nearest), summed as halves, cast back.  A unit is then four halves (8 bytes); the windows keep their
+// fp32 geometry and the half units use the first half of every slot.  The sum of two halves is taken in fp32 and rounded to
+// half (what a half addition without a native instruction does), rank after rank.
+__device__ __forceinline__ uint2 dense_to_half4(const float4& v)
+{
+    const __half2 a = __halves2half2(__float2half_rn(v.x), __float2half_rn(v.y));
+    const __half2 b = __halves2half2(__float2half_rn(v.z), __float2half_rn(v.w));
+    uint2 r;
+    r.x = *reinterpret_cast<const unsigned*>(&a);
+    r.y = *reinterpret_cast<const unsigned*>(&b);
+    return r;
+}
+__device__ __forceinline__ float4 dense_from_half4(const uint2& h)
+{
+    const __half2 a = *reinterpret_cast<const __half2*>(&h.x);
+    const __half2 b = *reinterpret_cast<const __half2*>(&h.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ float dense_half_round(float x)
+{
+    return __half2float(__float2half_rn(x));
+}
+
 // last CTA of a kernel: re-arm the counter and release the peers' flags (every CTA's stores were fenced before its arrival)
 __device__ __forceinline__ void dense_finish(unsigned* counters, const Signal& signal)
 {
@@ -105,6 +131,7 @@ __device__ __forceinline__ void dense_finish(unsigned* counters, const Signal& s
     }
 }
 
+template <bool HALF>
 __global__ void __launch_bounds__(DT) k_dense_scatter(const DenseTensor* __restrict__ tensors, int nT, long long total4, long long slice4,
                                                       const DensePeers dst, unsigned* __restrict__ counters, const Signal signal)
 {
@@ -114,17 +141,39 @@ __global__ void __launch_bounds__(DT) k_dense_scatter(const DenseTensor* __restr
         cur = dense_find(tensors, nT, u, cur);
         const float4 v = dense_load_unit(tensors[cur], u);
         const int p = (int) (u / slice4);
-        reinterpret_cast<float4*>(dst.base[p])[u - (long long) p * slice4] = v;
+        if (HALF)
+            reinterpret_cast<uint2*>(dst.base[p])[u - (long long) p * slice4] = dense_to_half4(v);
+        else
+            reinterpret_cast<float4*>(dst.base[p])[u - (long long) p * slice4] = v;
     }
     dense_finish(counters, signal);
 }
 
 // recv: this rank's receive window, K slots of slice4 units (slot s = rank s's floats of this rank's slice)
+template <bool HALF>
 __global__ void __launch_bounds__(DT) k_dense_reduce(const float4* __restrict__ recv, int K, long long slice4, long long mine4, int rank,
                                                      const DensePeers dst, unsigned* __restrict__ counters, const Signal signal)
 {
     for (long long j = (long long) blockIdx.x * DT + threadIdx.x; j < mine4; j += (long long) gridDim.x * DT)
     {
+        if (HALF)
+        {
+            // slot src starts where it does in fp32 geometry: 2 * slice4 eight-byte units further on
+            const uint2* recv2 = reinterpret_cast<const uint2*>(recv);
+            float4 s = dense_from_half4(__ldcs(recv2 + j));
+            for (int src = 1; src < K; ++src)
+            {
+                const float4 v = dense_from_half4(__ldcs(recv2 + 2 * (long long) src * slice4 + j));
+                s.x = dense_half_round(__fadd_rn(s.x, v.x));
+                s.y = dense_half_round(__fadd_rn(s.y, v.y));
+                s.z = dense_half_round(__fadd_rn(s.z, v.z));
+                s.w = dense_half_round(__fadd_rn(s.w, v.w));
+            }
+            const uint2 h = dense_to_half4(s);
+            for (int p = 0; p < dst.K; ++p)
+                reinterpret_cast<uint2*>(dst.base[p])[2 * (long long) rank * slice4 + j] = h;
+            continue;
+        }
         float4 s = __ldcs(recv + j);
         for (int src = 1; src < K; ++src)
         {
@@ -140,24 +189,38 @@ __global__ void __launch_bounds__(DT) k_dense_reduce(const float4* __restrict__ 
     dense_finish(counters, signal);
 }
 
-__global__ void __launch_bounds__(DT) k_dense_unpack(const float4* __restrict__ flat, const DenseTensor* __restrict__ tensors, int nT, long long total4)
+// HALF: unit u of slice p sits at eight-byte unit p * sliceStride + (u - p * slice4) of `flat` (sliceStride = 2 * slice4 in a
+// window with fp32 geometry, slice4 in a contiguous buffer)
+template <bool HALF>
+__global__ void __launch_bounds__(DT) k_dense_unpack(const float4* __restrict__ flat, const DenseTensor* __restrict__ tensors, int nT, long long total4,
+                                                     long long slice4, long long sliceStride)
 {
     int cur = 0;
     for (long long u = (long long) blockIdx.x * DT + threadIdx.x; u < total4; u += (long long) gridDim.x * DT)
     {
         cur = dense_find(tensors, nT, u, cur);
-        dense_store_unit(tensors[cur], u, __ldcs(flat + u));
+        if (HALF)
+        {
+            const long long p = u / slice4;
+            dense_store_unit(tensors[cur], u, dense_from_half4(__ldcs(reinterpret_cast<const uint2*>(flat) + p * sliceStride + (u - p * slice4))));
+        }
+        else
+            dense_store_unit(tensors[cur], u, __ldcs(flat + u));
     }
 }
 
 // NCCL path: gradients -> flat buffer
+template <bool HALF>
 __global__ void __launch_bounds__(DT) k_dense_pack(float4* __restrict__ flat, const DenseTensor* __restrict__ tensors, int nT, long long total4)
 {
     int cur = 0;
     for (long long u = (long long) blockIdx.x * DT + threadIdx.x; u < total4; u += (long long) gridDim.x * DT)
     {
         cur = dense_find(tensors, nT, u, cur);
-        flat[u] = dense_load_unit(tensors[cur], u);
+        if (HALF)
+            reinterpret_cast<uint2*>(flat)[u] = dense_to_half4(dense_load_unit(tensors[cur], u));
+        else
+            flat[u] = dense_load_unit(tensors[cur], u);
     }
 }
 
@@ -189,6 +252,7 @@ struct qagg_dense_aggregator
     unsigned stepNo = 0;
     long long waitPolls = 20000000;
     int numSMs = 0;
+    bool fp16 = false; // values travel and are summed as halves
 
     float* recv(unsigned char* win) const { return reinterpret_cast<float*>(win + kFlagBytes); }
     float* gather(unsigned char* win) const { return recv(win) + (size_t) K * (size_t) slice4 * 4; }
@@ -352,8 +416,12 @@ static int dense_scatter(qagg_dense_aggregator* a, cudaStream_t st)
             sg.flag[sg.n++] = a->flags(a->peerWin[p]) + a->rank;
     }
     sg.value = a->stepNo;
-    k_dense_scatter<<<dense_grid(a, a->total4), DT, 0, st>>>(static_cast<const DenseTensor*>(a->table), a->T, a->total4, a->slice4, dst,
-                                                              static_cast<unsigned*>(a->queue), sg);
+    if (a->fp16)
+        k_dense_scatter<true><<<dense_grid(a, a->total4), DT, 0, st>>>(static_cast<const DenseTensor*>(a->table), a->T, a->total4, a->slice4, dst,
+                                                                        static_cast<unsigned*>(a->queue), sg);
+    else
+        k_dense_scatter<false><<<dense_grid(a, a->total4), DT, 0, st>>>(static_cast<const DenseTensor*>(a->table), a->T, a->total4, a->slice4, dst,
+                                                                         static_cast<unsigned*>(a->queue), sg);
     return check_cuda(cudaGetLastError(), "dense scatter launch");
 }
 
@@ -377,16 +445,24 @@ static int dense_reduce(qagg_dense_aggregator* a, cudaStream_t st)
     sg.value = a->stepNo;
     const long long first = (long long) a->rank * a->slice4;
     const long long mine4 = std::max<long long>(0, std::min(a->slice4, a->total4 - first));
-    k_dense_reduce<<<dense_grid(a, std::max<long long>(mine4, 1)), DT, 0, st>>>(reinterpret_cast<const float4*>(a->recv(static_cast<unsigned char*>(a->window))),
-                                                                                 a->K, a->slice4, mine4, a->rank, dst,
-                                                                                 static_cast<unsigned*>(a->queue) + QAGG_COUNTER_UINTS, sg);
+    const float4* recv = reinterpret_cast<const float4*>(a->recv(static_cast<unsigned char*>(a->window)));
+    unsigned* counters = static_cast<unsigned*>(a->queue) + QAGG_COUNTER_UINTS;
+    if (a->fp16)
+        k_dense_reduce<true><<<dense_grid(a, std::max<long long>(mine4, 1)), DT, 0, st>>>(recv, a->K, a->slice4, mine4, a->rank, dst, counters, sg);
+    else
+        k_dense_reduce<false><<<dense_grid(a, std::max<long long>(mine4, 1)), DT, 0, st>>>(recv, a->K, a->slice4, mine4, a->rank, dst, counters, sg);
     return check_cuda(cudaGetLastError(), "dense reduce launch");
 }
 
-static int dense_unpack(qagg_dense_aggregator* a, cudaStream_t st)
+// contiguous: the half units lie back to back (the all-reduced buffer of the NCCL path), not in fp32 slice geometry
+static int dense_unpack(qagg_dense_aggregator* a, cudaStream_t st, bool contiguous = false)
 {
-    k_dense_unpack<<<dense_grid(a, a->total4), DT, 0, st>>>(reinterpret_cast<const float4*>(a->gather(static_cast<unsigned char*>(a->window))),
-                                                             static_cast<const DenseTensor*>(a->table), a->T, a->total4);
+    const float4* flat = reinterpret_cast<const float4*>(a->gather(static_cast<unsigned char*>(a->window)));
+    const DenseTensor* table = static_cast<const DenseTensor*>(a->table);
+    if (a->fp16)
+        k_dense_unpack<true><<<dense_grid(a, a->total4), DT, 0, st>>>(flat, table, a->T, a->total4, a->slice4, contiguous ? a->slice4 : 2 * a->slice4);
+    else
+        k_dense_unpack<false><<<dense_grid(a, a->total4), DT, 0, st>>>(flat, table, a->T, a->total4, a->slice4, a->slice4);
     return check_cuda(cudaGetLastError(), "dense unpack launch");
 }
 
@@ -413,13 +489,16 @@ int qagg_dense_step(qagg_dense_aggregator* a, float* const* grads, void* stream)
     }
     // baseline path: one all-reduce of the flat buffer (kept in the gather area of the window)
     float* flat = a->gather(static_cast<unsigned char*>(a->window));
-    k_dense_pack<<<dense_grid(a, a->total4), DT, 0, st>>>(reinterpret_cast<float4*>(flat), static_cast<const DenseTensor*>(a->table), a->T, a->total4);
+    if (a->fp16)
+        k_dense_pack<true><<<dense_grid(a, a->total4), DT, 0, st>>>(reinterpret_cast<float4*>(flat), static_cast<const DenseTensor*>(a->table), a->T, a->total4);
+    else
+        k_dense_pack<false><<<dense_grid(a, a->total4), DT, 0, st>>>(reinterpret_cast<float4*>(flat), static_cast<const DenseTensor*>(a->table), a->T, a->total4);
     if ((rc = check_cuda(cudaGetLastError(), "dense pack launch")))
         return rc;
-    const ncclResult_t nr = ncclAllReduce(flat, flat, (size_t) a->total4 * 4, ncclFloat, ncclSum, a->nccl, st);
+    const ncclResult_t nr = ncclAllReduce(flat, flat, (size_t) a->total4 * 4, a->fp16 ? ncclHalf : ncclFloat, ncclSum, a->nccl, st);
     if (nr != ncclSuccess)
         return fail(QAGG_ENCCL, std::string("ncclAllReduce: ") + ncclGetErrorString(nr));
-    return dense_unpack(a, st);
+    return dense_unpack(a, st, true);
 }
 
 int qagg_dense_step_group(qagg_dense_aggregator* const* aggs, int num_ranks, float* const* const* grads, void* stream)
@@ -466,6 +545,14 @@ int qagg_dense_step_group(qagg_dense_aggregator* const* aggs, int num_ranks, flo
     return QAGG_OK;
 }
 
+int qagg_dense_set_fp16(qagg_dense_aggregator* a, int enabled)
+{
+    if (!a)
+        return fail(QAGG_EINVAL, "null aggregator");
+    a->fp16 = enabled != 0;
+    return QAGG_OK;
+}
+
 int qagg_dense_check(qagg_dense_aggregator* a, void* stream)
 {
     if (!a)
@@ -488,7 +575,7 @@ int64_t qagg_dense_wire_bytes(const qagg_dense_aggregator* a)
     if (!a)
         return fail(QAGG_EINVAL, "null aggregator");
     // scatter: every slice but the own one leaves; gather: the own slice goes to every peer
-    return a->K > 1 ? 2 * (int64_t) (a->K - 1) * a->slice4 * 16 : 0;
+    return a->K > 1 ? 2 * (int64_t) (a->K - 1) * a->slice4 * (a->fp16 ? 8 : 16) : 0;
 }
 
 int qagg_dense_destroy(qagg_dense_aggregator* a)

@@ -31,7 +31,7 @@ EXPORTS = [
     "qagg_packed_col_bytes_f64", "qagg_packed_bytes_f64", "qagg_quantize_f64", "qagg_unquantize_f64",
     "qagg_sgd_update", "qagg_unquantize_sgd", "qagg_agg_bind_update", "qagg_agg_set_update", "qagg_agg_clear_status",
     "qagg_agg_f64_create", "qagg_agg_f64_step", "qagg_agg_f64_step_group", "qagg_agg_f64_reset_residuals", "qagg_agg_f64_residuals",
-    "qagg_agg_f64_destroy", "qagg_agg_f64_copy_residual",
+    "qagg_agg_f64_destroy", "qagg_agg_f64_copy_residual", "qagg_dense_set_fp16",
 ]
 
 
@@ -100,6 +100,7 @@ _lib.qagg_agg_f64_step_group.argtypes = [ctypes.POINTER(c_vp), c_int, ctypes.POI
 _lib.qagg_agg_f64_reset_residuals.argtypes = [c_vp, c_vp]
 _lib.qagg_agg_f64_residuals.argtypes = [c_vp, c_int, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
 _lib.qagg_agg_f64_destroy.argtypes = [c_vp]
+_lib.qagg_dense_set_fp16.argtypes = [c_vp, c_int]
 _lib.qagg_agg_f64_copy_residual.argtypes = [c_vp, c_int, c_int, c_vp, c_vp]
 _lib.qagg_agg_bind_update.argtypes = [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp)]
 _lib.qagg_agg_set_update.argtypes = [c_vp, c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float]
@@ -456,6 +457,9 @@ class DenseAggregator:
         h = c_vp()
         _ok(_lib.qagg_dense_create(comm.h, T, Ms, Ns, ctypes.byref(h)))
         self.h = h
+
+    def set_fp16(self, enabled):
+        _ok(_lib.qagg_dense_set_fp16(self.h, int(bool(enabled))))
 
     def step(self, grad_ptrs, stream=0):
         _ok(_lib.qagg_dense_step(self.h, (c_vp * len(grad_ptrs))(*[c_vp(p) for p in grad_ptrs]), stream))

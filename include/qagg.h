@@ -314,6 +314,11 @@ int qagg_dense_step(qagg_dense_aggregator* a, float* const* grads, void* stream)
 int qagg_dense_step_group(qagg_dense_aggregator* const* aggs, int num_ranks, float* const* const* grads, void* stream);
 int qagg_dense_peer_handle(qagg_dense_aggregator* a, void* out);
 int qagg_dense_enable_peer(qagg_dense_aggregator* a, const void* handles);
+/* useFP16AllReduce (Source/CNTKv2LibraryDll/DistributedCommunicator.cpp:411-429; SGD.cpp:3327-3329): the gradients are cast
+ * to half (round to nearest), exchanged and summed as halves, and cast back -- half the wire bytes.  On the peer-memory path
+ * the sum runs in ascending rank order, each addition taken in fp32 and rounded to half; on the NCCL path the order and the
+ * intermediate precision are NCCL's.  Takes effect from the next step. */
+int qagg_dense_set_fp16(qagg_dense_aggregator* a, int enabled);
 int qagg_dense_check(qagg_dense_aggregator* a, void* stream);
 int64_t qagg_dense_wire_bytes(const qagg_dense_aggregator* a);
 int qagg_dense_destroy(qagg_dense_aggregator* a);

@@ -188,3 +188,17 @@ def dense_sum(grads):
             acc = (acc + grads[r][i]).astype(np.float32)
         out.append(acc)
     return out
+
+
+def dense_sum_fp16(grads):
+    """useFP16AllReduce (Source/CNTKv2LibraryDll/DistributedCommunicator.cpp:411-429): every rank's tensor is cast to half,
+    the halves are added in ascending rank order (each sum taken in fp32 and rounded to half), and the result is cast back
+    to fp32.  The reference leaves the order and the intermediate precision to MPI / NCCL; this fixes them."""
+    K = len(grads)
+    out = []
+    for i in range(len(grads[0])):
+        acc = grads[0][i].astype(np.float16)
+        for r in range(1, K):
+            acc = (acc.astype(np.float32) + grads[r][i].astype(np.float16).astype(np.float32)).astype(np.float16)
+        out.append(acc.astype(np.float32))
+    return out

@@ -95,3 +95,42 @@ def test_dense_unaligned_tensors_and_empty_ones(lib):
             a.destroy()
         for c in comms:
             c.destroy()
+
+
+@pytest.mark.parametrize("K", [2, 3, 8])
+def test_dense_fp16_transport_bit_exact(lib, K):
+    """useFP16AllReduce: values cast to half, summed as halves in ascending rank order, cast back (oracle.exchange.dense_sum_fp16);
+    switching it off again gives the fp32 sum; the wire bytes halve."""
+    dev = "cuda:0"
+    comms = lib.Comm.local_group(K, 0)
+    aggs = [lib.DenseAggregator(c, SHAPES) for c in comms]
+    hs = [a.peer_handle() for a in aggs]
+    for a in aggs:
+        a.enable_peer(hs)
+    rng = np.random.default_rng(29 + K)
+    try:
+        full = aggs[0].wire_bytes
+        for step in range(4):
+            half = step != 2
+            for a in aggs:
+                a.set_fp16(half)
+            # values across the half range, including some that overflow it and some below its smallest subnormal
+            host = [[(rng.standard_normal((N, M)) * 10.0 ** rng.integers(-9, 6, size=(N, M))).astype(np.float32) for (M, N) in SHAPES] for _ in range(K)]
+            dg = [[torch.from_numpy(a).to(dev) for a in host[r]] for r in range(K)]
+            lib.dense_step_group(aggs, [[t.data_ptr() for t in dg[r]] for r in range(K)])
+            torch.cuda.synchronize()
+            with np.errstate(over="ignore", invalid="ignore"):
+                want = ox.dense_sum_fp16(host) if half else ox.dense_sum(host)
+            for r in range(K):
+                for i in range(len(SHAPES)):
+                    got = dg[r][i].cpu().numpy()
+                    same = (got.view(np.uint32) == want[i].view(np.uint32)) | (np.isnan(got) & np.isnan(want[i]))
+                    assert same.all(), f"step {step} rank {r} tensor {i} (fp16 {half})"
+            assert aggs[0].wire_bytes == (full // 2 if half else full)
+        for a in aggs:
+            a.check()
+    finally:
+        for a in aggs:
+            a.destroy()
+        for c in comms:
+            c.destroy()
