@@ -176,6 +176,20 @@ struct qagg_aggregator
     // owner kernels, tall matrices apart: their table entries, form units and walk items come first (see launch_owner)
     OwnerSplit k2Split = {};
     bool k2SplitOn = false;
+    // Quantize kernel, very tall matrices apart (1 bit, threshold 0, whole tensors only): a column of tens of thousands of
+    // rows is one long chain of dependent adds, which the streaming kernel walks a chunk at a time with a fixed cost per
+    // chunk.  Such matrices go through the owner's form + walk kernel pair instead (one table entry per owner's stripe, the
+    // raw gradient as the only source), the walk beside the streaming kernel of the other matrices.
+    std::vector<QTensor> hK1t;
+    std::vector<int> k1tTensor;          // tensor index of each entry
+    std::vector<long long> k1tCol;       // first column (of the tensor) of each entry
+    std::vector<QItem> iK1t;
+    long long k1tUnits = 0;
+    QTensor* dK1t = nullptr;
+    QItem* dI1t = nullptr;
+    DevBuf k1tMaps, k1tStats, k1tCounters;
+    cudaStream_t k1Side = nullptr;
+    cudaEvent_t k1Fork = nullptr, k1Join = nullptr;
     // the stream the last step was enqueued on: calls that rewrite what that step reads (tables, tensor maps, residual
     // state) from another stream wait for it first
     cudaStream_t lastStream = nullptr;
@@ -202,8 +216,8 @@ struct qagg_aggregator
     struct Binding
     {
         std::vector<float*> grads;
-        QTensor *dK1 = nullptr, *dK2 = nullptr, *dK3 = nullptr;
-        QItem *dI1 = nullptr, *dI2 = nullptr;
+        QTensor *dK1 = nullptr, *dK2 = nullptr, *dK3 = nullptr, *dK1t = nullptr;
+        QItem *dI1 = nullptr, *dI2 = nullptr, *dI1t = nullptr;
     };
     Binding bindings[2];
     int curBinding = 0;
@@ -233,6 +247,12 @@ struct qagg_aggregator
             for (auto& e : slot)
                 if (e)
                     cudaEventDestroy(e);
+        if (k1Fork)
+            cudaEventDestroy(k1Fork);
+        if (k1Join)
+            cudaEventDestroy(k1Join);
+        if (k1Side)
+            cudaStreamDestroy(k1Side);
         if (k2Split.fork)
             cudaEventDestroy(k2Split.fork);
         if (k2Split.join)
@@ -455,6 +475,86 @@ int build_tables(qagg_aggregator* a)
         std::vector<std::pair<long long, long long>> k1Shapes;
         for (int i = 0; i < T; ++i)
             k1Shapes.push_back({a->M[i], (a->M[i] > 0 && a->N[i] > 0) ? a->N[i] : 0});
+        // very tall matrices leave the streaming kernel (tuning knob, results never change: QAGG_TALL_ROWS=<rows>, 0 = never)
+        long long tallRows = 16384;
+        if (const char* e = std::getenv("QAGG_TALL_ROWS"))
+            tallRows = std::atoll(e);
+        a->hK1t.clear();
+        a->k1tTensor.clear();
+        a->k1tCol.clear();
+        a->iK1t.clear();
+        a->k1tUnits = 0;
+        std::vector<std::pair<long long, long long>> tallShapes;
+        long long tallCols = 0;
+        for (int i = 0; i < T; ++i)
+        {
+            const bool whole = a->col0[i] == 0 && a->parentN[i] == a->N[i];
+            if (!(tallRows > 0 && a->M[i] >= tallRows && a->N[i] > 0 && (a->M[i] & 3) == 0 && whole && a->bits == 1))
+                continue;
+            k1Shapes[i].second = 0; // no streaming work items for this matrix
+            for (int p = 0; p < K; ++p)
+            {
+                const long long s0 = (K == 1) ? 0 : a->sStart[p][i], n = (K == 1) ? a->N[i] : a->sN[p][i];
+                if (n <= 0)
+                    continue;
+                QTensor e = {};
+                fill_layout(&e, a->M[i], n, a->bits);
+                e.res_in = e.res_out = a->res[i] + s0 * a->M[i];
+                e.lv = a->lv[i] + 2 * s0;
+                e.nsrc = 1;
+                e.selfRaw = 1;
+                e.pk[0] = a->hK1[i].pk[p]; // owner p's block of this matrix: its first column is that owner's stripe start
+                e.unit0 = a->k1tUnits;
+                a->k1tUnits += owner_form_units(a->M[i], n);
+                a->hK1t.push_back(e);
+                a->k1tTensor.push_back(i);
+                a->k1tCol.push_back(s0);
+                tallShapes.push_back({a->M[i], n});
+                tallCols += n;
+            }
+        }
+        if (!a->hK1t.empty())
+        {
+            int rc;
+            if (!a->k1tStats.p || a->k1tStats.bytes < (size_t) tallCols * 8)
+            {
+                if (a->k1tStats.p)
+                    cudaFree(a->k1tStats.p);
+                a->k1tStats.p = nullptr;
+                if ((rc = a->k1tStats.alloc((size_t) tallCols * 8, true)))
+                    return rc;
+            }
+            if (!a->k1tMaps.p || a->k1tMaps.bytes < a->hK1t.size() * 128)
+            {
+                if (a->k1tMaps.p)
+                    cudaFree(a->k1tMaps.p);
+                a->k1tMaps.p = nullptr;
+                if ((rc = a->k1tMaps.alloc(a->hK1t.size() * 128, true)))
+                    return rc;
+            }
+            if (!a->k1tCounters.p && (rc = a->k1tCounters.alloc(QAGG_COUNTER_UINTS * sizeof(unsigned), true)))
+                return rc;
+            long long col = 0;
+            std::vector<unsigned char> maps(a->hK1t.size() * 128);
+            bool mapsOk = true;
+            for (size_t e = 0; e < a->hK1t.size(); ++e)
+            {
+                a->hK1t[e].stats = static_cast<unsigned*>(a->k1tStats.p) + 2 * col;
+                col += a->hK1t[e].N;
+                mapsOk = owner_set_map(&a->hK1t[e], maps.data() + e * 128, static_cast<unsigned char*>(a->k1tMaps.p) + e * 128) && mapsOk;
+            }
+            (void) mapsOk; // an entry without a map is walked from global memory by the walk kernel
+            if ((rc = check_cuda(cudaMemcpy(a->k1tMaps.p, maps.data(), maps.size(), cudaMemcpyHostToDevice), "tensor map upload")))
+                return rc;
+            owner_make_items(tallShapes, a->iK1t);
+            if (!a->k1Side)
+            {
+                if ((rc = check_cuda(cudaStreamCreateWithFlags(&a->k1Side, cudaStreamNonBlocking), "cudaStreamCreate")) ||
+                    (rc = check_cuda(cudaEventCreateWithFlags(&a->k1Fork, cudaEventDisableTiming), "cudaEventCreate")) ||
+                    (rc = check_cuda(cudaEventCreateWithFlags(&a->k1Join, cudaEventDisableTiming), "cudaEventCreate")))
+                    return rc;
+            }
+        }
         std::vector<std::pair<int, int>> box;
         stream_make_items(k1Shapes, a->cfg.numSMs, a->bits, a->iK1, box);
         for (int i = 0; i < T; ++i)
@@ -496,8 +596,8 @@ int build_tables(qagg_aggregator* a)
 
 size_t table_bytes(const qagg_aggregator* a)
 {
-    return (a->hK1.size() + a->hK2.size() + a->hK3.size()) * sizeof(QTensor) +
-           (a->iK1.size() + a->iK2.size()) * sizeof(QItem) + 256;
+    return (a->hK1.size() + a->hK2.size() + a->hK3.size() + a->hK1t.size()) * sizeof(QTensor) +
+           (a->iK1.size() + a->iK2.size() + a->iK1t.size()) * sizeof(QItem) + 256;
 }
 
 // copies the host tables to table set `slot` on the device (synchronously: only when a new array of gradient pointers is bound)
@@ -527,6 +627,10 @@ int upload_tables(qagg_aggregator* a, int slot)
         return rc;
     if ((rc = put(a->iK2.data(), a->iK2.size() * sizeof(QItem), (void**) &a->dI2)))
         return rc;
+    if ((rc = put(a->hK1t.data(), a->hK1t.size() * sizeof(QTensor), (void**) &a->dK1t)))
+        return rc;
+    if ((rc = put(a->iK1t.data(), a->iK1t.size() * sizeof(QItem), (void**) &a->dI1t)))
+        return rc;
     return QAGG_OK;
 }
 
@@ -546,6 +650,8 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
             a->dK3 = b.dK3;
             a->dI1 = b.dI1;
             a->dI2 = b.dI2;
+            a->dK1t = b.dK1t;
+            a->dI1t = b.dI1t;
             return QAGG_OK;
         }
     }
@@ -564,6 +670,8 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
         const int i = a->k2Tensor[e];
         a->hK2[e].grad = grads[i] + a->sStart[r][i] * a->M[i];
     }
+    for (size_t e = 0; e < a->hK1t.size(); ++e)
+        a->hK1t[e].grad = grads[a->k1tTensor[e]] + a->k1tCol[e] * a->M[a->k1tTensor[e]];
     // an earlier step may still be reading the tables of that set -- on this stream or on the one it was enqueued on
     int rc = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize");
     if (rc)
@@ -590,6 +698,8 @@ int bind_grads(qagg_aggregator* a, float* const* grads, cudaStream_t st)
     b.dK3 = a->dK3;
     b.dI1 = a->dI1;
     b.dI2 = a->dI2;
+    b.dK1t = a->dK1t;
+    b.dI1t = a->dI1t;
     a->curBinding = slot;
     return QAGG_OK;
 }
@@ -629,6 +739,29 @@ Signal make_signal(const qagg_aggregator* a, bool gatherPhase)
 int launch_k1(qagg_aggregator* a, cudaStream_t st)
 {
     const Signal sg = make_signal(a, false);
+    if (a->deferred && !a->hK1t.empty())
+    {
+        // Very tall matrices: formed first, then walked on this stream while the streaming kernel takes the other matrices on
+        // a second stream (it is made to wait for the form launch only so that the walk, a same-stream successor, gets its
+        // SMs first: one walk CTA fills an SM's shared memory).  The flags are released by a kernel of their own once both
+        // are done; the header values still ride with the streaming kernel.
+        Signal quiet = sg;
+        quiet.n = 0;
+        int rc = check_cuda(launch_owner(st, a->dK1t, (int) a->hK1t.size(), a->k1tUnits, a->dI1t, (int) a->iK1t.size(), a->cfg,
+                                         static_cast<unsigned*>(a->k1tCounters.p), nullptr, a->status_word(), nullptr, a->k1Fork), "quantize launch (tall matrices)");
+        if (rc)
+            return rc;
+        if ((rc = check_cuda(cudaStreamWaitEvent(a->k1Side, a->k1Fork, 0), "cudaStreamWaitEvent")))
+            return rc;
+        if (!a->iK1.empty() &&
+            (rc = check_cuda(launch_stream1(a->k1Side, a->dK1, a->dI1, (int) a->iK1.size(), a->cfg, static_cast<unsigned*>(a->queue.p), &quiet, a->status_word()),
+                             "quantize launch")))
+            return rc;
+        if ((rc = check_cuda(cudaEventRecord(a->k1Join, a->k1Side), "cudaEventRecord")) ||
+            (rc = check_cuda(cudaStreamWaitEvent(st, a->k1Join, 0), "cudaStreamWaitEvent")))
+            return rc;
+        return sg.n > 0 ? check_cuda(launch_signal_only(st, sg), "flag release launch") : QAGG_OK;
+    }
     if (a->deferred)
         return check_cuda(launch_stream1(st, a->dK1, a->dI1, (int) a->iK1.size(), a->cfg, static_cast<unsigned*>(a->queue.p), &sg, a->status_word()),
                           "quantize launch");
@@ -2061,7 +2194,8 @@ int qagg_agg_launches_per_step(const qagg_aggregator* a)
     // quantize, owner (one kernel, or form + walk, or both twice when the tall matrices go apart), unquantize; + two flag waits
     // (+ the gather push) (+ a header push when the last step carried a header that the quantize kernel did not take along)
     // in peer mode
-    return 3 + (a->deferredOwner ? (a->k2SplitOn ? 3 : 1) : 0) +
+    const int tall = a->hK1t.empty() ? 0 : 2 + (a->peer ? 1 : 0) - (a->iK1.empty() ? 1 : 0); // form, walk, flag release; no streaming launch
+    return 3 + tall + (a->deferredOwner ? (a->k2SplitOn ? 3 : 1) : 0) +
            (a->peer ? 2 + (a->pushGather ? 1 : 0) + ((a->hdrN > 0 && !header_rides_with_k1(a)) ? 1 : 0) : 0);
 }
 

@@ -223,7 +223,8 @@ struct OwnerSplit
 };
 cudaError_t launch_owner(cudaStream_t st, const QTensor* tensors, int nTensors, long long formUnits, const QItem* items, int nItems,
                          const LaunchCfg& cfg, unsigned* counters, const Signal* signal = nullptr, unsigned* status = nullptr,
-                         const OwnerSplit* split = nullptr);
+                         const OwnerSplit* split = nullptr, cudaEvent_t afterForm = nullptr);
+// (afterForm: recorded on `st` between the form and the walk launch of the unsplit sequence)
 // runs the streaming kernel's bounded mbarrier wait on a barrier that nothing completes (see qagg_stream_wait_selftest)
 cudaError_t launch_stream_wait_selftest(cudaStream_t st, int maxTries, unsigned* status, long long* cycles);
 // dst[i, j] = buf[i, j] - (buf[i, j] >= 0 ? lv[2j + 1] : lv[2j]): the residual proper of a deferred state (dst may be buf)

@@ -523,7 +523,7 @@ static int form_grid(long long totalUnits, int numSMs)
 }
 
 cudaError_t launch_owner(cudaStream_t st, const QTensor* tensors, int nTensors, long long formUnits, const QItem* items, int nItems,
-                         const LaunchCfg& cfg, unsigned* counters, const Signal* signalp, unsigned* status, const OwnerSplit* split)
+                         const LaunchCfg& cfg, unsigned* counters, const Signal* signalp, unsigned* status, const OwnerSplit* split, cudaEvent_t afterForm)
 {
     static const Signal none = {};
     const Signal& signal = signalp ? *signalp : none;
@@ -563,6 +563,8 @@ cudaError_t launch_owner(cudaStream_t st, const QTensor* tensors, int nTensors, 
     }
     k_owner_form<<<form_grid(formUnits, cfg.numSMs), NT, 0, st>>>(tensors, nTensors, 0, formUnits, signal);
     if ((e = cudaGetLastError()) != cudaSuccess)
+        return e;
+    if (afterForm && (e = cudaEventRecord(afterForm, st)) != cudaSuccess)
         return e;
     int grid = cfg.numSMs; // one CTA per SM: the ring takes most of an SM's shared memory
     if (grid > nItems)

@@ -243,17 +243,24 @@ def test_lstm_shaped_set_ragged(G, oracle_port, K):
     run_group(G, oracle_port, LSTM_SMALL, K, 1, True, True, 10, lstm_inputs, check_every=5)
 
 
-@pytest.mark.parametrize("knob", ["QAGG_STREAM", "QAGG_OWNER", "QAGG_OWNER_SPLIT"])
-def test_kernel_choice_knob_changes_no_result(G, oracle_port, knob, monkeypatch):
+@pytest.mark.parametrize("knob,value", [("QAGG_STREAM", "0"), ("QAGG_OWNER", "0"), ("QAGG_OWNER_SPLIT", "0"), ("QAGG_TALL_ROWS", "1000"),
+                                        ("QAGG_TALL_ROWS", "200")])
+def test_kernel_choice_knob_changes_no_result(G, oracle_port, knob, value, monkeypatch):
     """Tuning knobs read when an aggregator is created: QAGG_STREAM=0 = resident-column kernels only (plain residuals),
     QAGG_OWNER=0 = resident-column kernel for the owner's reduce-requantize only (plain stripe residuals),
-    QAGG_OWNER_SPLIT=0 = one form and one walk launch instead of the tall matrices' walk on a stream of its own.  Either way
+    QAGG_OWNER_SPLIT=0 = one form and one walk launch instead of the tall matrices' walk on a stream of its own,
+    QAGG_TALL_ROWS=n = matrices of n rows or more leave the streaming quantize kernel for the form + walk pair (default
+    16384; here 1000 takes the tall matrix of the set, 200 all but the smallest, so the pair runs beside the streaming
+    kernel and alone).  Either way
     aggregates, both residual sets and the gathered packed words stay bit-identical to the oracle (the default -- streaming
     quantize kernel, form + walk owner kernels, both residual sets deferred -- is what every other 1-bit zero-threshold
     test in this file runs)."""
-    monkeypatch.setenv(knob, "0")
+    monkeypatch.setenv(knob, value)
     run_group(G, oracle_port, SPEECH_SMALL, 3, 1, True, True, 6, speech_inputs, check_every=3)
     run_group(G, oracle_port, mg.EXCHANGE_SHAPES, 2, 1, True, False, 4, mg.exchange_inputs, peer=True)
+    if knob == "QAGG_TALL_ROWS":
+        run_group(G, oracle_port, SPEECH_SMALL, 1, 1, True, True, 4, speech_inputs)
+        run_group(G, oracle_port, LSTM_SMALL, 4, 1, True, True, 4, lstm_inputs, peer=True)
 
 
 @pytest.mark.parametrize("K,peer", [(1, False), (2, False), (3, True), (8, True)])
