@@ -166,6 +166,14 @@ def cpu_reference_run(shapes, bits, K, steps, warmup):
                       f"{K} simulated rank(s) on {cores} host thread(s)"}
 
 
+def workload_config(workload, shapes, V, bits, K):
+    """The `config` object of a bench line: what is computed, identical for this build's arm and the reference arm (what
+    differs between the arms -- transport, timing method, host binding -- goes under "arm")."""
+    return {"workload": workload, "tensors": len(shapes), "values_per_rank": V, "bits": bits, "zero_threshold": True,
+            "self_stripe_quantized": True, "parallelism": f"dp{K} striped by columns",
+            "l2": f"inputs ({8 * V / 1e6:.0f} MB gradient + residual per rank and step) exceed the 126 MB L2"}
+
+
 def run_reference(args):
     rank, _, world = dist_env()
     if rank != 0:
@@ -180,9 +188,9 @@ def run_reference(args):
             "steps_cap": f"a full-size CPU step takes about a second: at most {REFERENCE_STEP_CAP} timed steps and 1 warm-up",
             "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "tensors": len(shapes), "values_per_rank": r["values_per_rank"], "bits": bits,
-                       "zero_threshold": True, "self_stripe_quantized": True, "parallelism": f"dp{K} striped by columns",
-                       "exchange": "reference CPU quantizer (MatrixQuantizerCPU arithmetic) + restated striped exchange in host memory, one thread per rank"},
+            "config": workload_config(args.workload, shapes, r["values_per_rank"], bits, K),
+            "arm": {"exchange": "reference CPU quantizer (MatrixQuantizerCPU arithmetic) + restated striped exchange in host memory, one thread per rank",
+                    "timing": "host clock around each step, max over rank threads"},
             "cpu_baseline": {"value": r["gbs_total"], "unit": UNIT, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]},
             "e2e": {"value": r["gbs_total"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -448,13 +456,12 @@ def run_ours(args):
             "per_gpu_value": 4.0 * V / (t_step * 1e-3) / 1e9,
             "n_gpus": K, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "tensors": len(shapes), "values_per_rank": V, "bits": bits,
-                       "zero_threshold": True, "self_stripe_quantized": True, "parallelism": f"dp{K} striped by columns", "exchange": exchange,
-                       "header": "a 5-value DistGradHeader is summed over the ranks inside every timed step",
-                       "l2": "inputs (361 MB gradient + residual per step) exceed the 126 MB L2; gradients are also re-copied "
-                             "from a pre-generated pool between steps, outside the per-step events",
-                       "timing": "CUDA events around each step on the launch stream, mean over steps, max over ranks",
-                       "host": affinity},
+            "config": workload_config(args.workload, shapes, V, bits, K),
+            "arm": {"exchange": exchange,
+                    "header": "a 5-value DistGradHeader is summed over the ranks inside every timed step",
+                    "l2_refresh": "gradients are re-copied from a pre-generated pool between steps, outside the per-step events",
+                    "timing": "CUDA events around each step on the launch stream, mean over steps, max over ranks",
+                    "host": affinity},
             "phases_ms": {"quantize": phases[0], "scatter": phases[1], "reduce_requantize": phases[2], "all_gather": phases[3],
                           "unquantize": phases[4]},
             "roofline": roofline,
