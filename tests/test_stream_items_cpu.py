@@ -57,9 +57,13 @@ def test_speech_set_queue_order_and_widths():
         return -(-M // r)
     first = [chunks(t, n) for t, c0, n in items[:256]]
     assert min(first) >= 37
-    # ... and ends on short items: the last tenth has no item longer than a cut 2048-row item
+    # ... and ends on short items: the last tenth has no item longer than a 12-column item of a 2048-row matrix (16 chunks
+    # of 128 rows)
     tail = [chunks(t, n) for t, c0, n in items[-len(items) // 10:]]
-    assert max(tail) <= 11
+    assert max(tail) <= 16
+    # items hold at most 24 K values wherever the eight-column minimum allows
+    for t, c0, n in items:
+        assert n <= 8 or shapes[t][0] * n <= 24576
     # deterministic
     assert items == lib.stream_items(shapes, bits=1, num_sms=148)
 
