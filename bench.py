@@ -99,7 +99,7 @@ class ClockSampler:
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the quantize kernel at ONE rank, from the ncu
 # capture summarised in profiles/k_stream1_speech_dnn_1bit.md (same workload).  Reported only for the configuration that
 # was captured; null elsewhere.
-NCU_TRAFFIC_BYTES = {("speech_dnn", 1): 505.39e6}
+NCU_TRAFFIC_BYTES = {("speech_dnn", 1): 504.58e6}
 
 
 def get_shapes(name):
