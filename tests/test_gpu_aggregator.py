@@ -365,3 +365,64 @@ def test_caller_owned_residual_buffers(G, oracle_port, keep_plain):
             a.destroy()
         for c in comms:
             c.destroy()
+
+
+def _same_or_both_nan(a, b, what):
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    assert a.shape == b.shape, what
+    ok = (a.view(np.uint32) == b.view(np.uint32)) | (np.isnan(a) & np.isnan(b))
+    assert ok.all(), f"{what}: {int((~ok).sum())} of {a.size} elements differ (NaN positions must agree, everything else bit for bit)"
+
+
+@pytest.mark.parametrize("K,tall_rows,zero_thr", [(1, None, True), (3, None, True), (3, "200", True), (2, "0", True), (2, None, False)])
+def test_nan_and_infinities_spread_like_the_reference(G, oracle_port, K, tall_rows, zero_thr, monkeypatch):
+    """A NaN (or a pair of opposite infinities) in a gradient makes its column's range NaN in the reference
+    (ColumnQuantizer.h:247-316: the value lands in the upper partition sum), its bit 0, and its residual NaN from then on;
+    a lone infinity gives an infinite range.  Streaming kernel, form + walk pair (QAGG_TALL_ROWS) and owner kernels must
+    spread them exactly the same way: NaN where the oracle has NaN, every other value and every packed bit identical.  Also
+    with the mean as threshold (resident-column kernels), where a NaN makes the column's mean NaN.  (Multi-bit modes are left
+    out: there the reference converts NaN to an integer, which C leaves undefined.)"""
+    from cntk_b200 import lib
+    if tall_rows is not None:
+        monkeypatch.setenv("QAGG_TALL_ROWS", tall_rows)
+    shapes = [(256, 24), (1163, 5), (64, 3)]
+    comms = lib.Comm.local_group(K, 0)
+    aggs = [lib.Aggregator(c, shapes, 1, (lib.ZERO_THRESHOLD if zero_thr else 0) | lib.SELF_QUANTIZED) for c in comms]
+    st = ox.ExchangeState(shapes, K)
+    rng = np.random.default_rng(77 + K)
+    try:
+        for step in range(3):
+            grads = [[(rng.standard_normal((N, M)) * 1e-3).astype(np.float32) for (M, N) in shapes] for _ in range(K)]
+            if step == 0:
+                grads[0][0][2, 17] = np.nan                 # one NaN in column 2 of tensor 0
+                grads[K - 1][1][1, 500] = np.inf            # a lone +inf
+                grads[0][1][3, 7] = np.inf                  # +inf and -inf in one column
+                grads[0][1][3, 900] = -np.inf
+                grads[K - 1][2][0, :] = np.nan              # a whole column of NaN
+            dg = [[G.dev(a) for a in grads[r]] for r in range(K)]
+            with np.errstate(invalid="ignore", over="ignore"):
+                packed = ox.aggregate_step(oracle_port, st, grads, 1, zero_thr)
+            lib.step_group(aggs, [[t.data_ptr() for t in dg[r]] for r in range(K)])
+            torch.cuda.synchronize()
+            for r in range(K):
+                for i, (M, N) in enumerate(shapes):
+                    what = f"K {K} zero threshold {zero_thr} step {step} rank {r} tensor {i}"
+                    _same_or_both_nan(G.host(dg[r][i]), grads[r][i], "aggregate: " + what)
+                    res = torch.empty((N, M), dtype=torch.float32, device=G.DEV)
+                    aggs[r].copy_residual(i, 0, res.data_ptr())
+                    _same_or_both_nan(G.host(res), st.res[r][i], "residual: " + what)
+                    pk = torch.zeros(lib.packed_bytes(M, N, 1), dtype=torch.uint8, device=G.DEV)
+                    aggs[r].copy_packed(i, pk.data_ptr())
+                    C = lib.packed_bytes(M, 1, 1)
+                    got = G.host(pk).reshape(N, C)
+                    want = packed[r][i].reshape(N, C)
+                    assert np.array_equal(got[:, 8:], want[:, 8:]), "packed bits: " + what
+                    _same_or_both_nan(got[:, :8].copy().view(np.float32), want[:, :8].copy().view(np.float32), "column ranges: " + what)
+        for a in aggs:
+            a.check()
+    finally:
+        for a in aggs:
+            a.destroy()
+        for c in comms:
+            c.destroy()
