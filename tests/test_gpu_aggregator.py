@@ -426,3 +426,11 @@ def test_nan_and_infinities_spread_like_the_reference(G, oracle_port, K, tall_ro
             a.destroy()
         for c in comms:
             c.destroy()
+
+
+def test_form_walk_quantize_path_with_caller_owned_residuals(G, oracle_port, monkeypatch):
+    """The form + walk pair as the quantize kernel (QAGG_TALL_ROWS low enough to take every matrix of the set) keeps its
+    state in caller-owned residual buffers like the streaming kernel does: bound content is used, the buffers hold plain
+    residuals after qagg_agg_materialize_residuals, zeroing and binding again starts over."""
+    monkeypatch.setenv("QAGG_TALL_ROWS", "100")
+    test_caller_owned_residual_buffers(G, oracle_port, False)

@@ -143,3 +143,10 @@ def test_identity_aggregator_refuses_update(G):
     finally:
         a.destroy()
         comms[0].destroy()
+
+
+def test_fused_update_behind_the_form_walk_quantize_path(G, oracle_port, monkeypatch):
+    """The fused learner step is the last kernel of a step whatever quantized the gradients: here the form + walk pair takes
+    every matrix with 2048 rows or more, the streaming kernel the others."""
+    monkeypatch.setenv("QAGG_TALL_ROWS", "2048")
+    test_aggregator_fused_update(G, oracle_port, 4, 1, True)
