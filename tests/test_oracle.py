@@ -295,3 +295,51 @@ def test_double_port_equals_reference_build_directly(oracle_port_f64):
             oracle_port_f64.unquantize(pa, oa, bits, add=bool(it % 2))
             ref.unquantize(pb, ob_, bits, add=bool(it % 2))
             np.testing.assert_array_equal(oa.view(np.uint64), ob_.view(np.uint64))
+
+
+def test_learner_update_restatement_known_answers(oracle_port):
+    """oracle_sgd_update (Matrix::MomentumSGDUpdate, Source/Math/Matrix.cpp:1681-1698 over ScaleAndAdd :5415-5429), on numbers
+    whose results can be written down: the three forms of the smoothed-gradient update, the fused multiply-add (one
+    rounding: 1 + 2^-24 * 2^-1 cannot come out of a separate multiply and add), and the parameter step."""
+    f = np.float32
+    # momentum == 1: smoothed += alpha * g;  alpha = unitGain * lr = 0.5 * 0.5
+    w, g, s = np.array([10.0], f), np.array([8.0], f), np.array([1.0], f)
+    oracle_port.sgd_update(w, g, s, 0.5, 1.0, 0.5)
+    assert s[0] == 3.0 and w[0] == 7.0
+    # momentum == 0: smoothed = alpha * g (the old value is not read: NaN does not spread)
+    w, g, s = np.array([10.0], f), np.array([8.0], f), np.array([np.nan], f)
+    oracle_port.sgd_update(w, g, s, 0.25, 0.0, 1.0)
+    assert s[0] == 2.0 and w[0] == 8.0
+    # otherwise: smoothed = (smoothed + (alpha / momentum) * g) * momentum
+    w, g, s = np.array([10.0], f), np.array([4.0], f), np.array([2.0], f)
+    oracle_port.sgd_update(w, g, s, 0.5, 0.5, 1.0)   # alpha / momentum = 1 -> (2 + 4) * 0.5 = 3
+    assert s[0] == 3.0 and w[0] == 7.0
+    # one rounding for alpha * g + smoothed: alpha = 1 + 2^-12, g = 1 + 2^-12 -> product 1 + 2^-11 + 2^-24 exactly; plus
+    # smoothed = -1 the exact sum 2^-11 + 2^-24 is representable, a rounded product (1 + 2^-11) would lose the 2^-24
+    a = f(1.0) + f(2.0 ** -12)
+    w, g, s = np.array([0.0], f), np.array([a], f), np.array([-1.0], f)
+    oracle_port.sgd_update(w, g, s, float(a), 1.0, 1.0)
+    assert s[0] == f(2.0 ** -11 + 2.0 ** -24), s[0]
+    # a vector: every element independently
+    w = np.arange(8, dtype=f)
+    g = np.ones(8, f)
+    s = np.zeros(8, f)
+    oracle_port.sgd_update(w, g, s, 0.5, 1.0, 1.0)
+    assert np.array_equal(s, np.full(8, 0.5, f)) and np.array_equal(w, np.arange(8, dtype=f) - f(0.5))
+
+
+def test_half_precision_sum_restatement_known_answers():
+    """oracle.exchange.dense_sum_fp16: cast to half, add in rank order with a rounding to half after every addition, cast
+    back.  2048 + 1 is a tie in half precision (spacing 2 above 2048) and goes to the even neighbour; the order of the
+    additions shows; values beyond the half range become infinities."""
+    from oracle import exchange as ox
+    one = lambda v: [np.array([[v]], np.float32)]
+    assert ox.dense_sum_fp16([one(2048.0), one(1.0)])[0][0, 0] == 2048.0
+    assert ox.dense_sum_fp16([one(2048.0), one(1.0), one(1.0)])[0][0, 0] == 2048.0      # (2048 + 1) + 1: both ties go down
+    assert ox.dense_sum_fp16([one(1.0), one(1.0), one(2048.0)])[0][0, 0] == 2050.0      # (1 + 1) + 2048 is exact
+    assert ox.dense_sum_fp16([one(0.1), one(0.2)])[0][0, 0] == np.float32(np.float16(np.float32(np.float16(0.1)) + np.float32(np.float16(0.2))))
+    with np.errstate(over="ignore"):
+        assert np.isinf(ox.dense_sum_fp16([one(70000.0), one(0.0)])[0][0, 0])
+    # and the fp32 sum next to it: rank order, one rounding per addition
+    big = [np.array([[1e8]], np.float32)], [np.array([[1.0]], np.float32)], [np.array([[-1e8]], np.float32)]
+    assert ox.dense_sum(list(big))[0][0, 0] == 0.0      # (1e8 + 1) rounds to 1e8, then - 1e8
